@@ -1,0 +1,73 @@
+"""ctypes binding of libie_b200.so (the C ABI of include/ie_b200.h).
+
+The library is the only compute path of this package: if it is missing or a
+call fails, an exception is raised; nothing falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libie_b200.so"
+
+MAT_Q4, MAT_F32, MAT_Q4K, MAT_Q6K = 0, 1, 3, 4
+GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
+GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
+
+_vp, _u32, _sz, _int, _f32 = C.c_void_p, C.c_uint32, C.c_size_t, C.c_int, C.c_float
+
+# name -> (restype, argtypes); every symbol include/ie_b200.h declares
+SIGNATURES = {
+    "ie_b200_last_error": (C.c_char_p, []),
+    "ie_b200_device_count": (_int, []),
+    "ie_b200_launch_count": (C.c_uint64, []),
+    "ie_b200_row_bytes": (_sz, [_int, _u32]),
+    "ie_b200_mat_bytes": (_sz, [_int, _u32, _u32]),
+    "ie_b200_repack_gguf": (_int, [_int, _vp, _u32, _u32, _vp, _vp]),
+    "ie_b200_repack_ref": (_int, [_int, _vp, _vp, _u32, _u32, _vp, _vp]),
+    "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
+    "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
+    "ie_b200_block_dots": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp]),
+    "ie_b200_embed": (_int, [_int, _vp, _u32, _vp, _vp, _u32, _sz, _vp]),
+    "ie_b200_rmsnorm": (_int, [_vp, _vp, _vp, _u32, _f32, _vp, _u32, _sz, _sz, _sz, _vp]),
+    "ie_b200_swiglu": (_int, [_vp, _vp, _u32, _vp, _u32, _sz, _sz, _vp]),
+    "ie_b200_rope_kv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _int, _u32, _u32, _sz, _vp]),
+    "ie_b200_attn_part_bytes": (_sz, [_u32, _u32, _u32, _u32]),
+    "ie_b200_attn_count_words": (_sz, [_u32, _u32]),
+    "ie_b200_attn_decode": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _u32, _u32, _u32, _sz, _sz, _sz, _vp, _vp, _vp]),
+    "ie_b200_argmax_part_bytes": (_sz, [_u32]),
+    "ie_b200_argmax": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp, _vp]),
+}
+
+
+class IeB200Error(RuntimeError):
+    """A call into libie_b200.so returned a negative status."""
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library (once). Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.is_file():
+            raise IeB200Error(f"{LIB_PATH} is missing: run `python -m amd_c_b200.build` (needs nvcc); there is no CPU fallback")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        msg = load().ie_b200_last_error().decode("utf-8", "replace")
+        raise IeB200Error(f"libie_b200 status {status}: {msg}")
+
+
+def require_gpu() -> None:
+    if load().ie_b200_device_count() < 1:
+        raise IeB200Error("no CUDA device: the amd_c_b200 kernels need a GPU (there is no CPU fallback)")

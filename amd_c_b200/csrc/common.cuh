@@ -1,0 +1,156 @@
+// common.cuh -- shared helpers of the sm_100a kernels: error plumbing, the
+// streaming-layout geometry, cache-hinted loads and the integer block dots.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ie_b200.h"
+
+namespace ieb {
+
+// ---- host-side error plumbing (abi.cu) ----
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+void count_launch(unsigned n = 1);
+int sm_count();
+
+#define IEB_CUDA(call)                                   \
+  do {                                                   \
+    cudaError_t e_ = (call);                             \
+    if (e_ != cudaSuccess) return ieb::cuda_fail(e_, #call); \
+  } while (0)
+
+// After a kernel launch: count it and surface a launch error.
+#define IEB_LAUNCHED(what)                                \
+  do {                                                    \
+    ieb::count_launch();                                  \
+    cudaError_t e_ = cudaPeekAtLastError();               \
+    if (e_ != cudaSuccess) return ieb::cuda_fail(e_, what); \
+  } while (0)
+
+static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+// ---- streaming layout geometry (see ie_b200.h) ----
+__host__ __device__ inline size_t round16(size_t n) { return (n + 15u) & ~(size_t)15u; }
+__host__ __device__ inline size_t row_bytes_of(int kind, uint32_t cols) {
+  const size_t nb = cols / 32u;
+  switch (kind) {
+    case IE_B200_MAT_Q4: return round16(nb * 18u);
+    case IE_B200_MAT_Q4K: return nb * 16u + (nb / 8u) * 16u;
+    case IE_B200_MAT_Q6K: return round16(nb * 26u + (nb / 8u) * 2u);
+    default: return (size_t)cols * 4u;
+  }
+}
+
+// ---- device helpers ----
+#ifdef __CUDACC__
+
+// 16-byte streaming load of weights that are read once: read-only path, not
+// kept in L1.
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream8(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint16_t ld_stream2(const void *p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_stream_f32(const void *p) {
+  float v;
+  asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// Sum over the 32 nibbles q (0..15) of q * a. Word k of the weight block
+// holds weights 4k..4k+3 in its low nibbles and 16+4k..16+4k+3 in its high
+// nibbles; a0 are activation words 0..3, a1 words 4..7. Nibble bytes are
+// below 128, so the signed byte product equals the unsigned-by-signed one.
+__device__ __forceinline__ int q4_dot(const uint4 &w, const uint4 &a0, const uint4 &a1) {
+  int acc = 0;
+  acc = __dp4a((int)(w.x & 0x0F0F0F0Fu), (int)a0.x, acc);
+  acc = __dp4a((int)((w.x >> 4) & 0x0F0F0F0Fu), (int)a1.x, acc);
+  acc = __dp4a((int)(w.y & 0x0F0F0F0Fu), (int)a0.y, acc);
+  acc = __dp4a((int)((w.y >> 4) & 0x0F0F0F0Fu), (int)a1.y, acc);
+  acc = __dp4a((int)(w.z & 0x0F0F0F0Fu), (int)a0.z, acc);
+  acc = __dp4a((int)((w.z >> 4) & 0x0F0F0F0Fu), (int)a1.z, acc);
+  acc = __dp4a((int)(w.w & 0x0F0F0F0Fu), (int)a0.w, acc);
+  acc = __dp4a((int)((w.w >> 4) & 0x0F0F0F0Fu), (int)a1.w, acc);
+  return acc;
+}
+
+// One byte-quad of Q6_K values minus 32 as signed bytes: v = nibbles | two
+// high bits << 4, then ((v | 0x80808080) - 0x20202020) ^ 0x80808080.
+__device__ __forceinline__ int q6_sw(uint32_t nib4, uint32_t hword, int k) {
+  const uint32_t v = nib4 | (((hword >> (2 * k)) & 0x03030303u) << 4);
+  return (int)(((v | 0x80808080u) - 0x20202020u) ^ 0x80808080u);
+}
+// The two half dots of a Q6_K sub-block: weights 0..15 against a0, 16..31 against a1.
+__device__ __forceinline__ void q6_dots(const uint4 &w, const uint2 &hw, const uint4 &a0, const uint4 &a1, int &d0, int &d1) {
+  int s0 = 0, s1 = 0;
+  s0 = __dp4a(q6_sw(w.x & 0x0F0F0F0Fu, hw.x, 0), (int)a0.x, s0);
+  s0 = __dp4a(q6_sw(w.y & 0x0F0F0F0Fu, hw.x, 1), (int)a0.y, s0);
+  s0 = __dp4a(q6_sw(w.z & 0x0F0F0F0Fu, hw.x, 2), (int)a0.z, s0);
+  s0 = __dp4a(q6_sw(w.w & 0x0F0F0F0Fu, hw.x, 3), (int)a0.w, s0);
+  s1 = __dp4a(q6_sw((w.x >> 4) & 0x0F0F0F0Fu, hw.y, 0), (int)a1.x, s1);
+  s1 = __dp4a(q6_sw((w.y >> 4) & 0x0F0F0F0Fu, hw.y, 1), (int)a1.y, s1);
+  s1 = __dp4a(q6_sw((w.z >> 4) & 0x0F0F0F0Fu, hw.y, 2), (int)a1.z, s1);
+  s1 = __dp4a(q6_sw((w.w >> 4) & 0x0F0F0F0Fu, hw.y, 3), (int)a1.w, s1);
+  d0 = s0, d1 = s1;
+}
+
+// The 12-bit (sc | mn << 6) field j of a Q4_K super-block header (words y, z, w).
+__device__ __forceinline__ uint32_t q4k_field(const uint4 &h, int j) {
+  const int o = 12 * j, i = o >> 5, sh = o & 31;
+  const uint32_t lo = i == 0 ? h.y : i == 1 ? h.z : h.w;
+  const uint32_t hi = i == 0 ? h.z : h.w;
+  return __funnelshift_r(lo, hi, sh) & 0xFFFu;
+}
+
+// The wave tree of the reference: shuffle down by 16, 8, 4, 2, 1; lane 0 holds the sum.
+__device__ __forceinline__ float warp_tree(float v) {
+  v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 16));
+  v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 8));
+  v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 4));
+  v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 2));
+  v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 1));
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum_all(float v) {
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Q8 of one block of 32 floats held one per lane: writes q, d, asum of block
+// b into a Q8 buffer of nb blocks. d = amax / 127 and q = round-half-away(x /
+// d) with IEEE division, as the CPU quantiser.
+__device__ __forceinline__ void quant_block_warp(float x, uint8_t *q, uint32_t nb, uint32_t b, int lane) {
+  const float amax = warp_max(fabsf(x));
+  const float d = __fdiv_rn(amax, 127.0f);
+  int v = 0;
+  if (d != 0.0f) v = (int)roundf(__fdiv_rn(x, d));
+  int s = v;
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  ((int8_t *)q)[32u * b + lane] = (int8_t)v;
+  if (lane == 0) {
+    ((float *)(q + 32u * (size_t)nb))[b] = d;
+    ((uint32_t *)(q + 36u * (size_t)nb))[b] = (uint32_t)s;
+  }
+}
+#endif  // __CUDACC__
+
+}  // namespace ieb

@@ -1,0 +1,290 @@
+// gemv.cu -- quantised-weight x Q8-activation GEMV (Q4_0, Q4_K, Q6_K) and the
+// f32 GEMV for batch-1 decode on sm_100a. HBM-bound: no tensor cores.
+//
+// Work split (the reference's, so results match its CPU backend bit for bit):
+// one warp per row; lane l accumulates blocks l, l+32, l+64, ... in that
+// order starting from 0.0f, then the warp reduces by shuffle-down 16, 8, 4,
+// 2, 1 and lane 0 applies the epilogue.
+//
+// Memory: a persistent grid (a few CTAs per SM) stages the token's Q8
+// activations once per CTA in shared memory as two 16-byte planes per block
+// (conflict-free 16-byte reads) and then streams row panels: each lane has
+// R x U 16-byte weight loads in flight (R rows per warp pass, U lane steps per
+// chunk) before any arithmetic depends on them.
+#include "common.cuh"
+
+namespace ieb {
+
+template <int KIND>
+struct Blk;
+
+// Q4_0: 16 B nibbles at 16 b, f16 scale at 16 nb + 2 b.
+template <>
+struct Blk<IE_B200_MAT_Q4> {
+  uint4 w;
+  uint16_t d;
+  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
+    w = ld_stream16(rp + 16u * (size_t)b);
+    d = ld_stream2(rp + 16u * (size_t)nb + 2u * b);
+  }
+  // acc = acc + (dw * da) * (float)dot, each operation rounded on its own.
+  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int asum, uint32_t) const {
+    const int dot = q4_dot(w, a0, a1) - 8 * asum;
+    return __fadd_rn(acc, __fmul_rn(__fmul_rn(h2f(d), da), (float)dot));
+  }
+};
+
+// Q4_K: nibbles as Q4_0; per super-block a 16 B header at 16 nb + 16 (b / 8).
+template <>
+struct Blk<IE_B200_MAT_Q4K> {
+  uint4 w, h;
+  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
+    w = ld_stream16(rp + 16u * (size_t)b);
+    h = ld_stream16(rp + 16u * (size_t)nb + 16u * (b >> 3));
+  }
+  // acc = fma(-(dmin mn), da * (float)asum, fma((d sc) * (float)dq, da, acc)).
+  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int asum, uint32_t b) const {
+    const int dq = q4_dot(w, a0, a1);
+    const uint32_t f = q4k_field(h, (int)(b & 7u));
+    const float s = __fmul_rn(h2f((uint16_t)(h.x & 0xFFFFu)), (float)(f & 63u));
+    const float mm = __fmul_rn(h2f((uint16_t)(h.x >> 16)), (float)(f >> 6));
+    return __fmaf_rn(-mm, __fmul_rn(da, (float)asum), __fmaf_rn(__fmul_rn(s, (float)dq), da, acc));
+  }
+};
+
+// Q6_K: nibbles at 16 b, high-bit words at 16 nb + 8 b, (sc0 | sc1 << 8) at
+// 24 nb + 2 b, f16 d at 26 nb + 2 (b / 8).
+template <>
+struct Blk<IE_B200_MAT_Q6K> {
+  uint4 w;
+  uint2 hw;
+  uint16_t sc, d;
+  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
+    w = ld_stream16(rp + 16u * (size_t)b);
+    hw = ld_stream8(rp + 16u * (size_t)nb + 8u * b);
+    sc = ld_stream2(rp + 24u * (size_t)nb + 2u * b);
+    d = ld_stream2(rp + 26u * (size_t)nb + 2u * (b >> 3));
+  }
+  // acc = fma(fma(d sc1, (float)d1, (d sc0) * (float)d0), da, acc).
+  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int, uint32_t) const {
+    int d0, d1;
+    q6_dots(w, hw, a0, a1, d0, d1);
+    const float df = h2f(d);
+    const float s0 = __fmul_rn(df, (float)(int8_t)(sc & 255u)), s1 = __fmul_rn(df, (float)(int8_t)(sc >> 8));
+    return __fmaf_rn(__fmaf_rn(s1, (float)d1, __fmul_rn(s0, (float)d0)), da, acc);
+  }
+};
+
+constexpr int GEMV_THREADS = 256, GEMV_WARPS = GEMV_THREADS / 32;
+
+// Stage one token's Q8 buffer into shared memory: plane A0 = words 0..3 of
+// every block, plane A1 = words 4..7, then the scales and the block sums.
+__device__ __forceinline__ void stage_q8(const uint8_t *xq, uint32_t nb, uint4 *A0, uint4 *A1, float *da, int *as) {
+  const uint4 *src = reinterpret_cast<const uint4 *>(xq);
+  for (uint32_t i = threadIdx.x; i < 2u * nb; i += blockDim.x) {
+    const uint4 v = src[i];
+    if (i & 1u) A1[i >> 1] = v;
+    else A0[i >> 1] = v;
+  }
+  const float *d = reinterpret_cast<const float *>(xq + 32u * (size_t)nb);
+  const int *s = reinterpret_cast<const int *>(xq + 36u * (size_t)nb);
+  for (uint32_t i = threadIdx.x; i < nb; i += blockDim.x) da[i] = d[i], as[i] = s[i];
+}
+
+template <int KIND, int R, int U>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_q_kernel(const uint8_t *__restrict__ w, size_t rowb, uint32_t rows, uint32_t nb, const uint8_t *__restrict__ x, float *y,
+              const float *__restrict__ bias, const float *res, size_t xs, size_t ys, size_t rs) {
+  extern __shared__ uint4 smem[];
+  uint4 *A0 = smem, *A1 = smem + nb;
+  float *da = reinterpret_cast<float *>(smem + 2u * nb);
+  int *as = reinterpret_cast<int *>(da + nb);
+  const uint32_t t = blockIdx.y;
+  stage_q8(x + t * xs, nb, A0, A1, da, as);
+  __syncthreads();
+  y = reinterpret_cast<float *>(reinterpret_cast<char *>(y) + t * ys);
+  if (res) res = reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + t * rs);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t stride = gridDim.x * GEMV_WARPS * R;
+  for (uint32_t r0 = (blockIdx.x * GEMV_WARPS + warp) * R; r0 < rows; r0 += stride) {
+    float acc[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) acc[i] = 0.0f;
+    for (uint32_t c = 0; c < nb; c += 32u * U) {
+      Blk<KIND> blk[R][U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t b = c + 32u * u + lane;
+#pragma unroll
+        for (int i = 0; i < R; i++)
+          if (b < nb && r0 + i < rows) blk[i][u].load(w + (size_t)(r0 + i) * rowb, b, nb);
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t b = c + 32u * u + lane;
+        if (b < nb) {
+          const uint4 a0 = A0[b], a1 = A1[b];
+          const float d = da[b];
+          const int s = as[b];
+#pragma unroll
+          for (int i = 0; i < R; i++)
+            if (r0 + i < rows) acc[i] = blk[i][u].accum(acc[i], a0, a1, d, s, b);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+      const float v = warp_tree(acc[i]);
+      const uint32_t r = r0 + i;
+      if (lane == 0 && r < rows) {
+        float o = v;
+        if (bias) o = __fadd_rn(o, bias[r]);
+        if (res) o = __fadd_rn(res[r], o);
+        y[r] = o;
+      }
+    }
+  }
+}
+
+// f32 matrix: lane l sums elements l, l+32, ... in order (product rounded,
+// then added), then the tree. x staged in shared memory; 8 loads in flight per lane.
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_f32_kernel(const float *__restrict__ w, uint32_t rows, uint32_t cols, const float *__restrict__ x, float *y,
+                const float *__restrict__ bias, const float *res, size_t xs, size_t ys, size_t rs) {
+  extern __shared__ uint4 smem[];
+  float *xsm = reinterpret_cast<float *>(smem);
+  const uint32_t t = blockIdx.y;
+  const float *xt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + t * xs);
+  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) xsm[i] = xt[i];
+  __syncthreads();
+  y = reinterpret_cast<float *>(reinterpret_cast<char *>(y) + t * ys);
+  if (res) res = reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + t * rs);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int U = 8;
+  for (uint32_t r = blockIdx.x * GEMV_WARPS + warp; r < rows; r += gridDim.x * GEMV_WARPS) {
+    const float *row = w + (size_t)r * cols;
+    float acc = 0.0f;
+    for (uint32_t c = 0; c < cols; c += 32u * U) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t i = c + 32u * u + lane;
+        v[u] = i < cols ? ld_stream_f32(row + i) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t i = c + 32u * u + lane;
+        if (i < cols) acc = __fadd_rn(acc, __fmul_rn(v[u], xsm[i]));
+      }
+    }
+    const float s = warp_tree(acc);
+    if (lane == 0) {
+      float o = s;
+      if (bias) o = __fadd_rn(o, bias[r]);
+      if (res) o = __fadd_rn(res[r], o);
+      y[r] = o;
+    }
+  }
+}
+
+// Test hook: one thread per (row, block).
+template <int KIND>
+__global__ void block_dots_kernel(const uint8_t *__restrict__ w, size_t rowb, uint32_t rows, uint32_t nb, const uint8_t *__restrict__ xq,
+                                  int32_t *dots) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
+  const uint8_t *rp = w + (size_t)r * rowb;
+  const uint4 *a = reinterpret_cast<const uint4 *>(xq) + 2u * b;
+  const uint4 a0 = a[0], a1 = a[1];
+  const uint4 q = *reinterpret_cast<const uint4 *>(rp + 16u * (size_t)b);
+  if (KIND == IE_B200_MAT_Q6K) {
+    const uint2 hw = *reinterpret_cast<const uint2 *>(rp + 16u * (size_t)nb + 8u * b);
+    int d0, d1;
+    q6_dots(q, hw, a0, a1, d0, d1);
+    dots[2 * i] = d0, dots[2 * i + 1] = d1;
+  } else if (KIND == IE_B200_MAT_Q4K) {
+    dots[i] = q4_dot(q, a0, a1);
+  } else {
+    const int asum = reinterpret_cast<const int *>(xq + 36u * (size_t)nb)[b];
+    dots[i] = q4_dot(q, a0, a1) - 8 * asum;
+  }
+}
+
+// Grid: enough CTAs to fill the machine a few times over, never more than the rows need.
+static unsigned gemv_grid(uint32_t rows, int rows_per_cta, int ctas_per_sm) {
+  const unsigned need = (rows + rows_per_cta - 1) / rows_per_cta;
+  const unsigned cap = (unsigned)(sm_count() * ctas_per_sm);
+  return need < cap ? (need ? need : 1u) : cap;
+}
+
+template <int KIND, int R, int U>
+static int launch_q(const void *w, uint32_t rows, uint32_t cols, const void *x, float *y, const float *bias, const float *res, uint32_t T,
+                    size_t xs, size_t ys, size_t rs, cudaStream_t st) {
+  const uint32_t nb = cols / 32u;
+  const size_t smem = (size_t)nb * 40u;
+  auto k = gemv_q_kernel<KIND, R, U>;
+  if (smem > 48u * 1024u) IEB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const dim3 grid(gemv_grid(rows, GEMV_WARPS * R, 8), T);
+  k<<<grid, GEMV_THREADS, smem, st>>>(static_cast<const uint8_t *>(w), row_bytes_of(KIND, cols), rows, nb, static_cast<const uint8_t *>(x), y,
+                                      bias, res, xs, ys, rs);
+  IEB_LAUNCHED("gemv_q_kernel");
+  return IE_B200_OK;
+}
+
+}  // namespace ieb
+
+using namespace ieb;
+
+extern "C" int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
+                            const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream) {
+  if (!d_w || !d_x || !d_y) return fail(IE_B200_E_ARG, "ie_b200_gemv: NULL pointer");
+  if (!aligned16(d_w) || !aligned16(d_x)) return fail(IE_B200_E_ARG, "ie_b200_gemv: weights and activations must be 16-byte aligned");
+  if (rows == 0 || T == 0) return IE_B200_OK;
+  if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: T %u > 65535", T);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint32_t nb = cols / 32u;
+  if (kind == IE_B200_MAT_F32) {
+    if (cols == 0 || (size_t)cols * 4u > 200u * 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: f32 cols %u unsupported", cols);
+    const size_t smem = (size_t)cols * 4u;
+    if (smem > 48u * 1024u) IEB_CUDA(cudaFuncSetAttribute(gemv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid(gemv_grid(rows, GEMV_WARPS, 8), T);
+    gemv_f32_kernel<<<grid, GEMV_THREADS, smem, st>>>(static_cast<const float *>(d_w), rows, cols, static_cast<const float *>(d_x), d_y, d_bias,
+                                                     d_res, x_stride, y_stride, res_stride);
+    IEB_LAUNCHED("gemv_f32_kernel");
+    return IE_B200_OK;
+  }
+  if (cols == 0 || cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: cols %u is not a multiple of 32", cols);
+  if (nb > 4096u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: %u blocks per row > 4096", nb);
+  if ((x_stride & 15u) != 0) return fail(IE_B200_E_ARG, "ie_b200_gemv: x_stride must be a multiple of 16");
+  switch (kind) {
+    case IE_B200_MAT_Q4: return launch_q<IE_B200_MAT_Q4, 2, 4>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
+    case IE_B200_MAT_Q4K:
+      if (nb % 8u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: Q4_K needs cols %% 256 == 0");
+      return launch_q<IE_B200_MAT_Q4K, 2, 4>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
+    case IE_B200_MAT_Q6K:
+      if (nb % 8u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: Q6_K needs cols %% 256 == 0");
+      return launch_q<IE_B200_MAT_Q6K, 2, 2>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
+    default: return fail(IE_B200_E_ARG, "ie_b200_gemv: unknown matrix kind %d", kind);
+  }
+}
+
+extern "C" int ie_b200_block_dots(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, int32_t *d_dots, void *stream) {
+  if (!d_w || !d_xq || !d_dots) return fail(IE_B200_E_ARG, "ie_b200_block_dots: NULL pointer");
+  if (cols == 0 || cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_block_dots: cols %u is not a multiple of 32", cols);
+  const uint32_t nb = cols / 32u;
+  const size_t n = (size_t)rows * nb;
+  if (n == 0) return IE_B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  const uint8_t *w = static_cast<const uint8_t *>(d_w), *x = static_cast<const uint8_t *>(d_xq);
+  switch (kind) {
+    case IE_B200_MAT_Q4: block_dots_kernel<IE_B200_MAT_Q4><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
+    case IE_B200_MAT_Q4K: block_dots_kernel<IE_B200_MAT_Q4K><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
+    case IE_B200_MAT_Q6K: block_dots_kernel<IE_B200_MAT_Q6K><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
+    default: return fail(IE_B200_E_ARG, "ie_b200_block_dots: unknown matrix kind %d", kind);
+  }
+  IEB_LAUNCHED("block_dots_kernel");
+  return IE_B200_OK;
+}

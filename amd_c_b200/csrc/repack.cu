@@ -1,0 +1,184 @@
+// repack.cu -- load-time re-layout of quantised weights into the streaming
+// "row panel" layout (see ie_b200.h): from raw GGUF tensor bytes, or from the
+// word/scale arrays that the reference's model loader hands to its matrix
+// sink. One thread per 32-weight block; runs once per matrix.
+#include "common.cuh"
+
+namespace ieb {
+
+__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) { return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24); }
+
+// The 6-bit scale and min of sub-block j from the 12 packed bytes of a GGUF
+// Q4_K super-block (ggml's get_scale_min_k4 rule).
+__device__ __forceinline__ void gguf_q4k_sc_mn(int j, const uint8_t *p, uint32_t &sc, uint32_t &mn) {
+  if (j < 4) {
+    sc = p[j] & 63u, mn = p[j + 4] & 63u;
+  } else {
+    sc = (p[j + 4] & 15u) | ((uint32_t)(p[j - 4] >> 6) << 4);
+    mn = (uint32_t)(p[j + 4] >> 4) | ((uint32_t)(p[j] >> 6) << 4);
+  }
+}
+
+// Eight (sc, mn) pairs -> three words of 12-bit fields (sc | mn << 6), field j at bit 12 j.
+__device__ __forceinline__ void pack_q4k_fields(const uint32_t *sc, const uint32_t *mn, uint32_t *w3) {
+  unsigned long long lo = 0;  // fields 0..4 (60 bits) + low 4 bits of field 5
+  uint32_t f[8];
+  for (int j = 0; j < 8; j++) f[j] = (sc[j] & 63u) | ((mn[j] & 63u) << 6);
+  for (int j = 0; j < 5; j++) lo |= (unsigned long long)f[j] << (12 * j);
+  lo |= (unsigned long long)(f[5] & 15u) << 60;
+  w3[0] = (uint32_t)lo, w3[1] = (uint32_t)(lo >> 32);
+  w3[2] = (f[5] >> 4) | (f[6] << 8) | (f[7] << 20);
+}
+
+// ---- from GGUF bytes ----
+__global__ void repack_gguf_q4_0(const uint8_t *__restrict__ src, uint32_t rows, uint32_t nb, uint8_t *dst, size_t rowb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
+  const uint16_t *s = reinterpret_cast<const uint16_t *>(src + i * 18u);  // 18 i is even
+  uint8_t *rp = dst + (size_t)r * rowb;
+  uint32_t w[4];
+  for (int k = 0; k < 4; k++) w[k] = (uint32_t)s[1 + 2 * k] | ((uint32_t)s[2 + 2 * k] << 16);
+  *reinterpret_cast<uint4 *>(rp + 16u * (size_t)b) = make_uint4(w[0], w[1], w[2], w[3]);
+  reinterpret_cast<uint16_t *>(rp + 16u * (size_t)nb)[b] = s[0];
+}
+
+__global__ void repack_gguf_q4_k(const uint8_t *__restrict__ src, uint32_t rows, uint32_t nb, uint8_t *dst, size_t rowb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb), k = b & 7u;
+  const uint8_t *blk = src + ((size_t)r * (nb / 8u) + b / 8u) * 144u;
+  const uint8_t *qb = blk + 16u + 32u * (k / 2u);
+  uint8_t *rp = dst + (size_t)r * rowb;
+  uint32_t by[16];
+  for (int j = 0; j < 16; j++) {
+    const uint32_t lo = (k & 1u) ? (uint32_t)(qb[j] >> 4) : (uint32_t)(qb[j] & 15u);
+    const uint32_t hi = (k & 1u) ? (uint32_t)(qb[j + 16] >> 4) : (uint32_t)(qb[j + 16] & 15u);
+    by[j] = lo | (hi << 4);
+  }
+  *reinterpret_cast<uint4 *>(rp + 16u * (size_t)b) =
+      make_uint4(pack4(by[0], by[1], by[2], by[3]), pack4(by[4], by[5], by[6], by[7]), pack4(by[8], by[9], by[10], by[11]),
+                 pack4(by[12], by[13], by[14], by[15]));
+  if (k == 0u) {
+    uint32_t sc[8], mn[8], w3[3];
+    for (int j = 0; j < 8; j++) gguf_q4k_sc_mn(j, blk + 4, sc[j], mn[j]);
+    pack_q4k_fields(sc, mn, w3);
+    const uint32_t ddm = (uint32_t)blk[0] | ((uint32_t)blk[1] << 8) | ((uint32_t)blk[2] << 16) | ((uint32_t)blk[3] << 24);
+    *reinterpret_cast<uint4 *>(rp + 16u * (size_t)nb + 16u * (b >> 3)) = make_uint4(ddm, w3[0], w3[1], w3[2]);
+  }
+}
+
+__global__ void repack_gguf_q6_k(const uint8_t *__restrict__ src, uint32_t rows, uint32_t nb, uint8_t *dst, size_t rowb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb), sub = b & 7u, n = sub / 4u, m = sub % 4u;
+  const uint8_t *blk = src + ((size_t)r * (nb / 8u) + b / 8u) * 210u;
+  uint8_t *rp = dst + (size_t)r * rowb;
+  uint32_t q[32];
+  for (int l = 0; l < 32; l++) {
+    const uint32_t ql = blk[64u * n + 32u * (m & 1u) + l], qh = blk[128u + 32u * n + l];
+    q[l] = (m < 2u ? (ql & 15u) : (ql >> 4)) | (((qh >> (2u * m)) & 3u) << 4);
+  }
+  uint32_t w[4], hw[2] = {0u, 0u};
+  for (int k = 0; k < 4; k++) {
+    w[k] = 0;
+    for (int e = 0; e < 4; e++) w[k] |= ((q[4 * k + e] & 15u) | ((q[4 * k + e + 16] & 15u) << 4)) << (8 * e);
+  }
+  for (int h = 0; h < 2; h++)
+    for (int e = 0; e < 16; e++) hw[h] |= ((q[16 * h + e] >> 4) & 3u) << (8 * (e % 4) + 2 * (e / 4));
+  *reinterpret_cast<uint4 *>(rp + 16u * (size_t)b) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint2 *>(rp + 16u * (size_t)nb + 8u * b) = make_uint2(hw[0], hw[1]);
+  reinterpret_cast<uint16_t *>(rp + 24u * (size_t)nb)[b] = (uint16_t)(blk[192u + 2u * sub] | (blk[192u + 2u * sub + 1u] << 8));
+  if (sub == 0u) reinterpret_cast<uint16_t *>(rp + 26u * (size_t)nb)[b >> 3] = (uint16_t)(blk[208] | (blk[209] << 8));
+}
+
+// ---- from the reference's repacked arrays (qw words, qs u16 entries) ----
+template <int KIND>
+__global__ void repack_ref_kernel(const uint32_t *__restrict__ qw, const uint16_t *__restrict__ qs, uint32_t rows, uint32_t nb, uint8_t *dst,
+                                  size_t rowb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
+  uint8_t *rp = dst + (size_t)r * rowb;
+  *reinterpret_cast<uint4 *>(rp + 16u * (size_t)b) = *reinterpret_cast<const uint4 *>(qw + i * 4u);
+  if (KIND == IE_B200_MAT_Q4) {
+    reinterpret_cast<uint16_t *>(rp + 16u * (size_t)nb)[b] = qs[i];
+  } else if (KIND == IE_B200_MAT_Q4K) {
+    if ((b & 7u) == 0u) {
+      uint32_t sc[8], mn[8], w3[3];
+      for (int j = 0; j < 8; j++) sc[j] = qs[i + j] & 63u, mn[j] = (qs[i + j] >> 8) & 63u;
+      pack_q4k_fields(sc, mn, w3);
+      const size_t dd = (size_t)rows * nb + ((size_t)r * (nb / 8u) + b / 8u) * 2u;
+      *reinterpret_cast<uint4 *>(rp + 16u * (size_t)nb + 16u * (b >> 3)) = make_uint4((uint32_t)qs[dd] | ((uint32_t)qs[dd + 1] << 16), w3[0], w3[1], w3[2]);
+    }
+  } else {  // Q6_K
+    const uint32_t *hw = qw + (size_t)rows * nb * 4u + i * 2u;
+    *reinterpret_cast<uint2 *>(rp + 16u * (size_t)nb + 8u * b) = make_uint2(hw[0], hw[1]);
+    reinterpret_cast<uint16_t *>(rp + 24u * (size_t)nb)[b] = qs[i];
+    if ((b & 7u) == 0u) reinterpret_cast<uint16_t *>(rp + 26u * (size_t)nb)[b >> 3] = qs[(size_t)rows * nb + (size_t)r * (nb / 8u) + b / 8u];
+  }
+}
+
+static int check_shape(const char *who, int kind, uint32_t rows, uint32_t cols) {
+  if (cols == 0 || cols % 32u) return fail(IE_B200_E_SIZE, "%s: cols %u is not a multiple of 32", who, cols);
+  if ((kind == IE_B200_MAT_Q4K || kind == IE_B200_MAT_Q6K) && cols % 256u) return fail(IE_B200_E_SIZE, "%s: K kinds need cols %% 256 == 0", who);
+  if ((uint64_t)rows * (cols / 32u) >= (1ull << 31)) return fail(IE_B200_E_SIZE, "%s: %u x %u has too many blocks", who, rows, cols);
+  return IE_B200_OK;
+}
+
+}  // namespace ieb
+
+using namespace ieb;
+
+extern "C" size_t ie_b200_row_bytes(int kind, uint32_t cols) { return row_bytes_of(kind, cols); }
+extern "C" size_t ie_b200_mat_bytes(int kind, uint32_t rows, uint32_t cols) { return row_bytes_of(kind, cols) * rows; }
+
+extern "C" int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t rows, uint32_t cols, void *d_dst, void *stream) {
+  if (!d_src || !d_dst) return fail(IE_B200_E_ARG, "ie_b200_repack_gguf: NULL pointer");
+  if (!aligned16(d_dst) || ((uintptr_t)d_src & 1u)) return fail(IE_B200_E_ARG, "ie_b200_repack_gguf: misaligned pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) return IE_B200_OK;
+  if (ggml_type == IE_B200_GGML_F32) {
+    IEB_CUDA(cudaMemcpyAsync(d_dst, d_src, (size_t)rows * cols * 4u, cudaMemcpyDeviceToDevice, st));
+    return IE_B200_OK;
+  }
+  const int kind = ggml_type == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : ggml_type == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K
+                   : ggml_type == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
+  if (kind < 0) return fail(IE_B200_E_ARG, "ie_b200_repack_gguf: GGML type %d unsupported", ggml_type);
+  if (int e = check_shape("ie_b200_repack_gguf", kind, rows, cols)) return e;
+  const uint32_t nb = cols / 32u;
+  const size_t n = (size_t)rows * nb, rowb = row_bytes_of(kind, cols);
+  const unsigned grid = (unsigned)((n + 127) / 128);
+  const uint8_t *s = static_cast<const uint8_t *>(d_src);
+  uint8_t *d = static_cast<uint8_t *>(d_dst);
+  if (kind == IE_B200_MAT_Q4) repack_gguf_q4_0<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
+  else if (kind == IE_B200_MAT_Q4K) repack_gguf_q4_k<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
+  else repack_gguf_q6_k<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
+  IEB_LAUNCHED("repack_gguf");
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, uint32_t rows, uint32_t cols, void *d_dst, void *stream) {
+  if (!d_qw || !d_dst) return fail(IE_B200_E_ARG, "ie_b200_repack_ref: NULL pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) return IE_B200_OK;
+  if (kind == IE_B200_MAT_F32) {
+    IEB_CUDA(cudaMemcpyAsync(d_dst, d_qw, (size_t)rows * cols * 4u, cudaMemcpyDeviceToDevice, st));
+    return IE_B200_OK;
+  }
+  if (!d_qs) return fail(IE_B200_E_ARG, "ie_b200_repack_ref: NULL scale array");
+  if (!aligned16(d_dst) || !aligned16(d_qw)) return fail(IE_B200_E_ARG, "ie_b200_repack_ref: misaligned pointer");
+  if (int e = check_shape("ie_b200_repack_ref", kind, rows, cols)) return e;
+  const uint32_t nb = cols / 32u;
+  const size_t n = (size_t)rows * nb, rowb = row_bytes_of(kind, cols);
+  const unsigned grid = (unsigned)((n + 127) / 128);
+  const uint32_t *qw = static_cast<const uint32_t *>(d_qw);
+  const uint16_t *qs = static_cast<const uint16_t *>(d_qs);
+  uint8_t *d = static_cast<uint8_t *>(d_dst);
+  if (kind == IE_B200_MAT_Q4) repack_ref_kernel<IE_B200_MAT_Q4><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
+  else if (kind == IE_B200_MAT_Q4K) repack_ref_kernel<IE_B200_MAT_Q4K><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
+  else if (kind == IE_B200_MAT_Q6K) repack_ref_kernel<IE_B200_MAT_Q6K><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
+  else return fail(IE_B200_E_ARG, "ie_b200_repack_ref: unknown matrix kind %d", kind);
+  IEB_LAUNCHED("repack_ref");
+  return IE_B200_OK;
+}

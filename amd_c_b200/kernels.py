@@ -1,0 +1,162 @@
+"""Thin torch-tensor wrappers over the kernel-level C ABI.
+
+torch is used for device memory and streams only; every computation is a
+call into libie_b200.so on the current torch CUDA stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import GGML_TO_MAT, MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K, check
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def q8_bytes(nb: int) -> int:
+    """Bytes of a Q8 activation buffer of nb blocks (int8 x 32 | f32 d | u32 asum)."""
+    return 40 * nb
+
+
+class Mat:
+    """A weight matrix in the streaming layout on the device."""
+
+    def __init__(self, kind: int, rows: int, cols: int, data: torch.Tensor):
+        self.kind, self.rows, self.cols, self.data = kind, rows, cols, data
+
+    @property
+    def nb(self) -> int:
+        return self.cols // 32
+
+    @property
+    def algorithmic_bytes(self) -> int:
+        """Bytes one GEMV must read: 18 B per Q4_0 / Q4_K block, 26.25 B per
+        Q6_K block, 4 B per f32 weight."""
+        if self.kind == MAT_F32:
+            return self.rows * self.cols * 4
+        per = {MAT_Q4: 18.0, MAT_Q4K: 18.0, MAT_Q6K: 26.25}[self.kind]
+        return int(self.rows * self.nb * per)
+
+    @staticmethod
+    def from_gguf(ggml_type: int, raw: torch.Tensor, rows: int, cols: int) -> "Mat":
+        """raw: uint8 CUDA tensor of the GGUF tensor bytes."""
+        lib = _lib.load()
+        kind = GGML_TO_MAT[ggml_type]
+        nbytes = lib.ie_b200_mat_bytes(kind, rows, cols)
+        dst = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=raw.device)
+        check(lib.ie_b200_repack_gguf(ggml_type, raw.data_ptr(), rows, cols, dst.data_ptr(), _stream()))
+        return Mat(kind, rows, cols, dst)
+
+    @staticmethod
+    def from_ref(kind: int, qw: torch.Tensor, qs: torch.Tensor | None, rows: int, cols: int) -> "Mat":
+        """qw / qs: the reference loader's repacked arrays (or the f32 weights in qw), on the device."""
+        lib = _lib.load()
+        nbytes = lib.ie_b200_mat_bytes(kind, rows, cols)
+        dst = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=qw.device)
+        check(lib.ie_b200_repack_ref(kind, qw.data_ptr(), _p(qs), rows, cols, dst.data_ptr(), _stream()))
+        return Mat(kind, rows, cols, dst)
+
+
+def quant_q8(x: torch.Tensor) -> torch.Tensor:
+    """x: [T, n] or [n] f32 -> uint8 [T, 40 n/32] Q8 buffers."""
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    T, n = x2.shape
+    nb = n // 32
+    q = torch.empty((T, q8_bytes(nb)), dtype=torch.uint8, device=x.device)
+    check(_lib.load().ie_b200_quant_q8(x2.data_ptr(), q.data_ptr(), nb, T, n * 4, q8_bytes(nb), _stream()))
+    return q
+
+
+def gemv(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.Tensor | None = None,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[T, rows] = W x (+bias) (+res). x: Q8 buffers [T, 40 nb] uint8 (f32 [T, cols] for MAT_F32)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    T = x2.shape[0]
+    y = out if out is not None else torch.empty((T, w.rows), dtype=torch.float32, device=x.device)
+    xs = x2.stride(0) * x2.element_size()
+    rs = 0 if res is None else res.reshape(T, -1).stride(0) * 4
+    check(_lib.load().ie_b200_gemv(w.kind, w.data.data_ptr(), w.rows, w.cols, x2.data_ptr(), y.data_ptr(), _p(bias), _p(res), T, xs,
+                                   w.rows * 4, rs, _stream()))
+    return y
+
+
+def block_dots(w: Mat, xq: torch.Tensor) -> torch.Tensor:
+    n = w.rows * w.nb * (2 if w.kind == MAT_Q6K else 1)
+    d = torch.empty(n, dtype=torch.int32, device=xq.device)
+    check(_lib.load().ie_b200_block_dots(w.kind, w.data.data_ptr(), w.rows, w.cols, xq.data_ptr(), d.data_ptr(), _stream()))
+    return d
+
+
+def embed(w: Mat, tok: torch.Tensor) -> torch.Tensor:
+    T = tok.numel()
+    out = torch.empty((T, w.cols), dtype=torch.float32, device=tok.device)
+    check(_lib.load().ie_b200_embed(w.kind, w.data.data_ptr(), w.cols, tok.data_ptr(), out.data_ptr(), T, w.cols * 4, _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, wt: torch.Tensor, eps: float, quant: bool = True):
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    T, n = x2.shape
+    y = torch.empty_like(x2)
+    q = torch.empty((T, q8_bytes(n // 32)), dtype=torch.uint8, device=x.device) if quant else None
+    check(_lib.load().ie_b200_rmsnorm(x2.data_ptr(), wt.data_ptr(), y.data_ptr(), n, eps, _p(q), T, n * 4, n * 4,
+                                      q8_bytes(n // 32), _stream()))
+    return y, q
+
+
+def swiglu(gu: torch.Tensor, n: int, quant: bool = True):
+    """gu: [T, 2 n] f32 ([gate | up]); gate is overwritten with silu(gate) * up."""
+    T = gu.shape[0]
+    q = torch.empty((T, q8_bytes(n // 32)), dtype=torch.uint8, device=gu.device) if quant else None
+    check(_lib.load().ie_b200_swiglu(gu.data_ptr(), gu.data_ptr() + 4 * n, n, _p(q), T, gu.stride(0) * 4, q8_bytes(n // 32), _stream()))
+    return gu[:, :n], q
+
+
+def rope_kv(qkv: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
+            nq: int, nkv: int, hd: int, neox: bool, kv_len: int) -> None:
+    """qkv: [T, (nq + 2 nkv) hd] f32, rotated in place; kc / vc: [nkv, kv_len, hd] half or float."""
+    T = qkv.shape[0]
+    base = qkv.data_ptr()
+    check(_lib.load().ie_b200_rope_kv(base, base + 4 * nq * hd, base + 4 * (nq + nkv) * hd, kc.data_ptr(), vc.data_ptr(), cos.data_ptr(),
+                                      sin.data_ptr(), pos.data_ptr(), nq, nkv, hd, int(neox), int(kc.dtype == torch.float32), kv_len, T,
+                                      qkv.stride(0) * 4, _stream()))
+
+
+class AttnScratch:
+    """Partials and arrival counters of the split-KV attention for one shape."""
+
+    def __init__(self, n_head: int, hd: int, n_ctx: int, T: int, device):
+        lib = _lib.load()
+        self.part = torch.empty(lib.ie_b200_attn_part_bytes(n_head, hd, n_ctx, T), dtype=torch.uint8, device=device)
+        self.count = torch.zeros(lib.ie_b200_attn_count_words(n_head, T), dtype=torch.int32, device=device)
+
+
+def attn_decode(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, pos: torch.Tensor, n_head: int, n_kv: int, hd: int, n_ctx: int,
+                scratch: AttnScratch, quant: bool = True):
+    """q: [T, >= n_head hd] f32 rows (stride taken from the tensor); returns (out [T, n_head hd], Q8 copy or None)."""
+    T = q.shape[0]
+    kv_len = kc.shape[1]
+    out = torch.empty((T, n_head * hd), dtype=torch.float32, device=q.device)
+    nbq = n_head * hd // 32
+    oq = torch.empty((T, q8_bytes(nbq)), dtype=torch.uint8, device=q.device) if quant else None
+    check(_lib.load().ie_b200_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), _p(oq), pos.data_ptr(), n_head, n_kv,
+                                          hd, int(kc.dtype == torch.float32), kv_len, n_ctx, T, q.stride(0) * 4, n_head * hd * 4,
+                                          q8_bytes(nbq), scratch.part.data_ptr(), scratch.count.data_ptr(), _stream()))
+    return out, oq
+
+
+def argmax(x: torch.Tensor) -> torch.Tensor:
+    """x: [T, n] f32 -> int32 [T, 2]: (index, float bits of the softmax probability of the maximum)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    T, n = x2.shape
+    lib = _lib.load()
+    part = torch.empty(lib.ie_b200_argmax_part_bytes(T), dtype=torch.uint8, device=x.device)
+    out = torch.empty((T, 2), dtype=torch.int32, device=x.device)
+    check(lib.ie_b200_argmax(x2.data_ptr(), n, out.data_ptr(), T, x2.stride(0) * 4, 8, part.data_ptr(), _stream()))
+    return out

@@ -1,0 +1,160 @@
+/* ie_b200.h -- the C ABI of libie_b200.so: hand-written sm_100a CUDA kernels
+ * for the decode hot path of amd-infer, and a small engine that runs a
+ * decode-step op list with them.
+ *
+ * Conventions
+ *  - Plain C types only. Pointers named d_* are device pointers, h_* host
+ *    pointers. `stream` is a cudaStream_t passed as void* (NULL: the legacy
+ *    default stream).
+ *  - Every function returns 0 on success or a negative IE_B200_E_* code;
+ *    ie_b200_last_error() gives the message of the calling thread's last
+ *    failure. Nothing here prints or exits: the C backend above this ABI
+ *    (src/cuda.c) turns an error into the reference's die-with-message
+ *    convention (src/common.c:6-14 of the reference).
+ *  - There is no CPU fallback: without a CUDA device every launch fails with
+ *    IE_B200_E_CUDA.
+ *
+ * Each entry point cites the reference interface it stands in for
+ * (path:line inside the amd-infer tree).
+ */
+#ifndef IE_B200_H
+#define IE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  IE_B200_OK = 0,
+  IE_B200_E_ARG = -1,   /* a NULL or misaligned pointer, an unknown kind */
+  IE_B200_E_SIZE = -2,  /* a size outside what the kernels support */
+  IE_B200_E_CUDA = -3,  /* a CUDA runtime error (message in last_error) */
+  IE_B200_E_STATE = -4, /* engine call out of order */
+  IE_B200_E_DEVICE = -5 /* a kernel set the device error word (a bounded wait ran out) */
+};
+
+/* Matrix kinds: the reference's MAT_* numbering (src/model.h:15). */
+enum { IE_B200_MAT_Q4 = 0, IE_B200_MAT_F32 = 1, IE_B200_MAT_Q4K = 3, IE_B200_MAT_Q6K = 4 };
+
+/* GGML tensor types accepted by the GGUF repack (src/common.h:11-13). */
+enum { IE_B200_GGML_F32 = 0, IE_B200_GGML_Q4_0 = 2, IE_B200_GGML_Q4_K = 12, IE_B200_GGML_Q6_K = 14 };
+
+const char *ie_b200_last_error(void);
+/* Number of CUDA devices visible (0 without a driver or a GPU). */
+int ie_b200_device_count(void);
+/* How many kernels this library has launched in this process (all threads). */
+uint64_t ie_b200_launch_count(void);
+
+/* ---------------------------------------------------------------- layout
+ * The streaming layout of a quantised matrix ("row panels"): each row is one
+ * contiguous, 16-byte aligned run of bytes holding, for its nb = cols/32
+ * blocks, first all 16-byte nibble blocks, then the per-block scales, then
+ * (K kinds) the per-super-block constants; rows follow each other at
+ * ie_b200_row_bytes(). A warp that owns a row therefore streams one
+ * contiguous span with 16-byte loads, and a group of rows is one bulk copy.
+ *   Q4_0: nb x 16 B nibbles (the GGUF nibble bytes), nb x f16 d          = 18 B/block
+ *   Q4_K: nb x 16 B nibbles (Q4_0 order per sub-block), nb/8 x 16 B
+ *         {f16 d, f16 dmin, 8 x 12 bit (sc | mn << 6)}                     = 18 B/block
+ *   Q6_K: nb x 16 B low nibbles, nb x 8 B high-bit words, nb x 2 B
+ *         (sc0 | sc1 << 8), nb/8 x f16 d                                   = 26.25 B/block
+ * Replaces the word/scale arrays of the reference's `mat`
+ * (src/model.h:15-43, index maps core/ie_core.h:72-77, :261-263, :323-327).
+ * Block ownership (lane l <- blocks l, l+32, ...) and block contents are
+ * unchanged; only addresses differ. F32 matrices stay rows x cols floats. */
+size_t ie_b200_row_bytes(int kind, uint32_t cols);
+size_t ie_b200_mat_bytes(int kind, uint32_t rows, uint32_t cols);
+
+/* GGUF tensor bytes (already on the device) -> streaming layout. Stands in
+ * for repack_q4 / repack_q4k / repack_q6k (src/model.c:205, :246, :271).
+ * ggml_type: IE_B200_GGML_*; F32 is a plain copy. */
+int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t rows, uint32_t cols, void *d_dst, void *stream);
+/* The reference's repacked arrays qw / qs (on the device, as ie_mat_sink
+ * receives them from model_load, src/model.c:649-658) -> streaming layout. */
+int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, uint32_t rows, uint32_t cols, void *d_dst, void *stream);
+
+/* ------------------------------------------------------------- kernels */
+
+/* Q8 activation quantiser for T token rows: per 32 floats d = amax/127,
+ * q = round(x/d), asum = sum q; output buffer [int8 x 32nb][f32 d x nb]
+ * [u32 asum x nb]. Bit-exact with cpu_quant_q8 (src/cpu.c:36-53); argument
+ * list after ie_quant_q8 {x,q,nb,xs,qs} (src/hip.c:924). Strides in bytes. */
+int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_t x_stride, size_t q_stride, void *stream);
+
+/* y[T][rows] = W x (+bias) (+res): W in the streaming layout, x a Q8 buffer
+ * per token (f32 for MAT_F32). One warp per (row, token); lane l accumulates
+ * blocks l, l+32, ... in order and the warp reduces by shuffle-down 16, 8, 4,
+ * 2, 1, so the result equals cpu_gemv_q4 / _q4k / _q6k / cpu_gemv_f32 bit for
+ * bit (src/cpu.c:64-148, :238-249); epilogue y = acc (+bias[r]), y = res[r] + y
+ * (src/cpu.c:515-520). Argument list after ie_gemv_q4q8
+ * {qw,qs,xq,y,rows,nb,bias,res,...} (src/hip.c:930) and its multi-token
+ * forms {...,T,xs,ys,rs} (src/hip.c:1000). res may alias y. */
+int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
+                 const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
+
+/* Test hook: the int32 dot of every (row, block) of a Q4_0 / Q4_K matrix
+ * (Q4_K: the unsigned-nibble dot) and, for Q6_K, the two half dots
+ * (dots[2 (r nb + b) + h]); what core/ie_core.h:161, :281, :385 define. */
+int ie_b200_block_dots(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, int32_t *d_dots, void *stream);
+
+/* Row `tok` of the token embedding as floats (MAT_Q4 or MAT_F32):
+ * mat_row (src/cpu.c:252-274), ie_embed_q4 / _f32 (kernels/ie_kernels.c:171-191).
+ * d_tok: T token ids on the device. */
+int ie_b200_embed(int kind, const void *d_w, uint32_t cols, const uint32_t *d_tok, float *d_out, uint32_t T, size_t out_stride,
+                  void *stream);
+
+/* y = x * rsqrt(mean x^2 + eps) * w, optionally with the Q8 copy of y
+ * (d_q != NULL): rmsnorm (src/cpu.c:276-281) + cpu_quant_q8; ie_rmsnorm
+ * {x,w,y,n,eps,q,xs,ys,qs} (src/hip.c:917). The sum of squares is a tree sum
+ * (differs from the CPU's sequential sum by rounding only). */
+int ie_b200_rmsnorm(const float *d_x, const float *d_w, float *d_y, uint32_t n, float eps, void *d_q, uint32_t T, size_t x_stride,
+                    size_t y_stride, size_t q_stride, void *stream);
+
+/* a = silu(a) * b, optionally with the Q8 copy (src/cpu.c:579-582, ie_swiglu
+ * kernels/ie_kernels.c:2458). */
+int ie_b200_swiglu(float *d_a, const float *d_b, uint32_t n, void *d_q, uint32_t T, size_t a_stride, size_t q_stride, void *stream);
+
+/* RoPE of q (nq heads) and k (nkv heads) in place with the table rows of
+ * each token's position, then store k and v of that position into the KV
+ * cache (half or float elements): OP_ROPE_KV (src/cpu.c:537-546), ie_rope_kv
+ * {q,k,v,kc,vc,cs,sn,nq,nkv,hd,neox} (src/hip.c:1284). d_pos: first position
+ * (device scalar); token t is at *d_pos + t. Cache row = position % kv_len. */
+int ie_b200_rope_kv(float *d_q, float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin,
+                    const uint32_t *d_pos, uint32_t nq, uint32_t nkv, uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t T,
+                    size_t qkv_stride, void *stream);
+
+/* Split-KV decode attention for T tokens (token t attends to positions
+ * 0 .. *d_pos + t): K/V of a KV head are streamed once for all its query
+ * heads; splits of the position range write (max, sum, out[hd]) partials to
+ * d_part and the last split to finish merges them. Optional Q8 copy of the
+ * output. The role of ie_attn_kv {q,kc,vc,part,out,pos,hd,nh,nkv,smax,...}
+ * (src/hip.c:1492-1493, kernels/ie_kernels.c:2721) and, for parity, of
+ * attention() (src/cpu.c:301-329). d_part: ie_b200_attn_part_bytes() of
+ * scratch; d_count: ie_b200_attn_count_words() zeroed u32 counters (left zero). */
+size_t ie_b200_attn_part_bytes(uint32_t n_head, uint32_t hd, uint32_t n_ctx, uint32_t T);
+size_t ie_b200_attn_count_words(uint32_t n_head, uint32_t T);
+int ie_b200_attn_decode(const float *d_q, const void *d_kc, const void *d_vc, float *d_out, void *d_oq, const uint32_t *d_pos,
+                        uint32_t n_head, uint32_t n_kv, uint32_t hd, int kv_f32, uint32_t kv_len, uint32_t n_ctx, uint32_t T,
+                        size_t q_stride, size_t out_stride, size_t oq_stride, void *d_part, uint32_t *d_count, void *stream);
+
+/* First index of the maximum of each of T rows, and the softmax probability
+ * of that maximum: OP_ARGMAX (src/cpu.c:608-614), ie_argmax
+ * {x,n,out,part,count,ng} (src/hip.c:1537). out: {u32 index, f32 prob} per row.
+ * d_part: ie_b200_argmax_part_bytes(T) of scratch. */
+size_t ie_b200_argmax_part_bytes(uint32_t T);
+int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *d_part,
+                   void *stream);
+
+/* Chunked-prefill GEMM: Y[T][rows] = Xq8 W^T for T >= 17 tokens with the
+ * weights read once per chunk; the role of ie_gemm_q4kr / ie_gemm_q6kr
+ * (kernels/ie_kernels.c:1315, :2015; dispatch src/hip.c:965-1003). Same
+ * operands as ie_b200_gemv. */
+int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
+                 const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

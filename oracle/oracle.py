@@ -1,0 +1,319 @@
+"""ctypes front end of the test oracles (TEST INFRASTRUCTURE).
+
+  Oracle  libie_oracle.so: the C restatement of the reference CPU backend
+  Ref     _ref/libie_ref.so: the reference's own src/cpu.c etc., when it was
+          built on a machine that has the reference tree
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+MAT_Q4, MAT_F32, MAT_Q8, MAT_Q4K, MAT_Q6K = 0, 1, 2, 3, 4
+GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
+GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
+
+_vp, _u32, _f32, _int = C.c_void_p, C.c_uint32, C.c_float, C.c_int
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(_vp)
+
+
+def q8_bytes(nb: int) -> int:
+    return 40 * nb
+
+
+class Oracle:
+    """The C restatement. Arrays are numpy; matrices are (qw u32, qs u16) in the reference's repacked form."""
+
+    def __init__(self):
+        from . import build
+
+        self.lib = C.CDLL(str(build.build_oracle()))
+        L = self.lib
+        L.ora_f16_to_f32.restype, L.ora_f16_to_f32.argtypes = _f32, [C.c_uint16]
+        L.ora_f32_to_f16.restype, L.ora_f32_to_f16.argtypes = C.c_uint16, [_f32]
+        L.ora_argmax.restype = _u32
+        L.ora_model_new.restype = _vp
+        L.ora_model_new.argtypes = [_u32] * 7 + [_f32, _f32, _int, _int]
+        L.ora_model_free.argtypes = [_vp]
+        L.ora_model_set_mat.argtypes = [_vp, _int, _int, _int, _u32, _u32, _vp, _vp, _vp]
+        L.ora_model_set_vec.argtypes = [_vp, _int, _int, _vp]
+        L.ora_model_set_trace.argtypes = [_vp, _vp]
+        L.ora_step.restype, L.ora_step.argtypes = _u32, [_vp, _u32, _u32, _vp]
+        for name, args in {
+            "ora_quant_q8": [_vp, _vp, _u32],
+            "ora_repack_q4_0": [_vp, _u32, _u32, _vp, _vp],
+            "ora_repack_q4_k": [_vp, _u32, _u32, _vp, _vp],
+            "ora_repack_q6_k": [_vp, _u32, _u32, _vp, _vp],
+            "ora_block_dots_q4": [_vp, _u32, _u32, _vp, _vp],
+            "ora_gemv_q4": [_vp, _vp, _u32, _u32, _vp, _vp],
+            "ora_gemv_q4k": [_vp, _vp, _u32, _u32, _vp, _vp],
+            "ora_gemv_q6k": [_vp, _vp, _u32, _u32, _vp, _vp],
+            "ora_gemv_f32": [_vp, _u32, _u32, _vp, _vp],
+            "ora_epilogue": [_vp, _u32, _vp, _vp],
+            "ora_embed_q4": [_vp, _vp, _u32, _u32, _vp],
+            "ora_rmsnorm": [_vp, _vp, _vp, _u32, _f32],
+            "ora_rope": [_vp, _u32, _u32, _u32, _int, _vp, _vp],
+            "ora_rope_tables": [_u32, _u32, _f32, _vp, _vp],
+            "ora_attention": [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp],
+            "ora_swiglu": [_vp, _vp, _u32],
+        }.items():
+            getattr(L, name).argtypes = args
+
+    # -- elementary pieces
+    def quant_q8(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        nb = x.size // 32
+        q = np.zeros(q8_bytes(nb), dtype=np.uint8)
+        self.lib.ora_quant_q8(_ptr(x), _ptr(q), nb)
+        return q
+
+    def repack(self, ggml_type: int, raw: np.ndarray, rows: int, cols: int):
+        """GGUF bytes -> (kind, qw, qs) in the reference's repacked form (f32: (MAT_F32, floats, None))."""
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        nb = cols // 32
+        if ggml_type == GGML_F32:
+            return MAT_F32, raw.view(np.float32).reshape(rows, cols).copy(), None
+        if ggml_type == GGML_Q4_0:
+            qw, qs = np.zeros(rows * nb * 4, np.uint32), np.zeros(rows * nb, np.uint16)
+            self.lib.ora_repack_q4_0(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
+        elif ggml_type == GGML_Q4_K:
+            qw, qs = np.zeros(rows * nb * 4, np.uint32), np.zeros(rows * nb + rows * (nb // 8) * 2, np.uint16)
+            self.lib.ora_repack_q4_k(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
+        elif ggml_type == GGML_Q6_K:
+            qw, qs = np.zeros(rows * nb * 6, np.uint32), np.zeros(rows * nb + rows * (nb // 8), np.uint16)
+            self.lib.ora_repack_q6_k(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
+        else:
+            raise ValueError(ggml_type)
+        return GGML_TO_MAT[ggml_type], qw, qs
+
+    def gemv(self, kind: int, qw: np.ndarray, qs, rows: int, cols: int, x: np.ndarray, bias=None, res=None) -> np.ndarray:
+        """x: a Q8 buffer (uint8) or, for MAT_F32, floats."""
+        y = np.zeros(rows, dtype=np.float32)
+        nb = cols // 32
+        if kind == MAT_F32:
+            self.lib.ora_gemv_f32(_ptr(qw), rows, cols, _ptr(np.ascontiguousarray(x, np.float32)), _ptr(y))
+        else:
+            fn = {MAT_Q4: self.lib.ora_gemv_q4, MAT_Q4K: self.lib.ora_gemv_q4k, MAT_Q6K: self.lib.ora_gemv_q6k}[kind]
+            fn(_ptr(qw), _ptr(qs), rows, nb, _ptr(x), _ptr(y))
+        if bias is not None or res is not None:
+            self.lib.ora_epilogue(_ptr(y), rows, _ptr(bias), _ptr(res))
+        return y
+
+    def block_dots_q4(self, qw: np.ndarray, rows: int, nb: int, xq: np.ndarray) -> np.ndarray:
+        d = np.zeros(rows * nb, dtype=np.int32)
+        self.lib.ora_block_dots_q4(_ptr(qw), rows, nb, _ptr(xq), _ptr(d))
+        return d
+
+    def embed_q4(self, qw, qs, nb: int, r: int) -> np.ndarray:
+        out = np.zeros(nb * 32, np.float32)
+        self.lib.ora_embed_q4(_ptr(qw), _ptr(qs), nb, r, _ptr(out))
+        return out
+
+    def rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros_like(x)
+        self.lib.ora_rmsnorm(_ptr(x), _ptr(np.ascontiguousarray(w, np.float32)), _ptr(y), x.size, eps)
+        return y
+
+    def rope_tables(self, n_ctx: int, nrot: int, base: float):
+        cs, sn = np.zeros((n_ctx, nrot // 2), np.float32), np.zeros((n_ctx, nrot // 2), np.float32)
+        self.lib.ora_rope_tables(n_ctx, nrot, base, _ptr(cs), _ptr(sn))
+        return cs, sn
+
+    def rope(self, x: np.ndarray, nh: int, hd: int, neox: bool, c: np.ndarray, s: np.ndarray) -> np.ndarray:
+        y = np.ascontiguousarray(x, np.float32).copy()
+        self.lib.ora_rope(_ptr(y), nh, hd, hd, int(neox), _ptr(np.ascontiguousarray(c)), _ptr(np.ascontiguousarray(s)))
+        return y
+
+    def attention(self, q: np.ndarray, kc: np.ndarray, vc: np.ndarray, pos: int, n_head: int, n_kv: int, hd: int) -> np.ndarray:
+        """kc, vc: f32 [>= pos + 1, n_kv * hd] (position major, the reference CPU layout)."""
+        n_ctx = kc.shape[0]
+        sc = np.zeros(n_head * n_ctx, np.float32)
+        out = np.zeros(n_head * hd, np.float32)
+        self.lib.ora_attention(_ptr(np.ascontiguousarray(q, np.float32)), _ptr(np.ascontiguousarray(kc, np.float32)),
+                               _ptr(np.ascontiguousarray(vc, np.float32)), pos, n_head, n_kv, hd, n_ctx, _ptr(sc), _ptr(out))
+        return out
+
+    def swiglu(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        y = np.ascontiguousarray(a, np.float32).copy()
+        self.lib.ora_swiglu(_ptr(y), _ptr(np.ascontiguousarray(b, np.float32)), y.size)
+        return y
+
+    def argmax(self, a: np.ndarray) -> int:
+        a = np.ascontiguousarray(a, np.float32)
+        return int(self.lib.ora_argmax(_ptr(a), a.size))
+
+
+class OracleModel:
+    """A llama / qwen2 decoder on the restatement, fed GGUF tensor bytes."""
+
+    WHICH = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate": 4, "ffn_up": 5, "ffn_down": 6}
+    VEC = {"attn_norm": 0, "ffn_norm": 1, "attn_q.bias": 2, "attn_k.bias": 3, "attn_v.bias": 4}
+
+    def __init__(self, ora: Oracle, cfg, n_ctx: int, kv_f16: bool = False):
+        """cfg: an amd_c_b200.gguf.ModelConfig with its tensors filled."""
+        from amd_c_b200.gguf import is_matrix
+
+        self.ora, self.cfg, self._keep = ora, cfg.as_dict(), []
+        L = ora.lib
+        c = self.cfg
+        self.h = L.ora_model_new(c["n_layer"], c["dim"], c["ffn"], c["n_head"], c["n_kv"], c["vocab"], n_ctx, c["eps"], c["rope_base"],
+                                 int(c["neox"]), int(kv_f16))
+        if "output.weight" not in cfg.tensors:
+            raise ValueError("tied output not supported by the oracle model")
+        for name, t in cfg.tensors.items():
+            if is_matrix(name):
+                kind, qw, qs = ora.repack(t.ggml_type, t.raw(), t.rows, t.cols)
+                self._keep += [qw, qs]
+                layer, which = self._mat_slot(name)
+                if kind == MAT_F32:
+                    L.ora_model_set_mat(self.h, layer, which, kind, t.rows, t.cols, None, None, _ptr(qw))
+                else:
+                    L.ora_model_set_mat(self.h, layer, which, kind, t.rows, t.cols, _ptr(qw), _ptr(qs), None)
+            else:
+                v = t.f32().copy()
+                self._keep.append(v)
+                layer, which = self._vec_slot(name)
+                L.ora_model_set_vec(self.h, layer, which, _ptr(v))
+        self.trace = None
+
+    @staticmethod
+    def _mat_slot(name: str):
+        if name == "token_embd.weight":
+            return -1, 0
+        if name == "output.weight":
+            return -1, 1
+        _, l, rest = name.split(".", 2)
+        return int(l), OracleModel.WHICH[rest[: -len(".weight")]]
+
+    @staticmethod
+    def _vec_slot(name: str):
+        if name == "output_norm.weight":
+            return -1, 0
+        _, l, rest = name.split(".", 2)
+        key = rest[: -len(".weight")] if rest.endswith(".weight") else rest
+        return int(l), OracleModel.VEC[key]
+
+    def enable_trace(self):
+        self.trace = np.zeros((self.cfg["n_layer"], self.cfg["dim"]), np.float32)
+        self.ora.lib.ora_model_set_trace(self.h, _ptr(self.trace))
+
+    def step(self, tok: int, pos: int):
+        logits = np.zeros(self.cfg["vocab"], np.float32)
+        nxt = self.ora.lib.ora_step(self.h, tok, pos, _ptr(logits))
+        return int(nxt), logits
+
+    def close(self):
+        if self.h:
+            self.ora.lib.ora_model_free(self.h)
+            self.h = None
+
+
+class Ref:
+    """The reference's own CPU code (libie_ref.so). `available()` is False where it was never built."""
+
+    def __init__(self):
+        from . import build
+
+        p = build.build_ref()
+        if p is None:
+            raise FileNotFoundError("oracle/_ref/libie_ref.so has not been built (the reference tree is absent)")
+        self.lib = C.CDLL(str(p))
+        L = self.lib
+        L.ref_quant_q8.argtypes = [_vp, _vp, _u32]
+        L.ref_mat_new.restype, L.ref_mat_new.argtypes = _vp, [_u32, _vp, _u32, _u32]
+        for n in ("ref_mat_qw", "ref_mat_qs", "ref_mat_f"):
+            getattr(L, n).restype, getattr(L, n).argtypes = _vp, [_vp]
+        L.ref_mat_kind.restype, L.ref_mat_kind.argtypes = _int, [_vp]
+        L.ref_mat_nb.restype, L.ref_mat_nb.argtypes = _u32, [_vp]
+        L.ref_mat_qw_words.restype, L.ref_mat_qw_words.argtypes = C.c_uint64, [_vp]
+        L.ref_mat_qs_n.restype, L.ref_mat_qs_n.argtypes = C.c_uint64, [_vp]
+        L.ref_mat_free.argtypes = [_vp]
+        L.ref_gemv.restype, L.ref_gemv.argtypes = _int, [_vp, _vp, _vp]
+        L.ref_open.restype, L.ref_open.argtypes = _vp, [C.c_char_p, _u32]
+        for n in ("ref_vocab", "ref_dim", "ref_n_layer"):
+            getattr(L, n).restype, getattr(L, n).argtypes = _u32, [_vp]
+        L.ref_weight_bytes_per_token.restype, L.ref_weight_bytes_per_token.argtypes = C.c_uint64, [_vp]
+        L.ref_step.restype, L.ref_step.argtypes = _u32, [_vp, _u32, _u32, _vp, _vp]
+        L.ref_layer_outputs.argtypes = [_vp, _u32, _u32, _vp]
+        L.ref_close.argtypes = [_vp]
+
+    @staticmethod
+    def available() -> bool:
+        from . import build
+
+        return build.build_ref() is not None
+
+    def quant_q8(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        nb = x.size // 32
+        q = np.zeros(q8_bytes(nb), dtype=np.uint8)
+        self.lib.ref_quant_q8(_ptr(x), _ptr(q), nb)
+        return q
+
+    def mat(self, ggml_type: int, raw: np.ndarray, rows: int, cols: int) -> "RefMat":
+        return RefMat(self, ggml_type, raw, rows, cols)
+
+
+class RefMat:
+    def __init__(self, ref: Ref, ggml_type: int, raw: np.ndarray, rows: int, cols: int):
+        self.ref, self.rows, self.cols = ref, rows, cols
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        self.h = ref.lib.ref_mat_new(ggml_type, _ptr(raw), rows, cols)
+        self.kind = ref.lib.ref_mat_kind(self.h)
+
+    def arrays(self):
+        L = self.ref.lib
+        if self.kind == MAT_F32:
+            return np.ctypeslib.as_array(C.cast(L.ref_mat_f(self.h), C.POINTER(C.c_float)), (self.rows * self.cols,)).copy(), None
+        nw, ns = L.ref_mat_qw_words(self.h), L.ref_mat_qs_n(self.h)
+        qw = np.ctypeslib.as_array(C.cast(L.ref_mat_qw(self.h), C.POINTER(C.c_uint32)), (nw,)).copy()
+        qs = np.ctypeslib.as_array(C.cast(L.ref_mat_qs(self.h), C.POINTER(C.c_uint16)), (ns,)).copy()
+        return qw, qs
+
+    def gemv(self, xq: np.ndarray) -> np.ndarray:
+        y = np.zeros(self.rows, np.float32)
+        if self.ref.lib.ref_gemv(self.h, _ptr(xq), _ptr(y)) != 0:
+            raise ValueError("reference GEMV: unsupported kind")
+        return y
+
+    def free(self):
+        if self.h:
+            self.ref.lib.ref_mat_free(self.h)
+            self.h = None
+
+
+class RefEngine:
+    """The reference's model loader + CPU backend on a GGUF file."""
+
+    def __init__(self, ref: Ref, path: str, n_ctx: int):
+        self.ref = ref
+        self.h = ref.lib.ref_open(str(path).encode(), n_ctx)
+        self.vocab, self.dim, self.n_layer = ref.lib.ref_vocab(self.h), ref.lib.ref_dim(self.h), ref.lib.ref_n_layer(self.h)
+
+    def step(self, tok: int, pos: int, want_logits: bool = True):
+        logits = np.zeros(self.vocab, np.float32) if want_logits else None
+        ms = C.c_double(0)
+        nxt = self.ref.lib.ref_step(self.h, tok, pos, _ptr(logits), C.byref(ms))
+        return int(nxt), logits, ms.value
+
+    def layer_outputs(self, tok: int, pos: int) -> np.ndarray:
+        out = np.zeros((self.n_layer, self.dim), np.float32)
+        self.ref.lib.ref_layer_outputs(self.h, tok, pos, _ptr(out))
+        return out
+
+    def weight_bytes_per_token(self) -> int:
+        return int(self.ref.lib.ref_weight_bytes_per_token(self.h))
+
+    def close(self):
+        if self.h:
+            self.ref.lib.ref_close(self.h)
+            self.h = None
