@@ -28,6 +28,8 @@ SIGNATURES = {
     "ie_b200_repack_ref": (_int, [_int, _vp, _vp, _u32, _u32, _vp, _vp]),
     "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
     "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
+    "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_block_dots": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp]),
     "ie_b200_embed": (_int, [_int, _vp, _u32, _vp, _vp, _u32, _sz, _vp]),
     "ie_b200_rmsnorm": (_int, [_vp, _vp, _vp, _u32, _f32, _vp, _u32, _sz, _sz, _sz, _vp]),
@@ -39,6 +41,49 @@ SIGNATURES = {
     "ie_b200_argmax_part_bytes": (_sz, [_u32]),
     "ie_b200_argmax": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp, _vp]),
 }
+
+
+# ---- the engine ABI (include/ie_b200_engine.h) ----
+class Op(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("mat", C.c_int32), ("vec", C.c_int32), ("layer", C.c_int32), ("n", C.c_uint32), ("nh", C.c_uint32),
+                ("a", C.c_uint64), ("b", C.c_uint64), ("c", C.c_uint64), ("qo", C.c_uint64), ("res", C.c_uint64),
+                ("a_stride", C.c_uint32), ("b_stride", C.c_uint32), ("c_stride", C.c_uint32), ("qo_stride", C.c_uint32),
+                ("res_stride", C.c_uint32)]
+
+
+class EngineDesc(C.Structure):
+    _fields_ = [("n_head", C.c_uint32), ("n_kv", C.c_uint32), ("hd", C.c_uint32), ("n_ctx", C.c_uint32), ("n_kv_layers", C.c_uint32),
+                ("T_max", C.c_uint32), ("vocab", C.c_uint32), ("eps", C.c_float), ("neox", C.c_int32), ("kv_f32", C.c_int32),
+                ("arena_bytes", C.c_uint64), ("logits_off", C.c_uint64), ("argmax_off", C.c_uint64), ("logits_stride", C.c_uint32),
+                ("argmax_stride", C.c_uint32)]
+
+
+_u64 = C.c_uint64
+ENGINE_SIGNATURES = {
+    "ie_b200_engine_create": (_int, [C.POINTER(EngineDesc), C.POINTER(_vp)]),
+    "ie_b200_engine_destroy": (None, [_vp]),
+    "ie_b200_engine_add_mat_gguf": (_int, [_vp, _int, _u32, _u32, _vp]),
+    "ie_b200_engine_add_mat_ref": (_int, [_vp, _int, _u32, _u32, _vp, _vp]),
+    "ie_b200_engine_add_mat_device": (_int, [_vp, _int, _u32, _u32, _vp]),
+    "ie_b200_engine_add_vec": (_int, [_vp, _vp, _u32]),
+    "ie_b200_engine_set_rope": (_int, [_vp, _vp, _vp]),
+    "ie_b200_engine_set_ops": (_int, [_vp, C.POINTER(Op), _u32, _u32]),
+    "ie_b200_engine_step": (_int, [_vp, _u32, _u32, _vp, C.POINTER(_u32), C.POINTER(C.c_double)]),
+    "ie_b200_engine_decode": (_int, [_vp, _u32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
+    "ie_b200_engine_enqueue_kinds": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
+    "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
+    "ie_b200_engine_read_rows": (_int, [_vp, _u64, _u32, _u32, _u32, _vp]),
+    "ie_b200_engine_copy_rows": (_int, [_vp, _u64, _u32, _u32, _u64, _u32, _u32, _u32, _u32, _int]),
+    "ie_b200_engine_set_input": (_int, [_vp, _vp, _u32, _u32, _vp]),
+    "ie_b200_engine_enqueue": (_int, [_vp, _u32, _u32, _u32, _vp]),
+    "ie_b200_engine_arena": (_vp, [_vp]),
+    "ie_b200_engine_input_scalars": (_vp, [_vp]),
+    "ie_b200_engine_weight_bytes_per_token": (_u64, [_vp]),
+    "ie_b200_engine_launches_per_step": (_u32, [_vp]),
+}
+
+
+SIGNATURES.update(ENGINE_SIGNATURES)
 
 
 class IeB200Error(RuntimeError):

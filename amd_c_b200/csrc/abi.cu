@@ -2,6 +2,10 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -24,6 +28,29 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *v = getenv("IE_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+int ensure_dynamic_smem(const void *func, size_t bytes) {
+  if (bytes <= 48u * 1024u) return IE_B200_OK;
+  static std::mutex mu;
+  static std::map<std::pair<const void *, int>, size_t> set_to;
+  int dev = 0;
+  IEB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  size_t &cur = set_to[{func, dev}];
+  if (bytes > cur) {
+    IEB_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    cur = bytes;
+  }
+  return IE_B200_OK;
+}
 
 int sm_count() {
   static thread_local int cached_dev = -1, cached = 0;

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   __shared__ float run_m[8], run_l[8];
   __shared__ uint32_t is_last;
 
+  pdl_prologue();
   const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
   const uint32_t np = *a.pos + t + 1u;
   uint32_t span = (np + S - 1u) / S;
@@ -245,9 +246,8 @@ static int launch_attn(const AttnArgs &a, uint32_t T, cudaStream_t st) {
   const size_t red = (size_t)ATT_WARPS * G * HD * sizeof(float);
   const size_t smem = tile > red ? tile : red;
   auto k = attn_decode_kernel<KV, HD, G>;
-  if (smem > 48u * 1024u) IEB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k<<<dim3(a.S, a.n_kv, T), ATT_THREADS, smem, st>>>(a);
-  IEB_LAUNCHED("attn_decode_kernel");
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  IEB_LAUNCH_PDL("attn_decode_kernel", k, dim3(a.S, a.n_kv, T), dim3(ATT_THREADS), smem, st, a);
   return IE_B200_OK;
 }
 

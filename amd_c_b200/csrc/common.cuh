@@ -15,6 +15,12 @@ int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
 int sm_count();
+// Programmatic dependent launch is on unless the environment says IE_B200_PDL=0 (then every launch is a
+// plain stream-ordered launch and the griddepcontrol instructions in the kernels do nothing).
+bool pdl_enabled();
+// Raise (never lower) a kernel's opt-in dynamic shared memory limit on the current device. Monotone, so that
+// launches already captured into a CUDA graph with a larger size stay valid when a smaller launch follows.
+int ensure_dynamic_smem(const void *func, size_t bytes);
 
 #define IEB_CUDA(call)                                   \
   do {                                                   \
@@ -32,6 +38,27 @@ int sm_count();
 
 static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
+#ifdef __CUDACC__
+// Launch with programmatic dependent launch: the kernel may start while its predecessor in the stream
+// is still running. Only for kernels that call pdl_wait() before touching anything a predecessor wrote.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at, cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define IEB_LAUNCH_PDL(what, kernel, grid, block, smem, st, ...)                                  \
+  do {                                                                                            \
+    cudaError_t e_ = ieb::launch_pdl(kernel, grid, block, smem, st, __VA_ARGS__);                 \
+    ieb::count_launch();                                                                          \
+    if (e_ != cudaSuccess) return ieb::cuda_fail(e_, what);                                       \
+  } while (0)
+#endif
+
 // ---- streaming layout geometry (see ie_b200.h) ----
 __host__ __device__ inline size_t round16(size_t n) { return (n + 15u) & ~(size_t)15u; }
 __host__ __device__ inline size_t row_bytes_of(int kind, uint32_t cols) {
@@ -46,6 +73,16 @@ __host__ __device__ inline size_t row_bytes_of(int kind, uint32_t cols) {
 
 // ---- device helpers ----
 #ifdef __CUDACC__
+
+// Programmatic dependent launch: let the next kernel of the stream start (its own pdl_wait keeps it from
+// reading our results early), and wait until the previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Every kernel launched through launch_pdl starts with this.
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
 
 // 16-byte streaming load of weights that are read once: read-only path, not
 // kept in L1.

@@ -1,0 +1,538 @@
+// engine.cu -- the decode engine: owns weights, arena, KV cache and scratch of
+// one GPU; runs a static op list with the kernels of this library. A
+// one-token step is one CUDA-graph launch bracketed by an 8-byte upload
+// (token, position) and an 8-byte download (argmax, probability).
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "ie_b200_engine.h"
+
+namespace ieb {
+
+struct EMat {
+  int kind;
+  uint32_t rows, cols;
+  void *d;
+  bool owned;
+};
+struct EVec {
+  float *d;
+  uint32_t n;
+};
+
+__global__ void add_kernel(const float *a, const float *b, float *c, uint32_t n, size_t as, size_t bs, size_t cs) {
+  const uint32_t t = blockIdx.y;
+  const float *at = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a) + as * t);
+  const float *bt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(b) + bs * t);
+  float *ct = reinterpret_cast<float *>(reinterpret_cast<char *>(c) + cs * t);
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) ct[i] = __fadd_rn(at[i], bt[i]);
+}
+
+// After a one-token step: feed the argmax back as the next token, advance the positions, and log the
+// token in a history ring (hist[cap] counts the steps since the last reset).
+__global__ void advance_kernel(uint32_t *scalars, uint32_t Tm, const uint32_t *argmax, uint32_t *hist, uint32_t cap) {
+  const uint32_t idx = argmax[0];
+  if (threadIdx.x == 0) {
+    const uint32_t c = hist[cap];
+    hist[c % cap] = idx;
+    hist[cap] = c + 1u;
+    scalars[0] = idx;
+    scalars[Tm] += 1u;
+  }
+  for (uint32_t t = threadIdx.x; t < Tm; t += blockDim.x) scalars[Tm + 1u + t] += 1u;
+}
+
+}  // namespace ieb
+
+using namespace ieb;
+
+constexpr uint32_t HIST_CAP = 4096;
+
+struct ie_b200_engine {
+  ie_b200_engine_desc d;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  uint8_t *arena = nullptr;
+  void *kc = nullptr, *vc = nullptr;  // [layer][kv head][n_ctx][hd]
+  size_t kv_layer_bytes = 0;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  uint32_t *scalars = nullptr;  // tokens[T_max], then the first position
+  uint32_t *h_scalars = nullptr, *h_result = nullptr;  // pinned
+  void *attn_part = nullptr;
+  uint32_t *attn_count = nullptr;
+  void *argmax_part = nullptr;
+  uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
+  uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out
+  uint32_t T_att = 1;
+  std::vector<EMat> mats;
+  std::vector<EVec> vecs;
+  std::vector<ie_b200_op> ops;
+  uint32_t i_head = 0;
+  cudaGraphExec_t step_graph = nullptr;
+  uint32_t step_launches = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+static inline void *at(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t t0) {
+  return off == IE_B200_NONE ? nullptr : e->arena + off + (size_t)stride * t0;
+}
+
+// Can the streaming (bulk-copy ring) GEMV take this matrix? Quantised kinds whose ring fits its shared-memory budget.
+static bool stream_ok(const EMat &m) {
+  if (m.kind == IE_B200_MAT_F32 || m.cols % 32u) return false;
+  const size_t nb = m.cols / 32u;
+  return nb <= 1024u && nb * 40u + 128u + 4u * row_bytes_of(m.kind, m.cols) <= 110u * 1024u;
+}
+
+// One op for tokens [t0, t0 + T) of a run.
+static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32_t T, cudaStream_t st) {
+  const ie_b200_engine_desc &d = e->d;
+  void *a = at(e, o.a, o.a_stride, t0), *b = at(e, o.b, o.b_stride, t0), *c = at(e, o.c, o.c_stride, t0);
+  void *qo = at(e, o.qo, o.qo_stride, t0), *res = at(e, o.res, o.res_stride, t0);
+  const uint32_t *tok = e->scalars + t0, *pos = e->scalars + d.T_max;
+  switch (o.kind) {
+    case IE_B200_OP_EMBED: {
+      if (o.mat < 0 || (size_t)o.mat >= e->mats.size()) return fail(IE_B200_E_ARG, "EMBED: bad matrix handle %d", o.mat);
+      const EMat &m = e->mats[o.mat];
+      return ie_b200_embed(m.kind, m.d, m.cols, tok, static_cast<float *>(a), T, o.a_stride, st);
+    }
+    case IE_B200_OP_RMSNORM: {
+      if (o.vec < 0 || (size_t)o.vec >= e->vecs.size()) return fail(IE_B200_E_ARG, "RMSNORM: bad vector handle %d", o.vec);
+      if (res) {  // a = a + res first (the reduced partial of a sharded GEMV)
+        add_kernel<<<dim3((o.n + 255u) / 256u, T), 256, 0, st>>>(static_cast<float *>(a), static_cast<float *>(res), static_cast<float *>(a), o.n,
+                                                                o.a_stride, o.res_stride, o.a_stride);
+        IEB_LAUNCHED("add_kernel");
+      }
+      return ie_b200_rmsnorm(static_cast<float *>(a), e->vecs[o.vec].d, static_cast<float *>(b), o.n, d.eps, qo, T, o.a_stride, o.b_stride,
+                             o.qo_stride, st);
+    }
+    case IE_B200_OP_QUANT: return ie_b200_quant_q8(static_cast<float *>(a), b, o.n / 32u, T, o.a_stride, o.b_stride, st);
+    case IE_B200_OP_GEMV: {
+      if (o.mat < 0 || (size_t)o.mat >= e->mats.size()) return fail(IE_B200_E_ARG, "GEMV: bad matrix handle %d", o.mat);
+      const EMat &m = e->mats[o.mat];
+      const float *bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr;
+      if (T == 1 && stream_ok(m))
+        return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), e->err, st);
+      return ie_b200_gemv(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
+                          o.res_stride, st);
+    }
+    case IE_B200_OP_ROPE_KV: {
+      char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+      // positions of tokens t0.. : the kernel adds its token index to *pos, so offset the q/k/v rows only
+      // and pass a position scalar that already includes t0 (scalars[T_max + 1 + t0] holds pos + t0)
+      return ie_b200_rope_kv(static_cast<float *>(a), static_cast<float *>(b), static_cast<float *>(c), kcl, vcl, e->rope_cos, e->rope_sin,
+                             pos + 1 + t0, o.nh, d.n_kv, d.hd, d.neox, d.kv_f32, d.n_ctx, T, o.a_stride, st);
+    }
+    case IE_B200_OP_ATTN: {
+      char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+      for (uint32_t s = 0; s < T; s += e->T_att) {  // bounded scratch: at most T_att tokens per launch
+        const uint32_t n = T - s < e->T_att ? T - s : e->T_att;
+        int r = ie_b200_attn_decode(static_cast<float *>(at(e, o.a, o.a_stride, t0 + s)), kcl, vcl, static_cast<float *>(at(e, o.b, o.b_stride, t0 + s)),
+                                    at(e, o.qo, o.qo_stride, t0 + s), pos + 1 + t0 + s, d.n_head, d.n_kv, d.hd, d.kv_f32, d.n_ctx, d.n_ctx, n,
+                                    o.a_stride, o.b_stride, o.qo_stride, e->attn_part, e->attn_count, st);
+        if (r) return r;
+      }
+      return IE_B200_OK;
+    }
+    case IE_B200_OP_SWIGLU: return ie_b200_swiglu(static_cast<float *>(a), static_cast<float *>(b), o.n, qo, T, o.a_stride, o.qo_stride, st);
+    case IE_B200_OP_ARGMAX:
+      return ie_b200_argmax(static_cast<float *>(a), o.n, static_cast<uint32_t *>(b), T, o.a_stride, o.b_stride, e->argmax_part, st);
+    case IE_B200_OP_ALLREDUCE: return IE_B200_OK;  // the caller's collective
+    case IE_B200_OP_ADD:
+      add_kernel<<<dim3((o.n + 255u) / 256u, T), 256, 0, st>>>(static_cast<float *>(a), static_cast<float *>(b), static_cast<float *>(c), o.n,
+                                                              o.a_stride, o.b_stride, o.c_stride);
+      IEB_LAUNCHED("add_kernel");
+      return IE_B200_OK;
+    default: return fail(IE_B200_E_ARG, "unknown op kind %d", o.kind);
+  }
+}
+
+// Ops [first, last) for T tokens. For one token, an RMSNORM whose Q8 copy feeds the GEMVs right after it is
+// folded into those GEMVs' prologues (every CTA recomputes the norm; CTA 0 of the first GEMV still writes the
+// norm's f32 and Q8 outputs for any later reader), which takes a kernel out of the dependency chain.
+static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t T, uint32_t kind_mask, cudaStream_t st) {
+  for (uint32_t i = first; i < last; i++) {
+    const ie_b200_op &o = e->ops[i];
+    if (!(kind_mask & (1u << o.kind))) continue;
+    if (T == 1 && o.kind == IE_B200_OP_RMSNORM && o.qo != IE_B200_NONE && o.res == IE_B200_NONE && o.vec >= 0 && o.n % 32u == 0) {
+      uint32_t j = i + 1;
+      while (j < last && e->ops[j].kind == IE_B200_OP_GEMV && e->ops[j].a == o.qo && e->ops[j].mat >= 0 && stream_ok(e->mats[e->ops[j].mat]) &&
+             e->mats[e->ops[j].mat].cols == o.n && e->ops[j].b != o.a && (kind_mask & (1u << IE_B200_OP_GEMV)))
+        j++;
+      if (j > i + 1) {
+        for (uint32_t k = i + 1; k < j; k++) {
+          const ie_b200_op &g = e->ops[k];
+          const EMat &m = e->mats[g.mat];
+          const bool firstg = k == i + 1;
+          int r = ie_b200_norm_gemv_stream(m.kind, m.d, m.rows, m.cols, static_cast<float *>(at(e, o.a, 0, 0)), e->vecs[o.vec].d, e->d.eps,
+                                           firstg ? static_cast<float *>(at(e, o.b, 0, 0)) : nullptr, firstg ? at(e, o.qo, 0, 0) : nullptr,
+                                           static_cast<float *>(at(e, g.b, 0, 0)), g.vec >= 0 ? e->vecs[g.vec].d : nullptr,
+                                           static_cast<float *>(at(e, g.res, 0, 0)), e->err, st);
+          if (r) return r;
+        }
+        i = j - 1;
+        continue;
+      }
+    }
+    if (int r = launch_op(e, o, 0, T, st)) return r;
+  }
+  return IE_B200_OK;
+}
+
+// scalars layout: [0, T_max) token ids; [T_max] first position; [T_max + 1 + t] = first position + t.
+static int upload_input(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, cudaStream_t st) {
+  const uint32_t Tm = e->d.T_max;
+  if (T == 0 || T > Tm) return fail(IE_B200_E_SIZE, "run of %u tokens (1 .. %u)", T, Tm);
+  if ((uint64_t)pos + T > e->d.n_ctx) return fail(IE_B200_E_SIZE, "positions %u .. %u exceed the context %u", pos, pos + T - 1, e->d.n_ctx);
+  for (uint32_t t = 0; t < T; t++) {
+    if (toks[t] >= e->d.vocab) return fail(IE_B200_E_SIZE, "token %u >= vocab %u", toks[t], e->d.vocab);
+    e->h_scalars[t] = toks[t];
+  }
+  e->h_scalars[Tm] = pos;
+  for (uint32_t t = 0; t < Tm; t++) e->h_scalars[Tm + 1 + t] = pos + t;
+  IEB_CUDA(cudaMemcpyAsync(e->scalars, e->h_scalars, (size_t)(2 * Tm + 1) * 4, cudaMemcpyHostToDevice, st));
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_engine **out) {
+  if (!desc || !out) return fail(IE_B200_E_ARG, "ie_b200_engine_create: NULL argument");
+  if (ie_b200_device_count() < 1) return fail(IE_B200_E_CUDA, "no CUDA device: the engine has no CPU fallback");
+  const ie_b200_engine_desc &d = *desc;
+  if (!d.n_head || !d.n_kv || d.n_head % d.n_kv || !d.hd || !d.n_ctx || !d.T_max || !d.vocab || !d.arena_bytes)
+    return fail(IE_B200_E_SIZE, "ie_b200_engine_create: empty or inconsistent description");
+  ie_b200_engine *e = new ie_b200_engine();
+  e->d = d;
+  int rc = IE_B200_OK;
+  auto chk = [&](cudaError_t err, const char *what) {
+    if (err != cudaSuccess && rc == IE_B200_OK) rc = cuda_fail(err, what);
+  };
+  chk(cudaGetDevice(&e->device), "cudaGetDevice");
+  chk(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  chk(cudaMalloc(&e->arena, d.arena_bytes + 256), "cudaMalloc(arena)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->arena, 0, d.arena_bytes + 256), "cudaMemset(arena)");
+  e->kv_layer_bytes = (size_t)d.n_kv * d.n_ctx * d.hd * (d.kv_f32 ? 4u : 2u);
+  const size_t kvb = e->kv_layer_bytes * (d.n_kv_layers ? d.n_kv_layers : 1u);
+  chk(cudaMalloc(&e->kc, kvb), "cudaMalloc(K cache)");
+  chk(cudaMalloc(&e->vc, kvb), "cudaMalloc(V cache)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->kc, 0, kvb), "cudaMemset"), chk(cudaMemset(e->vc, 0, kvb), "cudaMemset");
+  const size_t rope_n = (size_t)d.n_ctx * (d.hd / 2u) * 4u;
+  chk(cudaMalloc(&e->rope_cos, rope_n), "cudaMalloc(rope)");
+  chk(cudaMalloc(&e->rope_sin, rope_n), "cudaMalloc(rope)");
+  chk(cudaMalloc(&e->scalars, (size_t)(2 * d.T_max + 1) * 4), "cudaMalloc(scalars)");
+  chk(cudaMallocHost(&e->h_scalars, (size_t)(2 * d.T_max + 1) * 4), "cudaMallocHost");
+  chk(cudaMallocHost(&e->h_result, (size_t)d.T_max * 8 + 8), "cudaMallocHost");
+  e->T_att = d.T_max < 16u ? d.T_max : 16u;
+  chk(cudaMalloc(&e->attn_part, ie_b200_attn_part_bytes(d.n_head, d.hd, d.n_ctx, e->T_att)), "cudaMalloc(attention partials)");
+  const size_t cw = ie_b200_attn_count_words(d.n_head, e->T_att) * 4u;
+  chk(cudaMalloc(&e->attn_count, cw), "cudaMalloc(attention counters)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->attn_count, 0, cw), "cudaMemset");
+  chk(cudaMalloc(&e->argmax_part, ie_b200_argmax_part_bytes(d.T_max)), "cudaMalloc(argmax partials)");
+  chk(cudaMalloc(&e->err, 4), "cudaMalloc(error word)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 4), "cudaMemset");
+  chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");
+  chk(cudaEventCreate(&e->ev0), "cudaEventCreate");
+  chk(cudaEventCreate(&e->ev1), "cudaEventCreate");
+  if (rc != IE_B200_OK) {
+    ie_b200_engine_destroy(e);
+    return rc;
+  }
+  *out = e;
+  return IE_B200_OK;
+}
+
+extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
+  if (!e) return;
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  if (e->step_graph) cudaGraphExecDestroy(e->step_graph);
+  for (auto &m : e->mats)
+    if (m.owned) cudaFree(m.d);
+  for (auto &v : e->vecs) cudaFree(v.d);
+  cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
+  cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
+  if (e->h_scalars) cudaFreeHost(e->h_scalars);
+  if (e->h_result) cudaFreeHost(e->h_result);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+}
+
+static int kind_of_ggml(int t) {
+  return t == IE_B200_GGML_F32 ? IE_B200_MAT_F32 : t == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : t == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K
+         : t == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
+}
+static size_t gguf_bytes(int t, uint32_t rows, uint32_t cols) {
+  const size_t n = (size_t)rows * cols;
+  return t == IE_B200_GGML_F32 ? n * 4u : t == IE_B200_GGML_Q4_0 ? n / 32u * 18u : t == IE_B200_GGML_Q4_K ? n / 256u * 144u : n / 256u * 210u;
+}
+
+// Invalidate the captured step graph: the op list or a handle table changed.
+static void drop_graph(ie_b200_engine *e) {
+  if (e->step_graph) cudaGraphExecDestroy(e->step_graph), e->step_graph = nullptr;
+}
+
+extern "C" int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uint32_t rows, uint32_t cols, const void *h_bytes) {
+  if (!e || !h_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_gguf: NULL argument");
+  const int kind = kind_of_ggml(ggml_type);
+  if (kind < 0) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_gguf: GGML type %d unsupported", ggml_type);
+  const size_t src_n = gguf_bytes(ggml_type, rows, cols), dst_n = ie_b200_mat_bytes(kind, rows, cols);
+  void *tmp = nullptr, *dst = nullptr;
+  IEB_CUDA(cudaMalloc(&dst, dst_n ? dst_n : 16));
+  if (kind == IE_B200_MAT_F32) {
+    IEB_CUDA(cudaMemcpy(dst, h_bytes, src_n, cudaMemcpyHostToDevice));
+  } else {
+    IEB_CUDA(cudaMalloc(&tmp, src_n ? src_n : 16));
+    IEB_CUDA(cudaMemcpyAsync(tmp, h_bytes, src_n, cudaMemcpyHostToDevice, e->stream));
+    int r = ie_b200_repack_gguf(ggml_type, tmp, rows, cols, dst, e->stream);
+    cudaStreamSynchronize(e->stream);
+    cudaFree(tmp);
+    if (r) {
+      cudaFree(dst);
+      return r;
+    }
+  }
+  e->mats.push_back({kind, rows, cols, dst, true});
+  return (int)e->mats.size() - 1;
+}
+
+extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs) {
+  if (!e || !h_qw) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref: NULL argument");
+  const size_t nb = cols / 32u, n = (size_t)rows * nb;
+  size_t qw_n, qs_n;
+  switch (kind) {
+    case IE_B200_MAT_F32: qw_n = (size_t)rows * cols * 4u, qs_n = 0; break;
+    case IE_B200_MAT_Q4: qw_n = n * 16u, qs_n = n * 2u; break;
+    case IE_B200_MAT_Q4K: qw_n = n * 16u, qs_n = (n + (size_t)rows * (nb / 8u) * 2u) * 2u; break;
+    case IE_B200_MAT_Q6K: qw_n = n * 24u, qs_n = (n + (size_t)rows * (nb / 8u)) * 2u; break;
+    default: return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref: kind %d unsupported", kind);
+  }
+  if (kind != IE_B200_MAT_F32 && !h_qs) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref: NULL scale array");
+  void *dqw = nullptr, *dqs = nullptr, *dst = nullptr;
+  const size_t dst_n = ie_b200_mat_bytes(kind, rows, cols);
+  IEB_CUDA(cudaMalloc(&dst, dst_n ? dst_n : 16));
+  if (kind == IE_B200_MAT_F32) {
+    IEB_CUDA(cudaMemcpy(dst, h_qw, qw_n, cudaMemcpyHostToDevice));
+  } else {
+    IEB_CUDA(cudaMalloc(&dqw, qw_n ? qw_n : 16));
+    IEB_CUDA(cudaMalloc(&dqs, qs_n ? qs_n : 16));
+    IEB_CUDA(cudaMemcpyAsync(dqw, h_qw, qw_n, cudaMemcpyHostToDevice, e->stream));
+    IEB_CUDA(cudaMemcpyAsync(dqs, h_qs, qs_n, cudaMemcpyHostToDevice, e->stream));
+    int r = ie_b200_repack_ref(kind, dqw, dqs, rows, cols, dst, e->stream);
+    cudaStreamSynchronize(e->stream);
+    cudaFree(dqw), cudaFree(dqs);
+    if (r) {
+      cudaFree(dst);
+      return r;
+    }
+  }
+  e->mats.push_back({kind, rows, cols, dst, true});
+  return (int)e->mats.size() - 1;
+}
+
+extern "C" int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *d_data) {
+  if (!e || !d_data) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: NULL argument");
+  if (!aligned16(d_data)) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: the matrix must be 16-byte aligned");
+  e->mats.push_back({kind, rows, cols, const_cast<void *>(d_data), false});
+  return (int)e->mats.size() - 1;
+}
+
+extern "C" int ie_b200_engine_add_vec(ie_b200_engine *e, const float *h_f, uint32_t n) {
+  if (!e || !h_f) return fail(IE_B200_E_ARG, "ie_b200_engine_add_vec: NULL argument");
+  float *dptr = nullptr;
+  IEB_CUDA(cudaMalloc(&dptr, (size_t)(n ? n : 1) * 4));
+  IEB_CUDA(cudaMemcpy(dptr, h_f, (size_t)n * 4, cudaMemcpyHostToDevice));
+  e->vecs.push_back({dptr, n});
+  return (int)e->vecs.size() - 1;
+}
+
+extern "C" int ie_b200_engine_set_rope(ie_b200_engine *e, const float *h_cos, const float *h_sin) {
+  if (!e || !h_cos || !h_sin) return fail(IE_B200_E_ARG, "ie_b200_engine_set_rope: NULL argument");
+  const size_t n = (size_t)e->d.n_ctx * (e->d.hd / 2u) * 4u;
+  IEB_CUDA(cudaMemcpy(e->rope_cos, h_cos, n, cudaMemcpyHostToDevice));
+  IEB_CUDA(cudaMemcpy(e->rope_sin, h_sin, n, cudaMemcpyHostToDevice));
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, uint32_t n_ops, uint32_t i_head) {
+  if (!e || !ops) return fail(IE_B200_E_ARG, "ie_b200_engine_set_ops: NULL argument");
+  if (i_head > n_ops) return fail(IE_B200_E_ARG, "ie_b200_engine_set_ops: head index %u > %u ops", i_head, n_ops);
+  const uint64_t cap = e->d.arena_bytes;
+  for (uint32_t i = 0; i < n_ops; i++) {
+    const ie_b200_op &o = ops[i];
+    const uint64_t offs[5] = {o.a, o.b, o.c, o.qo, o.res};
+    for (uint64_t off : offs)
+      if (off != IE_B200_NONE && off >= cap) return fail(IE_B200_E_ARG, "op %u: offset %llu outside the arena (%llu bytes)", i, (unsigned long long)off, (unsigned long long)cap);
+    if ((o.kind == IE_B200_OP_ROPE_KV || o.kind == IE_B200_OP_ATTN) && (o.layer < 0 || (uint32_t)o.layer >= e->d.n_kv_layers))
+      return fail(IE_B200_E_ARG, "op %u: KV layer %d of %u", i, o.layer, e->d.n_kv_layers);
+    if (o.mat >= (int)e->mats.size() || o.vec >= (int)e->vecs.size()) return fail(IE_B200_E_ARG, "op %u: unknown handle", i);
+  }
+  e->ops.assign(ops, ops + n_ops);
+  e->i_head = i_head;
+  drop_graph(e);
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_set_input(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, void *stream) {
+  if (!e || !toks) return fail(IE_B200_E_ARG, "ie_b200_engine_set_input: NULL argument");
+  return upload_input(e, toks, T, pos, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ie_b200_engine_enqueue(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t T, void *stream) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue: NULL engine");
+  if (first > last || last > e->ops.size()) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue: ops [%u, %u) of %zu", first, last, e->ops.size());
+  if (T == 0 || T > e->d.T_max) return fail(IE_B200_E_SIZE, "ie_b200_engine_enqueue: %u tokens (1 .. %u)", T, e->d.T_max);
+  return enqueue_range(e, first, last, T, ~0u, static_cast<cudaStream_t>(stream));
+}
+
+// Capture ops [0, n_ops) for one token into an executable graph.
+static int capture_step(ie_b200_engine *e) {
+  cudaGraph_t g = nullptr;
+  const uint64_t before = ie_b200_launch_count();
+  IEB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+  int r = IE_B200_OK;
+  r = enqueue_range(e, 0, (uint32_t)e->ops.size(), 1, ~0u, e->stream);
+  if (r == IE_B200_OK) {
+    advance_kernel<<<1, 256, 0, e->stream>>>(e->scalars, e->d.T_max, reinterpret_cast<const uint32_t *>(e->arena + e->d.argmax_off), e->hist, HIST_CAP);
+    count_launch();
+  }
+  cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+  if (r != IE_B200_OK) {
+    if (g) cudaGraphDestroy(g);
+    return r;
+  }
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamEndCapture");
+  e->step_launches = (uint32_t)(ie_b200_launch_count() - before);
+  ce = cudaGraphInstantiate(&e->step_graph, g, 0);
+  cudaGraphDestroy(g);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGraphInstantiate");
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms) {
+  if (!e || !next) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
+  if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_step: no op list");
+  IEB_CUDA(cudaSetDevice(e->device));
+  if (!e->step_graph)
+    if (int r = capture_step(e)) return r;
+  cudaStream_t st = e->stream;
+  if (ms) IEB_CUDA(cudaEventRecord(e->ev0, st));
+  if (int r = upload_input(e, &tok, 1, pos, st)) return r;
+  IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
+  count_launch(e->step_launches);
+  IEB_CUDA(cudaMemcpyAsync(e->h_result, e->arena + e->d.argmax_off, 8, cudaMemcpyDeviceToHost, st));
+  IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
+  if (h_logits) IEB_CUDA(cudaMemcpyAsync(h_logits, e->arena + e->d.logits_off, (size_t)e->d.vocab * 4, cudaMemcpyDeviceToHost, st));
+  if (ms) IEB_CUDA(cudaEventRecord(e->ev1, st));
+  IEB_CUDA(cudaStreamSynchronize(st));
+  if (ms) {
+    float f = 0;
+    IEB_CUDA(cudaEventElapsedTime(&f, e->ev0, e->ev1));
+    *ms = f;
+  }
+  if (e->h_result[2]) return fail(IE_B200_E_DEVICE, "a kernel gave up a bounded wait (device error word %u)", e->h_result[2]);
+  *next = e->h_result[0];
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K, uint32_t *h_out, double *ms) {
+  if (!e || !h_out) return fail(IE_B200_E_ARG, "ie_b200_engine_decode: NULL argument");
+  if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_decode: no op list");
+  if (K == 0) return IE_B200_OK;
+  if (K > HIST_CAP) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: %u steps > %u per call", K, HIST_CAP);
+  if ((uint64_t)pos + K > e->d.n_ctx) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: positions %u .. %u exceed the context %u", pos, pos + K - 1, e->d.n_ctx);
+  IEB_CUDA(cudaSetDevice(e->device));
+  if (!e->step_graph)
+    if (int r = capture_step(e)) return r;
+  cudaStream_t st = e->stream;
+  if (int r = upload_input(e, &tok, 1, pos, st)) return r;
+  IEB_CUDA(cudaMemsetAsync(e->hist + HIST_CAP, 0, 4, st));
+  IEB_CUDA(cudaEventRecord(e->ev0, st));
+  for (uint32_t k = 0; k < K; k++) IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
+  IEB_CUDA(cudaEventRecord(e->ev1, st));
+  count_launch(e->step_launches * K);
+  IEB_CUDA(cudaMemcpyAsync(h_out, e->hist, (size_t)K * 4, cudaMemcpyDeviceToHost, st));
+  IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
+  IEB_CUDA(cudaStreamSynchronize(st));
+  if (e->h_result[2]) return fail(IE_B200_E_DEVICE, "a kernel gave up a bounded wait (device error word %u)", e->h_result[2]);
+  if (ms) {
+    float f = 0;
+    IEB_CUDA(cudaEventElapsedTime(&f, e->ev0, e->ev1));
+    *ms = f;
+  }
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_enqueue_kinds(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t kind_mask, uint32_t T, void *stream) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue_kinds: NULL engine");
+  if (first > last || last > e->ops.size()) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue_kinds: ops [%u, %u) of %zu", first, last, e->ops.size());
+  if (T == 0 || T > e->d.T_max) return fail(IE_B200_E_SIZE, "ie_b200_engine_enqueue_kinds: %u tokens (1 .. %u)", T, e->d.T_max);
+  return enqueue_range(e, first, last, T, kind_mask, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob) {
+  if (!e || !toks || !out) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
+  if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_run: no op list");
+  IEB_CUDA(cudaSetDevice(e->device));
+  cudaStream_t st = e->stream;
+  if (int r = upload_input(e, toks, T, pos, st)) return r;
+  const uint32_t n_ops = (uint32_t)e->ops.size(), ih = last_only ? e->i_head : n_ops;
+  for (uint32_t i = 0; i < ih; i++)
+    if (int r = launch_op(e, e->ops[i], 0, T, st)) return r;
+  for (uint32_t i = ih; i < n_ops; i++)  // the output head for the last token only
+    if (int r = launch_op(e, e->ops[i], T - 1, 1, st)) return r;
+  IEB_CUDA(cudaMemcpy2DAsync(e->h_result, 8, e->arena + e->d.argmax_off, e->d.argmax_stride ? e->d.argmax_stride : 8, 8, T, cudaMemcpyDeviceToHost, st));
+  IEB_CUDA(cudaStreamSynchronize(st));
+  for (uint32_t t = 0; t < T; t++) {
+    out[t] = e->h_result[2 * t];
+    if (prob) std::memcpy(&prob[t], &e->h_result[2 * t + 1], 4);
+  }
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, void *h_dst) {
+  if (!e || !h_dst) return fail(IE_B200_E_ARG, "ie_b200_engine_read_rows: NULL argument");
+  const uint64_t lo = off + (uint64_t)stride * r0, len = (uint64_t)stride * n;
+  if (lo + len > e->d.arena_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_read_rows: rows outside the arena");
+  IEB_CUDA(cudaMemcpyAsync(h_dst, e->arena + lo, len, cudaMemcpyDeviceToHost, e->stream));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uint32_t dst_stride, uint32_t d0, uint64_t src_off, uint32_t src_stride,
+                                        uint32_t r0, uint32_t n, uint32_t row_bytes, int zero) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_copy_rows: NULL engine");
+  if (n == 0) return IE_B200_OK;
+  uint8_t *dst = e->arena + dst_off + (uint64_t)dst_stride * d0;
+  if (dst_off + (uint64_t)dst_stride * (d0 + n - 1) + row_bytes > e->d.arena_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_copy_rows: outside the arena");
+  if (zero) {
+    IEB_CUDA(cudaMemset2DAsync(dst, dst_stride, 0, row_bytes, n, e->stream));
+  } else {
+    if (src_off + (uint64_t)src_stride * (r0 + n - 1) + row_bytes > e->d.arena_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_copy_rows: outside the arena");
+    IEB_CUDA(cudaMemcpy2DAsync(dst, dst_stride, e->arena + src_off + (uint64_t)src_stride * r0, src_stride, row_bytes, n, cudaMemcpyDeviceToDevice, e->stream));
+  }
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return IE_B200_OK;
+}
+
+extern "C" void *ie_b200_engine_arena(ie_b200_engine *e) { return e ? e->arena : nullptr; }
+extern "C" void *ie_b200_engine_input_scalars(ie_b200_engine *e) { return e ? e->scalars : nullptr; }
+
+extern "C" uint64_t ie_b200_engine_weight_bytes_per_token(ie_b200_engine *e) {
+  if (!e) return 0;
+  uint64_t wb = 0;
+  for (const auto &o : e->ops) {
+    if (o.kind != IE_B200_OP_GEMV || o.mat < 0) continue;
+    const EMat &m = e->mats[o.mat];
+    const uint64_t nblk = (uint64_t)m.rows * (m.cols / 32u);
+    wb += m.kind == IE_B200_MAT_F32 ? (uint64_t)m.rows * m.cols * 4u : m.kind == IE_B200_MAT_Q6K ? nblk * 210u / 8u : nblk * 18u;
+  }
+  return wb;
+}
+
+extern "C" uint32_t ie_b200_engine_launches_per_step(ie_b200_engine *e) {
+  if (!e) return 0;
+  if (!e->step_graph && !e->ops.empty()) capture_step(e);
+  return e->step_launches;
+}

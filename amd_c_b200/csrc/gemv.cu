@@ -12,68 +12,9 @@
 // R x U 16-byte weight loads in flight (R rows per warp pass, U lane steps per
 // chunk) before any arithmetic depends on them.
 #include "common.cuh"
+#include "gemv_blocks.cuh"
 
 namespace ieb {
-
-template <int KIND>
-struct Blk;
-
-// Q4_0: 16 B nibbles at 16 b, f16 scale at 16 nb + 2 b.
-template <>
-struct Blk<IE_B200_MAT_Q4> {
-  uint4 w;
-  uint16_t d;
-  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
-    w = ld_stream16(rp + 16u * (size_t)b);
-    d = ld_stream2(rp + 16u * (size_t)nb + 2u * b);
-  }
-  // acc = acc + (dw * da) * (float)dot, each operation rounded on its own.
-  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int asum, uint32_t) const {
-    const int dot = q4_dot(w, a0, a1) - 8 * asum;
-    return __fadd_rn(acc, __fmul_rn(__fmul_rn(h2f(d), da), (float)dot));
-  }
-};
-
-// Q4_K: nibbles as Q4_0; per super-block a 16 B header at 16 nb + 16 (b / 8).
-template <>
-struct Blk<IE_B200_MAT_Q4K> {
-  uint4 w, h;
-  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
-    w = ld_stream16(rp + 16u * (size_t)b);
-    h = ld_stream16(rp + 16u * (size_t)nb + 16u * (b >> 3));
-  }
-  // acc = fma(-(dmin mn), da * (float)asum, fma((d sc) * (float)dq, da, acc)).
-  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int asum, uint32_t b) const {
-    const int dq = q4_dot(w, a0, a1);
-    const uint32_t f = q4k_field(h, (int)(b & 7u));
-    const float s = __fmul_rn(h2f((uint16_t)(h.x & 0xFFFFu)), (float)(f & 63u));
-    const float mm = __fmul_rn(h2f((uint16_t)(h.x >> 16)), (float)(f >> 6));
-    return __fmaf_rn(-mm, __fmul_rn(da, (float)asum), __fmaf_rn(__fmul_rn(s, (float)dq), da, acc));
-  }
-};
-
-// Q6_K: nibbles at 16 b, high-bit words at 16 nb + 8 b, (sc0 | sc1 << 8) at
-// 24 nb + 2 b, f16 d at 26 nb + 2 (b / 8).
-template <>
-struct Blk<IE_B200_MAT_Q6K> {
-  uint4 w;
-  uint2 hw;
-  uint16_t sc, d;
-  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
-    w = ld_stream16(rp + 16u * (size_t)b);
-    hw = ld_stream8(rp + 16u * (size_t)nb + 8u * b);
-    sc = ld_stream2(rp + 24u * (size_t)nb + 2u * b);
-    d = ld_stream2(rp + 26u * (size_t)nb + 2u * (b >> 3));
-  }
-  // acc = fma(fma(d sc1, (float)d1, (d sc0) * (float)d0), da, acc).
-  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int, uint32_t) const {
-    int d0, d1;
-    q6_dots(w, hw, a0, a1, d0, d1);
-    const float df = h2f(d);
-    const float s0 = __fmul_rn(df, (float)(int8_t)(sc & 255u)), s1 = __fmul_rn(df, (float)(int8_t)(sc >> 8));
-    return __fmaf_rn(__fmaf_rn(s1, (float)d1, __fmul_rn(s0, (float)d0)), da, acc);
-  }
-};
 
 constexpr int GEMV_THREADS = 256, GEMV_WARPS = GEMV_THREADS / 32;
 
@@ -112,7 +53,7 @@ gemv_q_kernel(const uint8_t *__restrict__ w, size_t rowb, uint32_t rows, uint32_
 #pragma unroll
     for (int i = 0; i < R; i++) acc[i] = 0.0f;
     for (uint32_t c = 0; c < nb; c += 32u * U) {
-      Blk<KIND> blk[R][U];
+      Blk<KIND, false> blk[R][U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
         const uint32_t b = c + 32u * u + lane;
@@ -225,7 +166,7 @@ static int launch_q(const void *w, uint32_t rows, uint32_t cols, const void *x, 
   const uint32_t nb = cols / 32u;
   const size_t smem = (size_t)nb * 40u;
   auto k = gemv_q_kernel<KIND, R, U>;
-  if (smem > 48u * 1024u) IEB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
   const dim3 grid(gemv_grid(rows, GEMV_WARPS * R, 8), T);
   k<<<grid, GEMV_THREADS, smem, st>>>(static_cast<const uint8_t *>(w), row_bytes_of(KIND, cols), rows, nb, static_cast<const uint8_t *>(x), y,
                                       bias, res, xs, ys, rs);
@@ -248,7 +189,7 @@ extern "C" int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t c
   if (kind == IE_B200_MAT_F32) {
     if (cols == 0 || (size_t)cols * 4u > 200u * 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: f32 cols %u unsupported", cols);
     const size_t smem = (size_t)cols * 4u;
-    if (smem > 48u * 1024u) IEB_CUDA(cudaFuncSetAttribute(gemv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_f32_kernel), smem)) return r;
     const dim3 grid(gemv_grid(rows, GEMV_WARPS, 8), T);
     gemv_f32_kernel<<<grid, GEMV_THREADS, smem, st>>>(static_cast<const float *>(d_w), rows, cols, static_cast<const float *>(d_x), d_y, d_bias,
                                                      d_res, x_stride, y_stride, res_stride);
@@ -257,7 +198,7 @@ extern "C" int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t c
   }
   if (cols == 0 || cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: cols %u is not a multiple of 32", cols);
   if (nb > 4096u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: %u blocks per row > 4096", nb);
-  if ((x_stride & 15u) != 0) return fail(IE_B200_E_ARG, "ie_b200_gemv: x_stride must be a multiple of 16");
+  if (T > 1 && (x_stride & 15u) != 0) return fail(IE_B200_E_ARG, "ie_b200_gemv: x_stride must be a multiple of 16");
   switch (kind) {
     case IE_B200_MAT_Q4: return launch_q<IE_B200_MAT_Q4, 2, 4>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
     case IE_B200_MAT_Q4K:

@@ -16,6 +16,7 @@ __device__ __forceinline__ T *row_ptr(T *p, size_t stride, uint32_t t) {
 
 // ---- Q8 quantiser: one warp per block of 32 ----
 __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *q, uint32_t nb, size_t xs, size_t qs) {
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t b = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -26,6 +27,7 @@ __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *
 
 // ---- embedding row ----
 __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t rowb, uint32_t nb, const uint32_t *tok, float *out, size_t os) {
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const uint8_t *rp = w + (size_t)tok[t] * rowb;
   float *o = row_ptr(out, os, t);
@@ -38,6 +40,7 @@ __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t 
   }
 }
 __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t cols, const uint32_t *tok, float *out, size_t os) {
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const float *rp = w + (size_t)tok[t] * cols;
   float *o = row_ptr(out, os, t);
@@ -47,6 +50,7 @@ __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t
 // ---- RMSNorm (+Q8): one CTA of 1024 threads per token ----
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const float *__restrict__ w, float *y, uint32_t n, float eps, uint8_t *q,
                                                       size_t xs, size_t ys, size_t qs) {
+  pdl_prologue();
   __shared__ float red[32];
   const uint32_t t = blockIdx.x;
   const float *xt = row_ptr(x, xs, t);
@@ -73,6 +77,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const flo
 
 // ---- SwiGLU (+Q8): one warp per 32 elements ----
 __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, uint32_t n, uint8_t *q, size_t as, size_t qs) {
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t blk = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -95,6 +100,7 @@ template <typename KV>
 __global__ void __launch_bounds__(256)
 rope_kv_kernel(float *q, float *k, const float *v, KV *kc, KV *vc, const float *__restrict__ cs, const float *__restrict__ sn,
                const uint32_t *pos0, uint32_t nq, uint32_t nkv, uint32_t hd, int neox, uint32_t kv_len, size_t stride) {
+  pdl_prologue();
   const uint32_t t = blockIdx.y, pos = *pos0 + t, h2 = hd / 2u;
   const uint32_t npair = (nq + nkv) * h2, total = npair + nkv * hd;
   float *qt = row_ptr(q, stride, t), *kt = row_ptr(k, stride, t);
@@ -129,6 +135,7 @@ struct ArgPart {
   uint32_t pad;
 };
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32_t n, ArgPart *part, size_t xs) {
+  pdl_prologue();
   __shared__ float smx[8], ssum[8];
   __shared__ uint32_t sidx[8];
   const uint32_t t = blockIdx.y;
@@ -165,6 +172,7 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32
   }
 }
 __global__ void __launch_bounds__(32) argmax_merge_kernel(const ArgPart *part, uint32_t *out, size_t os) {
+  pdl_prologue();
   const uint32_t t = blockIdx.x;
   const int lane = threadIdx.x;
   float mx = -INFINITY, sum = 0.0f;
@@ -206,8 +214,8 @@ extern "C" int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32
   if (((uintptr_t)d_q & 3u) || (q_stride & 3u)) return fail(IE_B200_E_ARG, "ie_b200_quant_q8: output must be 4-byte aligned");
   if (nb == 0 || T == 0) return IE_B200_OK;
   if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_quant_q8: T %u > 65535", T);
-  quant_q8_kernel<<<dim3((nb + 7u) / 8u, T), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, static_cast<uint8_t *>(d_q), nb, x_stride, q_stride);
-  IEB_LAUNCHED("quant_q8_kernel");
+  IEB_LAUNCH_PDL("quant_q8_kernel", quant_q8_kernel, dim3((nb + 7u) / 8u, T), dim3(256), 0, static_cast<cudaStream_t>(stream), d_x,
+                 static_cast<uint8_t *>(d_q), nb, x_stride, q_stride);
   return IE_B200_OK;
 }
 
@@ -220,13 +228,13 @@ extern "C" int ie_b200_embed(int kind, const void *d_w, uint32_t cols, const uin
   const dim3 grid((cols + 255u) / 256u, T);
   if (kind == IE_B200_MAT_Q4) {
     if (cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_embed: cols %u is not a multiple of 32", cols);
-    embed_q4_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(d_w), row_bytes_of(kind, cols), cols / 32u, d_tok, d_out, out_stride);
+    IEB_LAUNCH_PDL("embed_q4_kernel", embed_q4_kernel, grid, dim3(256), 0, st, static_cast<const uint8_t *>(d_w), row_bytes_of(kind, cols),
+                   cols / 32u, d_tok, d_out, out_stride);
   } else if (kind == IE_B200_MAT_F32) {
-    embed_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float *>(d_w), cols, d_tok, d_out, out_stride);
+    IEB_LAUNCH_PDL("embed_f32_kernel", embed_f32_kernel, grid, dim3(256), 0, st, static_cast<const float *>(d_w), cols, d_tok, d_out, out_stride);
   } else {
     return fail(IE_B200_E_ARG, "ie_b200_embed: kind %d has no embedding kernel", kind);
   }
-  IEB_LAUNCHED("embed_kernel");
   return IE_B200_OK;
 }
 
@@ -235,8 +243,8 @@ extern "C" int ie_b200_rmsnorm(const float *d_x, const float *d_w, float *d_y, u
   if (!d_x || !d_w || !d_y) return fail(IE_B200_E_ARG, "ie_b200_rmsnorm: NULL pointer");
   if (d_q && n % 32u) return fail(IE_B200_E_SIZE, "ie_b200_rmsnorm: the Q8 copy needs n %% 32 == 0 (n = %u)", n);
   if (n == 0 || T == 0) return IE_B200_OK;
-  rmsnorm_kernel<<<T, 1024, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_w, d_y, n, eps, static_cast<uint8_t *>(d_q), x_stride, y_stride, q_stride);
-  IEB_LAUNCHED("rmsnorm_kernel");
+  IEB_LAUNCH_PDL("rmsnorm_kernel", rmsnorm_kernel, dim3(T), dim3(1024), 0, static_cast<cudaStream_t>(stream), d_x, d_w, d_y, n, eps,
+                 static_cast<uint8_t *>(d_q), x_stride, y_stride, q_stride);
   return IE_B200_OK;
 }
 
@@ -246,8 +254,8 @@ extern "C" int ie_b200_swiglu(float *d_a, const float *d_b, uint32_t n, void *d_
   if (n == 0 || T == 0) return IE_B200_OK;
   if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_swiglu: T %u > 65535", T);
   const uint32_t nblk = (n + 31u) / 32u;
-  swiglu_kernel<<<dim3((nblk + 7u) / 8u, T), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_a, d_b, n, static_cast<uint8_t *>(d_q), a_stride, q_stride);
-  IEB_LAUNCHED("swiglu_kernel");
+  IEB_LAUNCH_PDL("swiglu_kernel", swiglu_kernel, dim3((nblk + 7u) / 8u, T), dim3(256), 0, static_cast<cudaStream_t>(stream), d_a, d_b, n,
+                 static_cast<uint8_t *>(d_q), a_stride, q_stride);
   return IE_B200_OK;
 }
 
@@ -262,12 +270,11 @@ extern "C" int ie_b200_rope_kv(float *d_q, float *d_k, const float *d_v, void *d
   const dim3 grid((total + 255u) / 256u, T);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (kv_f32)
-    rope_kv_kernel<float><<<grid, 256, 0, st>>>(d_q, d_k, d_v, static_cast<float *>(d_kc), static_cast<float *>(d_vc), d_cos, d_sin, d_pos, nq,
-                                                nkv, hd, neox, kv_len, qkv_stride);
+    IEB_LAUNCH_PDL("rope_kv_kernel", rope_kv_kernel<float>, grid, dim3(256), 0, st, d_q, d_k, d_v, static_cast<float *>(d_kc),
+                   static_cast<float *>(d_vc), d_cos, d_sin, d_pos, nq, nkv, hd, neox, kv_len, qkv_stride);
   else
-    rope_kv_kernel<__half><<<grid, 256, 0, st>>>(d_q, d_k, d_v, static_cast<__half *>(d_kc), static_cast<__half *>(d_vc), d_cos, d_sin, d_pos,
-                                                 nq, nkv, hd, neox, kv_len, qkv_stride);
-  IEB_LAUNCHED("rope_kv_kernel");
+    IEB_LAUNCH_PDL("rope_kv_kernel", rope_kv_kernel<__half>, grid, dim3(256), 0, st, d_q, d_k, d_v, static_cast<__half *>(d_kc),
+                   static_cast<__half *>(d_vc), d_cos, d_sin, d_pos, nq, nkv, hd, neox, kv_len, qkv_stride);
   return IE_B200_OK;
 }
 
@@ -280,9 +287,7 @@ extern "C" int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uin
   if (T == 0) return IE_B200_OK;
   if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_argmax: T %u > 65535", T);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  argmax_part_kernel<<<dim3(ARGMAX_NG, T), 256, 0, st>>>(d_x, n, static_cast<ArgPart *>(d_part), x_stride);
-  IEB_LAUNCHED("argmax_part_kernel");
-  argmax_merge_kernel<<<T, 32, 0, st>>>(static_cast<const ArgPart *>(d_part), d_out, out_stride);
-  IEB_LAUNCHED("argmax_merge_kernel");
+  IEB_LAUNCH_PDL("argmax_part_kernel", argmax_part_kernel, dim3(ARGMAX_NG, T), dim3(256), 0, st, d_x, n, static_cast<ArgPart *>(d_part), x_stride);
+  IEB_LAUNCH_PDL("argmax_merge_kernel", argmax_merge_kernel, dim3(T), dim3(32), 0, st, static_cast<const ArgPart *>(d_part), d_out, out_stride);
   return IE_B200_OK;
 }

@@ -232,3 +232,28 @@ def read_gguf(path) -> ModelConfig:
     cfg.t_embd = t["token_embd.weight"].ggml_type
     cfg.t_out = t["output.weight"].ggml_type if "output.weight" in t else cfg.t_embd
     return cfg
+
+
+def make_model_device(cfg: ModelConfig, seed: int = 0, sigma: float = 0.02, device="cuda"):
+    """As make_model, for the large configurations: matrices are generated on the GPU (torch generator, same
+    block definition) and returned as name -> (ggml_type, rows, cols, uint8 CUDA tensor); the small float
+    vectors go to cfg.tensors as numpy. Pass the dict as Backend(device_tensors=...)."""
+    import torch
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    rng = np.random.default_rng(seed)
+    cfg.tensors, dev = {}, {}
+    for name, typ, rows, cols in tensor_plan(cfg):
+        if not is_matrix(name):
+            if name.endswith("norm.weight"):
+                v = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+            else:
+                v = (sigma * rng.standard_normal(cols)).astype(np.float32)
+            cfg.tensors[name] = Tensor(GGML_F32, 1, cols, v.view(np.uint8))
+        elif typ == GGML_Q4_0:
+            dev[name] = (typ, rows, cols, synth.q4_0_normal_torch(gen, rows, cols, sigma, device=device).reshape(-1))
+        elif typ == GGML_F32:
+            dev[name] = (typ, rows, cols, (torch.randn((rows, cols), generator=gen, device=device) * sigma).view(torch.uint8).reshape(-1))
+        else:
+            dev[name] = (typ, rows, cols, synth.k_random_torch(typ, gen, rows, cols, sigma, device=device).reshape(-1))
+    return dev

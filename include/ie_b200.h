@@ -94,6 +94,21 @@ int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_
 int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
                  const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
 
+/* The one-token GEMV of a decode step, same result as ie_b200_gemv with T = 1: the row panels stream through a
+ * shared-memory ring filled by bulk asynchronous copies, and the launch uses programmatic dependent launch, so
+ * the ring fills while the previous kernel of the stream still runs (the weights do not depend on it; the
+ * activations are read only after the previous kernel has completed). d_err (may be NULL): a device word set to
+ * 1 if a bounded wait inside the kernel ran out. Replaces ie_gemv_q4q8 / _q4kq8 / _q6kq8 at decode
+ * (kernels/ie_kernels.c:310, :401, :675). */
+int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
+                        const float *d_res, uint32_t *d_err, void *stream);
+/* The same with RMSNorm + the Q8 quantiser of the f32 vector d_x (cols floats) folded into the prologue: the role
+ * of the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285; src/model.c:1265-1293) moved
+ * to the consumer side. d_xn_out / d_xq_out (may be NULL): the normalised vector and its Q8 copy, written once. */
+int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, const float *d_norm_w, float eps,
+                             float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, uint32_t *d_err,
+                             void *stream);
+
 /* Test hook: the int32 dot of every (row, block) of a Q4_0 / Q4_K matrix
  * (Q4_K: the unsigned-nibble dot) and, for Q6_K, the two half dots
  * (dots[2 (r nb + b) + h]); what core/ie_core.h:161, :281, :385 define. */
@@ -146,13 +161,6 @@ int ie_b200_attn_decode(const float *d_q, const void *d_kc, const void *d_vc, fl
 size_t ie_b200_argmax_part_bytes(uint32_t T);
 int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *d_part,
                    void *stream);
-
-/* Chunked-prefill GEMM: Y[T][rows] = Xq8 W^T for T >= 17 tokens with the
- * weights read once per chunk; the role of ie_gemm_q4kr / ie_gemm_q6kr
- * (kernels/ie_kernels.c:1315, :2015; dispatch src/hip.c:965-1003). Same
- * operands as ie_b200_gemv. */
-int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
-                 const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,128 @@
+/* ie_b200_engine.h -- the decode engine of libie_b200.so: it owns the
+ * weights, the activation arena and the KV cache of ONE GPU and runs a static
+ * op list (the reference's "graph", src/model.h:177-331) for one token per
+ * step or T tokens per run. It is what a backend behind the reference's
+ * `struct backend` vtable (src/backend.h:7-49) drives: src/cuda.c of this
+ * repository translates the reference's model / graph into these calls, and
+ * the Python host (amd_c_b200/backend.py) builds the same op list itself.
+ *
+ * A one-token step is captured once into a CUDA graph and replayed; token id
+ * and position travel through device scalars, so the graph is static.
+ * All functions return 0 or a negative IE_B200_E_* code (see ie_b200.h);
+ * handles are non-negative ints.
+ */
+#ifndef IE_B200_ENGINE_H
+#define IE_B200_ENGINE_H
+
+#include "ie_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ie_b200_engine ie_b200_engine;
+
+#define IE_B200_NONE UINT64_MAX
+
+/* Op kinds: the subset of the reference's op enum (src/model.h:177-231) that
+ * llama / qwen2 graphs emit, plus two ops for tensor-parallel shards. */
+enum {
+  IE_B200_OP_EMBED = 0,   /* a = row tok of matrix `mat`                                   (OP_EMBED) */
+  IE_B200_OP_RMSNORM = 1, /* b = rmsnorm(a) * vec, Q8 copy in qo; if res is set, first
+                             a = a + res (the all-reduced partial of a sharded GEMV)      (OP_RMSNORM) */
+  IE_B200_OP_QUANT = 2,   /* b = Q8(a)                                                     (OP_QUANT) */
+  IE_B200_OP_GEMV = 3,    /* b = mat a (+ vec bias) (+ res); a is Q8 (f32 for MAT_F32)    (OP_GEMV_*) */
+  IE_B200_OP_ROPE_KV = 4, /* rotate a (q, nh heads) and b (k); store b and c (v) in the
+                             KV cache of `layer`                                          (OP_ROPE_KV) */
+  IE_B200_OP_ATTN = 5,    /* b = attention(q = a, cache of `layer`), Q8 copy in qo       (OP_ATTN) */
+  IE_B200_OP_SWIGLU = 6,  /* a = silu(a) * b, Q8 copy in qo                               (OP_SWIGLU) */
+  IE_B200_OP_ARGMAX = 7,  /* b = {argmax(a), prob}                                        (OP_ARGMAX) */
+  IE_B200_OP_ALLREDUCE = 8, /* a (n floats per token) is summed over the ranks by the caller: the
+                               engine only stops an enqueue range here (see ie_b200_engine_enqueue) */
+  IE_B200_OP_ADD = 9      /* c = a + b, n floats                                          (OP_ADD) */
+};
+
+typedef struct {
+  int32_t kind;
+  int32_t mat;   /* matrix handle or -1 */
+  int32_t vec;   /* vector handle (bias / norm weight) or -1 */
+  int32_t layer; /* KV-cache layer index (ROPE_KV, ATTN) */
+  uint32_t n;    /* elements of a (the reference's op.n) */
+  uint32_t nh;   /* ROPE_KV: query heads */
+  /* arena byte offsets of token 0, IE_B200_NONE if absent; *_stride: bytes from one token row to the next */
+  uint64_t a, b, c, qo, res;
+  uint32_t a_stride, b_stride, c_stride, qo_stride, res_stride;
+} ie_b200_op;
+
+typedef struct {
+  uint32_t n_head, n_kv, hd; /* heads held by this engine (a tensor-parallel rank holds a slice) */
+  uint32_t n_ctx;            /* KV-cache positions */
+  uint32_t n_kv_layers;      /* layers with a KV cache */
+  uint32_t T_max;            /* most tokens of one run (graph.T of the reference) */
+  uint32_t vocab;            /* logits per row */
+  float eps;                 /* RMSNorm epsilon */
+  int32_t neox;              /* RoPE pairs (i, i + hd/2) instead of (2i, 2i+1) */
+  int32_t kv_f32;            /* 1: float KV cache (parity runs), 0: half */
+  uint64_t arena_bytes;      /* activation arena (plan_arena's graph.arena, src/plan.c:24) */
+  uint64_t logits_off, argmax_off; /* arena offsets of the logits and of the {index, prob} pair */
+  uint32_t logits_stride, argmax_stride;
+} ie_b200_engine_desc;
+
+/* gpu_open (src/hip.c:568): allocate arena, KV cache and scratch on the current CUDA device. */
+int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_engine **out);
+/* backend.close (src/backend.h:12). */
+void ie_b200_engine_destroy(ie_b200_engine *e);
+
+/* Upload one matrix and re-lay it out for streaming; returns its handle.
+ *  _gguf: raw GGUF tensor bytes on the host (what model_load reads, src/model.c:401).
+ *  _ref:  the reference loader's repacked arrays, as its matrix sink receives them
+ *         (ie_mat_sink, src/model.h:160-163; the upload of src/hip.c:278-303). h_qs NULL for MAT_F32
+ *         (h_qw then points at the floats).
+ *  _device: adopt a matrix already in the streaming layout in device memory (not freed by the engine). */
+int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uint32_t rows, uint32_t cols, const void *h_bytes);
+int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs);
+int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *d_data);
+/* A float vector (norm weight, bias); returns its handle. */
+int ie_b200_engine_add_vec(ie_b200_engine *e, const float *h_f, uint32_t n);
+/* RoPE tables [n_ctx][hd / 2] (graph.rope_cos / rope_sin, src/model.c:1655-1664). */
+int ie_b200_engine_set_rope(ie_b200_engine *e, const float *h_cos, const float *h_sin);
+/* The op list; i_head = first op of the output head (graph.i_head): a run with last_only executes the
+ * ops before it for all T tokens and the head for the last token only (src/hip.c:1560-1563). */
+int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, uint32_t n_ops, uint32_t i_head);
+
+/* backend.step (src/backend.h:10): one token at position pos; h_logits (vocab floats) may be NULL;
+ * *next = the argmax token; *ms (may be NULL) = device time of the step. Host buffers in and out. */
+int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms);
+/* K greedy tokens without a host round trip per token: the step graph is replayed K times and a one-CTA
+ * kernel feeds each argmax back as the next token on the device (what the decode loop of src/main.c:192-225
+ * does on the host). h_out: the K generated tokens; *ms: device time of the K steps. K <= 4096 per call. */
+int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K, uint32_t *h_out, double *ms);
+/* backend.run (src/backend.h:20), section 0: T tokens at positions pos .. pos + T - 1; out: T argmax
+ * tokens (only out[T-1] is meaningful when last_only), prob: T floats or NULL. */
+int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob);
+/* backend.read_rows / copy_rows (src/backend.h:27-31) on arena offsets: n rows of `stride` bytes. */
+int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, void *h_dst);
+int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uint32_t dst_stride, uint32_t d0, uint64_t src_off, uint32_t src_stride,
+                             uint32_t r0, uint32_t n, uint32_t row_bytes, int zero);
+
+/* For callers that interleave their own work (collectives of a tensor-parallel run) with the ops:
+ * write token ids and the first position to the device scalars on `stream`, then enqueue ops
+ * [first, last) for T tokens on `stream`. OP_ALLREDUCE ops inside the range are skipped. */
+int ie_b200_engine_set_input(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, void *stream);
+int ie_b200_engine_enqueue(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t T, void *stream);
+/* As enqueue, restricted to the ops whose kind bit (1 << IE_B200_OP_*) is set in kind_mask: lets a
+ * benchmark time one kernel family on the shapes of the real op list. */
+int ie_b200_engine_enqueue_kinds(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t kind_mask, uint32_t T, void *stream);
+/* Device address of the arena (to hand buffers to a collective) and of the {tokens[T_max], pos} scalars. */
+void *ie_b200_engine_arena(ie_b200_engine *e);
+void *ie_b200_engine_input_scalars(ie_b200_engine *e);
+/* Bytes of weights this engine streams per decode step (the GEMVs of the op list): the reference's
+ * graph.weight_bytes_per_token (src/model.c:1617-1635), 18 B per Q4_0/Q4_K block, 26.25 B per Q6_K block. */
+uint64_t ie_b200_engine_weight_bytes_per_token(ie_b200_engine *e);
+/* Kernels launched per one-token step (the nodes of the captured graph). */
+uint32_t ie_b200_engine_launches_per_step(ie_b200_engine *e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,346 @@
+"""Parity of the CUDA kernels (through the C ABI) with the oracle on the same
+seeded inputs. Integer / byte work and the GEMV floats: bit-exact. Ops whose
+reduction order differs from the CPU's (RMSNorm sum, attention): relative
+tolerance 1e-4 of the output scale, written at each assertion."""
+import numpy as np
+import pytest
+
+from amd_c_b200 import synth
+from conftest import bits
+from oracle.oracle import MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K
+
+pytestmark = pytest.mark.gpu
+
+Q4_SHAPES = [(1, 1), (7, 3), (9, 11), (8, 32), (13, 33), (17, 36), (5, 64), (3, 100), (2, 511)]
+K_SHAPES = [(3, 8), (9, 16), (8, 40), (5, 112), (2, 448)]
+KINDS = [(synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k")]
+
+
+def dev(a, cuda):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def expected_layout(kind, qw, qs, rows, cols, row_bytes):
+    """The streaming layout built in numpy from the reference-form arrays."""
+    nb = cols // 32
+    out = np.zeros((rows, row_bytes), np.uint8)
+    out[:, : 16 * nb] = qw[: rows * nb * 4].view(np.uint8).reshape(rows, 16 * nb)
+    if kind == MAT_Q4:
+        out[:, 16 * nb: 18 * nb] = qs.view(np.uint8).reshape(rows, 2 * nb)
+    elif kind == MAT_Q4K:
+        sm = qs[: rows * nb].reshape(rows, nb // 8, 8).astype(np.uint64)
+        f = (sm & 63) | (((sm >> 8) & 63) << 6)
+        lo = np.zeros((rows, nb // 8), np.uint64)
+        for j in range(5):
+            lo |= f[:, :, j] << np.uint64(12 * j)
+        lo |= (f[:, :, 5] & 15) << np.uint64(60)
+        w2 = (f[:, :, 5] >> 4) | (f[:, :, 6] << 8) | (f[:, :, 7] << 20)
+        dd = qs[rows * nb:].reshape(rows, nb // 8, 2).astype(np.uint32)
+        hdr = np.zeros((rows, nb // 8, 4), np.uint32)
+        hdr[:, :, 0] = dd[:, :, 0] | (dd[:, :, 1] << 16)
+        hdr[:, :, 1] = (lo & 0xFFFFFFFF).astype(np.uint32)
+        hdr[:, :, 2] = (lo >> 32).astype(np.uint32)
+        hdr[:, :, 3] = w2.astype(np.uint32)
+        out[:, 16 * nb: 16 * nb + 2 * nb] = hdr.view(np.uint8).reshape(rows, 2 * nb)
+    else:
+        out[:, 16 * nb: 24 * nb] = qw[rows * nb * 4:].view(np.uint8).reshape(rows, 8 * nb)
+        out[:, 24 * nb: 26 * nb] = qs[: rows * nb].view(np.uint8).reshape(rows, 2 * nb)
+        out[:, 26 * nb: 26 * nb + nb // 4] = qs[rows * nb:].view(np.uint8).reshape(rows, nb // 4)
+    return out
+
+
+def test_quant_q8_bit_exact(ora, cuda, golden_kernels):
+    from amd_c_b200 import kernels as K
+
+    g = golden_kernels
+    got = K.quant_q8(dev(g["quant_x"], cuda)).cpu().numpy().reshape(-1)
+    assert (got == g["quant_q"]).all()  # the reference's own output
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((7, 14336)) * rng.choice([1e-3, 1.0, 300.0], size=(7, 1))).astype(np.float32)
+    x[3, 640:672] = 0.0
+    got = K.quant_q8(dev(x, cuda)).cpu().numpy()
+    for t in range(x.shape[0]):
+        assert (got[t] == ora.quant_q8(x[t])).all(), t
+
+
+def test_quant_q8_empty(cuda, lib):
+    assert lib.ie_b200_quant_q8(256, 256, 0, 1, 0, 0, None) == 0  # zero blocks: nothing launched, nothing read
+
+
+@pytest.mark.parametrize("typ,shapes,tag", KINDS)
+def test_repack_layout_and_gemv_bit_exact(ora, cuda, golden_kernels, lib, typ, shapes, tag):
+    """Both repack entry points give the documented layout; block dots and GEMV match the golden outputs bit for bit."""
+    from amd_c_b200 import kernels as K
+
+    g = golden_kernels
+    for rows, nb in shapes:
+        cols, key = nb * 32, f"{tag}_{rows}x{nb}"
+        raw = g[key + "_raw"]
+        kind, qw, qs = ora.repack(typ, raw, rows, cols)
+        m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+        rowb = lib.ie_b200_row_bytes(kind, cols)
+        want = expected_layout(kind, qw, qs, rows, cols, rowb)
+        got = m.data.cpu().numpy()[: rows * rowb].reshape(rows, rowb)
+        used = {MAT_Q4: 18 * nb, MAT_Q4K: 18 * nb, MAT_Q6K: 26 * nb + nb // 4}[kind]
+        assert (got[:, :used] == want[:, :used]).all(), key
+        m2 = K.Mat.from_ref(kind, dev(qw, cuda), dev(qs, cuda), rows, cols)
+        assert (m2.data.cpu().numpy()[: rows * rowb].reshape(rows, rowb)[:, :used] == want[:, :used]).all(), key
+        xq = ora.quant_q8(g[key + "_x"])
+        y = K.gemv(m, dev(xq, cuda).reshape(1, -1)).cpu().numpy().reshape(-1)
+        assert (bits(y) == bits(g[key + "_y"])).all(), key
+        if kind == MAT_Q4:
+            d = K.block_dots(m, dev(xq, cuda)).cpu().numpy()
+            assert (d == ora.block_dots_q4(qw, rows, nb, xq)).all(), key
+
+
+@pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 1000, 4096), (synth.GGML_Q4_0, 260, 14336), (synth.GGML_Q4_K, 520, 3584),
+                                           (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944), (synth.GGML_Q4_K, 96, 5120)])
+def test_gemv_model_shapes_with_epilogue(ora, cuda, typ, rows, cols):
+    """Llama / Qwen column counts, rows not a multiple of the CTA tile, bias + residual, 3 tokens."""
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows + cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    T = 3
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    bias = rng.standard_normal(rows).astype(np.float32)
+    res = rng.standard_normal((T, rows)).astype(np.float32)
+    xq = np.stack([ora.quant_q8(x[t]) for t in range(T)])
+    y = K.gemv(m, dev(xq, cuda), bias=dev(bias, cuda), res=dev(res, cuda)).cpu().numpy()
+    for t in range(T):
+        want = ora.gemv(kind, qw, qs, rows, cols, xq[t], bias=bias, res=res[t])
+        assert (bits(y[t]) == bits(want)).all(), t
+    y0 = K.gemv(m, dev(xq[:1], cuda)).cpu().numpy()[0]
+    assert (bits(y0) == bits(ora.gemv(kind, qw, qs, rows, cols, xq[0]))).all()
+
+
+def test_gemv_linearity_full_size(ora, cuda):
+    """At a full benchmark size (14336 x 4096) the oracle is too slow to sweep, so check properties: integer block
+    dots are additive in the activations, and the GEMV of a zero activation is exactly zero."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rows, cols = 14336, 4096
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    raw = synth.q4_0_normal_torch(gen, rows, cols, device=cuda)
+    m = K.Mat.from_gguf(synth.GGML_Q4_0, raw.reshape(-1), rows, cols)
+    rng = np.random.default_rng(0)
+    nb = cols // 32
+    qa = rng.integers(-60, 60, (2, cols)).astype(np.int8)
+
+    def q8buf(q):
+        b = np.zeros(40 * nb, np.uint8)
+        b[: 32 * nb] = q.view(np.uint8)
+        b[32 * nb: 36 * nb] = np.ones(nb, np.float32).view(np.uint8)
+        b[36 * nb:] = q.reshape(nb, 32).astype(np.int64).sum(axis=1).astype(np.uint32).view(np.uint8)
+        return b
+
+    d0 = K.block_dots(m, dev(q8buf(qa[0]), cuda))
+    d1 = K.block_dots(m, dev(q8buf(qa[1]), cuda))
+    d01 = K.block_dots(m, dev(q8buf((qa[0].astype(np.int16) + qa[1]).astype(np.int8)), cuda))
+    assert torch.equal(d0 + d1, d01)
+    y = K.gemv(m, dev(np.zeros((1, 40 * nb), np.uint8), cuda))
+    assert float(y.abs().max()) == 0.0
+    # a sample of rows against the oracle, bit for bit
+    sel = rng.choice(rows, 64, replace=False)
+    sub = raw.reshape(rows, nb, 18)[torch.from_numpy(sel).to(cuda)].cpu().numpy()
+    kind, qw, qs = ora.repack(synth.GGML_Q4_0, sub, 64, cols)
+    xq = ora.quant_q8(rng.standard_normal(cols).astype(np.float32))
+    yy = K.gemv(m, dev(xq, cuda).reshape(1, -1)).cpu().numpy()[0]
+    assert (bits(yy[sel]) == bits(ora.gemv(kind, qw, qs, 64, cols, xq))).all()
+
+
+def test_gemv_f32_bit_exact(ora, cuda):
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(11)
+    for rows, cols in [(1024, 256), (37, 100), (5, 4096), (3, 31)]:
+        w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+        x = rng.standard_normal(cols).astype(np.float32)
+        m = K.Mat(MAT_F32, rows, cols, dev(w, cuda))
+        y = K.gemv(m, dev(x, cuda).reshape(1, -1)).cpu().numpy()[0]
+        assert (bits(y) == bits(ora.gemv(MAT_F32, w, None, rows, cols, x))).all(), (rows, cols)
+
+
+def test_embed_rmsnorm_swiglu_argmax(ora, cuda):
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(2)
+    # embedding rows of a Q4_0 matrix: exact
+    rows, cols = 300, 256
+    raw = synth.make_gguf_bytes(synth.GGML_Q4_0, rng, rows, cols)
+    kind, qw, qs = ora.repack(synth.GGML_Q4_0, raw, rows, cols)
+    m = K.Mat.from_gguf(synth.GGML_Q4_0, dev(raw, cuda), rows, cols)
+    toks = np.array([0, 299, 17], np.uint32)
+    e = K.embed(m, dev(toks, cuda)).cpu().numpy()
+    for i, t in enumerate(toks):
+        assert (bits(e[i]) == bits(ora.embed_q4(qw, qs, cols // 32, int(t)))).all()
+    # RMSNorm: tree sum vs sequential sum -> 1e-5 relative; the Q8 copy must be the quantiser of the kernel's own output
+    for n in (256, 4096, 5120):
+        x = rng.standard_normal((2, n)).astype(np.float32)
+        w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        y, q = K.rmsnorm(dev(x, cuda), dev(w, cuda), 1e-5)
+        y, q = y.cpu().numpy(), q.cpu().numpy()
+        for t in range(2):
+            want = ora.rmsnorm(x[t], w, 1e-5)
+            assert np.abs(y[t] - want).max() <= 1e-5 * np.abs(want).max()
+            assert (q[t] == ora.quant_q8(y[t])).all()
+    # SwiGLU: expf differs by an ulp or two from the host libm -> 1e-6 relative
+    n = 14336
+    gu = rng.standard_normal((2, 2 * n)).astype(np.float32) * 3
+    d = dev(gu, cuda)
+    a, q = K.swiglu(d, n)
+    a, q = a.cpu().numpy(), q.cpu().numpy()
+    for t in range(2):
+        want = ora.swiglu(gu[t, :n], gu[t, n:])
+        assert np.abs(a[t] - want).max() <= 1e-6 * np.abs(want).max()
+        assert (q[t] == ora.quant_q8(a[t])).all()
+    # argmax: first index among equal maxima
+    x = rng.standard_normal((3, 128256)).astype(np.float32)
+    x[1, 77] = x[1, 99000] = 50.0
+    x[2, :] = 1.0
+    out = K.argmax(dev(x, cuda)).cpu().numpy()
+    for t in range(3):
+        assert out[t, 0] == ora.argmax(x[t])
+    p = out[:, 1].copy().view(np.float32)
+    want_p = 1.0 / np.exp(x[0].astype(np.float64) - x[0].max()).sum()
+    assert abs(p[0] - want_p) <= 1e-4 * want_p
+    assert torch.cuda.is_available()
+
+
+@pytest.mark.parametrize("n_head,n_kv,hd,neox,kv_f32", [(8, 4, 32, False, True), (8, 4, 32, False, False), (32, 8, 128, False, False),
+                                                        (28, 4, 128, True, False), (40, 8, 128, True, True), (4, 4, 64, False, False)])
+def test_rope_kv_and_attention(ora, cuda, n_head, n_kv, hd, neox, kv_f32):
+    """RoPE + cache store is exact (f32 cache) or exact after half rounding; attention agrees with the oracle's
+    two-pass softmax over the same cache within 1e-4 of the output scale, at positions that cross tile and split edges."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(n_head * 1000 + hd)
+    n_ctx = 700
+    cs, sn = ora.rope_tables(n_ctx, hd, 10000.0)
+    qd, kvd = n_head * hd, n_kv * hd
+    dt = torch.float32 if kv_f32 else torch.float16
+    kc = torch.zeros((n_kv, n_ctx, hd), dtype=dt, device=cuda)
+    vc = torch.zeros_like(kc)
+    kc_ref, vc_ref = np.zeros((n_ctx, kvd), np.float32), np.zeros((n_ctx, kvd), np.float32)
+    scratch = K.AttnScratch(n_head, hd, n_ctx, 1, cuda)
+    d_cs, d_sn = dev(cs, cuda), dev(sn, cuda)
+    check_at = {0, 1, 31, 63, 64, 65, 127, 128, 300, 511, 512, 699}
+    # fill the cache in bulk for positions not checked one by one
+    for pos in range(n_ctx):
+        qkv = rng.standard_normal(qd + 2 * kvd).astype(np.float32)
+        q_ref = ora.rope(qkv[:qd], n_head, hd, neox, cs[pos], sn[pos])
+        k_ref = ora.rope(qkv[qd: qd + kvd], n_kv, hd, neox, cs[pos], sn[pos])
+        v_ref = qkv[qd + kvd:]
+        if not kv_f32:
+            k_ref, v_ref = k_ref.astype(np.float16).astype(np.float32), v_ref.astype(np.float16).astype(np.float32)
+        kc_ref[pos], vc_ref[pos] = k_ref, v_ref
+        if pos in check_at:
+            d = dev(qkv.reshape(1, -1), cuda)
+            K.rope_kv(d, kc, vc, d_cs, d_sn, dev(np.array([pos], np.uint32), cuda), n_head, n_kv, hd, neox, n_ctx)
+            got = d.cpu().numpy()[0]
+            assert (bits(got[:qd]) == bits(q_ref)).all()
+            assert (bits(kc[:, pos, :].float().cpu().numpy().reshape(-1)) == bits(k_ref)).all()
+            assert (bits(vc[:, pos, :].float().cpu().numpy().reshape(-1)) == bits(v_ref)).all()
+            out, oq = K.attn_decode(d, kc, vc, dev(np.array([pos], np.uint32), cuda), n_head, n_kv, hd, n_ctx, scratch)
+            out, oq = out.cpu().numpy()[0], oq.cpu().numpy()[0]
+            want = ora.attention(q_ref, kc_ref, vc_ref, pos, n_head, n_kv, hd)
+            assert np.abs(out - want).max() <= 1e-4 * np.abs(want).max(), pos
+            assert (oq == ora.quant_q8(out)).all(), pos
+            assert int(scratch.count.abs().max()) == 0  # arrival counters are left at zero
+        else:
+            kc[:, pos, :] = torch.from_numpy(k_ref.reshape(n_kv, hd)).to(cuda).to(dt)
+            vc[:, pos, :] = torch.from_numpy(v_ref.reshape(n_kv, hd)).to(cuda).to(dt)
+
+
+def test_attention_multi_token_rows(ora, cuda):
+    """T = 3 tokens in one launch: token t sees positions 0 .. pos + t (the chunk is causal)."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(8)
+    n_head, n_kv, hd, n_ctx, T, pos0 = 8, 4, 32, 256, 3, 70
+    kvd = n_kv * hd
+    kc_ref = rng.standard_normal((n_ctx, kvd)).astype(np.float32)
+    vc_ref = rng.standard_normal((n_ctx, kvd)).astype(np.float32)
+    kc = torch.from_numpy(kc_ref.reshape(n_ctx, n_kv, hd).transpose(1, 0, 2).copy()).to(cuda)
+    vc = torch.from_numpy(vc_ref.reshape(n_ctx, n_kv, hd).transpose(1, 0, 2).copy()).to(cuda)
+    q = rng.standard_normal((T, n_head * hd)).astype(np.float32)
+    scratch = K.AttnScratch(n_head, hd, n_ctx, T, cuda)
+    out, _ = K.attn_decode(dev(q, cuda), kc, vc, dev(np.array([pos0], np.uint32), cuda), n_head, n_kv, hd, n_ctx, scratch)
+    out = out.cpu().numpy()
+    for t in range(T):
+        want = ora.attention(q[t], kc_ref, vc_ref, pos0 + t, n_head, n_kv, hd)
+        assert np.abs(out[t] - want).max() <= 1e-4 * np.abs(want).max(), t
+
+
+STREAM_SHAPES = [(synth.GGML_Q4_0, 1000, 4096), (synth.GGML_Q4_0, 260, 14336), (synth.GGML_Q4_0, 7, 96), (synth.GGML_Q4_0, 1536, 256),
+                 (synth.GGML_Q4_0, 149, 1056), (synth.GGML_Q4_K, 520, 3584), (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944),
+                 (synth.GGML_Q4_K, 333, 5120), (synth.GGML_Q4_0, 2, 16352), (synth.GGML_Q4_0, 4096, 14336), (synth.GGML_Q6_K, 3000, 18944),
+                 (synth.GGML_Q4_0, 9000, 4096), (synth.GGML_Q4_K, 5000, 256)]
+
+
+@pytest.mark.parametrize("typ,rows,cols", STREAM_SHAPES)
+def test_gemv_stream_bit_exact(ora, cuda, typ, rows, cols):
+    """The bulk-copy-ring GEMV (decode path): same bits as the oracle, with bias and residual, for row counts
+    below, at and above the CTA count and for rings of every stage geometry."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows * 7 + cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    bias = rng.standard_normal(rows).astype(np.float32)
+    res = rng.standard_normal(rows).astype(np.float32)
+    xq = ora.quant_q8(x)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    y = K.gemv_stream(m, dev(xq, cuda), bias=dev(bias, cuda), res=dev(res, cuda), err=err).cpu().numpy()[0]
+    assert int(err.item()) == 0
+    assert (bits(y) == bits(ora.gemv(kind, qw, qs, rows, cols, xq, bias=bias, res=res))).all()
+    y2 = K.gemv_stream(m, dev(xq, cuda), err=err).cpu().numpy()[0]
+    assert (bits(y2) == bits(ora.gemv(kind, qw, qs, rows, cols, xq))).all()
+    # back-to-back launches on one stream (each may start before the previous one ends) still see finished inputs
+    ys = [K.gemv_stream(m, dev(xq, cuda), err=err) for _ in range(4)]
+    assert all(torch.equal(ys[0], t) for t in ys[1:]) and int(err.item()) == 0
+
+
+@pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 6144, 4096), (synth.GGML_Q4_0, 1536, 256), (synth.GGML_Q4_K, 700, 3584),
+                                           (synth.GGML_Q6_K, 512, 5120)])
+def test_norm_gemv_stream(ora, cuda, typ, rows, cols):
+    """RMSNorm + Q8 folded into the GEMV prologue: the normalised vector within 1e-5 of the oracle's sequential-sum
+    norm; its Q8 copy is exactly the quantiser of that vector; the GEMV of it is bit-exact."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows + 3 * cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    res = rng.standard_normal(rows).astype(np.float32)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    y, xn, xq = K.norm_gemv_stream(m, dev(x, cuda), dev(nw, cuda), 1e-5, res=dev(res, cuda), err=err)
+    y, xn, xq = y.cpu().numpy()[0], xn.cpu().numpy(), xq.cpu().numpy()
+    assert int(err.item()) == 0
+    want = ora.rmsnorm(x, nw, 1e-5)
+    assert np.abs(xn - want).max() <= 1e-5 * np.abs(want).max()
+    assert (xq == ora.quant_q8(xn)).all()
+    assert (bits(y) == bits(ora.gemv(kind, qw, qs, rows, cols, xq, res=res))).all()
+    # and the same vector as the stand-alone norm kernel
+    yn, qn = K.rmsnorm(dev(x.reshape(1, -1), cuda), dev(nw, cuda), 1e-5)
+    assert torch.equal(qn.reshape(-1).cpu(), torch.from_numpy(xq))
