@@ -30,7 +30,10 @@
 // is complete", so a waiter must never be two phases ahead of its stage. Every
 // consumer warp therefore waits on every stage in iteration order, also for
 // the stages whose rows belong to another warp group.
+#include <cstdlib>
+
 #include "common.cuh"
+#include "act_stage.cuh"
 #include "gemv_blocks.cuh"
 
 namespace ieb {
@@ -162,54 +165,9 @@ __global__ void __launch_bounds__(GS_THREADS, 2) gemv_stream_kernel(const GsArgs
   // ---------------- consumers ----------------
   pdl_wait();  // the previous kernel's results (activations, residual) are complete and visible
   if (skip) return;
-  const int tid = threadIdx.x;  // 0 .. 255
-  if (!NORM) {
-    const uint4 *src = reinterpret_cast<const uint4 *>(a.xq);
-    for (uint32_t i = tid; i < 2u * nb; i += GS_CONSUMER_WARPS * 32) {
-      const uint4 v = src[i];
-      if (i & 1u) A1[i >> 1] = v;
-      else A0[i >> 1] = v;
-    }
-    const float *d = reinterpret_cast<const float *>(a.xq + 32u * (size_t)nb);
-    const int *s = reinterpret_cast<const int *>(a.xq + 36u * (size_t)nb);
-    for (uint32_t i = tid; i < nb; i += GS_CONSUMER_WARPS * 32) da[i] = d[i], as[i] = s[i];
-  } else {
-    // rmsnorm + Q8 of the f32 vector; each warp takes whole blocks of 32
-    const uint32_t n = nb * 32u;
-    float ss = 0.0f;
-    for (uint32_t i = tid; i < n; i += GS_CONSUMER_WARPS * 32) ss = fmaf(a.xf[i], a.xf[i], ss);
-    ss = warp_sum_all(ss);
-    if (lane == 0) red[warp] = ss;
-    consumer_sync();
-    float tot = lane < GS_CONSUMER_WARPS ? red[lane] : 0.0f;
-    tot = warp_sum_all(tot);
-    const float sc = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)n), a.eps)));
-    const bool writer = c == 0;
-    for (uint32_t b = warp; b < nb; b += GS_CONSUMER_WARPS) {
-      const uint32_t i = 32u * b + lane;
-      const float v = __fmul_rn(__fmul_rn(a.xf[i], sc), a.norm_w[i]);
-      const float amax = warp_max(fabsf(v));
-      const float d = __fdiv_rn(amax, 127.0f);
-      int q = 0;
-      if (d != 0.0f) q = (int)roundf(__fdiv_rn(v, d));
-      int s = q;
-      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-      // lane j holds activation j of the block: word j >> 2 of the block, byte j & 3
-      int8_t *plane = reinterpret_cast<int8_t *>(lane < 16 ? A0 + b : A1 + b);
-      plane[lane & 15] = (int8_t)q;
-      if (lane == 0) da[b] = d, as[b] = s;
-      if (writer) {
-        if (a.xn_out) a.xn_out[i] = v;
-        if (a.xq_out) {
-          reinterpret_cast<int8_t *>(a.xq_out)[i] = (int8_t)q;
-          if (lane == 0) {
-            reinterpret_cast<float *>(a.xq_out + 32u * (size_t)nb)[b] = d;
-            reinterpret_cast<int *>(a.xq_out + 36u * (size_t)nb)[b] = s;
-          }
-        }
-      }
-    }
-  }
+  ActSrc src;
+  src.xq = a.xq, src.xf = a.xf, src.norm_w = a.norm_w, src.eps = a.eps, src.xn_out = a.xn_out, src.xq_out = a.xq_out;
+  stage_activations<NORM, GS_CONSUMER_WARPS>(src, nb, A0, A1, da, as, red, c == 0, [] { consumer_sync(); });
   consumer_sync();
 
   const uint32_t grp = warp / wps, wrow = (warp % wps) * 2u;
@@ -288,6 +246,18 @@ static int dispatch_stream(int kind, GsArgs &a, cudaStream_t st) {
   }
 }
 
+int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
+                const float *d_res, cudaStream_t st);  // gemv_direct.cu
+
+// Which decode GEMV runs: "direct" (registers, default) or "ring" (bulk copies into shared memory); IE_B200_GEMV selects.
+static bool use_ring() {
+  static const bool ring = [] {
+    const char *v = getenv("IE_B200_GEMV");
+    return v && v[0] == 'r';
+  }();
+  return ring;
+}
+
 }  // namespace ieb
 
 using namespace ieb;
@@ -307,6 +277,11 @@ extern "C" int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uin
   if (int e = check_common("ie_b200_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_xq || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_stream: activations must be a 16-byte aligned Q8 buffer");
   if (rows == 0) return IE_B200_OK;
+  if (!use_ring()) {
+    ActSrc act = {};
+    act.xq = static_cast<const uint8_t *>(d_xq);
+    return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, static_cast<cudaStream_t>(stream));
+  }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.w_bytes = a.rowb * rows;
@@ -320,6 +295,11 @@ extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows
   if (int e = check_common("ie_b200_norm_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_norm_gemv_stream: NULL pointer");
   if (rows == 0) return IE_B200_OK;
+  if (!use_ring()) {
+    ActSrc act = {};
+    act.xf = d_x, act.norm_w = d_norm_w, act.eps = eps, act.xn_out = d_xn_out, act.xq_out = static_cast<uint8_t *>(d_xq_out);
+    return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, static_cast<cudaStream_t>(stream));
+  }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.w_bytes = a.rowb * rows;
