@@ -85,6 +85,15 @@ ENGINE_SIGNATURES = {
 
 SIGNATURES.update(ENGINE_SIGNATURES)
 
+# ---- the tensor-parallel all-reduce (include/ie_b200_tp.h) ----
+SIGNATURES.update({
+    "ie_b200_ar_create": (_int, [_u32, _u32, _u32, C.POINTER(_vp)]),
+    "ie_b200_ar_handles": (_int, [_vp, _vp]),
+    "ie_b200_ar_connect": (_int, [_vp, _vp]),
+    "ie_b200_ar_allreduce_add": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp]),
+    "ie_b200_ar_destroy": (None, [_vp]),
+})
+
 
 class IeB200Error(RuntimeError):
     """A call into libie_b200.so returned a negative status."""

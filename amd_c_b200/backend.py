@@ -229,8 +229,8 @@ class Backend:
                 self._op(OP_RMSNORM, a="x", b="xn", qo="xq", vec=nxt_norm, n=c.dim)
             else:
                 self._op(OP_GEMV, a="attq", b="part", mat=wo, n=qd)
-                self._op(OP_ALLREDUCE, a="part", n=c.dim)
-                self._op(OP_RMSNORM, a="x", b="xn", qo="xq", res="part", vec=nxt_norm, n=c.dim)
+                self._op(OP_ALLREDUCE, a="part", c="x", n=c.dim)  # x = x + sum over ranks of part
+                self._op(OP_RMSNORM, a="x", b="xn", qo="xq", vec=nxt_norm, n=c.dim)
             self._gemv_group([(p + "ffn_gate.weight", f0, f0 + self.ffn_l), (p + "ffn_up.weight", f0, f0 + self.ffn_l)], "xq", "xn", "gu")
             self._op(OP_SWIGLU, a="gu", b="gu", boff=self.ffn_l * 4, qo="guq", n=self.ffn_l)
             wd = self._add_mat([self._cols(p + "ffn_down.weight", f0, f0 + self.ffn_l)])
@@ -241,8 +241,8 @@ class Backend:
                 self._op(OP_RMSNORM, a="x", b="xn", qo="xq", vec=nxt_norm, n=c.dim)
             else:
                 self._op(OP_GEMV, a="guq", b="part", mat=wd, n=self.ffn_l)
-                self._op(OP_ALLREDUCE, a="part", n=c.dim)
-                self._op(OP_RMSNORM, a="x", b="xn", qo="xq", res="part", vec=nxt_norm, n=c.dim)
+                self._op(OP_ALLREDUCE, a="part", c="x", n=c.dim)
+                self._op(OP_RMSNORM, a="x", b="xn", qo="xq", vec=nxt_norm, n=c.dim)
         self.i_head = len(self.ops)
         v0 = r * self.vocab_l
         head = self._rows("output.weight" if ("output.weight" in c.tensors or "output.weight" in self._dev) else "token_embd.weight", v0,
@@ -306,6 +306,14 @@ class Backend:
     @property
     def launches_per_step(self) -> int:
         return int(self.lib.ie_b200_engine_launches_per_step(self.h))
+
+    def enqueue_kinds(self, first: int, last: int, kind_mask: int, stream: int, T: int = 1) -> None:
+        """Enqueue the ops [first, last) whose kind bit is in kind_mask on a CUDA stream (no input upload, no sync)."""
+        check(self.lib.ie_b200_engine_enqueue_kinds(self.h, first, last, kind_mask, T, stream))
+
+    def set_input(self, toks, pos: int, stream: int) -> None:
+        t = np.ascontiguousarray(toks, dtype=np.uint32)
+        check(self.lib.ie_b200_engine_set_input(self.h, t.ctypes.data_as(_vp), t.size, pos, stream))
 
     def run_ops(self, tok: int, pos: int, last_op: int) -> None:
         """Debug aid for parity tests: ops [0, last_op) of one token, synchronously (no graph)."""

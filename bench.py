@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: Llama-3-8B-shaped Q4_0 greedy decode, batch 1.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one decode token (one pass of the op list over the weights). One JSON
+line goes to stdout (rank 0):
+  value     decode tokens/s with everything resident on the device: the step
+            graph replayed K times, the argmax fed back on the device
+  e2e       the same through backend.step(): token id and position from host
+            memory every step, argmax read back every step
+  roofline  the GEMV kernels of the step (the dominant kernel) alone, timed
+            with CUDA events on their stream: algorithmic weight bytes / time
+            against the measured HBM copy bandwidth
+  cpu_baseline  the reference's own CPU GEMV (oracle/_ref, built from its
+            sources) or the oracle port, on a bounded sample, 1 core
+Weights are seeded synthetic (no network, no checkpoint): N(0, 0.02) quantised
+to Q4_0 as the benchmark definition says; the prompt is 128 seeded uniform ids.
+With --gpus N > 1 (under torchrun) the model is sharded tensor-parallel.
+--impl reference times the reference CPU implementation instead (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+PROMPT_LEN = 128
+
+
+def measured_peaks() -> tuple[float, str]:
+    """HBM GB/s to hold achieved bandwidth against: the driver-measured copy bandwidth, else the documented fallback."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.idx)],
+                                         stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])), mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------ CPU side
+
+def layer_sample_bytes(cfg) -> tuple[int, int]:
+    """(algorithmic weight bytes of one layer's GEMVs, of the whole step) at 18 B per Q4_0 block."""
+    kvd = cfg.n_kv * cfg.hd
+    layer = (cfg.dim * cfg.dim * 2 + 2 * kvd * cfg.dim + 3 * cfg.ffn * cfg.dim) // 32 * 18
+    head = cfg.vocab * cfg.dim // 32 * 18
+    return layer, layer * cfg.n_layer + head
+
+
+def cpu_layer_sample(cfg, seed: int = 0):
+    """One layer's seven matrices (seeded, same block definition) as the CPU implementation wants them, and a Q8
+    activation for each input width. Returns (callable that runs the seven GEMVs once, kind, cores)."""
+    import numpy as np
+
+    from amd_c_b200 import synth
+    from oracle.oracle import Oracle, Ref
+
+    rng = np.random.default_rng(seed)
+    kvd = cfg.n_kv * cfg.hd
+    shapes = [(cfg.dim, cfg.dim), (kvd, cfg.dim), (kvd, cfg.dim), (cfg.dim, cfg.dim), (cfg.ffn, cfg.dim), (cfg.ffn, cfg.dim), (cfg.dim, cfg.ffn)]
+    ora = Oracle()
+    xq = {c: ora.quant_q8(rng.standard_normal(c).astype(np.float32)) for c in {s[1] for s in shapes}}
+    if Ref.available():
+        ref = Ref()
+        mats = [ref.mat(synth.GGML_Q4_0, synth.q4_0_normal(rng, r, c), r, c) for r, c in shapes]
+
+        def run():
+            for m in mats:
+                m.gemv(xq[m.cols])
+        return run, "reference", 1
+    packed = []
+    for r, c in shapes:
+        kind, qw, qs = ora.repack(synth.GGML_Q4_0, synth.q4_0_normal(rng, r, c), r, c)
+        packed.append((kind, qw, qs, r, c))
+
+    def run():
+        for kind, qw, qs, r, c in packed:
+            ora.gemv(kind, qw, qs, r, c, xq[c])
+    return run, "port", 1
+
+
+def cpu_baseline(cfg, budget_s: float = 12.0) -> dict:
+    """The reference CPU GEMV on one of the n_layer layers, repeated for about budget_s seconds; tokens/s
+    extrapolated by weight bytes to the whole step (the GEMVs are 99 % of a CPU step)."""
+    run, kind, cores = cpu_layer_sample(cfg)
+    layer_b, step_b = layer_sample_bytes(cfg)
+    run()
+    t0, reps = time.perf_counter(), 0
+    while reps < 3 or time.perf_counter() - t0 < budget_s:
+        run()
+        reps += 1
+    per = (time.perf_counter() - t0) / reps
+    return {"value": 1.0 / (per * step_b / layer_b), "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"the 7 Q4_0 GEMVs of 1 of {cfg.n_layer} layers ({layer_b / 1e6:.1f} MB of weights), {reps} repetitions, "
+                      f"extrapolated by weight bytes to the {step_b / 1e9:.3f} GB of one token", "gb_per_s": layer_b / per / 1e9}
+
+
+def run_reference_arm(args, cfg, rank: int) -> None:
+    """--impl reference: the reference's single-threaded CPU backend. One step = one layer's GEMVs (a bounded
+    sample of a token); tokens/s extrapolated by weight bytes. Rank 0 alone works."""
+    if rank != 0:
+        return
+    run, kind, cores = cpu_layer_sample(cfg)
+    layer_b, step_b = layer_sample_bytes(cfg)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    per = (time.perf_counter() - t0) / args.steps
+    v = 1.0 / (per * step_b / layer_b)
+    sample = (f"each step = the 7 Q4_0 GEMVs of 1 of {cfg.n_layer} layers on the CPU ({layer_b / 1e6:.1f} MB of weights); tokens/s "
+              f"extrapolated by weight bytes to one token ({step_b / 1e9:.3f} GB)")
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                      "dtype": "int8 dot4 + f32 accumulate", "data": "synthetic", "config": workload_config(cfg, args.gpus),
+                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)
+
+
+def workload_config(cfg, n_gpus: int) -> dict:
+    return {"workload": "Llama-3-8B-shaped random-init Q4_0 greedy decode, batch 1 (32 layers, d_model 4096, 32/8 heads of 128, FFN 14336, "
+                        "vocab 128256, Q4_0 embedding and output head, f16 KV cache), 128-token seeded prompt",
+            "prompt_len": PROMPT_LEN, "parallelism": f"tp{n_gpus}", "l2": "every step streams 4.2 GB of weights, far more than the 126 MB L2; no flush needed"}
+
+
+# ------------------------------------------------------------------ GPU side
+
+def build_backend(cfg, n_ctx: int, tp: int, rank: int, device):
+    import torch
+
+    from amd_c_b200 import gguf
+    from amd_c_b200.backend import Backend
+
+    dev_tensors = gguf.make_model_device(cfg, seed=0, device=device)
+    b = Backend(cfg, n_ctx, T=1, device_tensors=dev_tensors, tp=tp, rank=rank, device=device)
+    del dev_tensors
+    torch.cuda.empty_cache()
+    return b
+
+
+def time_gemvs(b, reps: int = 20) -> dict:
+    """The GEMV kernels of one step (with their fused norm prologues), in op-list order on the real matrices,
+    captured into a graph and timed with CUDA events on the capturing stream. Every pass streams all weights
+    (4.2 GB), so nothing is served from L2."""
+    import torch
+
+    from amd_c_b200 import _lib
+    from amd_c_b200.backend import OP_GEMV, OP_RMSNORM
+
+    lib = _lib.load()
+    mask = (1 << OP_GEMV) | (1 << OP_RMSNORM)
+    s = torch.cuda.Stream(device=b.device)
+    with torch.cuda.device(b.device), torch.cuda.stream(s):
+        before = lib.ie_b200_launch_count()
+        b.enqueue_kinds(0, len(b.ops), mask, s.cuda_stream)
+        launches = lib.ie_b200_launch_count() - before
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            b.enqueue_kinds(0, len(b.ops), mask, s.cuda_stream)
+        for _ in range(3):
+            g.replay()
+        s.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            g.replay()
+        e1.record(s)
+        s.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"ms_per_pass": ms, "launches": int(launches), "bytes": b.weight_bytes_per_token}
+
+
+def run_ours_single(args, cfg) -> dict:
+    import numpy as np
+    import torch
+
+    from amd_c_b200 import _lib
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    K, W = args.steps, args.warmup
+    n_ctx = PROMPT_LEN + 2 * (K + W) + 8
+    b = build_backend(cfg, n_ctx, 1, 0, dev)
+    lib = _lib.load()
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, cfg.vocab, PROMPT_LEN)
+    tok = 0
+    for pos, t in enumerate(prompt):  # the prompt, token by token (the reference has no Q4_0 prompt kernel either)
+        tok, _ = b.step(int(t), pos)
+    pos = PROMPT_LEN
+    # ---- device-resident decode: W warm-up steps, then K timed steps
+    out, _ = b.decode(tok, pos, W)
+    tok, pos = int(out[-1]), pos + W
+    torch.cuda.synchronize()
+    with ClockSampler(0) as cs:
+        l0 = lib.ie_b200_launch_count()
+        out, ms = b.decode(tok, pos, K)
+        launches = lib.ie_b200_launch_count() - l0
+        tok, pos = int(out[-1]), pos + K
+        # ---- end to end: token in from the host, argmax out to the host, every step
+        for _ in range(W):
+            tok, _ = b.step(tok, pos)
+            pos += 1
+        t0 = time.perf_counter()
+        for _ in range(K):
+            tok, _ = b.step(tok, pos)
+            pos += 1
+        e2e_s = time.perf_counter() - t0
+    clocks = cs.summary()
+    gem = time_gemvs(b)
+    peak, peak_src = measured_peaks()
+    achieved = gem["bytes"] / (gem["ms_per_pass"] * 1e-3) / 1e9
+    res = {
+        "value": K / (ms * 1e-3), "ms_per_step": ms / K, "gpu_launches": int(launches),
+        "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 12},
+        "roofline": {"bound": "hbm", "kernel": "gemv (Q4_0 x Q8, decode)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": f"{peak_src} copy bandwidth", "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
+                     "launches_per_step": gem["launches"], "avg_launch_us": gem["ms_per_pass"] * 1e3 / max(1, gem["launches"]),
+                     "algorithmic_bytes_per_step": gem["bytes"]},
+        "step_weight_gb_per_s": b.weight_bytes_per_token / (ms / K * 1e-3) / 1e9,
+        "launches_per_step": b.launches_per_step, "clocks": clocks,
+    }
+    b.close()
+    return res
+
+
+def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
+    """Tensor-parallel decode under torchrun: one process per GPU, NCCL for the rendezvous, the per-half-layer
+    sums through the peer-memory all-reduce kernel (amd_c_b200/tp.py). Returns the result dict on rank 0."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from amd_c_b200 import _lib
+    from amd_c_b200.tp import TensorParallelBackend
+
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    K, W = args.steps, args.warmup
+    n_ctx = PROMPT_LEN + 2 * (K + W) + 8
+    b = build_backend(cfg, n_ctx, world, rank, dev)
+    tpb = TensorParallelBackend(b, dist.group.WORLD)
+    lib = _lib.load()
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, cfg.vocab, PROMPT_LEN)
+    tok = 0
+    for pos, t in enumerate(prompt):
+        tok = tpb.step(int(t), pos)
+    pos = PROMPT_LEN
+    out = tpb.decode(tok, pos, W)
+    tok, pos = int(out[-1]), pos + W
+    torch.cuda.synchronize()
+    dist.barrier()
+    with ClockSampler(local) as cs:
+        torch.cuda.synchronize()
+        l0 = lib.ie_b200_launch_count()
+        out, ms = tpb.decode(tok, pos, K, timed=True)
+        launches = lib.ie_b200_launch_count() - l0
+        tok, pos = int(out[-1]), pos + K
+        for _ in range(W):
+            tok = tpb.step(tok, pos)
+            pos += 1
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            tok = tpb.step(tok, pos)
+            pos += 1
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    clocks = cs.summary()
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's device time is the job's time
+    ms, e2e_ms = float(t[0]), float(t[1])
+    gem = time_gemvs(b)
+    g = torch.tensor([gem["ms_per_pass"]], dtype=torch.float64, device=dev)
+    dist.all_reduce(g, op=dist.ReduceOp.MAX)
+    peak, peak_src = measured_peaks()
+    achieved = gem["bytes"] / (float(g[0]) * 1e-3) / 1e9  # per GPU: this rank's shard bytes over the slowest rank's time
+    res = None
+    if rank == 0:
+        res = {
+            "value": K / (ms * 1e-3), "ms_per_step": ms / K, "gpu_launches": int(launches),
+            "e2e": {"value": K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 12 * world, "d2h_bytes_per_step": 8 * world},
+            "roofline": {"bound": "hbm", "kernel": "gemv (Q4_0 x Q8, decode), per GPU", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": f"{peak_src} copy bandwidth", "frac_of_nominal_8000": achieved / 8000.0,
+                         "traffic": None, "launches_per_step": gem["launches"], "algorithmic_bytes_per_step": gem["bytes"]},
+            "allreduce": tpb.describe(), "clocks": clocks,
+        }
+    tpb.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="llama3-8b")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    from amd_c_b200 import gguf
+
+    cfg = gguf.config(args.config)
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank)
+        return
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    if args.gpus > 1 and world == 1:
+        sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    res = run_ours_single(args, cfg) if world == 1 else run_ours_tp(args, cfg, rank, world)
+    if rank != 0:
+        return
+    line = {"metric": METRIC, "value": res.pop("value"), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res.pop("ms_per_step"), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 dot4 + f32 accumulate", "data": "synthetic", "config": workload_config(cfg, world)}
+    line.update(res)
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(cfg)
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

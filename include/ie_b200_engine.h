@@ -37,7 +37,7 @@ enum {
   IE_B200_OP_ATTN = 5,    /* b = attention(q = a, cache of `layer`), Q8 copy in qo       (OP_ATTN) */
   IE_B200_OP_SWIGLU = 6,  /* a = silu(a) * b, Q8 copy in qo                               (OP_SWIGLU) */
   IE_B200_OP_ARGMAX = 7,  /* b = {argmax(a), prob}                                        (OP_ARGMAX) */
-  IE_B200_OP_ALLREDUCE = 8, /* a (n floats per token) is summed over the ranks by the caller: the
+  IE_B200_OP_ALLREDUCE = 8, /* c = c + sum over the ranks of a (n floats per token), done by the caller: the
                                engine only stops an enqueue range here (see ie_b200_engine_enqueue) */
   IE_B200_OP_ADD = 9      /* c = a + b, n floats                                          (OP_ADD) */
 };

@@ -122,3 +122,44 @@ def test_step_argument_checks(cuda):
         b.run(1, [1], 0)
     assert b.launches_per_step > 0
     b.close()
+
+
+def test_ie_run_drop_in(cuda, tmp_path):
+    """The reference's own ie-run host program (main.c, gen.c, model.c, plan.c compiled unchanged) linked with
+    src/cuda.c: `--backend gpu` prints the same greedy ids as `--backend cpu`, token by token (--dump-logits
+    forces one-token steps) and with the prompt run as a chunk. Skipped where the binary was never built."""
+    import os
+    import subprocess
+    from pathlib import Path
+
+    exe = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "ie-run-cuda"
+    if not exe.is_file():
+        pytest.skip("oracle/_ref/ie-run-cuda not built (reference tree absent at build time)")
+    cfg = gguf.make_model(gguf.config("tiny"), seed=0)
+    path = tmp_path / "tiny.gguf"
+    gguf.write_gguf(path, cfg)
+    env = {**os.environ, "IE_KV_F32": "1"}
+
+    def run(*extra):
+        r = subprocess.run([str(exe), str(path), "--tokens", "1,2,3,7,900,12", "--n", "24", "--ctx", "64", *extra], capture_output=True, text=True,
+                           timeout=300, env=env)
+        assert r.returncode == 0, r.stderr[-2000:]
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("ids:")][0]
+        return [int(t) for t in line.split()[1:]]
+
+    def dump(p):
+        rows = [ln.split() for ln in Path(p).read_text().splitlines()]
+        return [(int(r[1]), np.array(r[2:], dtype=np.float32)) for r in rows]
+
+    want = run("--backend", "cpu", "--dump-logits", str(tmp_path / "cpu.txt"))
+    got = run("--backend", "gpu", "--dump-logits", str(tmp_path / "gpu.txt"))  # --dump-logits forces one-token steps
+    lc, lg = dump(tmp_path / "cpu.txt"), dump(tmp_path / "gpu.txt")
+    for pos, ((tc, c), (tg, g)) in enumerate(zip(lc, lg)):
+        if tc != tg:  # the runs took different tokens at the previous step: it must have been a near tie on the CPU
+            top2 = np.sort(lc[pos - 1][1])[-2:]
+            assert top2[1] - top2[0] <= 2e-4 * np.abs(lc[pos - 1][1]).max(), f"tokens differ at {pos} without a near tie"
+            break
+        assert rel_err(g, c) <= REL, pos
+    assert got[:9] == want[:9]
+    chunked = run("--backend", "gpu", "--chunk", "4")  # the prompt in chunks of 4 through backend.run
+    assert chunked[:9] == want[:9]
