@@ -41,7 +41,7 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
     const uint32_t n = nb * 32u;
     float ss = 0.0f;
     for (uint32_t i = 4u * tid; i < n; i += 4u * NT) {
-      const float4 v = *reinterpret_cast<const float4 *>(a.xf + i);
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(a.xf + i));  // L2: other CTAs may just have written it
       ss = fmaf(v.x, v.x, ss), ss = fmaf(v.y, v.y, ss), ss = fmaf(v.z, v.z, ss), ss = fmaf(v.w, v.w, ss);
     }
     ss = warp_sum_all(ss);
@@ -58,7 +58,7 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
         float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
-        if (valid) x4 = *reinterpret_cast<const float4 *>(a.xf + base + j), w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
+        if (valid) x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + base + j)), w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
         v[j] = __fmul_rn(__fmul_rn(x4.x, sc), w4.x), v[j + 1] = __fmul_rn(__fmul_rn(x4.y, sc), w4.y);
         v[j + 2] = __fmul_rn(__fmul_rn(x4.z, sc), w4.z), v[j + 3] = __fmul_rn(__fmul_rn(x4.w, sc), w4.w);
         amax = fmaxf(fmaxf(amax, fabsf(v[j])), fmaxf(fabsf(v[j + 1]), fmaxf(fabsf(v[j + 2]), fabsf(v[j + 3]))));
@@ -77,8 +77,10 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
       s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
       if (valid) {
         const uint4 packed = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        (h ? A1 : A0)[b] = packed;
-        if (h == 0u) da[b] = d, as[b] = s;
+        if (A0) {  // A0 == nullptr: only the global copies are wanted (the norm tail of a producing GEMV)
+          (h ? A1 : A0)[b] = packed;
+          if (h == 0u) da[b] = d, as[b] = s;
+        }
         if (writer) {
           if (a.xn_out) {
 #pragma unroll

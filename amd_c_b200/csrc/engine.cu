@@ -2,6 +2,7 @@
 // one GPU; runs a static op list with the kernels of this library. A
 // one-token step is one CUDA-graph launch bracketed by an 8-byte upload
 // (token, position) and an 8-byte download (argmax, probability).
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -63,7 +64,8 @@ struct ie_b200_engine {
   uint32_t *attn_count = nullptr;
   void *argmax_part = nullptr;
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
-  uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out
+  uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[1]: the norm tail's arrival counter
+  int norm_mode = 0;         // 0: norm tail in the producing GEMV, 1: norm in the consuming GEMVs' prologue, 2: a kernel of its own
   uint32_t T_att = 1;
   std::vector<EMat> mats;
   std::vector<EVec> vecs;
@@ -155,7 +157,21 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
   for (uint32_t i = first; i < last; i++) {
     const ie_b200_op &o = e->ops[i];
     if (!(kind_mask & (1u << o.kind))) continue;
-    if (T == 1 && o.kind == IE_B200_OP_RMSNORM && o.qo != IE_B200_NONE && o.res == IE_B200_NONE && o.vec >= 0 && o.n % 32u == 0) {
+    // norm tail: a one-token GEMV whose result is normalised by the very next op
+    if (T == 1 && e->norm_mode == 0 && o.kind == IE_B200_OP_GEMV && i + 1 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) &&
+        (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
+      const ie_b200_op &nx = e->ops[i + 1];
+      const EMat &m = e->mats[o.mat];
+      if (nx.kind == IE_B200_OP_RMSNORM && nx.a == o.b && nx.res == IE_B200_NONE && nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
+        int r = ie_b200_gemv_norm_tail(m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)),
+                                       o.vec >= 0 ? e->vecs[o.vec].d : nullptr, static_cast<float *>(at(e, o.res, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
+                                       static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->err + 1, st);
+        if (r) return r;
+        i++;
+        continue;
+      }
+    }
+    if (T == 1 && e->norm_mode == 1 && o.kind == IE_B200_OP_RMSNORM && o.qo != IE_B200_NONE && o.res == IE_B200_NONE && o.vec >= 0 && o.n % 32u == 0) {
       uint32_t j = i + 1;
       while (j < last && e->ops[j].kind == IE_B200_OP_GEMV && e->ops[j].a == o.qo && e->ops[j].mat >= 0 && stream_ok(e->mats[e->ops[j].mat]) &&
              e->mats[e->ops[j].mat].cols == o.n && e->ops[j].b != o.a && (kind_mask & (1u << IE_B200_OP_GEMV)))
@@ -228,8 +244,9 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->attn_count, cw), "cudaMalloc(attention counters)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->attn_count, 0, cw), "cudaMemset");
   chk(cudaMalloc(&e->argmax_part, ie_b200_argmax_part_bytes(d.T_max)), "cudaMalloc(argmax partials)");
-  chk(cudaMalloc(&e->err, 4), "cudaMalloc(error word)");
-  if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 4), "cudaMemset");
+  chk(cudaMalloc(&e->err, 8), "cudaMalloc(error word)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 8), "cudaMemset");
+  if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 's' ? 2 : 0;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");
   chk(cudaEventCreate(&e->ev0), "cudaEventCreate");

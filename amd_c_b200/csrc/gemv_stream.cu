@@ -247,7 +247,7 @@ static int dispatch_stream(int kind, GsArgs &a, cudaStream_t st) {
 }
 
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, cudaStream_t st);  // gemv_direct.cu
+                const float *d_res, const ActSrc *tail, uint32_t *counter, cudaStream_t st);  // gemv_direct.cu
 
 // Which decode GEMV runs: "direct" (registers, default) or "ring" (bulk copies into shared memory); IE_B200_GEMV selects.
 static bool use_ring() {
@@ -280,7 +280,7 @@ extern "C" int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uin
   if (!use_ring()) {
     ActSrc act = {};
     act.xq = static_cast<const uint8_t *>(d_xq);
-    return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, static_cast<cudaStream_t>(stream));
+    return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
   }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
@@ -298,7 +298,7 @@ extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows
   if (!use_ring()) {
     ActSrc act = {};
     act.xf = d_x, act.norm_w = d_norm_w, act.eps = eps, act.xn_out = d_xn_out, act.xq_out = static_cast<uint8_t *>(d_xq_out);
-    return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, static_cast<cudaStream_t>(stream));
+    return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
   }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
@@ -306,4 +306,18 @@ extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows
   a.xf = d_x, a.norm_w = d_norm_w, a.eps = eps, a.xn_out = d_xn_out, a.xq_out = static_cast<uint8_t *>(d_xq_out);
   a.y = d_y, a.bias = d_bias, a.res = d_res, a.err = d_err;
   return dispatch_stream<true>(kind, a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ie_b200_gemv_norm_tail(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
+                                      const float *d_res, const float *d_norm_w, float eps, float *d_xn_out, void *d_xq_out, uint32_t *d_counter,
+                                      void *stream) {
+  if (int e = check_common("ie_b200_gemv_norm_tail", kind, d_w, rows, cols, d_y)) return e;
+  if (!d_xq || !aligned16(d_xq) || !d_norm_w || !d_counter) return fail(IE_B200_E_ARG, "ie_b200_gemv_norm_tail: NULL or misaligned pointer");
+  if (rows == 0 || rows % 32u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_norm_tail: the norm of the result needs rows %% 32 == 0 (rows = %u)", rows);
+  if ((d_xn_out && !aligned16(d_xn_out)) || (d_xq_out && !aligned16(d_xq_out)) || !aligned16(d_y))
+    return fail(IE_B200_E_ARG, "ie_b200_gemv_norm_tail: outputs must be 16-byte aligned");
+  ActSrc act = {}, tail = {};
+  act.xq = static_cast<const uint8_t *>(d_xq);
+  tail.norm_w = d_norm_w, tail.eps = eps, tail.xn_out = d_xn_out, tail.xq_out = static_cast<uint8_t *>(d_xq_out);
+  return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, &tail, d_counter, static_cast<cudaStream_t>(stream));
 }

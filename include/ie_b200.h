@@ -109,6 +109,14 @@ int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t 
                              float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, uint32_t *d_err,
                              void *stream);
 
+/* The one-token GEMV with the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285;
+ * IE_NORM_FUSE, src/model.c:1265-1293): after y = W x (+bias) (+res) is complete, the last CTA to finish writes
+ * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: one
+ * u32 in device memory, zero before the first call and left zero by every call. */
+int ie_b200_gemv_norm_tail(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
+                           const float *d_res, const float *d_norm_w, float eps, float *d_xn_out, void *d_xq_out, uint32_t *d_counter,
+                           void *stream);
+
 /* Test hook: the int32 dot of every (row, block) of a Q4_0 / Q4_K matrix
  * (Q4_K: the unsigned-nibble dot) and, for Q6_K, the two half dots
  * (dots[2 (r nb + b) + h]); what core/ie_core.h:161, :281, :385 define. */

@@ -344,3 +344,36 @@ def test_norm_gemv_stream(ora, cuda, typ, rows, cols):
     # and the same vector as the stand-alone norm kernel
     yn, qn = K.rmsnorm(dev(x.reshape(1, -1), cuda), dev(nw, cuda), 1e-5)
     assert torch.equal(qn.reshape(-1).cpu(), torch.from_numpy(xq))
+
+
+@pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 4096, 4096), (synth.GGML_Q4_0, 256, 768), (synth.GGML_Q6_K, 3584, 2048), (synth.GGML_Q4_0, 4096, 14336)])
+def test_gemv_norm_tail(ora, cuda, lib, typ, rows, cols):
+    """The GEMV whose last CTA normalises and quantises the finished result: y bit-exact, the norm within 1e-5 of
+    the oracle's, its Q8 copy exactly the quantiser of that vector, the arrival counter back at zero; twice in a row."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows + cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    nw = (1 + 0.1 * rng.standard_normal(rows)).astype(np.float32)
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for rep in range(2):
+        x = rng.standard_normal(cols).astype(np.float32)
+        res = rng.standard_normal(rows).astype(np.float32)
+        xq = ora.quant_q8(x)
+        y = dev(res.copy(), cuda)  # in place: y = res + W x
+        xn = torch.empty(rows, dtype=torch.float32, device=cuda)
+        xnq = torch.empty(40 * (rows // 32), dtype=torch.uint8, device=cuda)
+        d_xq, d_nw = dev(xq, cuda), dev(nw, cuda)  # named: a temporary would be freed (and its memory reused) before the kernel runs
+        K.check(lib.ie_b200_gemv_norm_tail(m.kind, m.data.data_ptr(), rows, cols, d_xq.data_ptr(), y.data_ptr(), None, y.data_ptr(),
+                                           d_nw.data_ptr(), 1e-5, xn.data_ptr(), xnq.data_ptr(), counter.data_ptr(), None))
+        want_y = ora.gemv(kind, qw, qs, rows, cols, xq, res=res)
+        assert (bits(y.cpu().numpy()) == bits(want_y)).all(), rep
+        want_n = ora.rmsnorm(want_y, nw, 1e-5)
+        got_n = xn.cpu().numpy()
+        assert np.abs(got_n - want_n).max() <= 1e-5 * np.abs(want_n).max()
+        assert (xnq.cpu().numpy() == ora.quant_q8(got_n)).all()
+        assert int(counter.item()) == 0
