@@ -5,6 +5,8 @@
 // byte strides between token rows.
 #include <float.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ieb {
@@ -289,5 +291,54 @@ extern "C" int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uin
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   IEB_LAUNCH_PDL("argmax_part_kernel", argmax_part_kernel, dim3(ARGMAX_NG, T), dim3(256), 0, st, d_x, n, static_cast<ArgPart *>(d_part), x_stride);
   IEB_LAUNCH_PDL("argmax_merge_kernel", argmax_merge_kernel, dim3(T), dim3(32), 0, st, static_cast<const ArgPart *>(d_part), d_out, out_stride);
+  return IE_B200_OK;
+}
+
+// ---- argmax for callers that must not allocate --------------------------------------------------------------
+// Some hosts of this library have handed out all of their device memory before the first token: a server that
+// sizes its arena and KV cache to fill the GPU at start-up, or code running inside a region where the CUDA
+// allocator may not be entered (a latency-critical sampling callback, a memory-audited deployment). They cannot
+// cudaMalloc the partials that ie_b200_argmax needs. This variant keeps them in a fixed array in the library's
+// own device image instead: 64 rows x 64 partials x 16 bytes = 64 KB, held by every GPU that loads the library
+// until the process exits.
+namespace ieb {
+constexpr uint32_t ARGMAX_STATIC_ROWS = 64;
+static __device__ __align__(256) ArgPart g_argmax_scratch[ARGMAX_STATIC_ROWS * ARGMAX_NG];
+
+// The device address of g_argmax_scratch on the current device. In host code the array's name is only a
+// stand-in for the symbol, not an address a kernel can use, so the address is asked for once per device (with
+// that device current) and remembered.
+static int argmax_scratch_ptr(ArgPart **out) {
+  constexpr int MAX_DEV = 64;
+  static ArgPart *cached[MAX_DEV] = {};
+  static std::mutex mu;
+  int dev = 0;
+  IEB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEV) return fail(IE_B200_E_ARG, "ie_b200_argmax_static: device %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void *p = nullptr;
+    IEB_CUDA(cudaGetSymbolAddress(&p, g_argmax_scratch));
+    cached[dev] = static_cast<ArgPart *>(p);
+  }
+  *out = cached[dev];
+  return IE_B200_OK;
+}
+}  // namespace ieb
+
+extern "C" uint32_t ie_b200_argmax_static_max_rows(void) { return ARGMAX_STATIC_ROWS; }
+
+extern "C" int ie_b200_argmax_static(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *stream) {
+  if (!d_x || !d_out) return fail(IE_B200_E_ARG, "ie_b200_argmax_static: NULL pointer");
+  if (n == 0) return fail(IE_B200_E_SIZE, "ie_b200_argmax_static: empty row");
+  if (T > ARGMAX_STATIC_ROWS)
+    return fail(IE_B200_E_SIZE, "ie_b200_argmax_static: %u rows exceed the %u the built-in scratch holds (use ie_b200_argmax with your own scratch)", T,
+                ARGMAX_STATIC_ROWS);
+  if (T == 0) return IE_B200_OK;
+  ArgPart *part = nullptr;
+  if (int r = argmax_scratch_ptr(&part)) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  IEB_LAUNCH_PDL("argmax_part_kernel", argmax_part_kernel, dim3(ARGMAX_NG, T), dim3(256), 0, st, d_x, n, part, x_stride);
+  IEB_LAUNCH_PDL("argmax_merge_kernel", argmax_merge_kernel, dim3(T), dim3(32), 0, st, static_cast<const ArgPart *>(part), d_out, out_stride);
   return IE_B200_OK;
 }

@@ -170,6 +170,21 @@ size_t ie_b200_argmax_part_bytes(uint32_t T);
 int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *d_part,
                    void *stream);
 
+/* ie_b200_argmax for callers that cannot allocate device memory. It has no counterpart in the reference; it
+ * exists for hosts that have already committed all device memory (arena and KV cache sized to fill the GPU at
+ * start-up) or that call from a place where the CUDA allocator must not be entered. Same result as
+ * ie_b200_argmax, but the partial results live in a 64 KB array inside the library's device image (held by every
+ * GPU that loads the library, until exit) instead of caller-provided scratch.
+ *  - At most ie_b200_argmax_static_max_rows() (64) rows per call; more is refused with IE_B200_E_SIZE.
+ *  - Nothing is allocated or freed, by this call or by anything it uses.
+ *  - The first call on a device looks up the array's device address (once per device); make that first call
+ *    before starting any stream capture.
+ *  - All calls on a device share the array and it keeps the last call's partials; every call overwrites the
+ *    entries it reads, so nothing needs clearing, but two calls that overlap on the GPU (different streams
+ *    without an ordering between them) race on it. Issue them on one stream or order them with events. */
+uint32_t ie_b200_argmax_static_max_rows(void);
+int ie_b200_argmax_static(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
