@@ -64,13 +64,13 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
         amax = fmaxf(fmaxf(amax, fabsf(v[j])), fmaxf(fabsf(v[j + 1]), fmaxf(fabsf(v[j + 2]), fabsf(v[j + 3]))));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));  // the other half of the block
-      const float d = __fdiv_rn(amax, 127.0f);
+      const float d = __fdiv_rn(amax, 127.0f), rinv = __frcp_rn(d);
       uint32_t pk[4] = {0u, 0u, 0u, 0u};
       int s = 0;
 #pragma unroll
       for (int j = 0; j < 16; j++) {
         int q = 0;
-        if (d != 0.0f) q = (int)roundf(__fdiv_rn(v[j], d));
+        if (d != 0.0f) q = q8_round(v[j], d, rinv);
         s += q;
         pk[j >> 2] |= (uint32_t)(q & 255) << (8 * (j & 3));
       }

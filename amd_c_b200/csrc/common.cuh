@@ -172,6 +172,17 @@ __device__ __forceinline__ float warp_sum_all(float v) {
   return v;
 }
 
+// q = round-half-away(v / d) exactly as the CPU quantiser's IEEE division gives it, without paying for a division
+// per element: t = v * (1/d) is within 7e-5 of the rounded quotient (|t| <= 127), so away from a rounding
+// boundary (k + 0.5) by more than 2.5e-4 both round to the same integer; only the rare element near a boundary,
+// or a block with a denormal-range scale, takes the exact division. rinv = __frcp_rn(d), once per block.
+__device__ __forceinline__ int q8_round(float v, float d, float rinv) {
+  const float t = __fmul_rn(v, rinv);
+  const float f = fabsf(t) - truncf(fabsf(t));
+  if (!(d > 1e-30f) || fabsf(f - 0.5f) < 2.5e-4f) return (int)roundf(__fdiv_rn(v, d));
+  return (int)roundf(t);
+}
+
 // Q8 of one block of 32 floats held one per lane: writes q, d, asum of block
 // b into a Q8 buffer of nb blocks. d = amax / 127 and q = round-half-away(x /
 // d) with IEEE division, as the CPU quantiser.
@@ -179,7 +190,7 @@ __device__ __forceinline__ void quant_block_warp(float x, uint8_t *q, uint32_t n
   const float amax = warp_max(fabsf(x));
   const float d = __fdiv_rn(amax, 127.0f);
   int v = 0;
-  if (d != 0.0f) v = (int)roundf(__fdiv_rn(x, d));
+  if (d != 0.0f) v = q8_round(x, d, __frcp_rn(d));
   int s = v;
   for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
   ((int8_t *)q)[32u * b + lane] = (int8_t)v;

@@ -64,7 +64,7 @@ struct ie_b200_engine {
   uint32_t *attn_count = nullptr;
   void *argmax_part = nullptr;
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
-  uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[1]: the norm tail's arrival counter
+  uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[2..3]: the GEMVs' work and arrival counters
   int norm_mode = 0;         // 0: norm tail in the producing GEMV, 1: norm in the consuming GEMVs' prologue, 2: a kernel of its own
   uint32_t T_att = 1;
   std::vector<EMat> mats;
@@ -115,7 +115,7 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       const EMat &m = e->mats[o.mat];
       const float *bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr;
       if (T == 1 && stream_ok(m))
-        return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), e->err, st);
+        return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), e->err, e->err + 2, st);
       return ie_b200_gemv(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
                           o.res_stride, st);
     }
@@ -165,7 +165,7 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       if (nx.kind == IE_B200_OP_RMSNORM && nx.a == o.b && nx.res == IE_B200_NONE && nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
         int r = ie_b200_gemv_norm_tail(m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)),
                                        o.vec >= 0 ? e->vecs[o.vec].d : nullptr, static_cast<float *>(at(e, o.res, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
-                                       static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->err + 1, st);
+                                       static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->err + 2, st);
         if (r) return r;
         i++;
         continue;
@@ -184,7 +184,7 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
           int r = ie_b200_norm_gemv_stream(m.kind, m.d, m.rows, m.cols, static_cast<float *>(at(e, o.a, 0, 0)), e->vecs[o.vec].d, e->d.eps,
                                            firstg ? static_cast<float *>(at(e, o.b, 0, 0)) : nullptr, firstg ? at(e, o.qo, 0, 0) : nullptr,
                                            static_cast<float *>(at(e, g.b, 0, 0)), g.vec >= 0 ? e->vecs[g.vec].d : nullptr,
-                                           static_cast<float *>(at(e, g.res, 0, 0)), e->err, st);
+                                           static_cast<float *>(at(e, g.res, 0, 0)), e->err, e->err + 2, st);
           if (r) return r;
         }
         i = j - 1;
@@ -244,8 +244,8 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->attn_count, cw), "cudaMalloc(attention counters)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->attn_count, 0, cw), "cudaMemset");
   chk(cudaMalloc(&e->argmax_part, ie_b200_argmax_part_bytes(d.T_max)), "cudaMalloc(argmax partials)");
-  chk(cudaMalloc(&e->err, 8), "cudaMalloc(error word)");
-  if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 8), "cudaMemset");
+  chk(cudaMalloc(&e->err, 16), "cudaMalloc(error word)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 's' ? 2 : 0;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");

@@ -14,6 +14,8 @@
 //
 // Arithmetic and order are the reference's (one warp per row, blocks
 // l, l+32, ... in order, shuffle-down tree): bit-exact with its CPU GEMV.
+#include <type_traits>
+
 #include "act_stage.cuh"
 #include "common.cuh"
 #include "gemv_blocks.cuh"
@@ -31,8 +33,8 @@ struct GdArgs {
   const float *bias, *res;
   // norm tail (optional): once every CTA has written its rows, the last CTA to finish computes
   // tail.xn_out = rmsnorm(y) * tail.norm_w and its Q8 copy tail.xq_out for the next GEMV
-  ActSrc tail;
-  uint32_t *counter;  // zero between launches
+  ActSrc tail;        // tail.norm_w == NULL: no tail
+  uint32_t *work;     // two words, zero between launches; word 1 counts the CTAs that have finished (norm tail only)
 };
 
 // R rows of one warp, U lane steps (blocks l, l+32, ... of each row) per chunk: R x U 16-byte loads per lane
@@ -51,8 +53,8 @@ __device__ __forceinline__ void gd_load(Blk<KIND, false> (&blk)[R][U], const uin
   }
 }
 
-template <int KIND, bool NORM, int R, int U>
-__global__ void __launch_bounds__(GD_THREADS, 3) gemv_direct_kernel(const GdArgs a) {
+template <int KIND, bool NORM, int R, int U, int MINB>
+__global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdArgs a) {
   extern __shared__ uint4 smem_gd[];
   const uint32_t nb = a.nb;
   uint4 *A0 = smem_gd, *A1 = smem_gd + nb;
@@ -63,18 +65,18 @@ __global__ void __launch_bounds__(GD_THREADS, 3) gemv_direct_kernel(const GdArgs
 
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // row groups of R are dealt round-robin over all warps of the grid: at any moment the grid reads one contiguous window
-  const uint32_t stride = gridDim.x * GD_WARPS * R, r_hi = a.rows;
-  uint32_t r = (blockIdx.x * GD_WARPS + warp) * R;
+  // Row groups of R are dealt round-robin over all warps of the grid, so at any moment the grid reads one
+  // contiguous window. (Handing groups out through a device counter was tried: one atomic per group on one
+  // address serialises in L2 and halved the bandwidth on large matrices.)
+  const uint32_t W = gridDim.x * GD_WARPS, groups = (a.rows + R - 1u) / R, r_hi = a.rows;
+  uint32_t grp = blockIdx.x * GD_WARPS + warp;
 
-  // the first chunk of this warp's first rows: in flight while we wait for the previous kernel
   Blk<KIND, false> first[R][U];
-  if (r < r_hi) gd_load<KIND, R, U>(first, a.w, a.rowb, r, r_hi, 0u, nb, lane);
+  if (grp < groups) gd_load<KIND, R, U>(first, a.w, a.rowb, grp * R, r_hi, 0u, nb, lane);
 
   pdl_wait();
   stage_activations<NORM, GD_WARPS>(a.act, nb, A0, A1, da, as, red, blockIdx.x == 0, [] { __syncthreads(); });
 
-  // one row group: chunk by chunk, R x U loads in flight, then the tree and the epilogue
   auto chunk = [&](const Blk<KIND, false>(&blk)[R][U], float(&acc)[R], uint32_t rr, uint32_t c) {
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -101,36 +103,32 @@ __global__ void __launch_bounds__(GD_THREADS, 3) gemv_direct_kernel(const GdArgs
       }
     }
   };
-  if (r < r_hi) {  // the first group: its first chunk is already in registers
+  // one row group; PRE: its first chunk is already in `first`
+  auto group = [&](uint32_t g, auto pre_tag) {
+    constexpr bool PRE = decltype(pre_tag)::value;
+    const uint32_t r = g * R;
     float acc[R];
 #pragma unroll
     for (int i = 0; i < R; i++) acc[i] = 0.0f;
-    chunk(first, acc, r, 0u);
-    for (uint32_t c = 32u * U; c < nb; c += 32u * U) {
+    if (PRE) chunk(first, acc, r, 0u);
+    for (uint32_t c = PRE ? 32u * U : 0u; c < nb; c += 32u * U) {
       Blk<KIND, false> blk[R][U];
       gd_load<KIND, R, U>(blk, a.w, a.rowb, r, r_hi, c, nb, lane);
       chunk(blk, acc, r, c);
     }
     finish(acc, r);
-    r += stride;
+  };
+  if (grp < groups) {
+    group(grp, std::true_type{});
+    grp += W;
   }
-  for (; r < r_hi; r += stride) {
-    float acc[R];
-#pragma unroll
-    for (int i = 0; i < R; i++) acc[i] = 0.0f;
-    for (uint32_t c = 0; c < nb; c += 32u * U) {
-      Blk<KIND, false> blk[R][U];
-      gd_load<KIND, R, U>(blk, a.w, a.rowb, r, r_hi, c, nb, lane);
-      chunk(blk, acc, r, c);
-    }
-    finish(acc, r);
-  }
-  if (a.counter) {  // the norm tail (uniform over the grid: every CTA takes this branch)
+  for (; grp < groups; grp += W) group(grp, std::false_type{});
+  if (a.work && a.tail.norm_w) {  // the norm tail: count arrivals, the last CTA normalises the finished vector
     __threadfence();  // this thread's rows are visible before the arrival is counted
     __syncthreads();
     if (threadIdx.x == 0) {
-      last = atomicAdd(a.counter, 1u) == gridDim.x - 1u;
-      if (last) *a.counter = 0u;
+      last = atomicAdd(a.work + 1, 1u) == gridDim.x - 1u;
+      if (last) a.work[0] = 0u, a.work[1] = 0u;
     }
     __syncthreads();
     if (last) {
@@ -140,35 +138,29 @@ __global__ void __launch_bounds__(GD_THREADS, 3) gemv_direct_kernel(const GdArgs
   }
 }
 
-template <int KIND, bool NORM, int R, int U>
+template <int KIND, bool NORM, int R, int U, int MINB>
 static int launch_direct(const GdArgs &a, cudaStream_t st) {
   const size_t smem = (size_t)a.nb * 40u;
-  auto k = gemv_direct_kernel<KIND, NORM, R, U>;
+  auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
-  // NORM (the activations are computed in every CTA's prologue): a persistent grid, two CTAs per SM, three for a
-  // large matrix. Otherwise R rows per warp and as many CTAs as one pass takes, capped at 8 per SM (three are
-  // resident; beyond the cap a CTA loops, which amortises its activation staging over more rows).
+  // One group per warp, capped at 8 CTAs per SM (MINB are resident; beyond the cap a CTA loops, which amortises
+  // its activation staging); a persistent grid of MINB per SM when every CTA computes the norm in its prologue.
   const unsigned need = (a.rows + R * GD_WARPS - 1) / (R * GD_WARPS);
-  unsigned grid;
-  if (NORM) {
-    const bool big = a.rowb * a.rows > (24u << 20);
-    grid = (unsigned)(sm_count() * (big ? 3 : GD_CTAS_PER_SM));
-  } else {
-    grid = (unsigned)(sm_count() * 8);
-  }
+  unsigned grid = (unsigned)(sm_count() * (NORM ? MINB : 8));
   if (grid > need) grid = need ? need : 1u;
   IEB_LAUNCH_PDL("gemv_direct_kernel", k, dim3(grid), dim3(GD_THREADS), smem, st, a);
   return IE_B200_OK;
 }
 
-// Long rows with few of them (the FFN down projection: 4096 x 14336) leave SMs short of warps at two rows per
-// warp; one row per warp with twice the lane steps in flight doubles the CTAs at the same bytes in flight.
+// Long rows with few of them (the FFN down projection: 4096 x 14336) are a chain of dependent chunks per warp at
+// two rows per warp; one row per warp with the whole row's loads in flight at once (up to 16 lane steps, 2 CTAs
+// per SM for the registers that takes) shortens the chain to one round trip per row.
 template <int KIND, bool NORM>
 static int pick_direct(const GdArgs &a, cudaStream_t st) {
   constexpr int U2 = KIND == IE_B200_MAT_Q4 ? 4 : 2;
-  const bool few_long = (a.rows + 15u) / 16u < (uint32_t)(sm_count() * 3) && a.nb >= 256u;
-  if (few_long) return launch_direct<KIND, NORM, 1, 2 * U2>(a, st);
-  return launch_direct<KIND, NORM, 2, U2>(a, st);
+  const bool few_long = a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
+  if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
+  return launch_direct<KIND, NORM, 2, U2, 3>(a, st);
 }
 
 template <bool NORM>
@@ -183,11 +175,12 @@ int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
 
 // Entry used by gemv_stream.cu's dispatcher.
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *counter, cudaStream_t st) {
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st) {
   GdArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.act = act, a.y = d_y, a.bias = d_bias, a.res = d_res;
-  if (tail) a.tail = *tail, a.tail.xf = d_y, a.counter = counter;
+  a.work = work;
+  if (tail) a.tail = *tail, a.tail.xf = d_y;
   return norm ? dispatch_direct<true>(kind, a, st) : dispatch_direct<false>(kind, a, st);
 }
 

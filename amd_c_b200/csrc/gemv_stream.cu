@@ -247,7 +247,7 @@ static int dispatch_stream(int kind, GsArgs &a, cudaStream_t st) {
 }
 
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *counter, cudaStream_t st);  // gemv_direct.cu
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st);  // gemv_direct.cu
 
 // Which decode GEMV runs: "direct" (registers, default) or "ring" (bulk copies into shared memory); IE_B200_GEMV selects.
 static bool use_ring() {
@@ -273,14 +273,14 @@ static int check_common(const char *who, int kind, const void *d_w, uint32_t row
 }
 
 extern "C" int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
-                                   const float *d_res, uint32_t *d_err, void *stream) {
+                                   const float *d_res, uint32_t *d_err, uint32_t *d_work, void *stream) {
   if (int e = check_common("ie_b200_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_xq || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_stream: activations must be a 16-byte aligned Q8 buffer");
   if (rows == 0) return IE_B200_OK;
   if (!use_ring()) {
     ActSrc act = {};
     act.xq = static_cast<const uint8_t *>(d_xq);
-    return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+    return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, nullptr, d_work, static_cast<cudaStream_t>(stream));
   }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
@@ -291,14 +291,14 @@ extern "C" int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uin
 
 extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, const float *d_norm_w,
                                         float eps, float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res,
-                                        uint32_t *d_err, void *stream) {
+                                        uint32_t *d_err, uint32_t *d_work, void *stream) {
   if (int e = check_common("ie_b200_norm_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_norm_gemv_stream: NULL pointer");
   if (rows == 0) return IE_B200_OK;
   if (!use_ring()) {
     ActSrc act = {};
     act.xf = d_x, act.norm_w = d_norm_w, act.eps = eps, act.xn_out = d_xn_out, act.xq_out = static_cast<uint8_t *>(d_xq_out);
-    return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+    return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, d_work, static_cast<cudaStream_t>(stream));
   }
   GsArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;

@@ -86,22 +86,23 @@ def gemv(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.T
     return y
 
 
-def gemv_stream(w: Mat, xq: torch.Tensor, bias=None, res=None, err: torch.Tensor | None = None) -> torch.Tensor:
-    """One-token GEMV through the bulk-copy ring (same result as gemv with one row)."""
+def gemv_stream(w: Mat, xq: torch.Tensor, bias=None, res=None, err: torch.Tensor | None = None, work: torch.Tensor | None = None) -> torch.Tensor:
+    """The one-token decode GEMV (same result as gemv with one row). work: two zeroed int32 for dynamic row scheduling."""
     y = torch.empty((1, w.rows), dtype=torch.float32, device=xq.device)
     check(_lib.load().ie_b200_gemv_stream(w.kind, w.data.data_ptr(), w.rows, w.cols, xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _p(err),
-                                          _stream()))
+                                          _p(work), _stream()))
     return y
 
 
-def norm_gemv_stream(w: Mat, x: torch.Tensor, norm_w: torch.Tensor, eps: float, bias=None, res=None, err: torch.Tensor | None = None):
+def norm_gemv_stream(w: Mat, x: torch.Tensor, norm_w: torch.Tensor, eps: float, bias=None, res=None, err: torch.Tensor | None = None,
+                     work: torch.Tensor | None = None):
     """y = W Q8(rmsnorm(x) * norm_w) with the norm folded into the GEMV; returns (y, xn, xq)."""
     n = w.cols
     y = torch.empty((1, w.rows), dtype=torch.float32, device=x.device)
     xn = torch.empty(n, dtype=torch.float32, device=x.device)
     xq = torch.empty(q8_bytes(n // 32), dtype=torch.uint8, device=x.device)
     check(_lib.load().ie_b200_norm_gemv_stream(w.kind, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), norm_w.data_ptr(), eps, xn.data_ptr(),
-                                               xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _p(err), _stream()))
+                                               xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _p(err), _p(work), _stream()))
     return y, xn, xq
 
 

@@ -98,21 +98,23 @@ int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const 
  * shared-memory ring filled by bulk asynchronous copies, and the launch uses programmatic dependent launch, so
  * the ring fills while the previous kernel of the stream still runs (the weights do not depend on it; the
  * activations are read only after the previous kernel has completed). d_err (may be NULL): a device word set to
- * 1 if a bounded wait inside the kernel ran out. Replaces ie_gemv_q4q8 / _q4kq8 / _q6kq8 at decode
+ * 1 if a bounded wait inside the kernel ran out. d_work (may be NULL): two u32 in device memory, zero before the
+ * first launch and left zero by every launch; reserved for work bookkeeping (the norm-tail variant counts finished
+ * CTAs there); launches that share them must not overlap on the GPU. Replaces ie_gemv_q4q8 / _q4kq8 / _q6kq8 at decode
  * (kernels/ie_kernels.c:310, :401, :675). */
 int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
-                        const float *d_res, uint32_t *d_err, void *stream);
+                        const float *d_res, uint32_t *d_err, uint32_t *d_work, void *stream);
 /* The same with RMSNorm + the Q8 quantiser of the f32 vector d_x (cols floats) folded into the prologue: the role
  * of the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285; src/model.c:1265-1293) moved
  * to the consumer side. d_xn_out / d_xq_out (may be NULL): the normalised vector and its Q8 copy, written once. */
 int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, const float *d_norm_w, float eps,
                              float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, uint32_t *d_err,
-                             void *stream);
+                             uint32_t *d_work, void *stream);
 
 /* The one-token GEMV with the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285;
  * IE_NORM_FUSE, src/model.c:1265-1293): after y = W x (+bias) (+res) is complete, the last CTA to finish writes
- * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: one
- * u32 in device memory, zero before the first call and left zero by every call. */
+ * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: the
+ * two work words of ie_b200_gemv_stream (required here: they also count the CTAs that have finished). */
 int ie_b200_gemv_norm_tail(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
                            const float *d_res, const float *d_norm_w, float eps, float *d_xn_out, void *d_xq_out, uint32_t *d_counter,
                            void *stream);
