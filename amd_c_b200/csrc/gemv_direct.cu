@@ -14,6 +14,7 @@
 //
 // Arithmetic and order are the reference's (one warp per row, blocks
 // l, l+32, ... in order, shuffle-down tree): bit-exact with its CPU GEMV.
+#include <cstdlib>
 #include <type_traits>
 
 #include "act_stage.cuh"
@@ -143,10 +144,10 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
   const size_t smem = (size_t)a.nb * 40u;
   auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
-  // One group per warp, capped at 8 CTAs per SM (MINB are resident; beyond the cap a CTA loops, which amortises
-  // its activation staging); a persistent grid of MINB per SM when every CTA computes the norm in its prologue.
+  // One group per warp up to a persistent grid of exactly the resident CTAs (MINB per SM), whose warps loop:
+  // measured on B200, 3 per SM gives 6.45 TB/s on a 295 MB matrix, 8 per SM 5.98, 4 per SM (1.33 waves) 5.17.
   const unsigned need = (a.rows + R * GD_WARPS - 1) / (R * GD_WARPS);
-  unsigned grid = (unsigned)(sm_count() * (NORM ? MINB : 8));
+  unsigned grid = (unsigned)(sm_count() * MINB);
   if (grid > need) grid = need ? need : 1u;
   IEB_LAUNCH_PDL("gemv_direct_kernel", k, dim3(grid), dim3(GD_THREADS), smem, st, a);
   return IE_B200_OK;
