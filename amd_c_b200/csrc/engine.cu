@@ -65,6 +65,7 @@ struct ie_b200_engine {
   void *argmax_part = nullptr;
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
   uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[2..3]: the GEMVs' work and arrival counters
+  bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
   int norm_mode = 0;         // 0: norm tail in the producing GEMV, 1: norm in the consuming GEMVs' prologue, 2: a kernel of its own
   uint32_t T_att = 1;
   std::vector<EMat> mats;
@@ -157,6 +158,19 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
   for (uint32_t i = first; i < last; i++) {
     const ie_b200_op &o = e->ops[i];
     if (!(kind_mask & (1u << o.kind))) continue;
+    // RoPE + KV store folded into the attention kernel of the same layer (one token)
+    if (T == 1 && o.kind == IE_B200_OP_ROPE_KV && i + 1 < last && e->ops[i + 1].kind == IE_B200_OP_ATTN && e->ops[i + 1].layer == o.layer &&
+        e->ops[i + 1].a == o.a && (kind_mask & (1u << IE_B200_OP_ATTN)) && !e->no_attn_fuse) {
+      const ie_b200_op &nx = e->ops[i + 1];
+      char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+      int r = ie_b200_attn_decode_fused(static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.b, 0, 0)),
+                                        static_cast<float *>(at(e, o.c, 0, 0)), kcl, vcl, e->rope_cos, e->rope_sin,
+                                        static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->scalars + e->d.T_max + 1, e->d.n_head,
+                                        e->d.n_kv, e->d.hd, e->d.neox, e->d.kv_f32, e->d.n_ctx, e->d.n_ctx, e->attn_part, e->attn_count, st);
+      if (r) return r;
+      i++;
+      continue;
+    }
     // norm tail: a one-token GEMV whose result is normalised by the very next op
     if (T == 1 && e->norm_mode == 0 && o.kind == IE_B200_OP_GEMV && i + 1 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) &&
         (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
@@ -246,6 +260,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->argmax_part, ie_b200_argmax_part_bytes(d.T_max)), "cudaMalloc(argmax partials)");
   chk(cudaMalloc(&e->err, 16), "cudaMalloc(error word)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
+  if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 's' ? 2 : 0;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");

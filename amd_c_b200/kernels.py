@@ -171,6 +171,20 @@ def attn_decode(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, pos: torch.
     return out, oq
 
 
+def attn_decode_fused(qkv: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
+                      n_head: int, n_kv: int, hd: int, neox: bool, n_ctx: int, scratch: AttnScratch, quant: bool = True):
+    """One token: qkv [(n_head + 2 n_kv) hd] un-rotated; RoPE, cache store and attention in one kernel. Returns (out, Q8 copy)."""
+    out = torch.empty((1, n_head * hd), dtype=torch.float32, device=qkv.device)
+    nbq = n_head * hd // 32
+    oq = torch.empty((1, q8_bytes(nbq)), dtype=torch.uint8, device=qkv.device) if quant else None
+    base = qkv.data_ptr()
+    check(_lib.load().ie_b200_attn_decode_fused(base, base + 4 * n_head * hd, base + 4 * (n_head + n_kv) * hd, kc.data_ptr(), vc.data_ptr(),
+                                                cos.data_ptr(), sin.data_ptr(), out.data_ptr(), _p(oq), pos.data_ptr(), n_head, n_kv, hd, int(neox),
+                                                int(kc.dtype == torch.float32), kc.shape[1], n_ctx, scratch.part.data_ptr(),
+                                                scratch.count.data_ptr(), _stream()))
+    return out, oq
+
+
 def argmax(x: torch.Tensor) -> torch.Tensor:
     """x: [T, n] f32 -> int32 [T, 2]: (index, float bits of the softmax probability of the maximum)."""
     x2 = x.reshape(-1, x.shape[-1])

@@ -164,6 +164,14 @@ int ie_b200_attn_decode(const float *d_q, const void *d_kc, const void *d_vc, fl
                         uint32_t n_head, uint32_t n_kv, uint32_t hd, int kv_f32, uint32_t kv_len, uint32_t n_ctx, uint32_t T,
                         size_t q_stride, size_t out_stride, size_t oq_stride, void *d_part, uint32_t *d_count, void *stream);
 
+/* One decode token: OP_ROPE_KV and OP_ATTN in one kernel. d_q / d_k / d_v are the un-rotated q, k and the v of the
+ * position *d_pos (the parts of the qkv buffer); q is rotated in registers (it is not written back), k is rotated
+ * and stored with v into the caches and taken into the attention from registers. Same results as ie_b200_rope_kv
+ * followed by ie_b200_attn_decode (src/cpu.c:537-546 + :301-329; ie_rope_kv + ie_attn_kv, src/hip.c:1284, :1492). */
+int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos,
+                              const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd,
+                              int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count, void *stream);
+
 /* First index of the maximum of each of T rows, and the softmax probability
  * of that maximum: OP_ARGMAX (src/cpu.c:608-614), ie_argmax
  * {x,n,out,part,count,ng} (src/hip.c:1537). out: {u32 index, f32 prob} per row.

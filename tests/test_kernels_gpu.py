@@ -254,6 +254,7 @@ def test_rope_kv_and_attention(ora, cuda, n_head, n_kv, hd, neox, kv_f32):
     dt = torch.float32 if kv_f32 else torch.float16
     kc = torch.zeros((n_kv, n_ctx, hd), dtype=dt, device=cuda)
     vc = torch.zeros_like(kc)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)  # the caches of the fused (RoPE + store + attention) kernel
     kc_ref, vc_ref = np.zeros((n_ctx, kvd), np.float32), np.zeros((n_ctx, kvd), np.float32)
     scratch = K.AttnScratch(n_head, hd, n_ctx, 1, cuda)
     d_cs, d_sn = dev(cs, cuda), dev(sn, cuda)
@@ -269,6 +270,7 @@ def test_rope_kv_and_attention(ora, cuda, n_head, n_kv, hd, neox, kv_f32):
         kc_ref[pos], vc_ref[pos] = k_ref, v_ref
         if pos in check_at:
             d = dev(qkv.reshape(1, -1), cuda)
+            d_raw = d.clone()
             K.rope_kv(d, kc, vc, d_cs, d_sn, dev(np.array([pos], np.uint32), cuda), n_head, n_kv, hd, neox, n_ctx)
             got = d.cpu().numpy()[0]
             assert (bits(got[:qd]) == bits(q_ref)).all()
@@ -280,9 +282,15 @@ def test_rope_kv_and_attention(ora, cuda, n_head, n_kv, hd, neox, kv_f32):
             assert np.abs(out - want).max() <= 1e-4 * np.abs(want).max(), pos
             assert (oq == ora.quant_q8(out)).all(), pos
             assert int(scratch.count.abs().max()) == 0  # arrival counters are left at zero
+            # the fused kernel: same cache rows bit for bit, same output as the two-kernel path to the last bit
+            out2, oq2 = K.attn_decode_fused(d_raw, kc2, vc2, d_cs, d_sn, dev(np.array([pos], np.uint32), cuda), n_head, n_kv, hd, neox, n_ctx, scratch)
+            assert torch.equal(kc2[:, pos, :], kc[:, pos, :]) and torch.equal(vc2[:, pos, :], vc[:, pos, :]), pos
+            assert (bits(out2.cpu().numpy()[0]) == bits(out)).all(), pos
+            assert (oq2.cpu().numpy()[0] == oq).all()
         else:
             kc[:, pos, :] = torch.from_numpy(k_ref.reshape(n_kv, hd)).to(cuda).to(dt)
             vc[:, pos, :] = torch.from_numpy(v_ref.reshape(n_kv, hd)).to(cuda).to(dt)
+            kc2[:, pos, :], vc2[:, pos, :] = kc[:, pos, :], vc[:, pos, :]
 
 
 def test_attention_multi_token_rows(ora, cuda):
