@@ -37,12 +37,32 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
   } else {
     // Thread t owns half-blocks t, t + NT, ...: 16 consecutive elements each, so the quantiser needs no
     // warp-wide reductions (one exchange with the neighbour lane that holds the other half) and one thread
-    // writes a whole 16-byte plane entry.
-    const uint32_t n = nb * 32u;
+    // writes a whole 16-byte plane entry. The first half-block (all of them when n <= 16 * NT) stays in
+    // registers between the sum of squares and the quantiser: one round trip to L2 instead of two.
+    const uint32_t n = nb * 32u, HB = 2u * nb;
+    float x0[16], w0[16];
+    {
+      const bool own = (uint32_t)tid < HB;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
+        if (own) {
+          x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + 16u * tid + j));  // L2: other CTAs may just have written it
+          w4 = *reinterpret_cast<const float4 *>(a.norm_w + 16u * tid + j);
+        }
+        x0[j] = x4.x, x0[j + 1] = x4.y, x0[j + 2] = x4.z, x0[j + 3] = x4.w;
+        w0[j] = w4.x, w0[j + 1] = w4.y, w0[j + 2] = w4.z, w0[j + 3] = w4.w;
+      }
+    }
     float ss = 0.0f;
-    for (uint32_t i = 4u * tid; i < n; i += 4u * NT) {
-      const float4 v = __ldcg(reinterpret_cast<const float4 *>(a.xf + i));  // L2: other CTAs may just have written it
-      ss = fmaf(v.x, v.x, ss), ss = fmaf(v.y, v.y, ss), ss = fmaf(v.z, v.z, ss), ss = fmaf(v.w, v.w, ss);
+#pragma unroll
+    for (int j = 0; j < 16; j++) ss = fmaf(x0[j], x0[j], ss);
+    for (uint32_t hb = tid + NT; hb < HB; hb += NT) {
+      float4 x4[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) x4[j] = __ldcg(reinterpret_cast<const float4 *>(a.xf + 16u * hb) + j);
+#pragma unroll
+      for (int j = 0; j < 4; j++) ss = fmaf(x4[j].x, x4[j].x, ss), ss = fmaf(x4[j].y, x4[j].y, ss), ss = fmaf(x4[j].z, x4[j].z, ss), ss = fmaf(x4[j].w, x4[j].w, ss);
     }
     ss = warp_sum_all(ss);
     if (lane == 0) red[warp] = ss;
@@ -50,18 +70,24 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
     float tot = lane < WARPS ? red[lane] : 0.0f;
     tot = warp_sum_all(tot);
     const float sc = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)n), a.eps)));
-    for (uint32_t k0 = 0; k0 < 2u * nb; k0 += NT) {  // uniform trip count: the shuffles below need every lane
+    for (uint32_t k0 = 0; k0 < HB; k0 += NT) {  // uniform trip count: the shuffles below need every lane
       const uint32_t hb = k0 + tid, b = hb >> 1, h = hb & 1u, base = 16u * hb;
-      const bool valid = hb < 2u * nb;
+      const bool valid = hb < HB;
       float v[16];
+      if (k0 != 0u) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
+          if (valid) x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + base + j)), w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
+          x0[j] = x4.x, x0[j + 1] = x4.y, x0[j + 2] = x4.z, x0[j + 3] = x4.w;
+          w0[j] = w4.x, w0[j + 1] = w4.y, w0[j + 2] = w4.z, w0[j + 3] = w4.w;
+        }
+      }
       float amax = 0.0f;
 #pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
-        if (valid) x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + base + j)), w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
-        v[j] = __fmul_rn(__fmul_rn(x4.x, sc), w4.x), v[j + 1] = __fmul_rn(__fmul_rn(x4.y, sc), w4.y);
-        v[j + 2] = __fmul_rn(__fmul_rn(x4.z, sc), w4.z), v[j + 3] = __fmul_rn(__fmul_rn(x4.w, sc), w4.w);
-        amax = fmaxf(fmaxf(amax, fabsf(v[j])), fmaxf(fabsf(v[j + 1]), fmaxf(fabsf(v[j + 2]), fabsf(v[j + 3]))));
+      for (int j = 0; j < 16; j++) {
+        v[j] = __fmul_rn(__fmul_rn(x0[j], sc), w0[j]);
+        amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));  // the other half of the block
       const float d = __fdiv_rn(amax, 127.0f), rinv = __frcp_rn(d);

@@ -53,6 +53,10 @@ struct AttnArgs {
   // and the v of this position, cs / sn the RoPE table rows of all positions
   const float *k_new, *v_new, *cs, *sn;
   int neox;
+  // The launcher guarantees that the kernel before this one in the stream lets its dependents go only after its own
+  // dependency wait, so when this kernel starts everything older than that kernel is complete: the position
+  // scalar and the cache rows of earlier steps may then be read ahead of this kernel's own wait.
+  int early_kv;
 };
 
 constexpr uint32_t ATT_MIN_SPAN = 256;  // positions a split covers at least: short contexts stay in one CTA per KV head (no merge)
@@ -61,21 +65,30 @@ constexpr uint32_t ATT_MIN_SPAN = 256;  // positions a split covers at least: sh
 __device__ __forceinline__ float rope_lo(float a, float b, float c, float s) { return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)); }
 __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)); }
 
+template <typename KV, int HD>
+struct AttGeom {
+  static constexpr int TILE_BYTES = 2 * ATT_TILE * HD * (int)sizeof(KV);  // one K tile + one V tile
+  static constexpr int NB_FIT = 200 * 1024 / TILE_BYTES;
+  static constexpr int NB = NB_FIT > 4 ? 4 : (NB_FIT < 2 ? 2 : NB_FIT);  // tile buffers: NB - 1 tiles in flight ahead of the one in use
+};
+
 template <typename KV, int HD, int G, bool FUSED>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs a) {
   constexpr int DPL = HD / 8;   // dims per lane in the q.k phase (8 lanes per position)
   constexpr int DPV = HD / 32;  // dims per lane in the p.v phase
-  constexpr int TILE = ATT_TILE;
-  constexpr int TILE_ELEMS = TILE * HD;
+  constexpr int TILE = ATT_TILE, TILE_ELEMS = TILE * HD, NB = AttGeom<KV, HD>::NB;
+  constexpr int PPW = TILE / ATT_WARPS;  // positions of a tile per warp
+  static_assert(PPW % 4 == 0, "a warp scores four positions at a time");
   extern __shared__ uint4 smem_raw[];
-  KV *kbuf = reinterpret_cast<KV *>(smem_raw);           // [2][TILE][HD]
-  KV *vbuf = kbuf + 2 * TILE_ELEMS;                      // [2][TILE][HD]
-  float *P = reinterpret_cast<float *>(vbuf + 2 * TILE_ELEMS);  // [G][TILE] scores, then probabilities
-  float *alpha = P + G * TILE;                           // [G]
-  __shared__ float run_m[8], run_l[8];
+  KV *kbuf = reinterpret_cast<KV *>(smem_raw);                          // [NB][TILE][HD]
+  KV *vbuf = kbuf + NB * TILE_ELEMS;                                     // [NB][TILE][HD]
+  float *Pw = reinterpret_cast<float *>(vbuf + NB * TILE_ELEMS);         // [warp][PPW][G] probabilities of the warp's positions
   __shared__ uint32_t is_last;
 
-  pdl_prologue();
+  tl_mark(TL_ATTN, 0);
+  pdl_launch_dependents();
+  const bool early = FUSED && a.early_kv;
+  if (!early) pdl_wait();
   const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
   const uint32_t np = *a.pos + t + 1u;
   uint32_t span = max((np + S - 1u) / S, ATT_MIN_SPAN);
@@ -85,109 +98,127 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
   const bool owns_new = FUSED && s == A - 1u;  // this CTA's span ends with the step's own position
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, grp = lane >> 3;
   const float *qt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * t) + (size_t)g * G * HD;
   const KV *kh = static_cast<const KV *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const KV *>(a.vc) + (size_t)g * a.kv_len * HD;
+  const uint32_t n_tiles = (p_hi - p_lo + TILE - 1u) / TILE;
 
-  float o[G][DPV];
+  // Tile `it` of the span into buffer it % NB: only rows that exist in the cache are copied (the step's own row
+  // arrives from registers, rows past the span are never read).
+  constexpr int PER_ROW = HD * (int)sizeof(KV) / 16;  // 16-byte pieces per row
+  auto issue = [&](uint32_t it) {
+    if (it < n_tiles) {
+      const uint32_t tile_lo = p_lo + it * TILE;
+      const uint32_t rows = min((uint32_t)TILE, p_hi - tile_lo - ((owns_new && it + 1u == n_tiles) ? 1u : 0u));
+      const char *ks = reinterpret_cast<const char *>(kh + (size_t)tile_lo * HD), *vs = reinterpret_cast<const char *>(vh + (size_t)tile_lo * HD);
+      char *kd = reinterpret_cast<char *>(kbuf + (it % NB) * TILE_ELEMS), *vd = reinterpret_cast<char *>(vbuf + (it % NB) * TILE_ELEMS);
+      for (uint32_t c = threadIdx.x; c < rows * PER_ROW; c += ATT_THREADS) {
+        __pipeline_memcpy_async(kd + (size_t)c * 16u, ks + (size_t)c * 16u, 16);
+        __pipeline_memcpy_async(vd + (size_t)c * 16u, vs + (size_t)c * 16u, 16);
+      }
+    }
+    __pipeline_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < NB - 1; i++) issue(i);
+  if (early) pdl_wait();
+  tl_mark(TL_ATTN, 1);
+
+  // ---- q of this lane for the q.k phase (rotated here when fused), the step's own K / V row
+  float qr[G][DPL];
 #pragma unroll
   for (int h = 0; h < G; h++)
 #pragma unroll
-    for (int d = 0; d < DPV; d++) o[h][d] = 0.0f;
-  if (threadIdx.x < 8) run_m[threadIdx.x] = -INFINITY, run_l[threadIdx.x] = 0.0f;
-
-  if (p_lo < p_hi) {
-    // q slices of this lane for the q.k phase
-    const int sub = lane & 7, grp = lane >> 3;
-    float qr[G][DPL];
-#pragma unroll
-    for (int h = 0; h < G; h++)
-#pragma unroll
-      for (int j = 0; j < DPL; j++) qr[h][j] = qt[h * HD + sub * DPL + j];
-    if (FUSED) {  // rotate q in registers with the table row of this position
-      const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
-      if (!a.neox) {  // pairs (2i, 2i+1): both in this lane
-#pragma unroll
-        for (int j = 0; j < DPL; j += 2) {
-          const int i = (sub * DPL + j) / 2;
-          const float c = cs[i], sv = sn[i];
-#pragma unroll
-          for (int h = 0; h < G; h++) {
-            const float x0 = qr[h][j], x1 = qr[h][j + 1];
-            qr[h][j] = rope_lo(x0, x1, c, sv), qr[h][j + 1] = rope_hi(x0, x1, c, sv);
-          }
-        }
-      } else {  // pairs (i, i + hd/2): the partner dim sits in the lane 4 further in the 8-lane group
-#pragma unroll
-        for (int j = 0; j < DPL; j++) {
-          const int dim = sub * DPL + j, i = dim < HD / 2 ? dim : dim - HD / 2;
-          const float c = cs[i], sv = sn[i];
-#pragma unroll
-          for (int h = 0; h < G; h++) {
-            const float mine = qr[h][j], other = __shfl_xor_sync(0xFFFFFFFFu, mine, 4);
-            qr[h][j] = dim < HD / 2 ? rope_lo(mine, other, c, sv) : rope_hi(other, mine, c, sv);
-          }
-        }
-      }
+    for (int j = 0; j < DPL; j += 4) {
+      const float4 v = *reinterpret_cast<const float4 *>(qt + h * HD + sub * DPL + j);
+      qr[h][j] = v.x, qr[h][j + 1] = v.y, qr[h][j + 2] = v.z, qr[h][j + 3] = v.w;
     }
-    // the step's own K and V row: rotated, written to the cache, and (below) dropped into the last tile
-    KV newk0 = KV(0.f), newk1 = KV(0.f), newv = KV(0.f);
-    int nk0 = 0, nk1 = 0;
-    if (owns_new) {
-      const uint32_t row = (np - 1u) % a.kv_len;
+  KV newk0 = KV(0.f), newk1 = KV(0.f), newv = KV(0.f);
+  int nk0 = 0, nk1 = 0;
+  if (FUSED) {
+    const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
+    float x0 = 0.f, x1 = 0.f, kc_ = 0.f, ks_ = 0.f, vn = 0.f;
+    if (owns_new) {  // issue the loads of the new row together with the table loads below
       if (threadIdx.x < HD / 2) {
         const int i = threadIdx.x;
         nk0 = a.neox ? i : 2 * i, nk1 = a.neox ? i + HD / 2 : 2 * i + 1;
-        const float x0 = a.k_new[g * HD + nk0], x1 = a.k_new[g * HD + nk1];
-        const float c = a.cs[(size_t)(np - 1u) * (HD / 2) + i], sv = a.sn[(size_t)(np - 1u) * (HD / 2) + i];
-        newk0 = KV(rope_lo(x0, x1, c, sv)), newk1 = KV(rope_hi(x0, x1, c, sv));
+        x0 = a.k_new[g * HD + nk0], x1 = a.k_new[g * HD + nk1], kc_ = cs[i], ks_ = sn[i];
+      } else if (threadIdx.x >= 128 && threadIdx.x < 128 + HD) {
+        vn = a.v_new[g * HD + (threadIdx.x - 128)];
+      }
+    }
+    if (!a.neox) {  // pairs (2i, 2i+1): both in this lane
+      float c[DPL / 2], sv[DPL / 2];
+#pragma unroll
+      for (int j = 0; j < DPL / 2; j++) c[j] = cs[sub * (DPL / 2) + j], sv[j] = sn[sub * (DPL / 2) + j];
+#pragma unroll
+      for (int j = 0; j < DPL; j += 2)
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+          const float y0 = qr[h][j], y1 = qr[h][j + 1];
+          qr[h][j] = rope_lo(y0, y1, c[j / 2], sv[j / 2]), qr[h][j + 1] = rope_hi(y0, y1, c[j / 2], sv[j / 2]);
+        }
+    } else {  // pairs (i, i + hd/2): the partner dim sits in the lane 4 further in the 8-lane group
+      float c[DPL], sv[DPL];
+      const int i0 = (sub * DPL) % (HD / 2);
+#pragma unroll
+      for (int j = 0; j < DPL; j++) c[j] = cs[i0 + j], sv[j] = sn[i0 + j];
+#pragma unroll
+      for (int j = 0; j < DPL; j++)
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+          const float mine = qr[h][j], other = __shfl_xor_sync(0xFFFFFFFFu, mine, 4);
+          qr[h][j] = sub < 4 ? rope_lo(mine, other, c[j], sv[j]) : rope_hi(other, mine, c[j], sv[j]);
+        }
+    }
+    if (owns_new) {  // rotate k, store the row in the cache; it joins the last tile from registers below
+      const uint32_t row = (np - 1u) % a.kv_len;
+      if (threadIdx.x < HD / 2) {
+        newk0 = KV(rope_lo(x0, x1, kc_, ks_)), newk1 = KV(rope_hi(x0, x1, kc_, ks_));
         KV *dst = const_cast<KV *>(kh) + (size_t)row * HD;
         dst[nk0] = newk0, dst[nk1] = newk1;
       } else if (threadIdx.x >= 128 && threadIdx.x < 128 + HD) {
-        const int i = threadIdx.x - 128;
-        newv = KV(a.v_new[g * HD + i]);
-        const_cast<KV *>(vh)[(size_t)row * HD + i] = newv;
+        newv = KV(vn);
+        const_cast<KV *>(vh)[(size_t)row * HD + (threadIdx.x - 128)] = newv;
       }
     }
+  }
+  tl_mark(TL_ATTN, 2);
 
-    constexpr int CHUNKS = TILE_ELEMS * (int)sizeof(KV) / 16;  // 16-byte pieces per tile
-    constexpr int PER_ROW = HD * (int)sizeof(KV) / 16;
-    auto issue = [&](uint32_t tile_lo, int buf) {
-      const char *ks = reinterpret_cast<const char *>(kh + (size_t)tile_lo * HD), *vs = reinterpret_cast<const char *>(vh + (size_t)tile_lo * HD);
-      char *kd = reinterpret_cast<char *>(kbuf + buf * TILE_ELEMS), *vd = reinterpret_cast<char *>(vbuf + buf * TILE_ELEMS);
-      const uint32_t rows_ok = p_hi - tile_lo - (owns_new ? 1u : 0u);  // rows past the span (and the step's own row, placed below) are zero-filled
-      for (int c = threadIdx.x; c < CHUNKS; c += ATT_THREADS) {
-        const bool ok = (uint32_t)(c / PER_ROW) < rows_ok;
-        const size_t off = ok ? (size_t)c * 16u : 0u;
-        __pipeline_memcpy_async(kd + (size_t)c * 16u, ks + off, 16, ok ? 0 : 16);
-        __pipeline_memcpy_async(vd + (size_t)c * 16u, vs + off, 16, ok ? 0 : 16);
-      }
-      __pipeline_commit();
-    };
-
-    const uint32_t n_tiles = (p_hi - p_lo + TILE - 1u) / TILE;
-    issue(p_lo, 0);
-    for (uint32_t it = 0; it < n_tiles; it++) {
-      const int buf = it & 1;
-      const uint32_t tile_lo = p_lo + it * TILE;
-      if (it + 1 < n_tiles) issue(tile_lo + TILE, buf ^ 1);
-      else __pipeline_commit();
-      __pipeline_wait_prior(1);
-      __syncthreads();
-      if (owns_new && it + 1 == n_tiles) {  // the step's own row goes into the tile from registers
-        const uint32_t pr = np - 1u - tile_lo;
-        if (threadIdx.x < HD / 2) {
-          KV *dk = kbuf + buf * TILE_ELEMS + pr * HD;
-          dk[nk0] = newk0, dk[nk1] = newk1;
-        } else if (threadIdx.x >= 128 && threadIdx.x < 128 + HD) {
-          vbuf[buf * TILE_ELEMS + pr * HD + (threadIdx.x - 128)] = newv;
-        }
-        __syncthreads();
-      }
-      // ---- scores: 8 lanes per position, each warp 8 positions of the tile
-      const KV *kt = kbuf + buf * TILE_ELEMS;
+  // ---- the span, tile by tile. Every warp keeps its own running max / sum / output over the positions it owns
+  // (PPW per tile), so the only block-wide synchronisation is the hand-over of tile buffers.
+  float o[G][DPV], run_m[G], run_l[G];
 #pragma unroll
-      for (int r = 0; r < 2; r++) {
-        const int pi = warp * 8 + r * 4 + grp;
+  for (int h = 0; h < G; h++) {
+    run_m[h] = -INFINITY, run_l[h] = 0.0f;
+#pragma unroll
+    for (int d = 0; d < DPV; d++) o[h][d] = 0.0f;
+  }
+  float *pw = Pw + warp * PPW * G;
+  for (uint32_t it = 0; it < n_tiles; it++) {
+    const int buf = it % NB;
+    const uint32_t tile_lo = p_lo + it * TILE;
+    if (owns_new && it + 1u == n_tiles) {  // nobody else writes this row of the buffer
+      const uint32_t pr = np - 1u - tile_lo;
+      if (threadIdx.x < HD / 2) {
+        KV *dk = kbuf + buf * TILE_ELEMS + pr * HD;
+        dk[nk0] = newk0, dk[nk1] = newk1;
+      } else if (threadIdx.x >= 128 && threadIdx.x < 128 + HD) {
+        vbuf[buf * TILE_ELEMS + pr * HD + (threadIdx.x - 128)] = newv;
+      }
+    }
+    __pipeline_wait_prior(NB - 2);
+    __syncthreads();          // tile `it` is complete; everybody is done with tile it - 1, whose buffer is refilled now
+    issue(it + NB - 1u);
+    tl_mark(TL_ATTN, 3);
+    const uint32_t valid = p_hi - tile_lo;  // positions of this tile that exist (>= 1)
+    if ((uint32_t)(warp * PPW) < valid) {
+      const KV *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
+      // scores: 8 lanes per position, 4 positions per round
+      float sc[PPW / 4][G];
+#pragma unroll
+      for (int r = 0; r < PPW / 4; r++) {
+        const int pi = warp * PPW + r * 4 + grp;
         float kr[DPL];
         load_slice<KV>(kt + pi * HD + sub * DPL, kr, DPL);
 #pragma unroll
@@ -198,77 +229,93 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
           d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
           d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
           d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
-          if (sub == 0) P[h * TILE + pi] = tile_lo + pi < p_hi ? d * a.scale : -INFINITY;
+          sc[r][h] = (uint32_t)pi < valid ? d * a.scale : -INFINITY;
         }
       }
-      __syncthreads();
-      // ---- running max / sum: warp h owns head h
-      if (warp < G) {
-        const float s0 = P[warp * TILE + lane], s1 = P[warp * TILE + 32 + lane];
-        const float m_old = run_m[warp], m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
-        const float e0 = expf(s0 - m_new), e1 = expf(s1 - m_new);
-        P[warp * TILE + lane] = e0, P[warp * TILE + 32 + lane] = e1;
-        const float sum = warp_sum_all(e0 + e1), al = expf(m_old - m_new);
-        if (lane == 0) run_l[warp] = run_l[warp] * al + sum, run_m[warp] = m_new, alpha[warp] = al;
-      }
-      __syncthreads();
-      // ---- p.v: warp w takes positions w, w+8, ... of the tile
-      const KV *vt = vbuf + buf * TILE_ELEMS;
+      // the warp's running softmax; position warp * PPW exists, so the new maximum is finite
 #pragma unroll
       for (int h = 0; h < G; h++) {
-        const float al = alpha[h];
+        float mx = sc[0][h];
+#pragma unroll
+        for (int r = 1; r < PPW / 4; r++) mx = fmaxf(mx, sc[r][h]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
+        const float m_new = fmaxf(run_m[h], mx), al = expf(run_m[h] - m_new);
+        float sum = 0.0f;
+#pragma unroll
+        for (int r = 0; r < PPW / 4; r++) {
+          const float pv = expf(sc[r][h] - m_new);
+          sum += pv;
+          if (sub == 0) pw[(r * 4 + grp) * G + h] = pv;
+        }
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
+        run_l[h] = run_l[h] * al + sum, run_m[h] = m_new;
 #pragma unroll
         for (int d = 0; d < DPV; d++) o[h][d] *= al;
       }
-      for (int pi = warp; pi < TILE; pi += ATT_WARPS) {
-        float vr[DPV];
-        if (DPV >= 4) {
-          load_slice<KV>(vt + pi * HD + lane * DPV, vr, DPV);
-        } else {
+      __syncwarp();
+      // p.v over the warp's positions: every lane owns DPV output dims
 #pragma unroll
-          for (int d = 0; d < DPV; d++) vr[d] = (float)vt[pi * HD + lane * DPV + d];
-        }
+      for (int j = 0; j < PPW; j++) {
+        if ((uint32_t)(warp * PPW + j) < valid) {  // uniform over the warp
+          float vr[DPV];
+          if (DPV >= 4) {
+            load_slice<KV>(vt + (warp * PPW + j) * HD + lane * DPV, vr, DPV);
+          } else {
 #pragma unroll
-        for (int h = 0; h < G; h++) {
-          const float p = P[h * TILE + pi];
+            for (int d = 0; d < DPV; d++) vr[d] = (float)vt[(warp * PPW + j) * HD + lane * DPV + d];
+          }
 #pragma unroll
-          for (int d = 0; d < DPV; d++) o[h][d] = fmaf(p, vr[d], o[h][d]);
+          for (int h = 0; h < G; h++) {
+            const float pv = pw[j * G + h];
+#pragma unroll
+            for (int d = 0; d < DPV; d++) o[h][d] = fmaf(pv, vr[d], o[h][d]);
+          }
         }
       }
-      __syncthreads();
+      __syncwarp();
     }
-    __pipeline_wait_prior(0);
   }
+  __pipeline_wait_prior(0);
   __syncthreads();
+  tl_mark(TL_ATTN, 4);
 
-  // ---- reduce the 8 warps' partial outputs (shared memory, reusing the tile buffers)
-  float *red = reinterpret_cast<float *>(smem_raw);  // [ATT_WARPS][G][HD]
+  // ---- merge the warps' (max, sum, output) in shared memory, reusing the tile buffers
+  float *red = reinterpret_cast<float *>(smem_raw);   // [ATT_WARPS][G][HD]
+  float *ml = red + ATT_WARPS * G * HD;               // [ATT_WARPS][G][2]
+  float *fin = ml + ATT_WARPS * G * 2;                // [G][HD]
 #pragma unroll
-  for (int h = 0; h < G; h++)
+  for (int h = 0; h < G; h++) {
 #pragma unroll
     for (int d = 0; d < DPV; d++) red[(warp * G + h) * HD + lane * DPV + d] = o[h][d];
+    if (lane == 0) ml[(warp * G + h) * 2] = run_m[h], ml[(warp * G + h) * 2 + 1] = run_l[h];
+  }
   __syncthreads();
-  // ---- final values of this KV head's G heads in shared memory: directly when one split held everything,
-  // else through the partials buffer, merged by the last split to arrive
+  // final values of this KV head's G heads: directly when one split held everything, else through the partials
+  // buffer, merged by the last split to arrive
   const size_t rec = HD + 2;
-  float *fin = red + ATT_WARPS * G * HD;  // [G][HD]
-  if (A == 1u) {
-    for (int e = threadIdx.x; e < G * HD; e += ATT_THREADS) {
-      float acc = 0.0f;
+  for (int e = threadIdx.x; e < G * HD; e += ATT_THREADS) {
+    const int h = e / HD;
+    float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < ATT_WARPS; w++) acc += red[w * G * HD + e];
-      fin[e] = acc * (1.0f / run_l[e / HD]);
+    for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, ml[(w * G + h) * 2]);
+    float L = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) {
+      const float wk = expf(ml[(w * G + h) * 2] - M);  // a warp without positions has max -inf: weight 0
+      L = fmaf(wk, ml[(w * G + h) * 2 + 1], L);
+      acc = fmaf(wk, red[(w * G + h) * HD + (e % HD)], acc);
     }
-  } else {
-    for (int e = threadIdx.x; e < G * HD; e += ATT_THREADS) {
-      const int h = e / HD;
-      float acc = 0.0f;
-#pragma unroll
-      for (int w = 0; w < ATT_WARPS; w++) acc += red[w * G * HD + e];
+    if (A == 1u) {
+      fin[e] = acc * (1.0f / L);
+    } else {
       float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * rec;
       pr[2 + (e % HD)] = acc;
-      if (e % HD == 0) pr[0] = run_m[h], pr[1] = run_l[h];
+      if (e % HD == 0) pr[0] = M, pr[1] = L;
     }
+  }
+  if (A > 1u) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -293,6 +340,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     }
   }
   __syncthreads();
+  tl_mark(TL_ATTN, 5);
   // ---- write out, one warp per block of 32 values (which is also a Q8 block of the output vector)
   float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
   uint8_t *oqt = a.oq ? a.oq + a.oq_stride * t : nullptr;
@@ -302,12 +350,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     ot[32 * b + lane] = v;
     if (oqt) quant_block_warp(v, oqt, nbq, g * (G * HD / 32u) + b, lane);
   }
+  tl_mark(TL_ATTN, 15);
 }
 
 template <typename KV, int HD, int G, bool FUSED>
 static int launch_attn(const AttnArgs &a, uint32_t T, cudaStream_t st) {
-  const size_t tile = (size_t)4 * ATT_TILE * HD * sizeof(KV) + (size_t)(G * ATT_TILE + 8) * sizeof(float);
-  const size_t red = (size_t)(ATT_WARPS + 1) * G * HD * sizeof(float);
+  const size_t tile = (size_t)AttGeom<KV, HD>::NB * AttGeom<KV, HD>::TILE_BYTES + (size_t)ATT_WARPS * (ATT_TILE / ATT_WARPS) * G * sizeof(float);
+  const size_t red = (size_t)((ATT_WARPS + 1) * G * HD + ATT_WARPS * G * 2) * sizeof(float);
   const size_t smem = tile > red ? tile : red;
   auto k = attn_decode_kernel<KV, HD, G, FUSED>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
@@ -328,10 +377,11 @@ static int dispatch_g(const AttnArgs &a, uint32_t G, uint32_t T, cudaStream_t st
   }
 }
 
-// Splits (grid.x): enough CTAs for about two per SM when every split is busy, spans of at least ATT_MIN_SPAN positions.
+// Splits (grid.x): about one CTA per SM when every split is busy (the tile buffers of a CTA take most of an SM's
+// shared memory), spans of at least ATT_MIN_SPAN positions.
 static uint32_t attn_splits(uint32_t n_kv, uint32_t n_ctx, uint32_t T) {
   const uint32_t by_len = (n_ctx + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;
-  uint32_t by_sm = (2u * (uint32_t)sm_count() + n_kv * T - 1u) / (n_kv * T);
+  uint32_t by_sm = ((uint32_t)sm_count() + n_kv * T - 1u) / (n_kv * T);
   if (by_sm < 1u) by_sm = 1u;
   uint32_t S = by_len < by_sm ? by_len : by_sm;
   return S ? S : 1u;
@@ -383,7 +433,7 @@ extern "C" int ie_b200_attn_decode(const float *d_q, const void *d_kc, const voi
   a.q_stride = q_stride, a.out_stride = out_stride, a.oq_stride = oq_stride;
   a.part = static_cast<float *>(d_part), a.count = d_count;
   a.scale = 1.0f / sqrtf((float)hd);
-  a.k_new = a.v_new = a.cs = a.sn = nullptr, a.neox = 0;
+  a.k_new = a.v_new = a.cs = a.sn = nullptr, a.neox = 0, a.early_kv = 0;
   return dispatch_attn<false>(a, hd, kv_f32, T, static_cast<cudaStream_t>(stream));
 }
 
@@ -391,6 +441,7 @@ extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, con
                                          const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv,
                                          uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count,
                                          void *stream) {
+  const bool early = take_hints().after_late_trigger;
   if (!d_q || !d_k || !d_v || !d_kc || !d_vc || !d_cos || !d_sin || !d_out || !d_pos || !d_part || !d_count)
     return fail(IE_B200_E_ARG, "ie_b200_attn_decode_fused: NULL pointer");
   if (n_kv == 0 || n_head % n_kv) return fail(IE_B200_E_SIZE, "ie_b200_attn_decode_fused: %u heads over %u KV heads", n_head, n_kv);
@@ -403,5 +454,6 @@ extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, con
   a.part = static_cast<float *>(d_part), a.count = d_count;
   a.scale = 1.0f / sqrtf((float)hd);
   a.k_new = d_k, a.v_new = d_v, a.cs = d_cos, a.sn = d_sin, a.neox = neox;
+  a.early_kv = early ? 1 : 0;
   return dispatch_attn<true>(a, hd, kv_f32, 1, static_cast<cudaStream_t>(stream));
 }

@@ -155,14 +155,38 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
 // folded into those GEMVs' prologues (every CTA recomputes the norm; CTA 0 of the first GEMV still writes the
 // norm's f32 and Q8 outputs for any later reader), which takes a kernel out of the dependency chain.
 static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t T, uint32_t kind_mask, cudaStream_t st) {
+  // RoPE + KV store folded into the attention kernel of the same layer (one token)?
+  auto rope_fuses = [&](uint32_t i) {
+    if (T != 1 || i + 1 >= last || e->no_attn_fuse) return false;
+    const ie_b200_op &o = e->ops[i], &nx = e->ops[i + 1];
+    return o.kind == IE_B200_OP_ROPE_KV && nx.kind == IE_B200_OP_ATTN && nx.layer == o.layer && nx.a == o.a &&
+           (kind_mask & (1u << IE_B200_OP_ROPE_KV)) && (kind_mask & (1u << IE_B200_OP_ATTN));
+  };
+  // The fused attention kernel reads the position and older cache rows ahead of its dependency wait when the
+  // kernel launched right before it is a direct GEMV told to release its dependents late (see LaunchHints).
+  bool prev_late = false;
+  struct HintScope {  // hints never outlive the call they were set for
+    ~HintScope() { set_hints(LaunchHints()); }
+  };
   for (uint32_t i = first; i < last; i++) {
     const ie_b200_op &o = e->ops[i];
     if (!(kind_mask & (1u << o.kind))) continue;
-    // RoPE + KV store folded into the attention kernel of the same layer (one token)
-    if (T == 1 && o.kind == IE_B200_OP_ROPE_KV && i + 1 < last && e->ops[i + 1].kind == IE_B200_OP_ATTN && e->ops[i + 1].layer == o.layer &&
-        e->ops[i + 1].a == o.a && (kind_mask & (1u << IE_B200_OP_ATTN)) && !e->no_attn_fuse) {
+    HintScope scope;
+    const bool was_late = prev_late;
+    prev_late = false;
+    if (T == 1 && o.kind == IE_B200_OP_GEMV && o.mat >= 0 && (size_t)o.mat < e->mats.size() && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
+        rope_fuses(i + 1)) {
+      LaunchHints hints;
+      hints.late_trigger = true;
+      set_hints(hints);
+      prev_late = true;
+    }
+    if (rope_fuses(i)) {
       const ie_b200_op &nx = e->ops[i + 1];
       char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+      LaunchHints hints;
+      hints.after_late_trigger = was_late;
+      set_hints(hints);
       int r = ie_b200_attn_decode_fused(static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.b, 0, 0)),
                                         static_cast<float *>(at(e, o.c, 0, 0)), kcl, vcl, e->rope_cos, e->rope_sin,
                                         static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->scalars + e->d.T_max + 1, e->d.n_head,

@@ -36,6 +36,7 @@ struct GdArgs {
   // norm tail (optional): once every CTA has written its rows, the last CTA to finish computes
   // tail.xn_out = rmsnorm(y) * tail.norm_w and its Q8 copy tail.xq_out for the next GEMV
   ActSrc tail;        // tail.norm_w == NULL: no tail
+  uint32_t late;      // let dependents start only after this kernel's own dependency wait (LaunchHints::late_trigger)
   uint32_t *work;     // two words, zero between launches; word 1 counts the CTAs that have finished (norm tail only)
 };
 
@@ -65,7 +66,8 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   __shared__ float red[GD_WARPS];
   __shared__ uint32_t last;
 
-  pdl_launch_dependents();
+  tl_mark(TL_GEMV, 0);
+  if (!a.late) pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Row groups of R are dealt round-robin over all warps of the grid, so at any moment the grid reads one
   // contiguous window. (Handing groups out through a device counter was tried: one atomic per group on one
@@ -76,8 +78,18 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   Blk<KIND, false> first[R][U];
   if (grp < groups) gd_load<KIND, R, U>(first, a.w, a.rowb, grp * R, r_hi, 0u, nb, lane);
 
+  // the norm weights (a constant vector) into L2 while waiting: the norm after the wait then pays one L2 round trip
+  if (NORM) {
+    for (uint32_t i = 32u * threadIdx.x; i < 32u * nb; i += 32u * GD_THREADS) prefetch_l2(a.act.norm_w + i);
+  } else if (a.tail.norm_w && blockIdx.x == 0) {
+    for (uint32_t i = 32u * threadIdx.x; i < a.rows; i += 32u * GD_THREADS) prefetch_l2(a.tail.norm_w + i);
+  }
+  tl_mark(TL_GEMV, 2);
   pdl_wait();
+  if (a.late) pdl_launch_dependents();
+  tl_mark(TL_GEMV, 1);
   stage_activations<NORM, GD_WARPS>(a.act, nb, A0, A1, da, as, red, blockIdx.x == 0, [] { __syncthreads(); });
+  tl_mark(TL_GEMV, 3);
 
   auto chunk = [&](const Blk<KIND, false>(&blk)[R][U], float(&acc)[R], uint32_t rr, uint32_t c) {
 #pragma unroll
@@ -125,6 +137,7 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
     grp += W;
   }
   for (; grp < groups; grp += W) group(grp, std::false_type{});
+  tl_mark(TL_GEMV, 4);
   if (a.work && a.tail.norm_w) {  // the norm tail: count arrivals, the last CTA normalises the finished vector
     __threadfence();  // this thread's rows are visible before the arrival is counted
     __syncthreads();
@@ -136,8 +149,10 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
     if (last) {
       __threadfence();
       stage_activations<true, GD_WARPS>(a.tail, a.rows / 32u, nullptr, nullptr, nullptr, nullptr, red, true, [] { __syncthreads(); });
+      if (threadIdx.x == 0) tl_mark_any(TL_GEMV, 5);
     }
   }
+  tl_mark(TL_GEMV, 15);
 }
 
 template <int KIND, bool NORM, int R, int U, int MINB>
@@ -180,6 +195,7 @@ int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
                 const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st) {
   GdArgs a = {};
+  a.late = take_hints().late_trigger ? 1u : 0u;
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.act = act, a.y = d_y, a.bias = d_bias, a.res = d_res;
   a.work = work;

@@ -250,7 +250,7 @@ int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const A
                 const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st);  // gemv_direct.cu
 
 // Which decode GEMV runs: "direct" (registers, default) or "ring" (bulk copies into shared memory); IE_B200_GEMV selects.
-static bool use_ring() {
+bool gemv_uses_ring() {
   static const bool ring = [] {
     const char *v = getenv("IE_B200_GEMV");
     return v && v[0] == 'r';
@@ -277,7 +277,7 @@ extern "C" int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uin
   if (int e = check_common("ie_b200_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_xq || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_stream: activations must be a 16-byte aligned Q8 buffer");
   if (rows == 0) return IE_B200_OK;
-  if (!use_ring()) {
+  if (!gemv_uses_ring()) {
     ActSrc act = {};
     act.xq = static_cast<const uint8_t *>(d_xq);
     return gemv_direct(kind, d_w, rows, cols, act, false, d_y, d_bias, d_res, nullptr, d_work, static_cast<cudaStream_t>(stream));
@@ -295,7 +295,7 @@ extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows
   if (int e = check_common("ie_b200_norm_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
   if (!d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_norm_gemv_stream: NULL pointer");
   if (rows == 0) return IE_B200_OK;
-  if (!use_ring()) {
+  if (!gemv_uses_ring()) {
     ActSrc act = {};
     act.xf = d_x, act.norm_w = d_norm_w, act.eps = eps, act.xn_out = d_xn_out, act.xq_out = static_cast<uint8_t *>(d_xq_out);
     return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, d_work, static_cast<cudaStream_t>(stream));

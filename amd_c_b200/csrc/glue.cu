@@ -18,7 +18,7 @@ __device__ __forceinline__ T *row_ptr(T *p, size_t stride, uint32_t t) {
 
 // ---- Q8 quantiser: one warp per block of 32 ----
 __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *q, uint32_t nb, size_t xs, size_t qs) {
-  pdl_prologue();
+  pdl_prologue(TL_QUANT);
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t b = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *
 
 // ---- embedding row ----
 __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t rowb, uint32_t nb, const uint32_t *tok, float *out, size_t os) {
-  pdl_prologue();
+  pdl_prologue(TL_EMBED);
   const uint32_t t = blockIdx.y;
   const uint8_t *rp = w + (size_t)tok[t] * rowb;
   float *o = row_ptr(out, os, t);
@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t 
   }
 }
 __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t cols, const uint32_t *tok, float *out, size_t os) {
-  pdl_prologue();
+  pdl_prologue(TL_EMBED);
   const uint32_t t = blockIdx.y;
   const float *rp = w + (size_t)tok[t] * cols;
   float *o = row_ptr(out, os, t);
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t
 // ---- RMSNorm (+Q8): one CTA of 1024 threads per token ----
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const float *__restrict__ w, float *y, uint32_t n, float eps, uint8_t *q,
                                                       size_t xs, size_t ys, size_t qs) {
-  pdl_prologue();
+  pdl_prologue(TL_RMSNORM);
   __shared__ float red[32];
   const uint32_t t = blockIdx.x;
   const float *xt = row_ptr(x, xs, t);
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const flo
 
 // ---- SwiGLU (+Q8): one warp per 32 elements ----
 __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, uint32_t n, uint8_t *q, size_t as, size_t qs) {
-  pdl_prologue();
+  pdl_prologue(TL_SWIGLU);
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t blk = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, u
     at[i] = v;
   }
   if (q && 32u * blk + 32u <= n) quant_block_warp(v, row_ptr(q, qs, t), n / 32u, blk, lane);
+  tl_mark(TL_SWIGLU, 15);
 }
 
 // ---- RoPE of q and k in place, then K/V of the position into the cache ----
@@ -102,7 +103,7 @@ template <typename KV>
 __global__ void __launch_bounds__(256)
 rope_kv_kernel(float *q, float *k, const float *v, KV *kc, KV *vc, const float *__restrict__ cs, const float *__restrict__ sn,
                const uint32_t *pos0, uint32_t nq, uint32_t nkv, uint32_t hd, int neox, uint32_t kv_len, size_t stride) {
-  pdl_prologue();
+  pdl_prologue(TL_ROPE);
   const uint32_t t = blockIdx.y, pos = *pos0 + t, h2 = hd / 2u;
   const uint32_t npair = (nq + nkv) * h2, total = npair + nkv * hd;
   float *qt = row_ptr(q, stride, t), *kt = row_ptr(k, stride, t);
@@ -137,7 +138,7 @@ struct ArgPart {
   uint32_t pad;
 };
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32_t n, ArgPart *part, size_t xs) {
-  pdl_prologue();
+  pdl_prologue(TL_ARGMAX);
   __shared__ float smx[8], ssum[8];
   __shared__ uint32_t sidx[8];
   const uint32_t t = blockIdx.y;
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32
   }
 }
 __global__ void __launch_bounds__(32) argmax_merge_kernel(const ArgPart *part, uint32_t *out, size_t os) {
-  pdl_prologue();
+  pdl_prologue(TL_ARGMAX_MERGE);
   const uint32_t t = blockIdx.x;
   const int lane = threadIdx.x;
   float mx = -INFINITY, sum = 0.0f;
