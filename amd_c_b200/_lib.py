@@ -78,6 +78,7 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
     "ie_b200_engine_read_rows": (_int, [_vp, _u64, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_copy_rows": (_int, [_vp, _u64, _u32, _u32, _u64, _u32, _u32, _u32, _u32, _int]),
+    "ie_b200_engine_set_collective": (_int, [_vp, _vp, _u32]),
     "ie_b200_engine_set_input": (_int, [_vp, _vp, _u32, _u32, _vp]),
     "ie_b200_engine_enqueue": (_int, [_vp, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_arena": (_vp, [_vp]),
@@ -95,6 +96,8 @@ SIGNATURES.update({
     "ie_b200_ar_handles": (_int, [_vp, _vp]),
     "ie_b200_ar_connect": (_int, [_vp, _vp]),
     "ie_b200_ar_allreduce_add": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp]),
+    "ie_b200_ar_allreduce_norm": (_int, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _u32, _vp, _vp]),
+    "ie_b200_ar_argmax": (_int, [_vp, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_destroy": (None, [_vp]),
 })
 

@@ -85,6 +85,7 @@ class Backend:
         self.lib = _lib.load()
         self.torch = torch
         self.cfg, self.n_ctx, self.T, self.tp, self.rank = cfg, n_ctx, max(1, T), tp, rank
+        self.collective = False  # set once an all-reduce state is attached to the engine (tp.py)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         if cfg.n_head % tp or cfg.n_kv % tp or cfg.ffn % (32 * tp) or cfg.vocab % tp:
             raise ValueError(f"tp={tp} does not divide heads {cfg.n_head}/{cfg.n_kv}, ffn {cfg.ffn} or vocab {cfg.vocab}")
@@ -256,8 +257,8 @@ class Backend:
     # ---- the backend interface (src/backend.h:7-49) ----------------------------
     def step(self, tok: int, pos: int, logits: np.ndarray | None = None):
         """One decode step; returns (argmax token, device milliseconds). logits: optional float32[vocab] to fill."""
-        if self.tp != 1:
-            raise _lib.IeB200Error("a tensor-parallel shard is stepped through TensorParallelBackend")
+        if self.tp != 1 and not self.collective:
+            raise _lib.IeB200Error("a tensor-parallel shard needs its collective first (TensorParallelBackend attaches it)")
         nxt, ms = _u32(0), C.c_double(0)
         lp = logits.ctypes.data_as(_vp) if logits is not None else None
         with self.torch.cuda.device(self.device):
@@ -268,8 +269,8 @@ class Backend:
         """T tokens at positions pos..pos+T-1 (a prompt chunk); returns the T argmax tokens (and probabilities)."""
         if sec != 0:
             raise _lib.IeB200Error(f"run: section {sec} is not built (only the model, section 0)")
-        if self.tp != 1:
-            raise _lib.IeB200Error("a tensor-parallel shard is run through TensorParallelBackend")
+        if self.tp != 1 and not self.collective:
+            raise _lib.IeB200Error("a tensor-parallel shard needs its collective first (TensorParallelBackend attaches it)")
         toks = np.ascontiguousarray(toks, dtype=np.uint32)
         out = np.zeros(toks.size, np.uint32)
         prob = np.zeros(toks.size, np.float32) if want_prob else None
@@ -281,8 +282,8 @@ class Backend:
     def decode(self, tok: int, pos: int, K: int):
         """K greedy tokens with the argmax fed back on the device (no host round trip per token).
         Returns (tokens uint32[K], device milliseconds)."""
-        if self.tp != 1:
-            raise _lib.IeB200Error("a tensor-parallel shard is decoded through TensorParallelBackend")
+        if self.tp != 1 and not self.collective:
+            raise _lib.IeB200Error("a tensor-parallel shard needs its collective first (TensorParallelBackend attaches it)")
         out, ms = np.zeros(K, np.uint32), C.c_double(0)
         with self.torch.cuda.device(self.device):
             check(self.lib.ie_b200_engine_decode(self.h, tok, pos, K, out.ctypes.data_as(_vp), C.byref(ms)))

@@ -18,6 +18,12 @@
 // call ahead of the slowest rank, because finishing call k needs everybody's
 // flag k. The epoch lives on the device and is advanced by the last CTA of a
 // call, so the kernel can sit in a replayed CUDA graph.
+//
+// The decode step uses two leaner kernels built on the same state (one CTA each, no fences): every 32-bit
+// payload word travels as one 64-bit store {epoch, word}, so the receiver polls the data words themselves
+// and a value is complete as soon as its epoch matches ("low-latency" slots, double-buffered by parity):
+//   ar_norm_kernel    x = x + sum over ranks of part, then RMSNorm and the Q8 copy of x for the next GEMVs;
+//   ar_argmax_kernel  the (value, global index) pairs of the ranks' local argmax, best one to every rank.
 #include <cstring>
 
 #include "common.cuh"
@@ -31,6 +37,7 @@ constexpr uint64_t AR_WAIT_NS = 2000000000ull;  // 2 s
 struct ArDev {
   float *slots[AR_MAX_RANKS];     // rank j's receive buffer: [2][world][max_n] floats
   uint32_t *flags[AR_MAX_RANKS];  // rank j's flags: [world][AR_MAX_CTAS]
+  unsigned long long *ll[AR_MAX_RANKS];  // rank j's low-latency slots: [2][world][max_n] words of {epoch << 32 | payload}
   uint32_t *epoch;                // local: number of completed calls
   uint32_t *done;                 // local: CTAs that finished the current call
   uint32_t rank, world, max_n;
@@ -100,39 +107,217 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
   }
 }
 
+
+// ---- low-latency slots: one 64-bit store / load per payload word ----
+__device__ __forceinline__ void ll_store(unsigned long long *p, uint32_t epoch, uint32_t payload) {
+  const unsigned long long v = (unsigned long long)epoch << 32 | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Four consecutive words of epoch k; false (after the time limit, or at once when *gave_up is set) if they did not all arrive.
+__device__ __forceinline__ bool ll_wait4(const unsigned long long *p, uint32_t k, uint32_t (&out)[4], bool *gave_up, uint64_t t0) {
+  for (;;) {
+    unsigned long long v[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) v[c] = ll_load(p + c);
+    bool all = true;
+#pragma unroll
+    for (int c = 0; c < 4; c++) all = all && (uint32_t)(v[c] >> 32) == k;
+#pragma unroll
+    for (int c = 0; c < 4; c++) out[c] = (uint32_t)v[c];
+    if (all) return true;
+    if (*gave_up || ar_now() - t0 > AR_WAIT_NS) {
+      *gave_up = true;
+      return false;
+    }
+  }
+}
+
+constexpr int ARN_THREADS = 1024;
+
+// One CTA: x (= res, may alias out) + the ranks' partials in rank order, then y = x * rsqrt(mean x^2 + eps) * w
+// and the Q8 copy of y (the same arithmetic as the RMSNorm kernel and the norm tail of the GEMV).
+// Thread t owns elements 4 (t + 1024 it) .. + 3; eight neighbouring threads hold one Q8 block.
+template <int ITERS>
+__global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, const float *part, const float *res, float *out, const float *norm_w, float eps,
+                                                              float *xn, uint8_t *xq, uint32_t n, uint32_t *err) {
+  __shared__ float red[32];
+  pdl_prologue(TL_ALLREDUCE);
+  const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float4 acc[ITERS], mine[ITERS], w4[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    mine[it] = acc[it] = w4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < n) {
+      mine[it] = *reinterpret_cast<const float4 *>(part + i);
+      const uint32_t pw[4] = {__float_as_uint(mine[it].x), __float_as_uint(mine[it].y), __float_as_uint(mine[it].z), __float_as_uint(mine[it].w)};
+      for (uint32_t j = 0; j < s.world; j++) {
+        if (j == s.rank) continue;
+        unsigned long long *dst = s.ll[j] + ((size_t)par * s.world + s.rank) * s.max_n + i;
+#pragma unroll
+        for (int c = 0; c < 4; c++) ll_store(dst + c, k, pw[c]);
+      }
+      acc[it] = *reinterpret_cast<const float4 *>(res + i);
+      if (norm_w) w4[it] = *reinterpret_cast<const float4 *>(norm_w + i);
+    }
+  }
+  // ---- the sum, in rank order; peers' words are polled in place
+  bool gave_up = false;
+  const uint64_t t0 = ar_now();
+  const unsigned long long *my = s.ll[s.rank] + (size_t)par * s.world * s.max_n;
+  for (uint32_t j = 0; j < s.world; j++) {
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
+      const uint32_t i = 4u * (tid + ARN_THREADS * it);
+      if (i >= n) continue;
+      float4 v = mine[it];
+      if (j != s.rank) {
+        uint32_t wv[4];
+        ll_wait4(my + (size_t)j * s.max_n + i, k, wv, &gave_up, t0);
+        v = make_float4(__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3]));
+      }
+      acc[it].x = __fadd_rn(acc[it].x, v.x), acc[it].y = __fadd_rn(acc[it].y, v.y);
+      acc[it].z = __fadd_rn(acc[it].z, v.z), acc[it].w = __fadd_rn(acc[it].w, v.w);
+    }
+  }
+  if (gave_up && err) atomicExch(err, 3u);
+  float ss = 0.0f;
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    if (i < n) *reinterpret_cast<float4 *>(out + i) = acc[it];
+    ss = fmaf(acc[it].x, acc[it].x, ss), ss = fmaf(acc[it].y, acc[it].y, ss), ss = fmaf(acc[it].z, acc[it].z, ss), ss = fmaf(acc[it].w, acc[it].w, ss);
+  }
+  if (norm_w) {
+    ss = warp_sum_all(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float tot = warp_sum_all(red[lane]);
+    const float sc = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)n), eps)));
+    const uint32_t nb = n / 32u;
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
+      const uint32_t i = 4u * (tid + ARN_THREADS * it);
+      const float v[4] = {__fmul_rn(__fmul_rn(acc[it].x, sc), w4[it].x), __fmul_rn(__fmul_rn(acc[it].y, sc), w4[it].y),
+                          __fmul_rn(__fmul_rn(acc[it].z, sc), w4[it].z), __fmul_rn(__fmul_rn(acc[it].w, sc), w4[it].w)};
+      float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
+      const float d = __fdiv_rn(amax, 127.0f), rinv = __frcp_rn(d);
+      uint32_t pk = 0u;
+      int sum = 0;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        int q = 0;
+        if (d != 0.0f) q = q8_round(v[c], d, rinv);
+        sum += q;
+        pk |= (uint32_t)(q & 255) << (8 * c);
+      }
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+      if (i < n) {
+        if (xn) *reinterpret_cast<float4 *>(xn + i) = make_float4(v[0], v[1], v[2], v[3]);
+        if (xq) {
+          *reinterpret_cast<uint32_t *>(xq + i) = pk;
+          if ((tid & 7) == 0) {
+            reinterpret_cast<float *>(xq + 32u * (size_t)nb)[i / 32u] = d;
+            reinterpret_cast<int *>(xq + 36u * (size_t)nb)[i / 32u] = sum;
+          }
+        }
+      }
+    }
+  }
+  if (tid == 0) *(volatile uint32_t *)s.epoch = k;
+}
+
+// One warp: every rank's (logit, global index) of its local argmax to every rank; the largest logit wins, ties
+// go to the smaller index (what one argmax over the whole vocabulary gives). result[0] = the winning index.
+__global__ void __launch_bounds__(32) ar_argmax_kernel(const ArDev s, const float *logits, uint32_t *result, uint32_t vocab_offset, uint32_t *err) {
+  pdl_prologue(TL_ALLREDUCE);
+  const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
+  const uint32_t lane = threadIdx.x;
+  const uint32_t li = result[0], lp = result[1];  // local index and its probability within this rank's slice
+  const float lv = logits[li];
+  if (lane < s.world && lane != s.rank) {
+    unsigned long long *dst = s.ll[lane] + ((size_t)par * s.world + s.rank) * s.max_n;
+    ll_store(dst, k, __float_as_uint(lv));
+    ll_store(dst + 1, k, li + vocab_offset);
+    ll_store(dst + 2, k, lp);
+    ll_store(dst + 3, k, 0u);
+  }
+  float v = -INFINITY, pr = 0.0f;
+  uint32_t idx = 0xFFFFFFFFu;
+  bool gave_up = false;
+  if (lane == s.rank) {
+    v = lv, idx = li + vocab_offset, pr = __uint_as_float(lp);
+  } else if (lane < s.world) {
+    uint32_t wv[4];
+    if (ll_wait4(s.ll[s.rank] + ((size_t)par * s.world + lane) * s.max_n, k, wv, &gave_up, ar_now()))
+      v = __uint_as_float(wv[0]), idx = wv[1], pr = __uint_as_float(wv[2]);
+  }
+  if (gave_up && err) atomicExch(err, 3u);
+  float bv = v;
+  uint32_t bi = idx;
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+    const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+  }
+  // softmax denominator over all slices, relative to the winning logit: a slice's own is 1 / its probability
+  float den = pr > 0.0f ? expf(v - bv) / pr : 0.0f;
+  den = warp_sum_all(den);
+  if (lane == 0) {
+    result[0] = bi;
+    result[1] = __float_as_uint(den > 0.0f ? 1.0f / den : 0.0f);
+    *(volatile uint32_t *)s.epoch = k;
+  }
+}
+
 }  // namespace ieb
 
 using namespace ieb;
 
 struct ie_b200_allreduce {
   ArDev d = {};
-  float *slots = nullptr;
-  uint32_t *flags = nullptr, *epoch = nullptr;
-  void *opened[2 * AR_MAX_RANKS] = {};
+  char *base = nullptr;  // one allocation (one IPC handle): slots, flags, low-latency slots
+  size_t off_flags = 0, off_ll = 0;
+  uint32_t *epoch = nullptr;
+  void *opened[AR_MAX_RANKS] = {};
   int n_opened = 0;
   bool connected = false;
 };
+
+static inline size_t up256(size_t n) { return (n + 255u) & ~(size_t)255u; }
 
 extern "C" int ie_b200_ar_create(uint32_t rank, uint32_t world, uint32_t max_floats, ie_b200_allreduce **out) {
   if (!out || world < 1 || world > (uint32_t)AR_MAX_RANKS || rank >= world || max_floats == 0 || max_floats % 4u)
     return fail(IE_B200_E_ARG, "ie_b200_ar_create: rank %u of %u, %u floats (1..8 ranks, a multiple of 4 floats)", rank, world, max_floats);
   ie_b200_allreduce *a = new ie_b200_allreduce();
-  const size_t sb = (size_t)2 * world * max_floats * 4u, fb = (size_t)world * AR_MAX_CTAS * 4u;
-  cudaError_t e = cudaMalloc(&a->slots, sb);
-  if (e == cudaSuccess) e = cudaMalloc(&a->flags, fb);
+  const size_t sb = up256((size_t)2 * world * max_floats * 4u), fb = up256((size_t)world * AR_MAX_CTAS * 4u);
+  const size_t lb = up256((size_t)2 * world * max_floats * 8u);
+  a->off_flags = sb, a->off_ll = sb + fb;
+  cudaError_t e = cudaMalloc(&a->base, sb + fb + lb);
   if (e == cudaSuccess) e = cudaMalloc(&a->epoch, 8);
-  if (e == cudaSuccess) e = cudaMemset(a->slots, 0, sb);
-  if (e == cudaSuccess) e = cudaMemset(a->flags, 0, fb);
+  if (e == cudaSuccess) e = cudaMemset(a->base, 0, sb + fb + lb);
   if (e == cudaSuccess) e = cudaMemset(a->epoch, 0, 8);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
-    cudaFree(a->slots), cudaFree(a->flags), cudaFree(a->epoch);
+    cudaFree(a->base), cudaFree(a->epoch);
     delete a;
     return cuda_fail(e, "ie_b200_ar_create");
   }
   a->d.rank = rank, a->d.world = world, a->d.max_n = max_floats;
   a->d.epoch = a->epoch, a->d.done = a->epoch + 1;
-  a->d.slots[rank] = a->slots, a->d.flags[rank] = a->flags;
+  a->d.slots[rank] = reinterpret_cast<float *>(a->base), a->d.flags[rank] = reinterpret_cast<uint32_t *>(a->base + a->off_flags);
+  a->d.ll[rank] = reinterpret_cast<unsigned long long *>(a->base + a->off_ll);
   a->connected = world == 1;
   *out = a;
   return IE_B200_OK;
@@ -140,25 +325,28 @@ extern "C" int ie_b200_ar_create(uint32_t rank, uint32_t world, uint32_t max_flo
 
 extern "C" int ie_b200_ar_handles(ie_b200_allreduce *a, void *h_out128) {
   if (!a || !h_out128) return fail(IE_B200_E_ARG, "ie_b200_ar_handles: NULL argument");
-  cudaIpcMemHandle_t h[2];
-  IEB_CUDA(cudaIpcGetMemHandle(&h[0], a->slots));
-  IEB_CUDA(cudaIpcGetMemHandle(&h[1], a->flags));
-  static_assert(sizeof(h) == 128, "two IPC handles are 128 bytes");
-  memcpy(h_out128, h, sizeof h);
+  cudaIpcMemHandle_t h;
+  IEB_CUDA(cudaIpcGetMemHandle(&h, a->base));
+  static_assert(sizeof(h) == 64, "an IPC handle is 64 bytes");
+  memset(h_out128, 0, 128);
+  memcpy(h_out128, &h, sizeof h);
   return IE_B200_OK;
 }
 
 extern "C" int ie_b200_ar_connect(ie_b200_allreduce *a, const void *h_all) {
   if (!a || !h_all) return fail(IE_B200_E_ARG, "ie_b200_ar_connect: NULL argument");
-  const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(h_all);
+  if (a->connected) return IE_B200_OK;
+  const char *blobs = static_cast<const char *>(h_all);
   for (uint32_t j = 0; j < a->d.world; j++) {
     if (j == a->d.rank) continue;
-    void *ps = nullptr, *pf = nullptr;
-    IEB_CUDA(cudaIpcOpenMemHandle(&ps, h[2 * j], cudaIpcMemLazyEnablePeerAccess));
-    a->opened[a->n_opened++] = ps;
-    IEB_CUDA(cudaIpcOpenMemHandle(&pf, h[2 * j + 1], cudaIpcMemLazyEnablePeerAccess));
-    a->opened[a->n_opened++] = pf;
-    a->d.slots[j] = static_cast<float *>(ps), a->d.flags[j] = static_cast<uint32_t *>(pf);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, blobs + (size_t)128 * j, sizeof h);
+    void *pb = nullptr;
+    IEB_CUDA(cudaIpcOpenMemHandle(&pb, h, cudaIpcMemLazyEnablePeerAccess));
+    a->opened[a->n_opened++] = pb;
+    char *b = static_cast<char *>(pb);
+    a->d.slots[j] = reinterpret_cast<float *>(b), a->d.flags[j] = reinterpret_cast<uint32_t *>(b + a->off_flags);
+    a->d.ll[j] = reinterpret_cast<unsigned long long *>(b + a->off_ll);
   }
   a->connected = true;
   return IE_B200_OK;
@@ -177,10 +365,37 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
   return IE_B200_OK;
 }
 
+extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                                         uint32_t n, uint32_t *d_err, void *stream) {
+  if (!a || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: NULL argument");
+  if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_allreduce_norm: peers not connected");
+  if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_THREADS)
+    return fail(IE_B200_E_SIZE, "ie_b200_ar_allreduce_norm: %u floats (a multiple of 32, at most %u)", n, a->d.max_n < 16384u ? a->d.max_n : 16384u);
+  if (!aligned16(d_part) || !aligned16(d_x) || !aligned16(d_norm_w) || (d_xn && !aligned16(d_xn)) || (d_xq && !aligned16(d_xq)))
+    return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: 16-byte alignment");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t *xq = static_cast<uint8_t *>(d_xq);
+  const uint32_t iters = (n + 4u * ARN_THREADS - 1u) / (4u * ARN_THREADS);
+  switch (iters) {
+    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
+    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
+    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
+  }
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {
+  if (!a || !d_logits || !d_result) return fail(IE_B200_E_ARG, "ie_b200_ar_argmax: NULL argument");
+  if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_argmax: peers not connected");
+  IEB_LAUNCH_PDL("ar_argmax_kernel", ar_argmax_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), a->d, d_logits, d_result, vocab_offset,
+                 d_err);
+  return IE_B200_OK;
+}
+
 extern "C" void ie_b200_ar_destroy(ie_b200_allreduce *a) {
   if (!a) return;
   cudaDeviceSynchronize();
   for (int i = 0; i < a->n_opened; i++) cudaIpcCloseMemHandle(a->opened[i]);
-  cudaFree(a->slots), cudaFree(a->flags), cudaFree(a->epoch);
+  cudaFree(a->base), cudaFree(a->epoch);
   delete a;
 }

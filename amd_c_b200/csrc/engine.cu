@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "ie_b200_engine.h"
+#include "ie_b200_tp.h"
 
 namespace ieb {
 
@@ -68,6 +69,8 @@ struct ie_b200_engine {
   bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
   int norm_mode = 0;         // 0: norm tail in the producing GEMV, 1: norm in the consuming GEMVs' prologue, 2: a kernel of its own
   uint32_t T_att = 1;
+  ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
+  uint32_t vocab_off = 0;           // first vocabulary row of this shard's output head
   std::vector<EMat> mats;
   std::vector<EVec> vecs;
   std::vector<ie_b200_op> ops;
@@ -139,9 +142,23 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       return IE_B200_OK;
     }
     case IE_B200_OP_SWIGLU: return ie_b200_swiglu(static_cast<float *>(a), static_cast<float *>(b), o.n, qo, T, o.a_stride, o.qo_stride, st);
-    case IE_B200_OP_ARGMAX:
-      return ie_b200_argmax(static_cast<float *>(a), o.n, static_cast<uint32_t *>(b), T, o.a_stride, o.b_stride, e->argmax_part, st);
-    case IE_B200_OP_ALLREDUCE: return IE_B200_OK;  // the caller's collective
+    case IE_B200_OP_ARGMAX: {
+      if (int r = ie_b200_argmax(static_cast<float *>(a), o.n, static_cast<uint32_t *>(b), T, o.a_stride, o.b_stride, e->argmax_part, st)) return r;
+      if (!e->ar) return IE_B200_OK;
+      for (uint32_t t = 0; t < T; t++)  // sharded head: the ranks' local winners, best one to everybody
+        if (int r = ie_b200_ar_argmax(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0 + t)), static_cast<uint32_t *>(at(e, o.b, o.b_stride, t0 + t)),
+                                      e->vocab_off, e->err, st))
+          return r;
+      return IE_B200_OK;
+    }
+    case IE_B200_OP_ALLREDUCE: {
+      if (!e->ar) return IE_B200_OK;  // no collective attached: the caller serves these stops between enqueue calls
+      for (uint32_t t = 0; t < T; t++) {
+        float *x = static_cast<float *>(at(e, o.c, o.c_stride, t0 + t));
+        if (int r = ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0 + t)), x, x, o.n, e->err, st)) return r;
+      }
+      return IE_B200_OK;
+    }
     case IE_B200_OP_ADD:
       add_kernel<<<dim3((o.n + 255u) / 256u, T), 256, 0, st>>>(static_cast<float *>(a), static_cast<float *>(b), static_cast<float *>(c), o.n,
                                                               o.a_stride, o.b_stride, o.c_stride);
@@ -194,6 +211,17 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       if (r) return r;
       i++;
       continue;
+    }
+    // tensor parallel: all-reduce + residual add + the RMSNorm that follows, one kernel
+    if (T == 1 && e->ar && o.kind == IE_B200_OP_ALLREDUCE && i + 1 < last && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
+      const ie_b200_op &nx = e->ops[i + 1];
+      if (nx.kind == IE_B200_OP_RMSNORM && nx.a == o.c && nx.res == IE_B200_NONE && nx.vec >= 0 && nx.n == o.n && o.n % 32u == 0 && o.n <= 16384u) {
+        int r = ie_b200_ar_allreduce_norm(e->ar, static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
+                                          static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), o.n, e->err, st);
+        if (r) return r;
+        i++;
+        continue;
+      }
     }
     // norm tail: a one-token GEMV whose result is normalised by the very next op
     if (T == 1 && e->norm_mode == 0 && o.kind == IE_B200_OP_GEMV && i + 1 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) &&
@@ -426,6 +454,13 @@ extern "C" int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, 
   }
   e->ops.assign(ops, ops + n_ops);
   e->i_head = i_head;
+  drop_graph(e);
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_set_collective(ie_b200_engine *e, ie_b200_allreduce *ar, uint32_t vocab_offset) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_set_collective: NULL engine");
+  e->ar = ar, e->vocab_off = vocab_offset;
   drop_graph(e);
   return IE_B200_OK;
 }

@@ -1,30 +1,21 @@
 """Tensor-parallel decode: one process per GPU (torch.distributed for the rendezvous), each with a Backend
-shard (backend.py, tp > 1). The op list of a shard stops at ALLREDUCE ops; this module runs the segments in
-between and serves each stop with the peer-memory all-reduce kernel of libie_b200 (csrc/allreduce.cu): the
-partial of the K-split GEMV is pushed to every rank over NVLink and summed in rank order onto the residual stream. The output head is split by vocabulary rows: every rank takes its
-local argmax and the (value, index) pairs are all-gathered; ties go to the smaller index, as one argmax would.
-
-A step is captured once into a CUDA graph per rank (segments, all-reduce kernels, the small selection ops) and
-replayed; token and position travel through the engine's device scalars.
+shard (backend.py, tp > 1). This module creates the peer-memory all-reduce state of libie_b200
+(csrc/allreduce.cu), exchanges the CUDA-IPC handles, and attaches the state to the shard's engine. From then
+on the engine serves the shard's ALLREDUCE stops itself: after every K-split GEMV (attn_output, ffn_down) one
+kernel pushes the partial to every rank over NVLink, sums in rank order onto the residual stream and applies
+the RMSNorm + Q8 that follows; after the vocabulary-split output head the ranks exchange their local argmax
+(value, index) and every rank keeps the best, ties to the smaller index, as one argmax would. A step is the
+engine's own CUDA graph, the same on every rank; nothing of it runs in Python.
 """
 from __future__ import annotations
 
 import ctypes as C
 
-import numpy as np
-
 from . import _lib
 from ._lib import check
-from .backend import OP_ALLREDUCE, Backend
+from .backend import Backend
 
 _vp = C.c_void_p
-
-
-class _DevView:
-    """A device address range as a __cuda_array_interface__ object, so torch can wrap engine memory."""
-
-    def __init__(self, ptr: int, n: int, typestr: str):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
 
 
 class TensorParallelBackend:
@@ -39,7 +30,6 @@ class TensorParallelBackend:
         self.lib = _lib.load()
         self.dev = shard.device
         c = shard.cfg
-        # ---- the all-reduce state: create, exchange IPC handles, connect
         h = _vp()
         with torch.cuda.device(self.dev):
             check(self.lib.ie_b200_ar_create(self.rank, self.world, c.dim, C.byref(h)))
@@ -51,104 +41,39 @@ class TensorParallelBackend:
             dist.all_gather_into_tensor(allb, mine, group=group)
             raw = (C.c_uint8 * (128 * self.world)).from_buffer_copy(allb.cpu().numpy().tobytes())
             check(self.lib.ie_b200_ar_connect(self.ar, raw))
-        # ---- torch views of engine memory
-        arena = self.lib.ie_b200_engine_arena(shard.h)
-        self.arena_ptr = arena
-        Tm = shard.T
-        self.scalars = torch.as_tensor(_DevView(self.lib.ie_b200_engine_input_scalars(shard.h), 2 * Tm + 1, "<i4"), device=self.dev)
-        lb, ab = shard.bufs["logits"], shard.bufs["argmax"]
-        self.logits = torch.as_tensor(_DevView(arena + lb.off, shard.vocab_l, "<f4"), device=self.dev)
-        self.argmax = torch.as_tensor(_DevView(arena + ab.off, 2, "<i4"), device=self.dev)
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        # ---- segments between the ALLREDUCE stops
-        self.stops = [i for i, o in enumerate(shard.ops) if o.kind == OP_ALLREDUCE]
-        self.hist = torch.zeros(4096, dtype=torch.int64, device=self.dev)
-        self.count = torch.zeros(1, dtype=torch.int64, device=self.dev)
-        self.pair_v = torch.empty(self.world, dtype=torch.float32, device=self.dev)
-        self.pair_i = torch.empty(self.world, dtype=torch.int64, device=self.dev)
-        self.stream = torch.cuda.Stream(device=self.dev)
-        self.graph = None
-        self.launches_per_step = 0
+            check(self.lib.ie_b200_engine_set_collective(shard.h, self.ar, self.rank * shard.vocab_l))
+        shard.collective = True
 
-    # ---- one step's work on the current stream (capturable)
-    def _enqueue_step(self):
-        torch, dist, b = self.torch, self.dist, self.b
-        st = torch.cuda.current_stream(self.dev).cuda_stream
-        first = 0
-        for s in self.stops + [len(b.ops)]:
-            check(self.lib.ie_b200_engine_enqueue(b.h, first, s, 1, st))
-            if s < len(b.ops):
-                o = b.ops[s]
-                part, x = self.arena_ptr + o.a, self.arena_ptr + o.c  # x = x + sum over ranks of part
-                check(self.lib.ie_b200_ar_allreduce_add(self.ar, part, x, x, o.n, self.err.data_ptr(), st))
-            first = s + 1
-        # the global argmax: (value, global index) of every rank, ties to the smaller index
-        idx = self.argmax[0:1].to(torch.int64)
-        val = self.logits.index_select(0, idx)
-        dist.all_gather_into_tensor(self.pair_v, val, group=self.group)
-        dist.all_gather_into_tensor(self.pair_i, idx + self.rank * b.vocab_l, group=self.group)
-        best = torch.where(self.pair_v == self.pair_v.max(), self.pair_i, torch.full_like(self.pair_i, 1 << 40)).min().reshape(1)
-        # feed it back: next token, positions + 1, history
-        self.hist.index_copy_(0, self.count % 4096, best)
-        self.count += 1
-        self.scalars[0:1] = best.to(torch.int32)
-        self.scalars[b.T:] += 1
-
-    def _ensure_graph(self, tok: int, pos: int):
-        if self.graph is not None:
-            return
-        torch = self.torch
-        with torch.cuda.device(self.dev), torch.cuda.stream(self.stream):
-            self._set_input(tok, pos)  # the warm pass is the real first step: what it writes (KV row) is what the replay rewrites
-            before = self.lib.ie_b200_launch_count()
-            self._enqueue_step()  # uncaptured: communicator set-up and other lazy initialisations happen outside the capture
-            self.launches_per_step = int(self.lib.ie_b200_launch_count() - before)
-            self.stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=self.stream):
-                self._enqueue_step()
-            self.graph = g
-
-    def _set_input(self, tok: int, pos: int):
-        t = np.array([tok], np.uint32)
-        check(self.lib.ie_b200_engine_set_input(self.b.h, t.ctypes.data_as(_vp), 1, pos, self.stream.cuda_stream))
-        self.count.zero_()
-
-    def _check_err(self):
-        e = int(self.err.item())
-        if e:
-            raise _lib.IeB200Error(f"a kernel gave up a bounded wait (device error word {e}): a rank is missing or stalled")
+    def _align(self):
+        """The kernels' waits for a peer are bounded (2 s): make sure no rank launches long before the others."""
+        with self.torch.cuda.device(self.dev):
+            self.dist.barrier(group=self.group)
 
     def step(self, tok: int, pos: int) -> int:
         """backend.step for the sharded model: host token in, host token out (identical on every rank)."""
-        return int(self.decode(tok, pos, 1)[0])
+        self._align()
+        return self.b.step(tok, pos)[0]
 
     def decode(self, tok: int, pos: int, K: int, timed: bool = False):
         """K greedy tokens, the argmax fed back on the device. timed: also return the device milliseconds."""
-        torch = self.torch
-        if K > 4096:
-            raise ValueError("at most 4096 steps per call")
-        self._ensure_graph(tok, pos)
-        with torch.cuda.device(self.dev), torch.cuda.stream(self.stream):
-            self._set_input(tok, pos)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(self.stream)
-            for _ in range(K):
-                self.graph.replay()
-            e1.record(self.stream)
-            self.stream.synchronize()
-            out = self.hist[:K].cpu().numpy().astype(np.uint32)
-        self._check_err()
-        return (out, e0.elapsed_time(e1)) if timed else out
+        self._align()
+        out, ms = self.b.decode(tok, pos, K)
+        return (out, ms) if timed else out
+
+    @property
+    def launches_per_step(self) -> int:
+        return self.b.launches_per_step
 
     def describe(self) -> dict:
-        return {"kind": "one-shot push over peer memory (CUDA IPC, plain stores over NVLink), summed in rank order, bounded waits",
-                "calls_per_step": len(self.stops), "floats_per_call": self.b.cfg.dim, "launches_per_step": self.launches_per_step}
+        n_stops = sum(1 for o in self.b.ops if o.kind == 8)
+        return {"kind": "one kernel per stop: push over peer memory (CUDA IPC, 64-bit {epoch, word} stores over NVLink, polled in place), "
+                        "sum in rank order + residual + RMSNorm + Q8; bounded waits",
+                "calls_per_step": n_stops + 1, "floats_per_call": self.b.cfg.dim, "launches_per_step": self.launches_per_step}
 
     def close(self):
-        self.graph = None
         self.torch.cuda.synchronize(self.dev)
         if self.ar:
+            check(self.lib.ie_b200_engine_set_collective(self.b.h, None, 0))
             self.lib.ie_b200_ar_destroy(self.ar)
             self.ar = None
         self.b.close()

@@ -89,6 +89,13 @@ int ie_b200_engine_set_rope(ie_b200_engine *e, const float *h_cos, const float *
 /* The op list; i_head = first op of the output head (graph.i_head): a run with last_only executes the
  * ops before it for all T tokens and the head for the last token only (src/hip.c:1560-1563). */
 int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, uint32_t n_ops, uint32_t i_head);
+/* Tensor parallel (no reference counterpart: the reference drives one device): attach the connected
+ * all-reduce state of include/ie_b200_tp.h. The engine then serves its ALLREDUCE ops itself (fused with the
+ * RMSNORM that follows where it can) and, after ARGMAX, exchanges the ranks' local winners, so step / decode /
+ * run return the argmax over the whole vocabulary on every rank; vocab_offset = first vocabulary row of this
+ * shard's output head. Every rank must make the same calls in the same order. The state is not owned. */
+struct ie_b200_allreduce;
+int ie_b200_engine_set_collective(ie_b200_engine *e, struct ie_b200_allreduce *ar, uint32_t vocab_offset);
 
 /* backend.step (src/backend.h:10): one token at position pos; h_logits (vocab floats) may be NULL;
  * *next = the argmax token; *ms (may be NULL) = device time of the step. Host buffers in and out. */

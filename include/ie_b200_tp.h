@@ -21,7 +21,7 @@ typedef struct ie_b200_allreduce ie_b200_allreduce;
 
 /* Receive buffers for vectors of up to max_floats (a multiple of 4) on the current device; world <= 8. */
 int ie_b200_ar_create(uint32_t rank, uint32_t world, uint32_t max_floats, ie_b200_allreduce **out);
-/* This rank's 128-byte IPC handle blob (receive buffer, flags). */
+/* This rank's 128-byte IPC handle blob (one allocation: receive buffers, flags; the rest is zero). */
 int ie_b200_ar_handles(ie_b200_allreduce *a, void *h_out128);
 /* h_all: the world blobs in rank order (world * 128 bytes). Not needed when world == 1. */
 int ie_b200_ar_connect(ie_b200_allreduce *a, const void *h_all);
@@ -30,6 +30,18 @@ int ie_b200_ar_connect(ie_b200_allreduce *a, const void *h_all);
  * alias res. */
 int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_out, uint32_t n, uint32_t *d_err,
                              void *stream);
+/* The decode step's form, one kernel of one CTA: x = x + sum over ranks of part (rank order), then
+ * xn = x * rsqrt(mean x^2 + eps) * norm_w and its Q8 copy xq (layout of ie_b200_quant_q8) for the GEMVs that
+ * follow: the all-reduce, the residual add and the RMSNorm of src/model.c's layer loop in one launch. n is a
+ * multiple of 32, at most min(max_floats, 16384). d_xn / d_xq may be NULL. Values travel as 64-bit
+ * {epoch, word} stores that the receiver polls in place, so there is no flag round and no fence. */
+int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                              uint32_t n, uint32_t *d_err, void *stream);
+/* The output head split by vocabulary rows: d_result = {local argmax index, its probability within the local
+ * slice (f32 bits)} as ie_b200_argmax leaves them, d_logits the local logits. On return d_result = {global
+ * index of the largest logit over all ranks (ties: the smaller index), its probability over the whole
+ * vocabulary}, the same on every rank. */
+int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream);
 void ie_b200_ar_destroy(ie_b200_allreduce *a);
 
 #ifdef __cplusplus

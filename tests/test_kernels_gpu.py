@@ -413,3 +413,42 @@ def test_gemv_norm_tail(ora, cuda, lib, typ, rows, cols):
         assert np.abs(got_n - want_n).max() <= 1e-5 * np.abs(want_n).max()
         assert (xnq.cpu().numpy() == ora.quant_q8(got_n)).all()
         assert int(counter.abs().max()) == 0
+
+
+@pytest.mark.parametrize("n", [256, 4096, 8192])
+def test_allreduce_norm_one_rank(ora, cuda, lib, n):
+    """The tensor-parallel stop kernel with a world of one rank (no peer to wait for): x + part bit-exact, the norm
+    within 1e-5 of the oracle's, its Q8 copy exactly the quantiser of that vector; the local-argmax exchange leaves
+    (index + offset, probability) of the single slice. Two calls in a row (the slots alternate by parity)."""
+    import ctypes as C
+
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(n)
+    h = C.c_void_p()
+    K.check(lib.ie_b200_ar_create(0, 1, n, C.byref(h)))
+    try:
+        nw = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        d_nw, err = dev(nw, cuda), torch.zeros(1, dtype=torch.int32, device=cuda)
+        for rep in range(2):
+            x, part = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+            d_x, d_part = dev(x.copy(), cuda), dev(part, cuda)
+            xn = torch.empty(n, dtype=torch.float32, device=cuda)
+            xq = torch.empty(40 * (n // 32), dtype=torch.uint8, device=cuda)
+            K.check(lib.ie_b200_ar_allreduce_norm(h, d_part.data_ptr(), d_x.data_ptr(), d_nw.data_ptr(), 1e-5, xn.data_ptr(), xq.data_ptr(), n,
+                                                  err.data_ptr(), None))
+            want_x = x + part
+            assert (bits(d_x.cpu().numpy()) == bits(want_x)).all(), rep
+            want_n, got_n = ora.rmsnorm(want_x, nw, 1e-5), xn.cpu().numpy()
+            assert np.abs(got_n - want_n).max() <= 1e-5 * np.abs(want_n).max()
+            assert (xq.cpu().numpy() == ora.quant_q8(got_n)).all()
+            logits = dev(rng.standard_normal(n).astype(np.float32), cuda)
+            res = torch.tensor([7, np.float32(0.25).view(np.int32)], dtype=torch.int32, device=cuda)
+            K.check(lib.ie_b200_ar_argmax(h, logits.data_ptr(), res.data_ptr(), 1000, err.data_ptr(), None))
+            got = res.cpu().numpy()
+            assert int(got[0]) == 1007 and abs(float(got[1:2].view(np.float32)[0]) - 0.25) < 1e-6
+        assert int(err.item()) == 0
+    finally:
+        lib.ie_b200_ar_destroy(h)
