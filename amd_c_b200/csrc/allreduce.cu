@@ -28,11 +28,11 @@
 
 #include "common.cuh"
 #include "ie_b200_tp.h"
+#include "peer_ll.cuh"
 
 namespace ieb {
 
-constexpr int AR_MAX_RANKS = 8, AR_THREADS = 256, AR_MAX_CTAS = 32;
-constexpr uint64_t AR_WAIT_NS = 2000000000ull;  // 2 s
+constexpr int AR_THREADS = 256, AR_MAX_CTAS = 32;
 
 struct ArDev {
   float *slots[AR_MAX_RANKS];     // rank j's receive buffer: [2][world][max_n] floats
@@ -42,12 +42,6 @@ struct ArDev {
   uint32_t *done;                 // local: CTAs that finished the current call
   uint32_t rank, world, max_n;
 };
-
-__device__ __forceinline__ uint64_t ar_now() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
 __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s, const float *part, const float *res, float *out, uint32_t n,
                                                                    uint32_t *err) {
@@ -108,35 +102,6 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
 }
 
 
-// ---- low-latency slots: one 64-bit store / load per payload word ----
-__device__ __forceinline__ void ll_store(unsigned long long *p, uint32_t epoch, uint32_t payload) {
-  const unsigned long long v = (unsigned long long)epoch << 32 | payload;
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-// Four consecutive words of epoch k; false (after the time limit, or at once when *gave_up is set) if they did not all arrive.
-__device__ __forceinline__ bool ll_wait4(const unsigned long long *p, uint32_t k, uint32_t (&out)[4], bool *gave_up, uint64_t t0) {
-  for (;;) {
-    unsigned long long v[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) v[c] = ll_load(p + c);
-    bool all = true;
-#pragma unroll
-    for (int c = 0; c < 4; c++) all = all && (uint32_t)(v[c] >> 32) == k;
-#pragma unroll
-    for (int c = 0; c < 4; c++) out[c] = (uint32_t)v[c];
-    if (all) return true;
-    if (*gave_up || ar_now() - t0 > AR_WAIT_NS) {
-      *gave_up = true;
-      return false;
-    }
-  }
-}
-
 constexpr int ARN_THREADS = 1024;
 
 // One CTA: x (= res, may alias out) + the ranks' partials in rank order, then y = x * rsqrt(mean x^2 + eps) * w
@@ -144,7 +109,7 @@ constexpr int ARN_THREADS = 1024;
 // Thread t owns elements 4 (t + 1024 it) .. + 3; eight neighbouring threads hold one Q8 block.
 template <int ITERS>
 __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, const float *part, const float *res, float *out, const float *norm_w, float eps,
-                                                              float *xn, uint8_t *xq, uint32_t n, uint32_t *err) {
+                                                              float *xn, uint8_t *xq, uint32_t n, uint32_t *err, int pushed) {
   __shared__ float red[32];
   pdl_prologue(TL_ALLREDUCE);
   const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
@@ -157,7 +122,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
     if (i < n) {
       mine[it] = *reinterpret_cast<const float4 *>(part + i);
       const uint32_t pw[4] = {__float_as_uint(mine[it].x), __float_as_uint(mine[it].y), __float_as_uint(mine[it].z), __float_as_uint(mine[it].w)};
-      for (uint32_t j = 0; j < s.world; j++) {
+      for (uint32_t j = 0; j < s.world && !pushed; j++) {  // pushed: the producing GEMV has already delivered its rows
         if (j == s.rank) continue;
         unsigned long long *dst = s.ll[j] + ((size_t)par * s.world + s.rank) * s.max_n + i;
 #pragma unroll
@@ -365,8 +330,8 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
   return IE_B200_OK;
 }
 
-extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
-                                         uint32_t n, uint32_t *d_err, void *stream) {
+static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
+                          uint32_t *d_err, void *stream, int pushed) {
   if (!a || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: NULL argument");
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_allreduce_norm: peers not connected");
   if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_THREADS)
@@ -377,11 +342,33 @@ extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_pa
   uint8_t *xq = static_cast<uint8_t *>(d_xq);
   const uint32_t iters = (n + 4u * ARN_THREADS - 1u) / (4u * ARN_THREADS);
   switch (iters) {
-    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
-    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
-    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err); break;
+    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
+    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
+    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
   }
   return IE_B200_OK;
+}
+
+extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                                         uint32_t n, uint32_t *d_err, void *stream) {
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 0);
+}
+
+extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
+                                           float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream) {
+  if (!a || !d_w || !d_xq || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: NULL argument");
+  if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_gemv_allreduce_norm: peers not connected");
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: matrix kind %d", kind);
+  if (rows == 0 || rows % 32u || rows > a->d.max_n) return fail(IE_B200_E_SIZE, "ie_b200_gemv_allreduce_norm: %u rows (a multiple of 32, at most %u)", rows, a->d.max_n);
+  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u) || cols / 32u > 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_allreduce_norm: %u columns", cols);
+  if (!aligned16(d_w) || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: 16-byte alignment");
+  ActSrc act = {};
+  act.xq = static_cast<const uint8_t *>(d_xq);
+  ArPush push = {};
+  for (uint32_t j = 0; j < a->d.world; j++) push.ll[j] = a->d.ll[j];
+  push.epoch = a->d.epoch, push.rank = a->d.rank, push.world = a->d.world, push.max_n = a->d.max_n;
+  if (int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push)) return r;
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1);
 }
 
 extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {

@@ -212,6 +212,22 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       i++;
       continue;
     }
+    // tensor parallel: a K-split GEMV that stores every finished row to the other ranks as well, then the one-CTA kernel
+    // that waits for the peers' rows, reduces onto the residual stream and normalises
+    if (T == 1 && e->ar && o.kind == IE_B200_OP_GEMV && i + 2 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
+        o.vec < 0 && o.res == IE_B200_NONE && (kind_mask & (1u << IE_B200_OP_ALLREDUCE)) && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
+      const ie_b200_op &ar = e->ops[i + 1], &nx = e->ops[i + 2];
+      const EMat &m = e->mats[o.mat];
+      if (ar.kind == IE_B200_OP_ALLREDUCE && ar.a == o.b && ar.n == m.rows && nx.kind == IE_B200_OP_RMSNORM && nx.a == ar.c && nx.res == IE_B200_NONE &&
+          nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
+        int r = ie_b200_gemv_allreduce_norm(e->ar, m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)),
+                                            static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps, static_cast<float *>(at(e, nx.b, 0, 0)),
+                                            at(e, nx.qo, 0, 0), e->err, st);
+        if (r) return r;
+        i += 2;
+        continue;
+      }
+    }
     // tensor parallel: all-reduce + residual add + the RMSNorm that follows, one kernel
     if (T == 1 && e->ar && o.kind == IE_B200_OP_ALLREDUCE && i + 1 < last && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
       const ie_b200_op &nx = e->ops[i + 1];

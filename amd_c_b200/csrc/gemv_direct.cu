@@ -21,6 +21,7 @@
 #include "act_stage.cuh"
 #include "common.cuh"
 #include "gemv_blocks.cuh"
+#include "peer_ll.cuh"
 
 namespace ieb {
 
@@ -38,6 +39,7 @@ struct GdArgs {
   ActSrc tail;        // tail.norm_w == NULL: no tail
   uint32_t late;      // let dependents start only after this kernel's own dependency wait (LaunchHints::late_trigger)
   uint32_t *work;     // two words, zero between launches; word 1 counts the CTAs that have finished (norm tail only)
+  ArPush push;        // TP kernels only: every finished row also goes to the other ranks' slots
 };
 
 // R rows of one warp, U lane steps (blocks l, l+32, ... of each row) per chunk: R x U 16-byte loads per lane
@@ -56,7 +58,7 @@ __device__ __forceinline__ void gd_load(Blk<KIND, false> (&blk)[R][U], const uin
   }
 }
 
-template <int KIND, bool NORM, int R, int U, int MINB>
+template <int KIND, bool NORM, int R, int U, int MINB, bool TP>
 __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdArgs a) {
   extern __shared__ uint4 smem_gd[];
   const uint32_t nb = a.nb;
@@ -88,6 +90,8 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   pdl_wait();
   if (a.late) pdl_launch_dependents();
   tl_mark(TL_GEMV, 1);
+  uint32_t ep = 0u;  // TP: the epoch of this exchange (the previous one is complete: its kernel is)
+  if (TP) ep = *(volatile uint32_t *)a.push.epoch + 1u;
   stage_activations<NORM, GD_WARPS>(a.act, nb, A0, A1, da, as, red, blockIdx.x == 0, [] { __syncthreads(); });
   tl_mark(TL_GEMV, 3);
 
@@ -114,6 +118,10 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
         if (a.bias) o = __fadd_rn(o, a.bias[rr + i]);
         if (a.res) o = __fadd_rn(a.res[rr + i], o);
         a.y[rr + i] = o;
+        if (TP) {  // the row goes to every other rank right away: the transfer overlaps the rest of the GEMV
+          for (uint32_t j = 0; j < a.push.world; j++)
+            if (j != a.push.rank) ll_store(a.push.ll[j] + ((size_t)(ep & 1u) * a.push.world + a.push.rank) * a.push.max_n + rr + i, ep, __float_as_uint(o));
+        }
       }
     }
   };
@@ -155,10 +163,10 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   tl_mark(TL_GEMV, 15);
 }
 
-template <int KIND, bool NORM, int R, int U, int MINB>
+template <int KIND, bool NORM, int R, int U, int MINB, bool TP>
 static int launch_direct(const GdArgs &a, cudaStream_t st) {
   const size_t smem = (size_t)a.nb * 40u;
-  auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB>;
+  auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB, TP>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
   // One group per warp up to a persistent grid of exactly the resident CTAs (MINB per SM), whose warps loop:
   // measured on B200, 3 per SM gives 6.45 TB/s on a 295 MB matrix, 8 per SM 5.98, 4 per SM (1.33 waves) 5.17.
@@ -173,34 +181,39 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
 // Long rows with few of them (the FFN down projection: 4096 x 14336) are a chain of dependent chunks per warp at
 // two rows per warp; one row per warp with the whole row's loads in flight at once (up to 16 lane steps, 2 CTAs
 // per SM for the registers that takes) shortens the chain to one round trip per row.
-template <int KIND, bool NORM>
+template <int KIND, bool NORM, bool TP>
 static int pick_direct(const GdArgs &a, cudaStream_t st) {
   constexpr int U2 = KIND == IE_B200_MAT_Q4 ? 4 : 2;
   const bool few_long = a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
-  if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
-  return launch_direct<KIND, NORM, 2, U2, 3>(a, st);
+  if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2, TP>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
+  return launch_direct<KIND, NORM, 2, U2, 3, TP>(a, st);
 }
 
-template <bool NORM>
+template <bool NORM, bool TP>
 int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
   switch (kind) {
-    case IE_B200_MAT_Q4: return pick_direct<IE_B200_MAT_Q4, NORM>(a, st);
-    case IE_B200_MAT_Q4K: return pick_direct<IE_B200_MAT_Q4K, NORM>(a, st);
-    case IE_B200_MAT_Q6K: return pick_direct<IE_B200_MAT_Q6K, NORM>(a, st);
+    case IE_B200_MAT_Q4: return pick_direct<IE_B200_MAT_Q4, NORM, TP>(a, st);
+    case IE_B200_MAT_Q4K: return pick_direct<IE_B200_MAT_Q4K, NORM, TP>(a, st);
+    case IE_B200_MAT_Q6K: return pick_direct<IE_B200_MAT_Q6K, NORM, TP>(a, st);
     default: return fail(IE_B200_E_ARG, "gemv_direct: matrix kind %d has no streaming kernel", kind);
   }
 }
 
 // Entry used by gemv_stream.cu's dispatcher.
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st) {
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push) {
   GdArgs a = {};
   a.late = take_hints().late_trigger ? 1u : 0u;
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.act = act, a.y = d_y, a.bias = d_bias, a.res = d_res;
   a.work = work;
   if (tail) a.tail = *tail, a.tail.xf = d_y;
-  return norm ? dispatch_direct<true>(kind, a, st) : dispatch_direct<false>(kind, a, st);
+  if (push) {
+    if (norm || tail || d_bias || d_res) return fail(IE_B200_E_ARG, "gemv_direct: a tensor-parallel partial takes no norm, bias or residual");
+    a.push = *push;
+    return dispatch_direct<false, true>(kind, a, st);
+  }
+  return norm ? dispatch_direct<true, false>(kind, a, st) : dispatch_direct<false, false>(kind, a, st);
 }
 
 }  // namespace ieb

@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "act_stage.cuh"
 #include "gemv_blocks.cuh"
+#include "peer_ll.cuh"
 
 namespace ieb {
 
@@ -246,8 +247,6 @@ static int dispatch_stream(int kind, GsArgs &a, cudaStream_t st) {
   }
 }
 
-int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st);  // gemv_direct.cu
 
 // Which decode GEMV runs: "direct" (registers, default) or "ring" (bulk copies into shared memory); IE_B200_GEMV selects.
 bool gemv_uses_ring() {

@@ -1,0 +1,62 @@
+// peer_ll.cuh -- "low-latency" slots for small cross-GPU exchanges over peer memory: every 32-bit payload word
+// travels as one 64-bit store {epoch << 32 | word} into the receiver's memory, and the receiver polls the words
+// themselves: a value is complete as soon as its epoch matches, so there is no separate flag and no fence.
+// Slots are [2][world][max_n] words per rank, double-buffered by the parity of the call's epoch (a rank can be
+// at most one call ahead of the slowest: finishing call k needs every rank's data of call k).
+#pragma once
+
+#include "act_stage.cuh"
+#include "common.cuh"
+
+namespace ieb {
+
+constexpr int AR_MAX_RANKS = 8;
+constexpr uint64_t AR_WAIT_NS = 2000000000ull;  // 2 s: a peer that has not delivered by then is reported, not waited for
+
+__device__ __forceinline__ uint64_t ar_now() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void ll_store(unsigned long long *p, uint32_t epoch, uint32_t payload) {
+  const unsigned long long v = (unsigned long long)epoch << 32 | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Four consecutive words of epoch k; false (after the time limit, or at once when *gave_up is set) if they did not all arrive.
+__device__ __forceinline__ bool ll_wait4(const unsigned long long *p, uint32_t k, uint32_t (&out)[4], bool *gave_up, uint64_t t0) {
+  for (;;) {
+    unsigned long long v[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) v[c] = ll_load(p + c);
+    bool all = true;
+#pragma unroll
+    for (int c = 0; c < 4; c++) all = all && (uint32_t)(v[c] >> 32) == k;
+#pragma unroll
+    for (int c = 0; c < 4; c++) out[c] = (uint32_t)v[c];
+    if (all) return true;
+    if (*gave_up || ar_now() - t0 > AR_WAIT_NS) {
+      *gave_up = true;
+      return false;
+    }
+  }
+}
+
+// What a GEMV needs to deliver its rows to the other ranks as it produces them (gemv_direct.cu); the reduction
+// kernel that follows (allreduce.cu) then only has to wait for the peers' rows.
+struct ArPush {
+  unsigned long long *ll[AR_MAX_RANKS];  // rank j's slots
+  uint32_t *epoch;                       // local: completed calls (this exchange is call *epoch + 1)
+  uint32_t rank, world, max_n;
+};
+
+// The direct decode GEMV (gemv_direct.cu). tail: RMSNorm + Q8 of the finished vector by the last CTA; push (no
+// tail / bias / res): a tensor-parallel partial whose rows are also stored into the other ranks' slots.
+int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push = nullptr);
+
+}  // namespace ieb

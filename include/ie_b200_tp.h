@@ -37,6 +37,13 @@ int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_part, const fl
  * {epoch, word} stores that the receiver polls in place, so there is no flag round and no fence. */
 int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
                               uint32_t n, uint32_t *d_err, void *stream);
+/* The same stop together with the K-split GEMV that produces the partial (the decode step's default): part = W xq
+ * (kind / layout / xq as ie_b200_gemv_stream; no bias), and every finished row is stored to the other ranks at
+ * once, so the transfer overlaps the rest of the GEMV; the one-CTA kernel launched behind it then only waits for
+ * the peers' rows, adds the partials in rank order onto d_x and writes RMSNorm(d_x) and its Q8 copy. rows = n of
+ * the exchange (a multiple of 32, at most max_floats). */
+int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
+                                float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream);
 /* The output head split by vocabulary rows: d_result = {local argmax index, its probability within the local
  * slice (f32 bits)} as ie_b200_argmax leaves them, d_logits the local logits. On return d_result = {global
  * index of the largest logit over all ranks (ties: the smaller index), its probability over the whole

@@ -452,3 +452,43 @@ def test_allreduce_norm_one_rank(ora, cuda, lib, n):
         assert int(err.item()) == 0
     finally:
         lib.ie_b200_ar_destroy(h)
+
+
+@pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 4096, 2048), (synth.GGML_Q4_0, 4096, 7168), (synth.GGML_Q6_K, 512, 1024)])
+def test_gemv_allreduce_norm_one_rank(ora, cuda, lib, typ, rows, cols):
+    """The K-split GEMV with the exchange folded in, in a world of one rank: part = W xq bit-exact, x + part bit-exact,
+    the norm within 1e-5 of the oracle's and its Q8 copy exactly the quantiser of that vector; twice in a row."""
+    import ctypes as C
+
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows + cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    nw = (1 + 0.1 * rng.standard_normal(rows)).astype(np.float32)
+    h = C.c_void_p()
+    K.check(lib.ie_b200_ar_create(0, 1, rows, C.byref(h)))
+    try:
+        err, d_nw = torch.zeros(1, dtype=torch.int32, device=cuda), dev(nw, cuda)
+        for rep in range(2):
+            act, x = rng.standard_normal(cols).astype(np.float32), rng.standard_normal(rows).astype(np.float32)
+            xq = ora.quant_q8(act)
+            d_xq, d_x = dev(xq, cuda), dev(x.copy(), cuda)
+            part = torch.empty(rows, dtype=torch.float32, device=cuda)
+            xn = torch.empty(rows, dtype=torch.float32, device=cuda)
+            xnq = torch.empty(40 * (rows // 32), dtype=torch.uint8, device=cuda)
+            K.check(lib.ie_b200_gemv_allreduce_norm(h, m.kind, m.data.data_ptr(), rows, cols, d_xq.data_ptr(), part.data_ptr(), d_x.data_ptr(),
+                                                    d_nw.data_ptr(), 1e-5, xn.data_ptr(), xnq.data_ptr(), err.data_ptr(), None))
+            want_p = ora.gemv(kind, qw, qs, rows, cols, xq)
+            assert (bits(part.cpu().numpy()) == bits(want_p)).all(), rep
+            want_x = x + want_p
+            assert (bits(d_x.cpu().numpy()) == bits(want_x)).all(), rep
+            want_n, got_n = ora.rmsnorm(want_x, nw, 1e-5), xn.cpu().numpy()
+            assert np.abs(got_n - want_n).max() <= 1e-5 * np.abs(want_n).max()
+            assert (xnq.cpu().numpy() == ora.quant_q8(got_n)).all()
+            assert int(err.item()) == 0
+    finally:
+        lib.ie_b200_ar_destroy(h)
