@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "ie_b200_tp.h"
+#include "norm_quant.cuh"
 #include "peer_ll.cuh"
 
 namespace ieb {
@@ -109,16 +110,31 @@ constexpr int ARN_THREADS = 1024;
 // Thread t owns elements 4 (t + 1024 it) .. + 3; eight neighbouring threads hold one Q8 block.
 template <int ITERS>
 __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, const float *part, const float *res, float *out, const float *norm_w, float eps,
-                                                              float *xn, uint8_t *xq, uint32_t n, uint32_t *err, int pushed) {
+                                                              float *xn, uint8_t *xq, uint32_t n, uint32_t *err, int pushed, int early) {
   __shared__ float red[32];
-  pdl_prologue(TL_ALLREDUCE);
-  const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   float4 acc[ITERS], mine[ITERS], w4[ITERS];
+  tl_mark(TL_ALLREDUCE, 0);
+  pdl_launch_dependents();
+  // ahead of the dependency wait: the norm weights (constant) and, when the kernel before this one releases its
+  // dependents late (`early`), everything older than that kernel: the epoch and the residual stream
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
     const uint32_t i = 4u * (tid + ARN_THREADS * it);
-    mine[it] = acc[it] = w4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    acc[it] = w4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < n && norm_w) w4[it] = *reinterpret_cast<const float4 *>(norm_w + i);
+    if (i < n && early) acc[it] = *reinterpret_cast<const float4 *>(res + i);
+  }
+  uint32_t k = 0u;
+  if (early) k = *(volatile uint32_t *)s.epoch + 1u;
+  pdl_wait();
+  tl_mark(TL_ALLREDUCE, 1);
+  if (!early) k = *(volatile uint32_t *)s.epoch + 1u;
+  const uint32_t par = k & 1u;
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    mine[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < n) {
       mine[it] = *reinterpret_cast<const float4 *>(part + i);
       const uint32_t pw[4] = {__float_as_uint(mine[it].x), __float_as_uint(mine[it].y), __float_as_uint(mine[it].z), __float_as_uint(mine[it].w)};
@@ -128,79 +144,66 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
 #pragma unroll
         for (int c = 0; c < 4; c++) ll_store(dst + c, k, pw[c]);
       }
-      acc[it] = *reinterpret_cast<const float4 *>(res + i);
-      if (norm_w) w4[it] = *reinterpret_cast<const float4 *>(norm_w + i);
+      if (!early) acc[it] = *reinterpret_cast<const float4 *>(res + i);
     }
   }
-  // ---- the sum, in rank order; peers' words are polled in place
+  // ---- the sum, in rank order; peers' words are polled in place, up to four peers' loads in flight together
   bool gave_up = false;
   const uint64_t t0 = ar_now();
   const unsigned long long *my = s.ll[s.rank] + (size_t)par * s.world * s.max_n;
-  for (uint32_t j = 0; j < s.world; j++) {
 #pragma unroll
-    for (int it = 0; it < ITERS; it++) {
-      const uint32_t i = 4u * (tid + ARN_THREADS * it);
-      if (i >= n) continue;
-      float4 v = mine[it];
-      if (j != s.rank) {
-        uint32_t wv[4];
-        ll_wait4(my + (size_t)j * s.max_n + i, k, wv, &gave_up, t0);
-        v = make_float4(__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3]));
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    if (i >= n) continue;
+    for (uint32_t j0 = 0; j0 < s.world; j0 += 4u) {
+      unsigned long long v[4][4];
+      for (;;) {
+        bool all = true;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const uint32_t j = j0 + q;
+          if (j < s.world && j != s.rank) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) v[q][c] = ll_load(my + (size_t)j * s.max_n + i + c);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const uint32_t j = j0 + q;
+          if (j < s.world && j != s.rank) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) all = all && (uint32_t)(v[q][c] >> 32) == k;
+          }
+        }
+        if (all) break;
+        if (gave_up || ar_now() - t0 > AR_WAIT_NS) {
+          gave_up = true;
+          break;
+        }
       }
-      acc[it].x = __fadd_rn(acc[it].x, v.x), acc[it].y = __fadd_rn(acc[it].y, v.y);
-      acc[it].z = __fadd_rn(acc[it].z, v.z), acc[it].w = __fadd_rn(acc[it].w, v.w);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const uint32_t j = j0 + q;
+        if (j >= s.world) continue;
+        float4 pv = mine[it];
+        if (j != s.rank)
+          pv = make_float4(__uint_as_float((uint32_t)v[q][0]), __uint_as_float((uint32_t)v[q][1]), __uint_as_float((uint32_t)v[q][2]),
+                           __uint_as_float((uint32_t)v[q][3]));
+        acc[it].x = __fadd_rn(acc[it].x, pv.x), acc[it].y = __fadd_rn(acc[it].y, pv.y);
+        acc[it].z = __fadd_rn(acc[it].z, pv.z), acc[it].w = __fadd_rn(acc[it].w, pv.w);
+      }
     }
   }
+  tl_mark(TL_ALLREDUCE, 2);
   if (gave_up && err) atomicExch(err, 3u);
-  float ss = 0.0f;
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
     const uint32_t i = 4u * (tid + ARN_THREADS * it);
     if (i < n) *reinterpret_cast<float4 *>(out + i) = acc[it];
-    ss = fmaf(acc[it].x, acc[it].x, ss), ss = fmaf(acc[it].y, acc[it].y, ss), ss = fmaf(acc[it].z, acc[it].z, ss), ss = fmaf(acc[it].w, acc[it].w, ss);
   }
-  if (norm_w) {
-    ss = warp_sum_all(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    const float tot = warp_sum_all(red[lane]);
-    const float sc = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)n), eps)));
-    const uint32_t nb = n / 32u;
-#pragma unroll
-    for (int it = 0; it < ITERS; it++) {
-      const uint32_t i = 4u * (tid + ARN_THREADS * it);
-      const float v[4] = {__fmul_rn(__fmul_rn(acc[it].x, sc), w4[it].x), __fmul_rn(__fmul_rn(acc[it].y, sc), w4[it].y),
-                          __fmul_rn(__fmul_rn(acc[it].z, sc), w4[it].z), __fmul_rn(__fmul_rn(acc[it].w, sc), w4[it].w)};
-      float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
-      const float d = __fdiv_rn(amax, 127.0f), rinv = __frcp_rn(d);
-      uint32_t pk = 0u;
-      int sum = 0;
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        int q = 0;
-        if (d != 0.0f) q = q8_round(v[c], d, rinv);
-        sum += q;
-        pk |= (uint32_t)(q & 255) << (8 * c);
-      }
-      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-      if (i < n) {
-        if (xn) *reinterpret_cast<float4 *>(xn + i) = make_float4(v[0], v[1], v[2], v[3]);
-        if (xq) {
-          *reinterpret_cast<uint32_t *>(xq + i) = pk;
-          if ((tid & 7) == 0) {
-            reinterpret_cast<float *>(xq + 32u * (size_t)nb)[i / 32u] = d;
-            reinterpret_cast<int *>(xq + 36u * (size_t)nb)[i / 32u] = sum;
-          }
-        }
-      }
-    }
-  }
+  if (norm_w) norm_quant_vec<ITERS, ARN_THREADS>(acc, w4, n, eps, xn, xq, red);
   if (tid == 0) *(volatile uint32_t *)s.epoch = k;
+  tl_mark(TL_ALLREDUCE, 15);
 }
 
 // One warp: every rank's (logit, global index) of its local argmax to every rank; the largest logit wins, ties
@@ -331,7 +334,7 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
 }
 
 static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
-                          uint32_t *d_err, void *stream, int pushed) {
+                          uint32_t *d_err, void *stream, int pushed, int early = 0) {
   if (!a || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: NULL argument");
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_allreduce_norm: peers not connected");
   if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_THREADS)
@@ -342,9 +345,9 @@ static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x,
   uint8_t *xq = static_cast<uint8_t *>(d_xq);
   const uint32_t iters = (n + 4u * ARN_THREADS - 1u) / (4u * ARN_THREADS);
   switch (iters) {
-    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
-    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
-    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed); break;
+    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
+    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
+    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
   }
   return IE_B200_OK;
 }
@@ -367,8 +370,15 @@ extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const
   ArPush push = {};
   for (uint32_t j = 0; j < a->d.world; j++) push.ll[j] = a->d.ll[j];
   push.epoch = a->d.epoch, push.rank = a->d.rank, push.world = a->d.world, push.max_n = a->d.max_n;
-  if (int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push)) return r;
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1);
+  // the GEMV releases its dependents only after its own dependency wait: when the reduction kernel starts, everything
+  // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
+  LaunchHints hints;
+  hints.late_trigger = true;
+  set_hints(hints);
+  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push);
+  set_hints(LaunchHints());
+  if (r) return r;
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
 }
 
 extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {

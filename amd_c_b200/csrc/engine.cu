@@ -67,7 +67,7 @@ struct ie_b200_engine {
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
   uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[2..3]: the GEMVs' work and arrival counters
   bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
-  int norm_mode = 0;         // 0: norm tail in the producing GEMV, 1: norm in the consuming GEMVs' prologue, 2: a kernel of its own
+  int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
   ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
   uint32_t vocab_off = 0;           // first vocabulary row of this shard's output head
@@ -329,7 +329,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->err, 16), "cudaMalloc(error word)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
-  if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 's' ? 2 : 0;
+  if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");
   chk(cudaEventCreate(&e->ev0), "cudaEventCreate");

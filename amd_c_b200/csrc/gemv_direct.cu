@@ -118,10 +118,11 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
         if (a.bias) o = __fadd_rn(o, a.bias[rr + i]);
         if (a.res) o = __fadd_rn(a.res[rr + i], o);
         a.y[rr + i] = o;
-        if (TP) {  // the row goes to every other rank right away: the transfer overlaps the rest of the GEMV
-          for (uint32_t j = 0; j < a.push.world; j++)
-            if (j != a.push.rank) ll_store(a.push.ll[j] + ((size_t)(ep & 1u) * a.push.world + a.push.rank) * a.push.max_n + rr + i, ep, __float_as_uint(o));
-        }
+      }
+      if (TP) {  // the row goes to every other rank right away (lane j stores to rank j): the transfer overlaps the rest of the GEMV
+        const float o = __shfl_sync(0xFFFFFFFFu, v, 0);
+        if ((uint32_t)lane < a.push.world && (uint32_t)lane != a.push.rank && rr + i < r_hi)
+          ll_store(a.push.ll[lane] + ((size_t)(ep & 1u) * a.push.world + a.push.rank) * a.push.max_n + rr + i, ep, __float_as_uint(o));
       }
     }
   };

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "norm_quant.cuh"
 
 namespace ieb {
 
@@ -75,6 +76,35 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const flo
     if (qt) quant_block_warp(v, qt, n / 32u, b, lane);
   }
   for (uint32_t i = (n / 32u) * 32u + threadIdx.x; i < n; i += blockDim.x) yt[i] = __fmul_rn(__fmul_rn(xt[i], s), w[i]);
+}
+
+// The same for vectors of whole 32-blocks up to 16384 elements, 16-byte aligned: each thread keeps its float4s in
+// registers (one pass over x), the norm weights are fetched ahead of the dependency wait, and the Q8 copy needs no
+// shared memory (norm_quant.cuh).
+template <int ITERS>
+__global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float *x, const float *__restrict__ w, float *y, uint32_t n, float eps, uint8_t *q,
+                                                          size_t xs, size_t ys, size_t qs) {
+  __shared__ float red[32];
+  const uint32_t t = blockIdx.x;
+  float4 x4[ITERS], w4[ITERS];
+  tl_mark(TL_RMSNORM, 0);
+  pdl_launch_dependents();
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (threadIdx.x + 1024u * it);
+    w4[it] = x4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < n) w4[it] = *reinterpret_cast<const float4 *>(w + i);
+  }
+  pdl_wait();
+  tl_mark(TL_RMSNORM, 1);
+  const float *xt = row_ptr(x, xs, t);
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const uint32_t i = 4u * (threadIdx.x + 1024u * it);
+    if (i < n) x4[it] = *reinterpret_cast<const float4 *>(xt + i);
+  }
+  norm_quant_vec<ITERS, 1024>(x4, w4, n, eps, row_ptr(y, ys, t), q ? row_ptr(q, qs, t) : nullptr, red);
+  tl_mark(TL_RMSNORM, 15);
 }
 
 // ---- SwiGLU (+Q8): one warp per 32 elements ----
@@ -246,6 +276,16 @@ extern "C" int ie_b200_rmsnorm(const float *d_x, const float *d_w, float *d_y, u
   if (!d_x || !d_w || !d_y) return fail(IE_B200_E_ARG, "ie_b200_rmsnorm: NULL pointer");
   if (d_q && n % 32u) return fail(IE_B200_E_SIZE, "ie_b200_rmsnorm: the Q8 copy needs n %% 32 == 0 (n = %u)", n);
   if (n == 0 || T == 0) return IE_B200_OK;
+  if (n % 32u == 0 && n <= 16384u && aligned16(d_x) && aligned16(d_w) && aligned16(d_y) && (!d_q || aligned16(d_q)) &&
+      (T == 1 || (x_stride % 16u == 0 && y_stride % 16u == 0 && q_stride % 16u == 0))) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *q = static_cast<uint8_t *>(d_q);
+    const uint32_t iters = (n + 4095u) / 4096u;
+    if (iters == 1) IEB_LAUNCH_PDL("rmsnorm_vec_kernel", rmsnorm_vec_kernel<1>, dim3(T), dim3(1024), 0, st, d_x, d_w, d_y, n, eps, q, x_stride, y_stride, q_stride);
+    else if (iters == 2) IEB_LAUNCH_PDL("rmsnorm_vec_kernel", rmsnorm_vec_kernel<2>, dim3(T), dim3(1024), 0, st, d_x, d_w, d_y, n, eps, q, x_stride, y_stride, q_stride);
+    else IEB_LAUNCH_PDL("rmsnorm_vec_kernel", rmsnorm_vec_kernel<4>, dim3(T), dim3(1024), 0, st, d_x, d_w, d_y, n, eps, q, x_stride, y_stride, q_stride);
+    return IE_B200_OK;
+  }
   IEB_LAUNCH_PDL("rmsnorm_kernel", rmsnorm_kernel, dim3(T), dim3(1024), 0, static_cast<cudaStream_t>(stream), d_x, d_w, d_y, n, eps,
                  static_cast<uint8_t *>(d_q), x_stride, y_stride, q_stride);
   return IE_B200_OK;
