@@ -72,8 +72,12 @@ struct AttGeom {
   static constexpr int NB = NB_FIT > 4 ? 4 : (NB_FIT < 2 ? 2 : NB_FIT);  // tile buffers: NB - 1 tiles in flight ahead of the one in use
 };
 
-template <typename KV, int HD, int G, bool FUSED>
-__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs a) {
+// HS: the G query heads of the KV head are dealt to HS groups of eight warps (G / HS heads each) that share the K / V
+// tiles: twice the warps halve the arithmetic per warp, which is what a short context waits for.
+template <typename KV, int HD, int G, bool FUSED, int HS>
+__global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const AttnArgs a) {
+  constexpr int GH = G / HS, THREADS = ATT_THREADS * HS;
+  static_assert(G % HS == 0, "heads split evenly over the warp groups");
   constexpr int DPL = HD / 8;   // dims per lane in the q.k phase (8 lanes per position)
   constexpr int DPV = HD / 32;  // dims per lane in the p.v phase
   constexpr int TILE = ATT_TILE, TILE_ELEMS = TILE * HD, NB = AttGeom<KV, HD>::NB;
@@ -82,7 +86,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   extern __shared__ uint4 smem_raw[];
   KV *kbuf = reinterpret_cast<KV *>(smem_raw);                          // [NB][TILE][HD]
   KV *vbuf = kbuf + NB * TILE_ELEMS;                                     // [NB][TILE][HD]
-  float *Pw = reinterpret_cast<float *>(vbuf + NB * TILE_ELEMS);         // [warp][PPW][G] probabilities of the warp's positions
+  float *Pw = reinterpret_cast<float *>(vbuf + NB * TILE_ELEMS);         // [warp][PPW][GH] probabilities of the warp's positions
   __shared__ uint32_t is_last;
 
   tl_mark(TL_ATTN, 0);
@@ -98,6 +102,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
   const bool owns_new = FUSED && s == A - 1u;  // this CTA's span ends with the step's own position
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wq = warp % ATT_WARPS, hg = warp / ATT_WARPS;  // which positions of a tile, which heads
   const int sub = lane & 7, grp = lane >> 3;
   const float *qt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * t) + (size_t)g * G * HD;
   const KV *kh = static_cast<const KV *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const KV *>(a.vc) + (size_t)g * a.kv_len * HD;
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
       const uint32_t rows = min((uint32_t)TILE, p_hi - tile_lo - ((owns_new && it + 1u == n_tiles) ? 1u : 0u));
       const char *ks = reinterpret_cast<const char *>(kh + (size_t)tile_lo * HD), *vs = reinterpret_cast<const char *>(vh + (size_t)tile_lo * HD);
       char *kd = reinterpret_cast<char *>(kbuf + (it % NB) * TILE_ELEMS), *vd = reinterpret_cast<char *>(vbuf + (it % NB) * TILE_ELEMS);
-      for (uint32_t c = threadIdx.x; c < rows * PER_ROW; c += ATT_THREADS) {
+      for (uint32_t c = threadIdx.x; c < rows * PER_ROW; c += THREADS) {
         __pipeline_memcpy_async(kd + (size_t)c * 16u, ks + (size_t)c * 16u, 16);
         __pipeline_memcpy_async(vd + (size_t)c * 16u, vs + (size_t)c * 16u, 16);
       }
@@ -121,54 +126,64 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   };
 #pragma unroll
   for (int i = 0; i < NB - 1; i++) issue(i);
+  // RoPE table values of this lane's q dims (pairs (2i, 2i+1): DPL / 2 of them; pairs (i, i + hd/2): DPL) and of the
+  // k pair this thread rotates: constants, fetched ahead of the dependency wait when the position is known by then
+  float tc[DPL], ts[DPL], kc_ = 0.f, ks_ = 0.f;
+  auto load_tables = [&]() {
+    if (!FUSED) return;
+    const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
+    const int nt = a.neox ? DPL : DPL / 2, i0 = a.neox ? (sub * DPL) % (HD / 2) : sub * (DPL / 2);
+#pragma unroll
+    for (int j = 0; j < DPL; j += 2) {
+      if (j < nt) {
+        const float2 c2 = *reinterpret_cast<const float2 *>(cs + i0 + j), s2 = *reinterpret_cast<const float2 *>(sn + i0 + j);
+        tc[j] = c2.x, tc[j + 1] = c2.y, ts[j] = s2.x, ts[j + 1] = s2.y;
+      }
+    }
+    if (owns_new && threadIdx.x < HD / 2) kc_ = cs[threadIdx.x], ks_ = sn[threadIdx.x];
+  };
+  if (early) load_tables();
   if (early) pdl_wait();
   tl_mark(TL_ATTN, 1);
 
   // ---- q of this lane for the q.k phase (rotated here when fused), the step's own K / V row
-  float qr[G][DPL];
+  float qr[GH][DPL];
 #pragma unroll
-  for (int h = 0; h < G; h++)
+  for (int h = 0; h < GH; h++)
 #pragma unroll
     for (int j = 0; j < DPL; j += 4) {
-      const float4 v = *reinterpret_cast<const float4 *>(qt + h * HD + sub * DPL + j);
+      const float4 v = *reinterpret_cast<const float4 *>(qt + (hg * GH + h) * HD + sub * DPL + j);
       qr[h][j] = v.x, qr[h][j + 1] = v.y, qr[h][j + 2] = v.z, qr[h][j + 3] = v.w;
     }
   KV newk0 = KV(0.f), newk1 = KV(0.f), newv = KV(0.f);
   int nk0 = 0, nk1 = 0;
   if (FUSED) {
-    const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
-    float x0 = 0.f, x1 = 0.f, kc_ = 0.f, ks_ = 0.f, vn = 0.f;
-    if (owns_new) {  // issue the loads of the new row together with the table loads below
+    float x0 = 0.f, x1 = 0.f, vn = 0.f;
+    if (owns_new) {  // the loads of the new row go out together with the q loads above
       if (threadIdx.x < HD / 2) {
         const int i = threadIdx.x;
         nk0 = a.neox ? i : 2 * i, nk1 = a.neox ? i + HD / 2 : 2 * i + 1;
-        x0 = a.k_new[g * HD + nk0], x1 = a.k_new[g * HD + nk1], kc_ = cs[i], ks_ = sn[i];
+        x0 = a.k_new[g * HD + nk0], x1 = a.k_new[g * HD + nk1];
       } else if (threadIdx.x >= 128 && threadIdx.x < 128 + HD) {
         vn = a.v_new[g * HD + (threadIdx.x - 128)];
       }
     }
+    if (!early) load_tables();
     if (!a.neox) {  // pairs (2i, 2i+1): both in this lane
-      float c[DPL / 2], sv[DPL / 2];
-#pragma unroll
-      for (int j = 0; j < DPL / 2; j++) c[j] = cs[sub * (DPL / 2) + j], sv[j] = sn[sub * (DPL / 2) + j];
 #pragma unroll
       for (int j = 0; j < DPL; j += 2)
 #pragma unroll
-        for (int h = 0; h < G; h++) {
+        for (int h = 0; h < GH; h++) {
           const float y0 = qr[h][j], y1 = qr[h][j + 1];
-          qr[h][j] = rope_lo(y0, y1, c[j / 2], sv[j / 2]), qr[h][j + 1] = rope_hi(y0, y1, c[j / 2], sv[j / 2]);
+          qr[h][j] = rope_lo(y0, y1, tc[j / 2], ts[j / 2]), qr[h][j + 1] = rope_hi(y0, y1, tc[j / 2], ts[j / 2]);
         }
     } else {  // pairs (i, i + hd/2): the partner dim sits in the lane 4 further in the 8-lane group
-      float c[DPL], sv[DPL];
-      const int i0 = (sub * DPL) % (HD / 2);
-#pragma unroll
-      for (int j = 0; j < DPL; j++) c[j] = cs[i0 + j], sv[j] = sn[i0 + j];
 #pragma unroll
       for (int j = 0; j < DPL; j++)
 #pragma unroll
-        for (int h = 0; h < G; h++) {
+        for (int h = 0; h < GH; h++) {
           const float mine = qr[h][j], other = __shfl_xor_sync(0xFFFFFFFFu, mine, 4);
-          qr[h][j] = sub < 4 ? rope_lo(mine, other, c[j], sv[j]) : rope_hi(other, mine, c[j], sv[j]);
+          qr[h][j] = sub < 4 ? rope_lo(mine, other, tc[j], ts[j]) : rope_hi(other, mine, tc[j], ts[j]);
         }
     }
     if (owns_new) {  // rotate k, store the row in the cache; it joins the last tile from registers below
@@ -187,14 +202,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
 
   // ---- the span, tile by tile. Every warp keeps its own running max / sum / output over the positions it owns
   // (PPW per tile), so the only block-wide synchronisation is the hand-over of tile buffers.
-  float o[G][DPV], run_m[G], run_l[G];
+  float o[GH][DPV], run_m[GH], run_l[GH];
 #pragma unroll
-  for (int h = 0; h < G; h++) {
+  for (int h = 0; h < GH; h++) {
     run_m[h] = -INFINITY, run_l[h] = 0.0f;
 #pragma unroll
     for (int d = 0; d < DPV; d++) o[h][d] = 0.0f;
   }
-  float *pw = Pw + warp * PPW * G;
+  float *pw = Pw + warp * PPW * GH;
   for (uint32_t it = 0; it < n_tiles; it++) {
     const int buf = it % NB;
     const uint32_t tile_lo = p_lo + it * TILE;
@@ -212,17 +227,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     issue(it + NB - 1u);
     tl_mark(TL_ATTN, 3);
     const uint32_t valid = p_hi - tile_lo;  // positions of this tile that exist (>= 1)
-    if ((uint32_t)(warp * PPW) < valid) {
+    if ((uint32_t)(wq * PPW) < valid) {
       const KV *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
       // scores: 8 lanes per position, 4 positions per round
-      float sc[PPW / 4][G];
+      float sc[PPW / 4][GH];
 #pragma unroll
       for (int r = 0; r < PPW / 4; r++) {
-        const int pi = warp * PPW + r * 4 + grp;
+        const int pi = wq * PPW + r * 4 + grp;
         float kr[DPL];
         load_slice<KV>(kt + pi * HD + sub * DPL, kr, DPL);
 #pragma unroll
-        for (int h = 0; h < G; h++) {
+        for (int h = 0; h < GH; h++) {
           float d = 0.0f;
 #pragma unroll
           for (int j = 0; j < DPL; j++) d = fmaf(qr[h][j], kr[j], d);
@@ -234,7 +249,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
       }
       // the warp's running softmax; position warp * PPW exists, so the new maximum is finite
 #pragma unroll
-      for (int h = 0; h < G; h++) {
+      for (int h = 0; h < GH; h++) {
         float mx = sc[0][h];
 #pragma unroll
         for (int r = 1; r < PPW / 4; r++) mx = fmaxf(mx, sc[r][h]);
@@ -246,7 +261,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         for (int r = 0; r < PPW / 4; r++) {
           const float pv = expf(sc[r][h] - m_new);
           sum += pv;
-          if (sub == 0) pw[(r * 4 + grp) * G + h] = pv;
+          if (sub == 0) pw[(r * 4 + grp) * GH + h] = pv;
         }
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
@@ -258,17 +273,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
       // p.v over the warp's positions: every lane owns DPV output dims
 #pragma unroll
       for (int j = 0; j < PPW; j++) {
-        if ((uint32_t)(warp * PPW + j) < valid) {  // uniform over the warp
+        if ((uint32_t)(wq * PPW + j) < valid) {  // uniform over the warp
           float vr[DPV];
           if (DPV >= 4) {
-            load_slice<KV>(vt + (warp * PPW + j) * HD + lane * DPV, vr, DPV);
+            load_slice<KV>(vt + (wq * PPW + j) * HD + lane * DPV, vr, DPV);
           } else {
 #pragma unroll
-            for (int d = 0; d < DPV; d++) vr[d] = (float)vt[(warp * PPW + j) * HD + lane * DPV + d];
+            for (int d = 0; d < DPV; d++) vr[d] = (float)vt[(wq * PPW + j) * HD + lane * DPV + d];
           }
 #pragma unroll
-          for (int h = 0; h < G; h++) {
-            const float pv = pw[j * G + h];
+          for (int h = 0; h < GH; h++) {
+            const float pv = pw[j * GH + h];
 #pragma unroll
             for (int d = 0; d < DPV; d++) o[h][d] = fmaf(pv, vr[d], o[h][d]);
           }
@@ -286,16 +301,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   float *ml = red + ATT_WARPS * G * HD;               // [ATT_WARPS][G][2]
   float *fin = ml + ATT_WARPS * G * 2;                // [G][HD]
 #pragma unroll
-  for (int h = 0; h < G; h++) {
+  for (int h = 0; h < GH; h++) {
+    const int hh = hg * GH + h;  // the head's index within the KV head
 #pragma unroll
-    for (int d = 0; d < DPV; d++) red[(warp * G + h) * HD + lane * DPV + d] = o[h][d];
-    if (lane == 0) ml[(warp * G + h) * 2] = run_m[h], ml[(warp * G + h) * 2 + 1] = run_l[h];
+    for (int d = 0; d < DPV; d++) red[(wq * G + hh) * HD + lane * DPV + d] = o[h][d];
+    if (lane == 0) ml[(wq * G + hh) * 2] = run_m[h], ml[(wq * G + hh) * 2 + 1] = run_l[h];
   }
   __syncthreads();
   // final values of this KV head's G heads: directly when one split held everything, else through the partials
   // buffer, merged by the last split to arrive
   const size_t rec = HD + 2;
-  for (int e = threadIdx.x; e < G * HD; e += ATT_THREADS) {
+  for (int e = threadIdx.x; e < G * HD; e += THREADS) {
     const int h = e / HD;
     float M = -INFINITY;
 #pragma unroll
@@ -326,7 +342,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int e = threadIdx.x; e < G * HD; e += ATT_THREADS) {  // merge the A partials in split order
+    for (int e = threadIdx.x; e < G * HD; e += THREADS) {  // merge the A partials in split order
       const float *pr = a.part + ((size_t)t * a.n_head + (size_t)g * G + e / HD) * S * rec;
       float M = -INFINITY;
       for (uint32_t k = 0; k < A; k++) M = fmaxf(M, __ldcg(pr + k * rec));
@@ -345,7 +361,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
   float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
   uint8_t *oqt = a.oq ? a.oq + a.oq_stride * t : nullptr;
   const uint32_t nbq = a.n_head * HD / 32u;
-  for (int b = warp; b < G * HD / 32; b += ATT_WARPS) {
+  for (int b = warp; b < G * HD / 32; b += ATT_WARPS * HS) {
     const float v = fin[32 * b + lane];
     ot[32 * b + lane] = v;
     if (oqt) quant_block_warp(v, oqt, nbq, g * (G * HD / 32u) + b, lane);
@@ -355,12 +371,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
 
 template <typename KV, int HD, int G, bool FUSED>
 static int launch_attn(const AttnArgs &a, uint32_t T, cudaStream_t st) {
+  constexpr int HS = (G % 2 == 0) ? 2 : 1;
   const size_t tile = (size_t)AttGeom<KV, HD>::NB * AttGeom<KV, HD>::TILE_BYTES + (size_t)ATT_WARPS * (ATT_TILE / ATT_WARPS) * G * sizeof(float);
   const size_t red = (size_t)((ATT_WARPS + 1) * G * HD + ATT_WARPS * G * 2) * sizeof(float);
   const size_t smem = tile > red ? tile : red;
-  auto k = attn_decode_kernel<KV, HD, G, FUSED>;
+  auto k = attn_decode_kernel<KV, HD, G, FUSED, HS>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
-  IEB_LAUNCH_PDL("attn_decode_kernel", k, dim3(a.S, a.n_kv, T), dim3(ATT_THREADS), smem, st, a);
+  IEB_LAUNCH_PDL("attn_decode_kernel", k, dim3(a.S, a.n_kv, T), dim3(ATT_THREADS * HS), smem, st, a);
   return IE_B200_OK;
 }
 

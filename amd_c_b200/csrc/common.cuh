@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "ie_b200.h"
 
@@ -94,26 +95,22 @@ struct TlRec {
   unsigned long long t;
   uint32_t tag, cta;
 };
-constexpr uint32_t TL_CAP = 1u << 16;
+// A record goes to the slot its own time stamp names (32 ns per slot, a window of 8 ms): one plain store, no
+// atomic whose round trip would stretch the phase being measured. Two marks in the same 32 ns lose one.
+constexpr uint32_t TL_CAP = 1u << 18;
 static __device__ TlRec tl_buf[TL_CAP];
-static __device__ uint32_t tl_n;
+__device__ __forceinline__ void tl_put(uint32_t kernel, uint32_t phase, uint32_t who) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  tl_buf[(uint32_t)(t >> 5) & (TL_CAP - 1u)] = TlRec{t, kernel << 8 | phase, who};
+}
 __device__ __forceinline__ void tl_mark(uint32_t kernel, uint32_t phase) {
   const bool first = (blockIdx.x | blockIdx.y | blockIdx.z) == 0u;
   const bool last = blockIdx.x == gridDim.x - 1u && blockIdx.y == gridDim.y - 1u && blockIdx.z == gridDim.z - 1u;
-  if ((threadIdx.x | threadIdx.y) == 0u && (first || last)) {
-    const uint32_t i = atomicAdd(&tl_n, 1u);
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    if (i < TL_CAP) tl_buf[i] = TlRec{t, kernel << 8 | phase, first ? 0u : 1u};
-  }
+  if ((threadIdx.x | threadIdx.y) == 0u && (first || last)) tl_put(kernel, phase, first ? 0u : 1u);
 }
 // one record from the calling thread, whatever its CTA
-__device__ __forceinline__ void tl_mark_any(uint32_t kernel, uint32_t phase) {
-  const uint32_t i = atomicAdd(&tl_n, 1u);
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  if (i < TL_CAP) tl_buf[i] = TlRec{t, kernel << 8 | phase, 2u};
-}
+__device__ __forceinline__ void tl_mark_any(uint32_t kernel, uint32_t phase) { tl_put(kernel, phase, 2u); }
 #else
 __device__ __forceinline__ void tl_mark(uint32_t, uint32_t) {}
 __device__ __forceinline__ void tl_mark_any(uint32_t, uint32_t) {}
@@ -123,13 +120,14 @@ __device__ __forceinline__ void tl_mark_any(uint32_t, uint32_t) {}
 // host side: every source file registers a reader of its own buffer
 void tl_register(uint32_t (*reader)(void *out, uint32_t cap));
 static uint32_t tl_read_tu(void *out, uint32_t cap) {
+  static TlRec *host = nullptr;
+  if (!host) host = static_cast<TlRec *>(malloc(sizeof(TlRec) * TL_CAP));
+  if (!host || cudaMemcpyFromSymbol(host, tl_buf, sizeof(TlRec) * TL_CAP) != cudaSuccess) return 0;
   uint32_t n = 0;
-  if (cudaMemcpyFromSymbol(&n, tl_n, 4) != cudaSuccess) return 0;
-  if (n > TL_CAP) n = TL_CAP;
-  if (n > cap) n = cap;
-  if (n) cudaMemcpyFromSymbol(out, tl_buf, (size_t)n * sizeof(TlRec));
-  const uint32_t zero = 0;
-  cudaMemcpyToSymbol(tl_n, &zero, 4);
+  for (uint32_t i = 0; i < TL_CAP && n < cap; i++)
+    if (host[i].t) static_cast<TlRec *>(out)[n++] = host[i];
+  void *dev = nullptr;
+  if (cudaGetSymbolAddress(&dev, tl_buf) == cudaSuccess) cudaMemset(dev, 0, sizeof(TlRec) * TL_CAP);
   return n;
 }
 namespace {

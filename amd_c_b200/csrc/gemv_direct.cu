@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
     }
   }
   tl_mark(TL_GEMV, 15);
+  if (threadIdx.x == 0) tl_mark_any(TL_GEMV, 14);  // every CTA's exit (timeline builds)
 }
 
 template <int KIND, bool NORM, int R, int U, int MINB, bool TP>
