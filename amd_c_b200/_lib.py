@@ -28,6 +28,7 @@ SIGNATURES = {
     "ie_b200_repack_ref": (_int, [_int, _vp, _vp, _u32, _u32, _vp, _vp]),
     "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
     "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
+    "ie_b200_gemm": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_gemv_norm_tail": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),

@@ -67,6 +67,7 @@ struct ie_b200_engine {
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
   uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[2..3]: the GEMVs' work and arrival counters
   bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
+  bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
   ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
@@ -120,6 +121,10 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       const float *bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr;
       if (T == 1 && stream_ok(m))
         return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), e->err, e->err + 2, st);
+      // a prompt chunk (the reference's threshold, src/hip.c:965): the tensor-core GEMM reads the weights once per 128 tokens
+      if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm)
+        return ie_b200_gemm(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
+                            o.res_stride, st);
       return ie_b200_gemv(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
                           o.res_stride, st);
     }
@@ -329,6 +334,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->err, 16), "cudaMalloc(error word)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
+  if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");

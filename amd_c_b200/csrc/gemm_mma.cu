@@ -1,0 +1,174 @@
+// gemm_mma.cu -- the prompt-chunk GEMM: Y[T x rows] = Q8(X)[T x cols] . W^T for the quantised kinds, T >= 17.
+//
+// One int8 tensor-core instruction (mma.sync m16n8k32, s8 x s8 -> s32) covers exactly one 32-weight quant block
+// for 16 weight rows x 8 tokens, so its result IS the exact int32 block dot of the reference; the per-block
+// scales are applied in fp32 right in the registers that hold it (acc = fma(sw * da, (float)dot, acc), or the
+// Q4_K / Q6_K nestings of the GEMV), block after block in order. That fp32 work, not the tensor pipe, bounds
+// the kernel (3-4 ALU operations per 32 MACs), which is why the dots stay in registers (mma.sync) instead of
+// travelling through tensor memory. Results equal the one-token GEMV's to fp32 rounding (the order of the
+// per-block sums differs: all blocks in sequence here, lane-strided + tree there), as in the reference
+// (kernels/ie_kernels.c:1315-1465: "not bitwise vs GEMV").
+//
+// The streaming row layout needs no staging: the lane that owns columns 4t..4t+3 and 16+4t..19+4t of a row in
+// the A fragment needs exactly nibble word t of the block (low nibbles = the first, high nibbles = the second),
+// one 4-byte load; the B fragment is two 4-byte loads from a token's Q8 row. CTA = 8 warps as 2 (rows) x 4
+// (tokens), warp tile 32 rows x 32 tokens, CTA tile 64 rows x 128 tokens.
+#include "common.cuh"
+
+namespace ieb {
+
+constexpr int GM_MT = 2, GM_NT = 4;  // 16-row and 8-token tiles per warp
+constexpr int GM_ROWS = 2 * 16 * GM_MT, GM_TOKS = 4 * 8 * GM_NT;
+
+struct GemmArgs {
+  const uint8_t *w;
+  size_t rowb;
+  uint32_t rows, nb, T;
+  const uint8_t *xq;
+  float *y;
+  const float *bias, *res;
+  size_t xs, ys, rs;
+};
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256, 2) gemm_mma_kernel(const GemmArgs a) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const uint32_t row0 = blockIdx.x * GM_ROWS + (warp & 1) * 16 * GM_MT, tok0 = blockIdx.y * GM_TOKS + (warp >> 1) * 8 * GM_NT;
+  if (row0 >= a.rows || tok0 >= a.T) return;
+  const uint32_t nb = a.nb;
+  // rows of the A fragments (g and g + 8 of each 16-row tile) and tokens of the B fragments (g) and of the C
+  // fragments (2t, 2t + 1), clamped into range: out-of-range rows / tokens compute a copy that is never stored
+  const uint8_t *rp[GM_MT][2];
+#pragma unroll
+  for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+    for (int h = 0; h < 2; h++) rp[i][h] = a.w + (size_t)min(row0 + 16u * i + 8u * h + g, a.rows - 1u) * a.rowb;
+  uint32_t ob[GM_NT], oc[GM_NT][2];
+#pragma unroll
+  for (int j = 0; j < GM_NT; j++) {
+    ob[j] = (uint32_t)(min(tok0 + 8u * j + g, a.T - 1u) * a.xs);
+    oc[j][0] = (uint32_t)(min(tok0 + 8u * j + 2u * t, a.T - 1u) * a.xs), oc[j][1] = (uint32_t)(min(tok0 + 8u * j + 2u * t + 1u, a.T - 1u) * a.xs);
+  }
+  float acc[GM_MT][GM_NT][4];
+#pragma unroll
+  for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+    for (int j = 0; j < GM_NT; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) acc[i][j][e] = 0.0f;
+
+  for (uint32_t b = 0; b < nb; b++) {
+    // ---- the tokens' side of block b
+    uint32_t bq[GM_NT][2];
+    float da[GM_NT][2], das[GM_NT][2];
+#pragma unroll
+    for (int j = 0; j < GM_NT; j++) {
+      const uint8_t *q = a.xq + ob[j] + 32u * b + 4u * t;
+      bq[j][0] = *reinterpret_cast<const uint32_t *>(q), bq[j][1] = *reinterpret_cast<const uint32_t *>(q + 16);
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        da[j][e] = *reinterpret_cast<const float *>(a.xq + oc[j][e] + 32u * (size_t)nb + 4u * b);
+        das[j][e] = 0.0f;
+        if (KIND == IE_B200_MAT_Q4K) das[j][e] = __fmul_rn(da[j][e], (float)*reinterpret_cast<const int *>(a.xq + oc[j][e] + 36u * (size_t)nb + 4u * b));
+      }
+    }
+    // ---- the rows' side, one 16-row tile at a time, and the products
+#pragma unroll
+    for (int i = 0; i < GM_MT; i++) {
+      uint32_t wl[2], wh[2];  // the A fragment: columns 4t.. (low nibbles) and 16 + 4t.. (high nibbles) of rows g, g + 8
+      float s0[2], s1[2];     // per row: Q4_0 d; Q4_K d * sc and dmin * mn; Q6_K d * sc0 and d * sc1
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const uint8_t *r = rp[i][h];
+        const uint32_t wv = *reinterpret_cast<const uint32_t *>(r + 16u * (size_t)b + 4u * t);
+        if (KIND == IE_B200_MAT_Q4) {
+          wl[h] = __vsub4(wv & 0x0F0F0F0Fu, 0x08080808u), wh[h] = __vsub4((wv >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+          s0[h] = h2f(*reinterpret_cast<const uint16_t *>(r + 16u * (size_t)nb + 2u * b)), s1[h] = 0.0f;
+        } else if (KIND == IE_B200_MAT_Q4K) {
+          wl[h] = wv & 0x0F0F0F0Fu, wh[h] = (wv >> 4) & 0x0F0F0F0Fu;
+          const uint4 hd = *reinterpret_cast<const uint4 *>(r + 16u * (size_t)nb + 16u * (b >> 3));
+          const uint32_t f = q4k_field(hd, (int)(b & 7u));
+          s0[h] = __fmul_rn(h2f((uint16_t)(hd.x & 0xFFFFu)), (float)(f & 63u));
+          s1[h] = __fmul_rn(h2f((uint16_t)(hd.x >> 16)), (float)(f >> 6));
+        } else {
+          const uint2 hw = *reinterpret_cast<const uint2 *>(r + 16u * (size_t)nb + 8u * b);
+          wl[h] = (uint32_t)q6_sw(wv & 0x0F0F0F0Fu, hw.x, t), wh[h] = (uint32_t)q6_sw((wv >> 4) & 0x0F0F0F0Fu, hw.y, t);
+          const uint16_t sc = *reinterpret_cast<const uint16_t *>(r + 24u * (size_t)nb + 2u * b);
+          const float df = h2f(*reinterpret_cast<const uint16_t *>(r + 26u * (size_t)nb + 2u * (b >> 3)));
+          s0[h] = __fmul_rn(df, (float)(int8_t)(sc & 255u)), s1[h] = __fmul_rn(df, (float)(int8_t)(sc >> 8));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < GM_NT; j++) {
+        int c[4];
+        if (KIND == IE_B200_MAT_Q6K) {  // the two 16-weight halves have scales of their own: two products with the other half zeroed
+          int c2[4];
+          mma_s8(c, wl[0], wl[1], 0u, 0u, bq[j][0], bq[j][1]);
+          mma_s8(c2, 0u, 0u, wh[0], wh[1], bq[j][0], bq[j][1]);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int h = e >> 1, tk = e & 1;
+            acc[i][j][e] = __fmaf_rn(__fmaf_rn(s1[h], (float)c2[e], __fmul_rn(s0[h], (float)c[e])), da[j][tk], acc[i][j][e]);
+          }
+        } else {
+          mma_s8(c, wl[0], wl[1], wh[0], wh[1], bq[j][0], bq[j][1]);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int h = e >> 1, tk = e & 1;  // C fragment: e = 0, 1: row g, tokens 2t, 2t + 1; e = 2, 3: row g + 8
+            if (KIND == IE_B200_MAT_Q4) acc[i][j][e] = __fmaf_rn(__fmul_rn(s0[h], da[j][tk]), (float)c[e], acc[i][j][e]);
+            else acc[i][j][e] = __fmaf_rn(-s1[h], das[j][tk], __fmaf_rn(__fmul_rn(s0[h], (float)c[e]), da[j][tk], acc[i][j][e]));
+          }
+        }
+      }
+    }
+  }
+  // ---- y = acc (+ bias[row]); y = res + y
+#pragma unroll
+  for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+    for (int j = 0; j < GM_NT; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t row = row0 + 16u * i + 8u * (e >> 1) + g, tok = tok0 + 8u * j + 2u * t + (e & 1);
+        if (row < a.rows && tok < a.T) {
+          float o = acc[i][j][e];
+          if (a.bias) o = __fadd_rn(o, a.bias[row]);
+          if (a.res) o = __fadd_rn(reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.res) + a.rs * tok)[row], o);
+          reinterpret_cast<float *>(reinterpret_cast<char *>(a.y) + a.ys * tok)[row] = o;
+        }
+      }
+}
+
+}  // namespace ieb
+
+using namespace ieb;
+
+extern "C" int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
+                            const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream) {
+  if (!d_w || !d_xq || !d_y) return fail(IE_B200_E_ARG, "ie_b200_gemm: NULL pointer");
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemm: matrix kind %d (Q4_0, Q4_K, Q6_K)", kind);
+  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u)) return fail(IE_B200_E_SIZE, "ie_b200_gemm: %u columns", cols);
+  if (rows == 0 || T == 0) return IE_B200_OK;
+  if (!aligned16(d_w) || ((uintptr_t)d_xq & 3u) || (x_stride & 3u) || (y_stride & 3u) || (res_stride & 3u))
+    return fail(IE_B200_E_ARG, "ie_b200_gemm: the matrix must be 16-byte aligned, activations and strides 4-byte aligned");
+  if ((uint64_t)T * x_stride > 0xFFFFFFFFull) return fail(IE_B200_E_SIZE, "ie_b200_gemm: %u tokens of %zu bytes exceed 4 GB of activations", T, x_stride);
+  GemmArgs a;
+  a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u, a.T = T;
+  a.xq = static_cast<const uint8_t *>(d_xq), a.y = d_y, a.bias = d_bias, a.res = d_res;
+  a.xs = x_stride, a.ys = y_stride, a.rs = res_stride;
+  const dim3 grid((rows + GM_ROWS - 1) / GM_ROWS, (T + GM_TOKS - 1) / GM_TOKS);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (kind) {
+    case IE_B200_MAT_Q4: IEB_LAUNCH_PDL("gemm_mma_kernel", gemm_mma_kernel<IE_B200_MAT_Q4>, grid, dim3(256), 0, st, a); break;
+    case IE_B200_MAT_Q4K: IEB_LAUNCH_PDL("gemm_mma_kernel", gemm_mma_kernel<IE_B200_MAT_Q4K>, grid, dim3(256), 0, st, a); break;
+    default: IEB_LAUNCH_PDL("gemm_mma_kernel", gemm_mma_kernel<IE_B200_MAT_Q6K>, grid, dim3(256), 0, st, a); break;
+  }
+  return IE_B200_OK;
+}

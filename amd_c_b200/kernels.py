@@ -86,6 +86,17 @@ def gemv(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.T
     return y
 
 
+def gemm(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.Tensor | None = None) -> torch.Tensor:
+    """The prompt-chunk form of gemv (tensor cores; equal to gemv to fp32 rounding). x: Q8 buffers [T, 40 nb] uint8."""
+    x2 = x.reshape(-1, x.shape[-1])
+    T = x2.shape[0]
+    y = torch.empty((T, w.rows), dtype=torch.float32, device=x.device)
+    rs = 0 if res is None else res.reshape(T, -1).stride(0) * 4
+    check(_lib.load().ie_b200_gemm(w.kind, w.data.data_ptr(), w.rows, w.cols, x2.data_ptr(), y.data_ptr(), _p(bias), _p(res), T,
+                                   x2.stride(0) * x2.element_size(), w.rows * 4, rs, _stream()))
+    return y
+
+
 def gemv_stream(w: Mat, xq: torch.Tensor, bias=None, res=None, err: torch.Tensor | None = None, work: torch.Tensor | None = None) -> torch.Tensor:
     """The one-token decode GEMV (same result as gemv with one row). work: two zeroed int32 for dynamic row scheduling."""
     y = torch.empty((1, w.rows), dtype=torch.float32, device=xq.device)

@@ -207,16 +207,16 @@ def build_backend(cfg, n_ctx: int, tp: int, rank: int, device):
 
 
 def time_gemvs(b, reps: int = 20) -> dict:
-    """The GEMV kernels of one step (with their fused norm prologues), in op-list order on the real matrices,
-    captured into a graph and timed with CUDA events on the capturing stream. Every pass streams all weights
-    (4.2 GB), so nothing is served from L2."""
+    """The GEMV kernels of one step alone, in op-list order on the real matrices (a chain of dependent launches, as
+    in the step), captured into a graph and timed with CUDA events on the capturing stream. Every pass streams all
+    weights (4.2 GB), so nothing is served from L2."""
     import torch
 
     from amd_c_b200 import _lib
-    from amd_c_b200.backend import OP_GEMV, OP_RMSNORM
+    from amd_c_b200.backend import OP_GEMV
 
     lib = _lib.load()
-    mask = (1 << OP_GEMV) | (1 << OP_RMSNORM)
+    mask = 1 << OP_GEMV
     s = torch.cuda.Stream(device=b.device)
     with torch.cuda.device(b.device), torch.cuda.stream(s):
         before = lib.ie_b200_launch_count()
@@ -237,6 +237,86 @@ def time_gemvs(b, reps: int = 20) -> dict:
         s.synchronize()
     ms = e0.elapsed_time(e1) / reps
     return {"ms_per_pass": ms, "launches": int(launches), "bytes": b.weight_bytes_per_token}
+
+
+# dram bytes read / algorithmic bytes of the decode GEMV, from the ncu capture summarised in
+# profiles/gemv_direct_q4_0_14336x4096_ncu_full.md (33.095 MB read, nothing written, for 33.030 MB of blocks)
+NCU_TRAFFIC_RATIO = 33.095 / 33.030
+SWEEP_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
+
+
+def time_gemv_sweep(device, peak: float) -> list[dict]:
+    """The stand-alone Q4_0 x Q8 GEMV at the Llama-3-8B shapes: seeded N(0, 0.02) weights, >= 1 GB of rotated copies
+    per shape (nothing is served from L2), 20 warm-up + 200 timed launches in one graph between two CUDA events."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+    from amd_c_b200 import synth
+
+    gen = torch.Generator(device=device).manual_seed(0)
+    out = []
+    s = torch.cuda.Stream(device=device)
+    for rows, cols in SWEEP_SHAPES:
+        raw = synth.q4_0_normal_torch(gen, rows, cols, device=device)
+        m = K.Mat.from_gguf(synth.GGML_Q4_0, raw.reshape(-1), rows, cols)
+        del raw
+        ncopy = max(4, min(64, int(1.2e9 // m.data.numel())))
+        copies = [K.Mat(m.kind, rows, cols, m.data.clone()) for _ in range(ncopy)]
+        xq = K.quant_q8(torch.randn(1, cols, device=device, generator=gen))
+        n = 200
+        with torch.cuda.stream(s):
+            for i in range(20):
+                K.gemv_stream(copies[i % ncopy], xq)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for i in range(n):
+                    K.gemv_stream(copies[i % ncopy], xq)
+            g.replay()
+            s.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            s.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        gbs = m.algorithmic_bytes / us / 1e3
+        out.append({"shape": f"{rows}x{cols}", "us": round(us, 2), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3),
+                    "frac_of_nominal_8000": round(gbs / 8000.0, 3), "copies": ncopy})
+        del copies, m, g
+        torch.cuda.empty_cache()
+    return out
+
+
+def time_prefill_gemm(device) -> dict:
+    """The prompt-chunk GEMM on the Qwen2-7B Q4_K_M FFN shapes, one chunk of 256 tokens: int8 tensor-core block dots +
+    fp32 scaling. Reported as 2 * rows * cols * T / time; the tensor peak is not the bound of this kernel (the per-block
+    fp32 scaling is), the figure is here for the record."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+    from amd_c_b200 import synth
+
+    gen = torch.Generator(device=device).manual_seed(3)
+    out = {}
+    for name, typ, rows, cols in (("q4_k 37888x3584", synth.GGML_Q4_K, 37888, 3584), ("q6_k 3584x18944", synth.GGML_Q6_K, 3584, 18944)):
+        raw = synth.k_random_torch(typ, gen, rows, cols, device=device)
+        m = K.Mat.from_gguf(typ, raw.reshape(-1), rows, cols)
+        xq = K.quant_q8(torch.randn(256, cols, device=device, generator=gen))
+        for _ in range(3):
+            K.gemm(m, xq)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            K.gemm(m, xq)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / 10
+        out[name] = {"T": 256, "us": round(ms * 1e3, 1), "TFLOP/s": round(2.0 * rows * cols * 256 / ms / 1e9, 1)}
+        del m, raw
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_ours_single(args, cfg) -> dict:
@@ -283,13 +363,20 @@ def run_ours_single(args, cfg) -> dict:
         "value": K / (ms * 1e-3), "ms_per_step": ms / K, "gpu_launches": int(launches),
         "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 12},
         "roofline": {"bound": "hbm", "kernel": "gemv (Q4_0 x Q8, decode)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": f"{peak_src} copy bandwidth", "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
+                     "peak_source": f"{peak_src} copy bandwidth", "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": gem["bytes"] * NCU_TRAFFIC_RATIO / max(1, gem["launches"]),
+                     "traffic_note": "dram bytes per launch: the ncu capture of one 14336x4096 launch (1.002 x its algorithmic bytes) scaled to the average launch",
+                     "algorithmic_bytes_per_launch": gem["bytes"] / max(1, gem["launches"]),
                      "launches_per_step": gem["launches"], "avg_launch_us": gem["ms_per_pass"] * 1e3 / max(1, gem["launches"]),
-                     "algorithmic_bytes_per_step": gem["bytes"]},
+                     "algorithmic_bytes_per_step": gem["bytes"],
+                     "scope": "all GEMV launches of one decode step, back to back in step order (dependent chain, real matrices)"},
         "step_weight_gb_per_s": b.weight_bytes_per_token / (ms / K * 1e-3) / 1e9,
         "launches_per_step": b.launches_per_step, "clocks": clocks,
     }
     b.close()
+    torch.cuda.empty_cache()
+    res["roofline"]["gemv_sweep"] = time_gemv_sweep(dev, peak)
+    res["prefill_gemm"] = time_prefill_gemm(dev)
     return res
 
 

@@ -94,6 +94,15 @@ int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_
 int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
                  const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
 
+/* The prompt-chunk GEMM: y[T][rows] = W Q8(x) (+bias) (+res) for T >= 17 tokens with the weights read once
+ * per 128 tokens; the role of ie_gemm_q4kr / ie_gemm_q6kr (kernels/ie_kernels.c:1315-1465, :2015-2158;
+ * dispatch src/hip.c:965-1003), for MAT_Q4 as well. Every 32-weight block dot is one int8 tensor-core product
+ * (exact int32, as the reference's MMA trick), scaled in fp32 block after block; the result equals
+ * ie_b200_gemv's to fp32 rounding (the order of the block sums differs), not bit for bit -- as in the
+ * reference. Same operands as ie_b200_gemv (Q8 buffers per token; strides in bytes, multiples of 4). */
+int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
+                 const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
+
 /* The one-token GEMV of a decode step, same result as ie_b200_gemv with T = 1: the row panels stream through a
  * shared-memory ring filled by bulk asynchronous copies, and the launch uses programmatic dependent launch, so
  * the ring fills while the previous kernel of the stream still runs (the weights do not depend on it; the

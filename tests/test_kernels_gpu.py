@@ -492,3 +492,30 @@ def test_gemv_allreduce_norm_one_rank(ora, cuda, lib, typ, rows, cols):
             assert int(err.item()) == 0
     finally:
         lib.ie_b200_ar_destroy(h)
+
+
+@pytest.mark.parametrize("typ,rows,cols,T", [(synth.GGML_Q4_0, 256, 256, 17), (synth.GGML_Q4_0, 1000, 4096, 100), (synth.GGML_Q4_K, 3584, 3584, 256),
+                                             (synth.GGML_Q6_K, 512, 1024, 131), (synth.GGML_Q4_K, 96, 512, 40)])
+def test_gemm_matches_gemv(ora, cuda, typ, rows, cols, T):
+    """The prompt-chunk GEMM (int8 tensor-core block dots, fp32 scaling in block order) against the multi-token GEMV,
+    which is bit-exact with the CPU reference: equal to fp32 rounding (1e-5 of the largest output; the reference's own
+    GEMM is "not bitwise" against its GEMV either), with bias and residual, ragged row and token counts."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows * 7 + cols + T)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    x = dev(rng.standard_normal((T, cols)).astype(np.float32), cuda)
+    xq = K.quant_q8(x)
+    bias = dev(rng.standard_normal(rows).astype(np.float32), cuda)
+    res = dev(rng.standard_normal((T, rows)).astype(np.float32), cuda)
+    want = K.gemv(m, xq, bias=bias, res=res).cpu().numpy()
+    got = K.gemm(m, xq, bias=bias, res=res).cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    # one token of it against the oracle itself
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    t = T // 2
+    ref = ora.gemv(kind, qw, qs, rows, cols, xq[t].cpu().numpy(), bias=bias.cpu().numpy(), res=res[t].cpu().numpy())
+    assert np.abs(got[t] - ref).max() <= 1e-5 * np.abs(ref).max()
