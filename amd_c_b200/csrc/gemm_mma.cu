@@ -13,6 +13,8 @@
 // the A fragment needs exactly nibble word t of the block (low nibbles = the first, high nibbles = the second),
 // one 4-byte load; the B fragment is two 4-byte loads from a token's Q8 row. CTA = 8 warps as 2 (rows) x 4
 // (tokens), warp tile 32 rows x 32 tokens, CTA tile 64 rows x 128 tokens.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ieb {
@@ -146,6 +148,208 @@ __global__ void __launch_bounds__(256, 2) gemm_mma_kernel(const GemmArgs a) {
       }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// The staged form (the default): the same arithmetic, operands brought into shared memory by 16 / 8 / 4-byte
+// asynchronous copies, three stages of four quant blocks each in flight, so the warps read fragments at
+// shared-memory latency instead of waiting on L2. Rows are padded to strides (80 B of nibbles, 144 B of int8
+// activations, 40 B of Q6_K high-bit words) that spread the eight rows / tokens of a fragment over all 32 banks.
+// Needs nb % 4 == 0 and 16-byte aligned token rows; other shapes take the direct kernel above.
+constexpr int GS_KB = 4, GS_STAGES = 3, GS_WS = 80, GS_XS = 144, GS_HS = 40;
+
+template <int KIND>
+struct GsLay {
+  static constexpr int W = 0;                                   // [64 rows][80 B]: 4 blocks of 16 B nibbles
+  static constexpr int SC = W + GM_ROWS * GS_WS;                // Q4_0: [64][4 f16]; Q4_K: [64][16 B header]; Q6_K: [64][4 u16]
+  static constexpr int SC_BYTES = KIND == IE_B200_MAT_Q4K ? GM_ROWS * 16 : GM_ROWS * 8;
+  static constexpr int HI = SC + SC_BYTES;                      // Q6_K: [64][40 B]: 4 blocks of 8 B high-bit words
+  static constexpr int HI_BYTES = KIND == IE_B200_MAT_Q6K ? GM_ROWS * GS_HS : 0;
+  static constexpr int X = HI + HI_BYTES;                       // [128 tokens][144 B]: 4 blocks of 32 int8
+  static constexpr int DA = X + GM_TOKS * GS_XS;                // [4 blocks][128 tokens] f32
+  static constexpr int AS = DA + GS_KB * GM_TOKS * 4;           // [4 blocks][128 tokens] i32
+  static constexpr int STAGE = AS + GS_KB * GM_TOKS * 4;
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int KIND>
+__global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
+  using L = GsLay<KIND>;
+  extern __shared__ uint4 gs_smem[];
+  uint8_t *sm = reinterpret_cast<uint8_t *>(gs_smem);
+  pdl_prologue();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int wm = warp & 1, wn = warp >> 1;  // warp tile: rows wm * 32 .., tokens wn * 32 .. of the CTA tile
+  const uint32_t row0 = blockIdx.x * GM_ROWS, tok0 = blockIdx.y * GM_TOKS, nb = a.nb;
+  const uint32_t n_steps = nb / GS_KB;
+
+  // what this thread copies per stage (rows / tokens past the end repeat the last one; their results are not stored)
+  const uint8_t *w_src = a.w + (size_t)min(row0 + (tid >> 2), a.rows - 1u) * a.rowb;  // row tid / 4, 16-byte piece tid % 4
+  const uint8_t *x_src[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) x_src[i] = a.xq + (size_t)min(tok0 + ((tid + 256 * i) >> 3), a.T - 1u) * a.xs;
+  const uint8_t *s_src = a.xq + (size_t)min(tok0 + (tid & 127), a.T - 1u) * a.xs;  // scales of token tid % 128, blocks (tid / 128) and + 2
+  auto issue = [&](uint32_t step) {
+    if (step < n_steps) {
+      uint8_t *st = sm + (step % GS_STAGES) * L::STAGE;
+      const uint32_t b0 = step * GS_KB;
+      cp_async16(st + L::W + (tid >> 2) * GS_WS + (tid & 3) * 16, w_src + 16u * (size_t)(b0 + (tid & 3)));
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int item = tid + 256 * i;
+        cp_async16(st + L::X + (item >> 3) * GS_XS + (item & 7) * 16, x_src[i] + 32u * (size_t)b0 + 16u * (item & 7));
+      }
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int kb = (tid >> 7) + 2 * i, tk = tid & 127;
+        cp_async4(st + L::DA + (kb * GM_TOKS + tk) * 4, s_src + 32u * (size_t)nb + 4u * (b0 + kb));
+        if (KIND == IE_B200_MAT_Q4K) cp_async4(st + L::AS + (kb * GM_TOKS + tk) * 4, s_src + 36u * (size_t)nb + 4u * (b0 + kb));
+      }
+      if (KIND == IE_B200_MAT_Q4) {
+        if (tid < GM_ROWS) cp_async8(st + L::SC + tid * 8, a.w + (size_t)min(row0 + tid, a.rows - 1u) * a.rowb + 16u * (size_t)nb + 2u * b0);
+      } else if (KIND == IE_B200_MAT_Q4K) {
+        if (tid < GM_ROWS) cp_async16(st + L::SC + tid * 16, a.w + (size_t)min(row0 + tid, a.rows - 1u) * a.rowb + 16u * (size_t)nb + 16u * (b0 >> 3));
+      } else {
+        cp_async8(st + L::HI + (tid >> 2) * GS_HS + (tid & 3) * 8, w_src + 16u * (size_t)nb + 8u * (size_t)(b0 + (tid & 3)));
+        if (tid < GM_ROWS) cp_async8(st + L::SC + tid * 8, a.w + (size_t)min(row0 + tid, a.rows - 1u) * a.rowb + 24u * (size_t)nb + 2u * b0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float acc[GM_MT][GM_NT][4];
+#pragma unroll
+  for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+    for (int j = 0; j < GM_NT; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) acc[i][j][e] = 0.0f;
+  // Q6_K: the f16 super-block scale of this lane's four rows (it changes every 8 blocks = 2 steps), read from global
+  const uint8_t *drow[GM_MT][2];
+  float dq6[GM_MT][2];
+  if (KIND == IE_B200_MAT_Q6K) {
+#pragma unroll
+    for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+      for (int h = 0; h < 2; h++)
+        drow[i][h] = a.w + (size_t)min(row0 + wm * 32 + 16 * i + 8 * h + g, a.rows - 1u) * a.rowb + 26u * (size_t)nb;
+  }
+
+#pragma unroll
+  for (int s = 0; s < GS_STAGES - 1; s++) issue(s);
+  for (uint32_t step = 0; step < n_steps; step++) {
+    cp_async_wait<GS_STAGES - 2>();
+    __syncthreads();  // step's stage is complete for everybody, and everybody is done with the stage refilled next
+    issue(step + GS_STAGES - 1);
+    const uint8_t *st = sm + (step % GS_STAGES) * L::STAGE;
+    if (KIND == IE_B200_MAT_Q6K && (step & 1u) == 0u) {
+#pragma unroll
+      for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) dq6[i][h] = h2f(*reinterpret_cast<const uint16_t *>(drow[i][h] + 2u * (step >> 1)));
+    }
+#pragma unroll
+    for (int kb = 0; kb < GS_KB; kb++) {
+      const uint32_t b = step * GS_KB + kb;
+      uint32_t wl[GM_MT][2], wh[GM_MT][2];
+      float s0[GM_MT][2], s1[GM_MT][2];
+#pragma unroll
+      for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int rl = wm * 32 + 16 * i + 8 * h + g;
+          const uint32_t wv = *reinterpret_cast<const uint32_t *>(st + L::W + rl * GS_WS + kb * 16 + 4 * t);
+          if (KIND == IE_B200_MAT_Q4) {
+            wl[i][h] = __vsub4(wv & 0x0F0F0F0Fu, 0x08080808u), wh[i][h] = __vsub4((wv >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+            s0[i][h] = h2f(*reinterpret_cast<const uint16_t *>(st + L::SC + rl * 8 + 2 * kb)), s1[i][h] = 0.0f;
+          } else if (KIND == IE_B200_MAT_Q4K) {
+            wl[i][h] = wv & 0x0F0F0F0Fu, wh[i][h] = (wv >> 4) & 0x0F0F0F0Fu;
+            const uint4 hd = *reinterpret_cast<const uint4 *>(st + L::SC + rl * 16);
+            const uint32_t f = q4k_field(hd, (int)(b & 7u));
+            s0[i][h] = __fmul_rn(h2f((uint16_t)(hd.x & 0xFFFFu)), (float)(f & 63u));
+            s1[i][h] = __fmul_rn(h2f((uint16_t)(hd.x >> 16)), (float)(f >> 6));
+          } else {
+            const uint2 hw = *reinterpret_cast<const uint2 *>(st + L::HI + rl * GS_HS + kb * 8);
+            wl[i][h] = (uint32_t)q6_sw(wv & 0x0F0F0F0Fu, hw.x, t), wh[i][h] = (uint32_t)q6_sw((wv >> 4) & 0x0F0F0F0Fu, hw.y, t);
+            const uint16_t sc = *reinterpret_cast<const uint16_t *>(st + L::SC + rl * 8 + 2 * kb);
+            s0[i][h] = __fmul_rn(dq6[i][h], (float)(int8_t)(sc & 255u)), s1[i][h] = __fmul_rn(dq6[i][h], (float)(int8_t)(sc >> 8));
+          }
+        }
+#pragma unroll
+      for (int j = 0; j < GM_NT; j++) {
+        const int tl = wn * 32 + 8 * j;
+        const uint8_t *q = st + L::X + (tl + g) * GS_XS + kb * 32 + 4 * t;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(q), b1 = *reinterpret_cast<const uint32_t *>(q + 16);
+        const float2 da2 = *reinterpret_cast<const float2 *>(st + L::DA + (kb * GM_TOKS + tl + 2 * t) * 4);
+        const float da[2] = {da2.x, da2.y};
+        float das[2] = {0.0f, 0.0f};
+        if (KIND == IE_B200_MAT_Q4K) {
+          const int2 as2 = *reinterpret_cast<const int2 *>(st + L::AS + (kb * GM_TOKS + tl + 2 * t) * 4);
+          das[0] = __fmul_rn(da[0], (float)as2.x), das[1] = __fmul_rn(da[1], (float)as2.y);
+        }
+#pragma unroll
+        for (int i = 0; i < GM_MT; i++) {
+          int c[4];
+          if (KIND == IE_B200_MAT_Q6K) {
+            int c2[4];
+            mma_s8(c, wl[i][0], wl[i][1], 0u, 0u, b0, b1);
+            mma_s8(c2, 0u, 0u, wh[i][0], wh[i][1], b0, b1);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int h = e >> 1, tk = e & 1;
+              acc[i][j][e] = __fmaf_rn(__fmaf_rn(s1[i][h], (float)c2[e], __fmul_rn(s0[i][h], (float)c[e])), da[tk], acc[i][j][e]);
+            }
+          } else {
+            mma_s8(c, wl[i][0], wl[i][1], wh[i][0], wh[i][1], b0, b1);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int h = e >> 1, tk = e & 1;
+              if (KIND == IE_B200_MAT_Q4) acc[i][j][e] = __fmaf_rn(__fmul_rn(s0[i][h], da[tk]), (float)c[e], acc[i][j][e]);
+              else acc[i][j][e] = __fmaf_rn(-s1[i][h], das[tk], __fmaf_rn(__fmul_rn(s0[i][h], (float)c[e]), da[tk], acc[i][j][e]));
+            }
+          }
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  // ---- y = acc (+ bias[row]); y = res + y
+#pragma unroll
+  for (int i = 0; i < GM_MT; i++)
+#pragma unroll
+    for (int j = 0; j < GM_NT; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t row = row0 + wm * 32 + 16u * i + 8u * (e >> 1) + g, tok = tok0 + wn * 32 + 8u * j + 2u * t + (e & 1);
+        if (row < a.rows && tok < a.T) {
+          float o = acc[i][j][e];
+          if (a.bias) o = __fadd_rn(o, a.bias[row]);
+          if (a.res) o = __fadd_rn(reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.res) + a.rs * tok)[row], o);
+          reinterpret_cast<float *>(reinterpret_cast<char *>(a.y) + a.ys * tok)[row] = o;
+        }
+      }
+}
+
+template <int KIND>
+static int launch_staged(const GemmArgs &a, dim3 grid, cudaStream_t st) {
+  const size_t smem = (size_t)GS_STAGES * GsLay<KIND>::STAGE;
+  auto k = gemm_staged_kernel<KIND>;
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  IEB_LAUNCH_PDL("gemm_staged_kernel", k, grid, dim3(256), smem, st, a);
+  return IE_B200_OK;
+}
+
 }  // namespace ieb
 
 using namespace ieb;
@@ -165,6 +369,17 @@ extern "C" int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t c
   a.xs = x_stride, a.ys = y_stride, a.rs = res_stride;
   const dim3 grid((rows + GM_ROWS - 1) / GM_ROWS, (T + GM_TOKS - 1) / GM_TOKS);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static const bool direct_only = [] {
+    const char *v = getenv("IE_B200_GEMM_KERNEL");
+    return v && v[0] == 'd';
+  }();
+  if (!direct_only && a.nb % GS_KB == 0 && aligned16(d_xq) && x_stride % 16u == 0) {
+    switch (kind) {
+      case IE_B200_MAT_Q4: return launch_staged<IE_B200_MAT_Q4>(a, grid, st);
+      case IE_B200_MAT_Q4K: return launch_staged<IE_B200_MAT_Q4K>(a, grid, st);
+      default: return launch_staged<IE_B200_MAT_Q6K>(a, grid, st);
+    }
+  }
   switch (kind) {
     case IE_B200_MAT_Q4: IEB_LAUNCH_PDL("gemm_mma_kernel", gemm_mma_kernel<IE_B200_MAT_Q4>, grid, dim3(256), 0, st, a); break;
     case IE_B200_MAT_Q4K: IEB_LAUNCH_PDL("gemm_mma_kernel", gemm_mma_kernel<IE_B200_MAT_Q4K>, grid, dim3(256), 0, st, a); break;
