@@ -14,6 +14,8 @@
 // Bound by HBM at long context: 2 * np * hd * sizeof(KV) bytes per KV head.
 #include <cuda_pipeline_primitives.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ieb {
@@ -64,6 +66,50 @@ constexpr uint32_t ATT_MIN_SPAN = 256;  // positions a split covers at least: sh
 // a * c - b * s and a * s + b * c with every product rounded, as the RoPE kernel and the CPU do
 __device__ __forceinline__ float rope_lo(float a, float b, float c, float s) { return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)); }
 __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)); }
+
+// The last split to arrive merges the A partial records (max, sum, out[hd]) of every head of its KV head, in split
+// order. The weights exp(max_k - max) and the denominators are worked out once in shared memory; the outputs are
+// then summed with eight independent loads in flight per thread (a plain loop over the splits is one L2 round trip
+// per split and per pass: 16 us at 17 splits).
+// part: the records of this token's first head of the KV head, [G][S][hd + 2]; scr: (2 A + 2) G floats of shared memory.
+template <int G, int HD, int THREADS>
+__device__ __forceinline__ void merge_partials(const float *part, uint32_t S, uint32_t A, float *fin, float *scr) {
+  const size_t rec = HD + 2;
+  float *mk = scr, *lk = scr + G * A, *mh = lk + G * A, *lh = mh + G;
+  for (uint32_t i = threadIdx.x; i < G * A; i += THREADS) {
+    const float *pr = part + ((size_t)(i / A) * S + i % A) * rec;
+    mk[i] = __ldcg(pr), lk[i] = __ldcg(pr + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    float M = -INFINITY;
+    for (uint32_t k = 0; k < A; k++) M = fmaxf(M, mk[threadIdx.x * A + k]);
+    mh[threadIdx.x] = M;
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < G * A; i += THREADS) mk[i] = expf(mk[i] - mh[i / A]);  // now the weight of split k
+  __syncthreads();
+  if (threadIdx.x < G) {
+    float L = 0.0f;
+    for (uint32_t k = 0; k < A; k++) L = fmaf(mk[threadIdx.x * A + k], lk[threadIdx.x * A + k], L);
+    lh[threadIdx.x] = L;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * HD; e += THREADS) {
+    const int h = e / HD;
+    const float *pr = part + (size_t)h * S * rec + 2 + (e % HD), *w = mk + h * A;
+    float acc = 0.0f;
+    for (uint32_t k0 = 0; k0 < A; k0 += 8u) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = k0 + j < A ? __ldcg(pr + (size_t)(k0 + j) * rec) : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (k0 + j < A) acc = fmaf(w[k0 + j], v[j], acc);
+    }
+    fin[e] = acc * (1.0f / lh[h]);
+  }
+}
 
 template <typename KV, int HD>
 struct AttGeom {
@@ -342,18 +388,7 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int e = threadIdx.x; e < G * HD; e += THREADS) {  // merge the A partials in split order
-      const float *pr = a.part + ((size_t)t * a.n_head + (size_t)g * G + e / HD) * S * rec;
-      float M = -INFINITY;
-      for (uint32_t k = 0; k < A; k++) M = fmaxf(M, __ldcg(pr + k * rec));
-      float L = 0.0f, acc = 0.0f;
-      for (uint32_t k = 0; k < A; k++) {
-        const float wk = expf(__ldcg(pr + k * rec) - M);
-        L = fmaf(wk, __ldcg(pr + k * rec + 1), L);
-        acc = fmaf(wk, __ldcg(pr + k * rec + 2 + (e % HD)), acc);
-      }
-      fin[e] = acc * (1.0f / L);
-    }
+    merge_partials<G, HD, THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
   }
   __syncthreads();
   tl_mark(TL_ATTN, 5);
@@ -373,12 +408,350 @@ template <typename KV, int HD, int G, bool FUSED>
 static int launch_attn(const AttnArgs &a, uint32_t T, cudaStream_t st) {
   constexpr int HS = (G % 2 == 0) ? 2 : 1;
   const size_t tile = (size_t)AttGeom<KV, HD>::NB * AttGeom<KV, HD>::TILE_BYTES + (size_t)ATT_WARPS * (ATT_TILE / ATT_WARPS) * G * sizeof(float);
-  const size_t red = (size_t)((ATT_WARPS + 1) * G * HD + ATT_WARPS * G * 2) * sizeof(float);
+  const size_t red = (size_t)((ATT_WARPS + 1) * G * HD + ATT_WARPS * G * 2 + (2 * a.S + 2) * G) * sizeof(float);
   const size_t smem = tile > red ? tile : red;
   auto k = attn_decode_kernel<KV, HD, G, FUSED, HS>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
   IEB_LAUNCH_PDL("attn_decode_kernel", k, dim3(a.S, a.n_kv, T), dim3(ATT_THREADS * HS), smem, st, a);
   return IE_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The half-precision-cache form on tensor cores (mma.sync m16n8k16, f16 x f16 -> f32): the scalar kernel above is
+// bound by instruction issue (about 8000 warp instructions per 64-position tile, 830 GB/s at 4096 positions); here
+// a tile is 4 warps x (64 MMAs + 16 ldmatrix), so the kernel waits on HBM only. The cache's f16 K / V rows are the
+// exact operands; the fp32 sides are split into two f16 terms so that nothing is rounded away: q = q_hi + q_lo
+// for S = q . k (two MMAs per step), p = p_hi + p_lo for O = p . v. Layout: S^T = Q[16 heads x hd] . K^T (rows =
+// the G heads, padded with zero rows; columns = positions), whose C fragment is directly the A fragment of
+// P[16 heads x 16 positions] for O[16 heads x hd] += P . V. Each warp owns 16 of the tile's 64 positions and keeps
+// its own running max / sum / output; rows are padded to hd + 8 halves so that the 8 rows of an ldmatrix hit 8
+// different bank groups.
+constexpr int AM_WARPS = 4, AM_THREADS = 128, AM_PAD = 8;
+// NB tile buffers (NB - 1 tiles in flight ahead of the one in use): 4 with one CTA per SM while the splits leave SMs
+// free anyway (short contexts: three of the first four tiles arrive during the kernel before this one), 3 with two
+// CTAs per SM once there are more splits than SMs (long contexts).
+
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// x = hi + lo with hi = f16(x), lo = f16(x - hi): two halves carry 22 bits of the float
+__device__ __forceinline__ void split2(float x, float y, uint32_t &hi, uint32_t &lo) {
+  const __half2 h = __floats2half2_rn(x, y);
+  const float2 hf = __half22float2(h);
+  const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+  hi = *reinterpret_cast<const uint32_t *>(&h), lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+template <int HD, int G, bool FUSED, int NB>
+__global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_kernel(const AttnArgs a) {
+  constexpr int TILE = ATT_TILE, ROW = HD + AM_PAD, TILE_ELEMS = TILE * ROW, KS = HD / 16;
+  static_assert(G <= 8, "the heads of a KV head fill the first 8 rows of the 16-row MMA");
+  extern __shared__ uint4 smem_raw[];
+  __half *kbuf = reinterpret_cast<__half *>(smem_raw);  // [NB][TILE][ROW]
+  __half *vbuf = kbuf + NB * TILE_ELEMS;                // [NB][TILE][ROW]
+  __shared__ uint32_t is_last;
+
+  tl_mark(TL_ATTN, 0);
+  pdl_launch_dependents();
+  const bool early = FUSED && a.early_kv;
+  if (!early) pdl_wait();
+  const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
+  const uint32_t np = *a.pos + t + 1u;
+  uint32_t span = max((np + S - 1u) / S, ATT_MIN_SPAN);
+  span = (span + TILE - 1u) / TILE * TILE;
+  const uint32_t A = (np + span - 1u) / span;
+  if (s >= A) return;
+  const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
+  const bool owns_new = FUSED && s == A - 1u;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hq = lane >> 2, tq = lane & 3;  // hq: the head (MMA row), tq: the column pair
+  const float *qt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * t) + (size_t)g * G * HD;
+  const __half *kh = static_cast<const __half *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const __half *>(a.vc) + (size_t)g * a.kv_len * HD;
+  const uint32_t n_tiles = (p_hi - p_lo + TILE - 1u) / TILE;
+
+  // tile `it` into buffer it % NB: cache rows by 16-byte async copies, rows past the span zero-filled (a zero
+  // probability times an uninitialised value must stay zero), the step's own row left to the registers below
+  constexpr int PER_ROW = HD * 2 / 16, RPP = AM_THREADS / PER_ROW;  // 16-byte pieces per row; rows covered by one pass of the CTA
+  const uint32_t my_piece = (threadIdx.x % PER_ROW) * 16u, my_row = threadIdx.x / PER_ROW;
+  auto issue = [&](uint32_t it) {
+    if (it < n_tiles) {
+      const uint32_t tile_lo = p_lo + it * TILE;
+      const uint32_t have = p_hi - tile_lo;
+      const bool with_new = owns_new && it + 1u == n_tiles;
+      const uint32_t rows = min((uint32_t)TILE, have - (with_new ? 1u : 0u));
+      const char *ks = reinterpret_cast<const char *>(kh + (size_t)tile_lo * HD) + my_piece, *vs = reinterpret_cast<const char *>(vh + (size_t)tile_lo * HD) + my_piece;
+      char *kd = reinterpret_cast<char *>(kbuf + (it % NB) * TILE_ELEMS) + my_piece, *vd = reinterpret_cast<char *>(vbuf + (it % NB) * TILE_ELEMS) + my_piece;
+#pragma unroll
+      for (int j = 0; j < TILE / RPP; j++) {
+        const uint32_t r = my_row + RPP * j;
+        if (with_new && r == have - 1u) continue;  // the new row comes from registers
+        const bool ok = r < rows;
+        const size_t src = ok ? (size_t)r * HD * 2u : 0u;
+        __pipeline_memcpy_async(kd + (size_t)r * ROW * 2u, ks + src, 16, ok ? 0 : 16);
+        __pipeline_memcpy_async(vd + (size_t)r * ROW * 2u, vs + src, 16, ok ? 0 : 16);
+      }
+    }
+    __pipeline_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < NB - 1; i++) issue(i);
+
+  // RoPE table values for this lane's q dims: it holds, for every 16-dim step ks, dims 16 ks + {2tq, 2tq+1, 2tq+8, 2tq+9}.
+  // Pairs (2i, 2i+1) sit side by side; pairs (i, i + hd/2) are steps ks and ks + KS/2 of the same lane.
+  float tc[KS][2], ts[KS][2], kc_ = 0.f, ks_ = 0.f;
+  auto load_tables = [&]() {
+    if (!FUSED) return;
+    const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
+    if (!a.neox) {  // (the other pairing reads its entries where it rotates)
+#pragma unroll
+      for (int k = 0; k < KS; k++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) tc[k][e] = cs[8 * k + tq + 4 * e], ts[k][e] = sn[8 * k + tq + 4 * e];  // pair (16k + 2tq + 8e) / 2
+    }
+    if (owns_new && threadIdx.x < HD / 2) kc_ = cs[threadIdx.x], ks_ = sn[threadIdx.x];
+  };
+  if (early) load_tables();
+  if (early) pdl_wait();
+  tl_mark(TL_ATTN, 1);
+
+  // ---- q of head hq in A-fragment order, rotated when fused, split into two f16 terms
+  float qf[KS][4];
+#pragma unroll
+  for (int k = 0; k < KS; k++) {
+    float2 lo2 = make_float2(0.f, 0.f), hi2 = lo2;
+    if (hq < G) {
+      lo2 = *reinterpret_cast<const float2 *>(qt + hq * HD + 16 * k + 2 * tq);
+      hi2 = *reinterpret_cast<const float2 *>(qt + hq * HD + 16 * k + 2 * tq + 8);
+    }
+    qf[k][0] = lo2.x, qf[k][1] = lo2.y, qf[k][2] = hi2.x, qf[k][3] = hi2.y;
+  }
+  __half newk0 = __half(0.f), newk1 = __half(0.f), newv = __half(0.f);
+  int nk0 = 0, nk1 = 0;
+  if (FUSED) {
+    float x0 = 0.f, x1 = 0.f, vn = 0.f;
+    if (owns_new) {
+      if (threadIdx.x < HD / 2) {
+        const int i = threadIdx.x;
+        nk0 = a.neox ? i : 2 * i, nk1 = a.neox ? i + HD / 2 : 2 * i + 1;
+        x0 = a.k_new[g * HD + nk0], x1 = a.k_new[g * HD + nk1];
+      }
+      if (threadIdx.x < HD) vn = a.v_new[g * HD + threadIdx.x];
+    }
+    if (!early) load_tables();
+    if (!a.neox) {
+#pragma unroll
+      for (int k = 0; k < KS; k++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const float y0 = qf[k][2 * e], y1 = qf[k][2 * e + 1];
+          qf[k][2 * e] = rope_lo(y0, y1, tc[k][e], ts[k][e]), qf[k][2 * e + 1] = rope_hi(y0, y1, tc[k][e], ts[k][e]);
+        }
+    } else {
+      const float *cs = a.cs + (size_t)(np - 1u) * (HD / 2), *sn = a.sn + (size_t)(np - 1u) * (HD / 2);
+#pragma unroll
+      for (int k = 0; k < KS / 2; k++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int i = 16 * k + 2 * tq + (e & 1) + 8 * (e >> 1);  // dim i pairs with dim i + hd/2 (step k + KS/2, same slot)
+          const float c = cs[i], sv = sn[i], y0 = qf[k][e], y1 = qf[k + KS / 2][e];
+          qf[k][e] = rope_lo(y0, y1, c, sv), qf[k + KS / 2][e] = rope_hi(y0, y1, c, sv);
+        }
+    }
+    if (owns_new) {
+      const uint32_t row = (np - 1u) % a.kv_len;
+      if (threadIdx.x < HD / 2) {
+        newk0 = __half(rope_lo(x0, x1, kc_, ks_)), newk1 = __half(rope_hi(x0, x1, kc_, ks_));
+        __half *dst = const_cast<__half *>(kh) + (size_t)row * HD;
+        dst[nk0] = newk0, dst[nk1] = newk1;
+      }
+      if (threadIdx.x < HD) {
+        newv = __half(vn);
+        const_cast<__half *>(vh)[(size_t)row * HD + threadIdx.x] = newv;
+      }
+    }
+  }
+  uint32_t qh[KS][2], ql[KS][2];  // A fragment registers a0, a2 (rows hq); a1, a3 (rows hq + 8) are zero
+#pragma unroll
+  for (int k = 0; k < KS; k++) {
+    split2(qf[k][0], qf[k][1], qh[k][0], ql[k][0]);
+    split2(qf[k][2], qf[k][3], qh[k][1], ql[k][1]);
+  }
+  tl_mark(TL_ATTN, 2);
+
+  float o[HD / 8][4], run_m = -INFINITY, run_l = 0.0f;  // O^T C fragments: o[n][0..1] = head hq, dims 8n + 2tq, + 1
+#pragma unroll
+  for (int n = 0; n < HD / 8; n++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[n][e] = 0.0f;
+  const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: this lane supplies row lr of matrix lm
+  for (uint32_t it = 0; it < n_tiles; it++) {
+    const int buf = it % NB;
+    const uint32_t tile_lo = p_lo + it * TILE;
+    if (owns_new && it + 1u == n_tiles) {  // nobody else writes this row of the buffer
+      const uint32_t pr = np - 1u - tile_lo;
+      if (threadIdx.x < HD / 2) {
+        __half *dk = kbuf + buf * TILE_ELEMS + pr * ROW;
+        dk[nk0] = newk0, dk[nk1] = newk1;
+      }
+      if (threadIdx.x < HD) vbuf[buf * TILE_ELEMS + pr * ROW + threadIdx.x] = newv;
+    }
+    __pipeline_wait_prior(NB - 2);
+    __syncthreads();
+    issue(it + NB - 1u);
+    tl_mark(TL_ATTN, 3);
+    const uint32_t valid = p_hi - tile_lo;
+    const int p0 = warp * 16;  // this warp's positions of the tile
+    if ((uint32_t)p0 < valid) {
+      const __half *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
+      // ---- S^T[heads x 16 positions] = Q . K^T: two column tiles (positions p0.. and p0 + 8..)
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < KS; k++) {
+        uint32_t kb[4];  // matrices: (tile a, dims lo), (tile a, dims hi), (tile b, dims lo), (tile b, dims hi)
+        ldsm4(kb, kt + (p0 + (lm >> 1) * 8 + lr) * ROW + 16 * k + (lm & 1) * 8);
+        mma_f16(sa, qh[k][0], 0u, qh[k][1], 0u, kb[0], kb[1]);
+        mma_f16(sa, ql[k][0], 0u, ql[k][1], 0u, kb[0], kb[1]);
+        mma_f16(sb, qh[k][0], 0u, qh[k][1], 0u, kb[2], kb[3]);
+        mma_f16(sb, ql[k][0], 0u, ql[k][1], 0u, kb[2], kb[3]);
+      }
+      // scores of head hq at positions p0 + 2tq, + 1 (sa[0..1]) and p0 + 8 + 2tq, + 1 (sb[0..1])
+      float sc[4];
+      sc[0] = (uint32_t)(p0 + 2 * tq) < valid ? sa[0] * a.scale : -INFINITY;
+      sc[1] = (uint32_t)(p0 + 2 * tq + 1) < valid ? sa[1] * a.scale : -INFINITY;
+      sc[2] = (uint32_t)(p0 + 8 + 2 * tq) < valid ? sb[0] * a.scale : -INFINITY;
+      sc[3] = (uint32_t)(p0 + 8 + 2 * tq + 1) < valid ? sb[1] * a.scale : -INFINITY;
+      float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const float m_new = fmaxf(run_m, mx), al = expf(run_m - m_new);  // position p0 exists: m_new is finite
+      float pv[4], sum = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; e++) pv[e] = expf(sc[e] - m_new), sum += pv[e];
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+      run_l = run_l * al + sum, run_m = m_new;
+      uint32_t ph[2], pl[2];  // A fragment of P: a0 = positions 2tq, +1; a2 = positions 8 + 2tq, +1 (rows hq)
+      split2(pv[0], pv[1], ph[0], pl[0]);
+      split2(pv[2], pv[3], ph[1], pl[1]);
+      // ---- O[heads x hd] = al * O + P . V, two 8-dim column tiles per ldmatrix
+#pragma unroll
+      for (int u = 0; u < HD / 16; u++) {
+        uint32_t vb[4];  // matrices: (positions lo, dims 16u..), (positions hi, dims 16u..), (positions lo, dims 16u + 8..), (positions hi, ...)
+        ldsm4t(vb, vt + (p0 + (lm & 1) * 8 + lr) * ROW + 16 * u + (lm >> 1) * 8);
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[2 * u][e] *= al, o[2 * u + 1][e] *= al;
+        mma_f16(o[2 * u], ph[0], 0u, ph[1], 0u, vb[0], vb[1]);
+        mma_f16(o[2 * u], pl[0], 0u, pl[1], 0u, vb[0], vb[1]);
+        mma_f16(o[2 * u + 1], ph[0], 0u, ph[1], 0u, vb[2], vb[3]);
+        mma_f16(o[2 * u + 1], pl[0], 0u, pl[1], 0u, vb[2], vb[3]);
+      }
+    }
+  }
+  __pipeline_wait_prior(0);
+  __syncthreads();
+  tl_mark(TL_ATTN, 4);
+
+  // ---- merge the warps' (max, sum, output) in shared memory, reusing the tile buffers
+  float *red = reinterpret_cast<float *>(smem_raw);  // [AM_WARPS][G][HD]
+  float *ml = red + AM_WARPS * G * HD;                // [AM_WARPS][G][2]
+  float *fin = ml + AM_WARPS * G * 2;                 // [G][HD]
+  if (hq < G) {
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) *reinterpret_cast<float2 *>(red + (warp * G + hq) * HD + 8 * n + 2 * tq) = make_float2(o[n][0], o[n][1]);
+    if (tq == 0) ml[(warp * G + hq) * 2] = run_m, ml[(warp * G + hq) * 2 + 1] = run_l;
+  }
+  __syncthreads();
+  const size_t rec = HD + 2;
+  for (int e = threadIdx.x; e < G * HD; e += AM_THREADS) {
+    const int h = e / HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; w++) M = fmaxf(M, ml[(w * G + h) * 2]);
+    float L = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; w++) {
+      const float wk = expf(ml[(w * G + h) * 2] - M);  // a warp without positions has max -inf: weight 0
+      L = fmaf(wk, ml[(w * G + h) * 2 + 1], L);
+      acc = fmaf(wk, red[(w * G + h) * HD + (e % HD)], acc);
+    }
+    if (A == 1u) {
+      fin[e] = acc * (1.0f / L);
+    } else {
+      float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * rec;
+      pr[2 + (e % HD)] = acc;
+      if (e % HD == 0) pr[0] = M, pr[1] = L;
+    }
+  }
+  if (A > 1u) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(&a.count[t * a.n_kv + g], 1u);
+      is_last = prev == A - 1u;
+      if (is_last) a.count[t * a.n_kv + g] = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    merge_partials<G, HD, AM_THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
+  }
+  __syncthreads();
+  tl_mark(TL_ATTN, 5);
+  float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
+  uint8_t *oqt = a.oq ? a.oq + a.oq_stride * t : nullptr;
+  const uint32_t nbq = a.n_head * HD / 32u;
+  for (int b = warp; b < G * HD / 32; b += AM_WARPS) {
+    const float v = fin[32 * b + lane];
+    ot[32 * b + lane] = v;
+    if (oqt) quant_block_warp(v, oqt, nbq, g * (G * HD / 32u) + b, lane);
+  }
+  tl_mark(TL_ATTN, 15);
+}
+
+template <int HD, int G, bool FUSED, int NB>
+static int launch_attn_mma_nb(const AttnArgs &a, uint32_t T, cudaStream_t st) {
+  const size_t tile = (size_t)NB * 2 * ATT_TILE * (HD + AM_PAD) * sizeof(__half);
+  const size_t red = (size_t)((AM_WARPS + 1) * G * HD + AM_WARPS * G * 2 + (2 * a.S + 2) * G) * sizeof(float);
+  const size_t smem = tile > red ? tile : red;
+  auto k = attn_decode_mma_kernel<HD, G, FUSED, NB>;
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  IEB_LAUNCH_PDL("attn_decode_mma_kernel", k, dim3(a.S, a.n_kv, T), dim3(AM_THREADS), smem, st, a);
+  return IE_B200_OK;
+}
+template <int HD, int G, bool FUSED>
+static int launch_attn_mma(const AttnArgs &a, uint32_t T, cudaStream_t st) {
+  if ((uint64_t)a.S * a.n_kv * T > (uint64_t)sm_count()) return launch_attn_mma_nb<HD, G, FUSED, 3>(a, T, st);
+  return launch_attn_mma_nb<HD, G, FUSED, 4>(a, T, st);
+}
+
+// IE_B200_ATTN=scalar keeps the CUDA-core kernel for the half cache as well.
+static bool attn_use_mma() {
+  static const bool on = [] {
+    const char *v = getenv("IE_B200_ATTN");
+    return !(v && v[0] == 's');
+  }();
+  return on;
+}
+
+template <int HD, bool FUSED>
+static int dispatch_g_mma(const AttnArgs &a, uint32_t G, uint32_t T, cudaStream_t st) {
+  switch (G) {
+    case 1: return launch_attn_mma<HD, 1, FUSED>(a, T, st);
+    case 2: return launch_attn_mma<HD, 2, FUSED>(a, T, st);
+    case 4: return launch_attn_mma<HD, 4, FUSED>(a, T, st);
+    case 5: return launch_attn_mma<HD, 5, FUSED>(a, T, st);
+    case 7: return launch_attn_mma<HD, 7, FUSED>(a, T, st);
+    case 8: return launch_attn_mma<HD, 8, FUSED>(a, T, st);
+    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: %u query heads per KV head unsupported (1, 2, 4, 5, 7, 8)", G);
+  }
 }
 
 template <typename KV, int HD, bool FUSED>
@@ -394,11 +767,11 @@ static int dispatch_g(const AttnArgs &a, uint32_t G, uint32_t T, cudaStream_t st
   }
 }
 
-// Splits (grid.x): about one CTA per SM when every split is busy (the tile buffers of a CTA take most of an SM's
-// shared memory), spans of at least ATT_MIN_SPAN positions.
-static uint32_t attn_splits(uint32_t n_kv, uint32_t n_ctx, uint32_t T) {
+// Splits (grid.x): as many as fit the SMs in one wave (ctas_per_sm resident CTAs each; a partial second wave would
+// double the time), spans of at least ATT_MIN_SPAN positions.
+static uint32_t attn_splits(uint32_t n_kv, uint32_t n_ctx, uint32_t T, uint32_t ctas_per_sm) {
   const uint32_t by_len = (n_ctx + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;
-  uint32_t by_sm = ((uint32_t)sm_count() + n_kv * T - 1u) / (n_kv * T);
+  uint32_t by_sm = ctas_per_sm * (uint32_t)sm_count() / (n_kv * T);
   if (by_sm < 1u) by_sm = 1u;
   uint32_t S = by_len < by_sm ? by_len : by_sm;
   return S ? S : 1u;
@@ -414,6 +787,8 @@ static int dispatch_attn(const AttnArgs &a, uint32_t hd, int kv_f32, uint32_t T,
       case 128: return dispatch_g<float, 128, FUSED>(a, G, T, st);
     }
   } else {
+    if (attn_use_mma() && hd == 64) return dispatch_g_mma<64, FUSED>(a, G, T, st);
+    if (attn_use_mma() && hd == 128) return dispatch_g_mma<128, FUSED>(a, G, T, st);
     switch (hd) {
       case 32: return dispatch_g<__half, 32, FUSED>(a, G, T, st);
       case 64: return dispatch_g<__half, 64, FUSED>(a, G, T, st);
@@ -422,6 +797,10 @@ static int dispatch_attn(const AttnArgs &a, uint32_t hd, int kv_f32, uint32_t T,
   }
   return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: head dim %u unsupported (32, 64, 128)", hd);
 }
+
+// Resident CTAs per SM of the kernel that will run (shared memory decides): the tensor-core kernel keeps 3 tile
+// buffers of 34 KB (hd 128), two CTAs per SM; the CUDA-core kernel fills an SM's shared memory with one.
+static uint32_t attn_ctas_per_sm(uint32_t hd, int kv_f32) { return (!kv_f32 && attn_use_mma() && (hd == 64 || hd == 128)) ? 2u : 1u; }
 
 }  // namespace ieb
 
@@ -446,7 +825,7 @@ extern "C" int ie_b200_attn_decode(const float *d_q, const void *d_kc, const voi
   if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: T %u > 65535", T);
   AttnArgs a;
   a.q = d_q, a.kc = d_kc, a.vc = d_vc, a.out = d_out, a.oq = static_cast<uint8_t *>(d_oq), a.pos = d_pos;
-  a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.S = attn_splits(n_kv, n_ctx, T);
+  a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.S = attn_splits(n_kv, n_ctx, T, attn_ctas_per_sm(hd, kv_f32));
   a.q_stride = q_stride, a.out_stride = out_stride, a.oq_stride = oq_stride;
   a.part = static_cast<float *>(d_part), a.count = d_count;
   a.scale = 1.0f / sqrtf((float)hd);
@@ -466,7 +845,7 @@ extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, con
   if (!aligned16(d_kc) || !aligned16(d_vc) || !aligned16(d_q)) return fail(IE_B200_E_ARG, "ie_b200_attn_decode_fused: q and the caches must be 16-byte aligned");
   AttnArgs a;
   a.q = d_q, a.kc = d_kc, a.vc = d_vc, a.out = d_out, a.oq = static_cast<uint8_t *>(d_oq), a.pos = d_pos;
-  a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.S = attn_splits(n_kv, n_ctx, 1);
+  a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.S = attn_splits(n_kv, n_ctx, 1, attn_ctas_per_sm(hd, kv_f32));
   a.q_stride = a.out_stride = a.oq_stride = 0;
   a.part = static_cast<float *>(d_part), a.count = d_count;
   a.scale = 1.0f / sqrtf((float)hd);
