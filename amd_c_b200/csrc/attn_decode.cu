@@ -69,7 +69,7 @@ __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { r
 
 // The last split to arrive merges the A partial records (max, sum, out[hd]) of every head of its KV head, in split
 // order. The weights exp(max_k - max) and the denominators are worked out once in shared memory; the outputs are
-// then summed with eight independent loads in flight per thread (a plain loop over the splits is one L2 round trip
+// then summed with many independent loads in flight per thread (a plain loop over the splits is one L2 round trip
 // per split and per pass: 16 us at 17 splits).
 // part: the records of this token's first head of the KV head, [G][S][hd + 2]; scr: (2 A + 2) G floats of shared memory.
 template <int G, int HD, int THREADS>
@@ -95,19 +95,35 @@ __device__ __forceinline__ void merge_partials(const float *part, uint32_t S, ui
     lh[threadIdx.x] = L;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < G * HD; e += THREADS) {
-    const int h = e / HD;
-    const float *pr = part + (size_t)h * S * rec + 2 + (e % HD), *w = mk + h * A;
-    float acc = 0.0f;
-    for (uint32_t k0 = 0; k0 < A; k0 += 8u) {
-      float v[8];
+  // all of a thread's elements together, four splits at a time: (elements x 4) independent loads per round trip
+  constexpr int EPT = (G * HD + THREADS - 1) / THREADS;
+  float acc[EPT];
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = k0 + j < A ? __ldcg(pr + (size_t)(k0 + j) * rec) : 0.0f;
+  for (int i = 0; i < EPT; i++) acc[i] = 0.0f;
+  for (uint32_t k0 = 0; k0 < A; k0 += 4u) {
+    float v[EPT][4];
 #pragma unroll
-      for (int j = 0; j < 8; j++)
-        if (k0 + j < A) acc = fmaf(w[k0 + j], v[j], acc);
+    for (int i = 0; i < EPT; i++) {
+      const int e = threadIdx.x + THREADS * i;
+      const float *pr = part + (size_t)(e / HD) * S * rec + 2 + (e % HD);
+#pragma unroll
+      for (int j = 0; j < 4; j++) v[i][j] = (e < G * HD && k0 + j < A) ? __ldcg(pr + (size_t)(k0 + j) * rec) : 0.0f;
     }
-    fin[e] = acc * (1.0f / lh[h]);
+#pragma unroll
+    for (int i = 0; i < EPT; i++) {
+      const int e = threadIdx.x + THREADS * i;
+      if (e < G * HD) {
+        const float *w = mk + (e / HD) * A;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (k0 + j < A) acc[i] = fmaf(w[k0 + j], v[i][j], acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < EPT; i++) {
+    const int e = threadIdx.x + THREADS * i;
+    if (e < G * HD) fin[e] = acc[i] * (1.0f / lh[e / HD]);
   }
 }
 
