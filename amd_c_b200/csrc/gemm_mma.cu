@@ -157,17 +157,17 @@ __global__ void __launch_bounds__(256, 2) gemm_mma_kernel(const GemmArgs a) {
 // Needs nb % 4 == 0 and 16-byte aligned token rows; other shapes take the direct kernel above.
 constexpr int GS_KB = 4, GS_STAGES = 3, GS_WS = 80, GS_XS = 144, GS_HS = 40;
 
-template <int KIND>
+template <int KIND, int TOKS>
 struct GsLay {
   static constexpr int W = 0;                                   // [64 rows][80 B]: 4 blocks of 16 B nibbles
   static constexpr int SC = W + GM_ROWS * GS_WS;                // Q4_0: [64][4 f16]; Q4_K: [64][16 B header]; Q6_K: [64][4 u16]
   static constexpr int SC_BYTES = KIND == IE_B200_MAT_Q4K ? GM_ROWS * 16 : GM_ROWS * 8;
   static constexpr int HI = SC + SC_BYTES;                      // Q6_K: [64][40 B]: 4 blocks of 8 B high-bit words
   static constexpr int HI_BYTES = KIND == IE_B200_MAT_Q6K ? GM_ROWS * GS_HS : 0;
-  static constexpr int X = HI + HI_BYTES;                       // [128 tokens][144 B]: 4 blocks of 32 int8
-  static constexpr int DA = X + GM_TOKS * GS_XS;                // [4 blocks][128 tokens] f32
-  static constexpr int AS = DA + GS_KB * GM_TOKS * 4;           // [4 blocks][128 tokens] i32
-  static constexpr int STAGE = AS + GS_KB * GM_TOKS * 4;
+  static constexpr int X = HI + HI_BYTES;                       // [TOKS tokens][144 B]: 4 blocks of 32 int8
+  static constexpr int DA = X + TOKS * GS_XS;                   // [4 blocks][TOKS tokens] f32
+  static constexpr int AS = DA + GS_KB * TOKS * 4;              // [4 blocks][TOKS tokens] i32
+  static constexpr int STAGE = AS + GS_KB * TOKS * 4;
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
@@ -183,38 +183,42 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int KIND>
+// NT: 8-token tiles per warp; the CTA covers 64 rows x (32 NT) tokens. NT = 4 by default, NT = 2 when the grid would
+// otherwise leave most SMs idle (few rows).
+template <int KIND, int NT>
 __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
-  using L = GsLay<KIND>;
+  constexpr int TOKS = 4 * 8 * NT;
+  using L = GsLay<KIND, TOKS>;
   extern __shared__ uint4 gs_smem[];
   uint8_t *sm = reinterpret_cast<uint8_t *>(gs_smem);
   pdl_prologue();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int wm = warp & 1, wn = warp >> 1;  // warp tile: rows wm * 32 .., tokens wn * 32 .. of the CTA tile
-  const uint32_t row0 = blockIdx.x * GM_ROWS, tok0 = blockIdx.y * GM_TOKS, nb = a.nb;
+  const int wm = warp & 1, wn = warp >> 1;  // warp tile: rows wm * 32 .., tokens wn * 8 NT .. of the CTA tile
+  const uint32_t row0 = blockIdx.x * GM_ROWS, tok0 = blockIdx.y * TOKS, nb = a.nb;
   const uint32_t n_steps = nb / GS_KB;
 
   // what this thread copies per stage (rows / tokens past the end repeat the last one; their results are not stored)
   const uint8_t *w_src = a.w + (size_t)min(row0 + (tid >> 2), a.rows - 1u) * a.rowb;  // row tid / 4, 16-byte piece tid % 4
-  const uint8_t *x_src[4];
+  constexpr int XI = TOKS * 8 / 256, SI = GS_KB * TOKS / 256;  // 16-byte activation pieces and 4-byte scales per thread and stage
+  const uint8_t *x_src[XI];
 #pragma unroll
-  for (int i = 0; i < 4; i++) x_src[i] = a.xq + (size_t)min(tok0 + ((tid + 256 * i) >> 3), a.T - 1u) * a.xs;
-  const uint8_t *s_src = a.xq + (size_t)min(tok0 + (tid & 127), a.T - 1u) * a.xs;  // scales of token tid % 128, blocks (tid / 128) and + 2
+  for (int i = 0; i < XI; i++) x_src[i] = a.xq + (size_t)min(tok0 + ((tid + 256 * i) >> 3), a.T - 1u) * a.xs;
+  const uint8_t *s_src = a.xq + (size_t)min(tok0 + (tid % TOKS), a.T - 1u) * a.xs;  // scales of token tid % TOKS, blocks tid / TOKS + (256 / TOKS) i
   auto issue = [&](uint32_t step) {
     if (step < n_steps) {
       uint8_t *st = sm + (step % GS_STAGES) * L::STAGE;
       const uint32_t b0 = step * GS_KB;
       cp_async16(st + L::W + (tid >> 2) * GS_WS + (tid & 3) * 16, w_src + 16u * (size_t)(b0 + (tid & 3)));
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
+      for (int i = 0; i < XI; i++) {
         const int item = tid + 256 * i;
         cp_async16(st + L::X + (item >> 3) * GS_XS + (item & 7) * 16, x_src[i] + 32u * (size_t)b0 + 16u * (item & 7));
       }
 #pragma unroll
-      for (int i = 0; i < 2; i++) {
-        const int kb = (tid >> 7) + 2 * i, tk = tid & 127;
-        cp_async4(st + L::DA + (kb * GM_TOKS + tk) * 4, s_src + 32u * (size_t)nb + 4u * (b0 + kb));
-        if (KIND == IE_B200_MAT_Q4K) cp_async4(st + L::AS + (kb * GM_TOKS + tk) * 4, s_src + 36u * (size_t)nb + 4u * (b0 + kb));
+      for (int i = 0; i < SI; i++) {
+        const int kb = tid / TOKS + (256 / TOKS) * i, tk = tid % TOKS;
+        cp_async4(st + L::DA + (kb * TOKS + tk) * 4, s_src + 32u * (size_t)nb + 4u * (b0 + kb));
+        if (KIND == IE_B200_MAT_Q4K) cp_async4(st + L::AS + (kb * TOKS + tk) * 4, s_src + 36u * (size_t)nb + 4u * (b0 + kb));
       }
       if (KIND == IE_B200_MAT_Q4) {
         if (tid < GM_ROWS) cp_async8(st + L::SC + tid * 8, a.w + (size_t)min(row0 + tid, a.rows - 1u) * a.rowb + 16u * (size_t)nb + 2u * b0);
@@ -228,11 +232,11 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
     cp_async_commit();
   };
 
-  float acc[GM_MT][GM_NT][4];
+  float acc[GM_MT][NT][4];
 #pragma unroll
   for (int i = 0; i < GM_MT; i++)
 #pragma unroll
-    for (int j = 0; j < GM_NT; j++)
+    for (int j = 0; j < NT; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) acc[i][j][e] = 0.0f;
   // Q6_K: the f16 super-block scale of this lane's four rows (it changes every 8 blocks = 2 steps), read from global
@@ -287,15 +291,15 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
           }
         }
 #pragma unroll
-      for (int j = 0; j < GM_NT; j++) {
-        const int tl = wn * 32 + 8 * j;
+      for (int j = 0; j < NT; j++) {
+        const int tl = wn * 8 * NT + 8 * j;
         const uint8_t *q = st + L::X + (tl + g) * GS_XS + kb * 32 + 4 * t;
         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(q), b1 = *reinterpret_cast<const uint32_t *>(q + 16);
-        const float2 da2 = *reinterpret_cast<const float2 *>(st + L::DA + (kb * GM_TOKS + tl + 2 * t) * 4);
+        const float2 da2 = *reinterpret_cast<const float2 *>(st + L::DA + (kb * TOKS + tl + 2 * t) * 4);
         const float da[2] = {da2.x, da2.y};
         float das[2] = {0.0f, 0.0f};
         if (KIND == IE_B200_MAT_Q4K) {
-          const int2 as2 = *reinterpret_cast<const int2 *>(st + L::AS + (kb * GM_TOKS + tl + 2 * t) * 4);
+          const int2 as2 = *reinterpret_cast<const int2 *>(st + L::AS + (kb * TOKS + tl + 2 * t) * 4);
           das[0] = __fmul_rn(da[0], (float)as2.x), das[1] = __fmul_rn(da[1], (float)as2.y);
         }
 #pragma unroll
@@ -328,10 +332,10 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
 #pragma unroll
   for (int i = 0; i < GM_MT; i++)
 #pragma unroll
-    for (int j = 0; j < GM_NT; j++)
+    for (int j = 0; j < NT; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const uint32_t row = row0 + wm * 32 + 16u * i + 8u * (e >> 1) + g, tok = tok0 + wn * 32 + 8u * j + 2u * t + (e & 1);
+        const uint32_t row = row0 + wm * 32 + 16u * i + 8u * (e >> 1) + g, tok = tok0 + wn * 8 * NT + 8u * j + 2u * t + (e & 1);
         if (row < a.rows && tok < a.T) {
           float o = acc[i][j][e];
           if (a.bias) o = __fadd_rn(o, a.bias[row]);
@@ -341,13 +345,22 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
       }
 }
 
-template <int KIND>
-static int launch_staged(const GemmArgs &a, dim3 grid, cudaStream_t st) {
-  const size_t smem = (size_t)GS_STAGES * GsLay<KIND>::STAGE;
-  auto k = gemm_staged_kernel<KIND>;
+template <int KIND, int NT>
+static int launch_staged_nt(const GemmArgs &a, cudaStream_t st) {
+  constexpr int TOKS = 4 * 8 * NT;
+  const size_t smem = (size_t)GS_STAGES * GsLay<KIND, TOKS>::STAGE;
+  auto k = gemm_staged_kernel<KIND, NT>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  const dim3 grid((a.rows + GM_ROWS - 1) / GM_ROWS, (a.T + TOKS - 1) / TOKS);
   IEB_LAUNCH_PDL("gemm_staged_kernel", k, grid, dim3(256), smem, st, a);
   return IE_B200_OK;
+}
+template <int KIND>
+static int launch_staged(const GemmArgs &a, cudaStream_t st) {
+  // 64 x 128 tiles unless they would fill less than two thirds of the resident CTA slots (2 per SM): then 64 x 64
+  const uint64_t big = (uint64_t)((a.rows + GM_ROWS - 1) / GM_ROWS) * ((a.T + 127) / 128);
+  if (a.T > 64 && big * 3 < (uint64_t)sm_count() * 2 * 2) return launch_staged_nt<KIND, 2>(a, st);
+  return launch_staged_nt<KIND, 4>(a, st);
 }
 
 }  // namespace ieb
@@ -375,9 +388,9 @@ extern "C" int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t c
   }();
   if (!direct_only && a.nb % GS_KB == 0 && aligned16(d_xq) && x_stride % 16u == 0) {
     switch (kind) {
-      case IE_B200_MAT_Q4: return launch_staged<IE_B200_MAT_Q4>(a, grid, st);
-      case IE_B200_MAT_Q4K: return launch_staged<IE_B200_MAT_Q4K>(a, grid, st);
-      default: return launch_staged<IE_B200_MAT_Q6K>(a, grid, st);
+      case IE_B200_MAT_Q4: return launch_staged<IE_B200_MAT_Q4>(a, st);
+      case IE_B200_MAT_Q4K: return launch_staged<IE_B200_MAT_Q4K>(a, st);
+      default: return launch_staged<IE_B200_MAT_Q6K>(a, st);
     }
   }
   switch (kind) {
