@@ -24,6 +24,7 @@
 // and a value is complete as soon as its epoch matches ("low-latency" slots, double-buffered by parity):
 //   ar_norm_kernel    x = x + sum over ranks of part, then RMSNorm and the Q8 copy of x for the next GEMVs;
 //   ar_argmax_kernel  the (value, global index) pairs of the ranks' local argmax, best one to every rank.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -140,9 +141,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
       const uint32_t pw[4] = {__float_as_uint(mine[it].x), __float_as_uint(mine[it].y), __float_as_uint(mine[it].z), __float_as_uint(mine[it].w)};
       for (uint32_t j = 0; j < s.world && !pushed; j++) {  // pushed: the producing GEMV has already delivered its rows
         if (j == s.rank) continue;
-        unsigned long long *dst = s.ll[j] + ((size_t)par * s.world + s.rank) * s.max_n + i;
-#pragma unroll
-        for (int c = 0; c < 4; c++) ll_store(dst + c, k, pw[c]);
+        ll_store4(s.ll[j] + ((size_t)par * s.world + s.rank) * s.max_n + i, k, pw);
       }
       if (!early) acc[it] = *reinterpret_cast<const float4 *>(res + i);
     }
@@ -162,10 +161,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           const uint32_t j = j0 + q;
-          if (j < s.world && j != s.rank) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) v[q][c] = ll_load(my + (size_t)j * s.max_n + i + c);
-          }
+          if (j < s.world && j != s.rank) ll_load4(my + (size_t)j * s.max_n + i, v[q]);
         }
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -370,15 +366,25 @@ extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const
   ArPush push = {};
   for (uint32_t j = 0; j < a->d.world; j++) push.ll[j] = a->d.ll[j];
   push.epoch = a->d.epoch, push.rank = a->d.rank, push.world = a->d.world, push.max_n = a->d.max_n;
+  // Who pushes: the GEMV, a warp's two rows at a time while it runs (the transfer overlaps it; a stop costs every
+  // rank rows / 2 x (world - 1) 16-byte packets), or the reduction kernel, in 32-byte pieces per thread after the GEMV
+  // (far fewer packets, no overlap). Measured at 2 / 4 / 8 ranks: 833 / 983 / 959 tok/s against 795 / 903 / 847, so
+  // the GEMV pushes; IE_B200_TP_PUSH=reduce selects the other form.
+  static const int forced = [] {
+    const char *v = getenv("IE_B200_TP_PUSH");
+    return !v ? 0 : v[0] == 'g' ? 1 : v[0] == 'r' ? 2 : 0;
+  }();
+  const bool gemv_pushes = forced != 2;
   // the GEMV releases its dependents only after its own dependency wait: when the reduction kernel starts, everything
   // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
   LaunchHints hints;
   hints.late_trigger = true;
   set_hints(hints);
-  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push);
+  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream),
+                            gemv_pushes ? &push : nullptr);
   set_hints(LaunchHints());
   if (r) return r;
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, gemv_pushes ? 1 : 0, 1);
 }
 
 extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {

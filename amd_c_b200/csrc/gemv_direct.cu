@@ -110,19 +110,33 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
     }
   };
   auto finish = [&](float(&acc)[R], uint32_t rr) {
+    float v[R];
 #pragma unroll
     for (int i = 0; i < R; i++) {
-      const float v = warp_tree(acc[i]);
+      v[i] = warp_tree(acc[i]);
       if (lane == 0 && rr + i < r_hi) {
-        float o = v;
+        float o = v[i];
         if (a.bias) o = __fadd_rn(o, a.bias[rr + i]);
         if (a.res) o = __fadd_rn(a.res[rr + i], o);
         a.y[rr + i] = o;
       }
-      if (TP) {  // the row goes to every other rank right away (lane j stores to rank j): the transfer overlaps the rest of the GEMV
-        const float o = __shfl_sync(0xFFFFFFFFu, v, 0);
-        if ((uint32_t)lane < a.push.world && (uint32_t)lane != a.push.rank && rr + i < r_hi)
-          ll_store(a.push.ll[lane] + ((size_t)(ep & 1u) * a.push.world + a.push.rank) * a.push.max_n + rr + i, ep, __float_as_uint(o));
+    }
+    if (TP) {
+      // The rows go to every other rank right away (lane j stores to rank j), so the transfer overlaps the rest of the
+      // GEMV; a warp's two adjacent rows travel as one 16-byte store (each half carries its own epoch). Collecting a
+      // whole CTA's rows first (one 128-byte store per rank and round) was tried: the barrier it needs per round cost
+      // the GEMV far more than the fewer packets saved.
+#pragma unroll
+      for (int i = 0; i < R; i++) v[i] = __shfl_sync(0xFFFFFFFFu, v[i], 0);
+      if ((uint32_t)lane < a.push.world && (uint32_t)lane != a.push.rank) {
+        unsigned long long *dst = a.push.ll[lane] + ((size_t)(ep & 1u) * a.push.world + a.push.rank) * a.push.max_n + rr;
+        if (R == 2 && rr + 1 < r_hi) {
+          ll_store2(dst, ep, __float_as_uint(v[0]), __float_as_uint(v[R - 1]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < R; i++)
+            if (rr + i < r_hi) ll_store(dst + i, ep, __float_as_uint(v[i]));
+        }
       }
     }
   };

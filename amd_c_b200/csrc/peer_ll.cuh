@@ -22,6 +22,20 @@ __device__ __forceinline__ void ll_store(unsigned long long *p, uint32_t epoch, 
   const unsigned long long v = (unsigned long long)epoch << 32 | payload;
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// Two adjacent words in one 16-byte store (p 16-byte aligned); each half is complete on its own epoch.
+__device__ __forceinline__ void ll_store2(unsigned long long *p, uint32_t epoch, uint32_t w0, uint32_t w1) {
+  const unsigned long long v0 = (unsigned long long)epoch << 32 | w0, v1 = (unsigned long long)epoch << 32 | w1;
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(v0), "l"(v1) : "memory");
+}
+// Four adjacent words in one 32-byte store / load (p 32-byte aligned): a warp then moves 1 KB contiguous, which the
+// links carry as a few full-size packets instead of 128 eight-byte ones.
+__device__ __forceinline__ void ll_store4(unsigned long long *p, uint32_t epoch, const uint32_t (&w)[4]) {
+  const unsigned long long e = (unsigned long long)epoch << 32;
+  asm volatile("st.relaxed.sys.global.v4.u64 [%0], {%1, %2, %3, %4};" ::"l"(p), "l"(e | w[0]), "l"(e | w[1]), "l"(e | w[2]), "l"(e | w[3]) : "memory");
+}
+__device__ __forceinline__ void ll_load4(const unsigned long long *p, unsigned long long (&v)[4]) {
+  asm volatile("ld.relaxed.sys.global.v4.u64 {%0, %1, %2, %3}, [%4];" : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]) : "l"(p) : "memory");
+}
 __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
   unsigned long long v;
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
