@@ -41,6 +41,7 @@ SIGNATURES = {
     "ie_b200_attn_count_words": (_sz, [_u32, _u32]),
     "ie_b200_attn_decode": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _u32, _u32, _u32, _sz, _sz, _sz, _vp, _vp, _vp]),
     "ie_b200_attn_decode_fused": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _int, _u32, _u32, _vp, _vp, _vp]),
+    "ie_b200_attn_prefill": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_argmax_part_bytes": (_sz, [_u32]),
     "ie_b200_argmax": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp, _vp]),
     "ie_b200_argmax_static_max_rows": (_u32, []),

@@ -748,6 +748,204 @@ static int launch_attn_mma(const AttnArgs &a, uint32_t T, cudaStream_t st) {
   return launch_attn_mma_nb<HD, G, FUSED, 4>(a, T, st);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Prompt chunks (T tokens at positions pos0 .. pos0 + T - 1, their K / V rows already in the cache): the same
+// tensor-core scheme with all 16 MMA rows in use: a CTA takes QT = 16 / G consecutive tokens of one KV head (rows =
+// token-major (token, head) pairs) and streams the cache once for all of them, masking every row at its own token's
+// position (causal). No split over positions: a chunk has T / QT x n_kv CTAs already.
+struct PrefillArgs {
+  const float *q;
+  const void *kc, *vc;
+  float *out;
+  uint8_t *oq;
+  const uint32_t *pos;  // position of token 0
+  uint32_t n_head, n_kv, kv_len, T;
+  size_t q_stride, out_stride, oq_stride;
+  float scale;
+};
+
+template <int HD, int G>
+__global__ void __launch_bounds__(AM_THREADS, 2) attn_prefill_mma_kernel(const PrefillArgs a) {
+  constexpr int TILE = ATT_TILE, ROW = HD + AM_PAD, TILE_ELEMS = TILE * ROW, KS = HD / 16, NB = 3;
+  constexpr int QT = 16 / G, ROWS = QT * G;  // tokens per CTA, MMA rows in use
+  static_assert(G >= 1 && G <= 16, "at least one token's heads fill the 16 MMA rows");
+  extern __shared__ uint4 smem_raw[];
+  __half *kbuf = reinterpret_cast<__half *>(smem_raw);
+  __half *vbuf = kbuf + NB * TILE_ELEMS;
+
+  pdl_prologue(TL_ATTN);
+  const uint32_t t0 = blockIdx.x * QT, g = blockIdx.y;
+  const uint32_t nt = min((uint32_t)QT, a.T - t0);            // tokens of this CTA
+  const uint32_t pos0 = *a.pos + t0, p_hi = pos0 + nt;         // token i sees positions 0 .. pos0 + i
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hq = lane >> 2, tq = lane & 3;
+  const __half *kh = static_cast<const __half *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const __half *>(a.vc) + (size_t)g * a.kv_len * HD;
+  const uint32_t n_tiles = (p_hi + TILE - 1u) / TILE;
+
+  constexpr int PER_ROW = HD * 2 / 16, RPP = AM_THREADS / PER_ROW;
+  const uint32_t my_piece = (threadIdx.x % PER_ROW) * 16u, my_row = threadIdx.x / PER_ROW;
+  auto issue = [&](uint32_t it) {
+    if (it < n_tiles) {
+      const uint32_t tile_lo = it * TILE, rows = min((uint32_t)TILE, p_hi - tile_lo);
+      const char *ks = reinterpret_cast<const char *>(kh + (size_t)tile_lo * HD) + my_piece, *vs = reinterpret_cast<const char *>(vh + (size_t)tile_lo * HD) + my_piece;
+      char *kd = reinterpret_cast<char *>(kbuf + (it % NB) * TILE_ELEMS) + my_piece, *vd = reinterpret_cast<char *>(vbuf + (it % NB) * TILE_ELEMS) + my_piece;
+#pragma unroll
+      for (int j = 0; j < TILE / RPP; j++) {
+        const uint32_t r = my_row + RPP * j;
+        const bool ok = r < rows;
+        const size_t src = ok ? (size_t)r * HD * 2u : 0u;
+        __pipeline_memcpy_async(kd + (size_t)r * ROW * 2u, ks + src, 16, ok ? 0 : 16);
+        __pipeline_memcpy_async(vd + (size_t)r * ROW * 2u, vs + src, 16, ok ? 0 : 16);
+      }
+    }
+    __pipeline_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < NB - 1; i++) issue(i);
+
+  // ---- q (already rotated) of this lane's two rows hq and hq + 8, split into two f16 terms; lim = positions the row sees
+  uint32_t qh[KS][4], ql[KS][4], lim[2];
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    const int r = hq + 8 * h, tk = r / G, hd_ = r % G;
+    const bool real = r < ROWS && (uint32_t)tk < nt;
+    lim[h] = real ? pos0 + tk + 1u : 0u;
+    const float *qp = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * (t0 + (real ? tk : 0))) + ((size_t)g * G + hd_) * HD;
+#pragma unroll
+    for (int k = 0; k < KS; k++) {
+      float2 lo2 = make_float2(0.f, 0.f), hi2 = lo2;
+      if (real) lo2 = *reinterpret_cast<const float2 *>(qp + 16 * k + 2 * tq), hi2 = *reinterpret_cast<const float2 *>(qp + 16 * k + 2 * tq + 8);
+      split2(lo2.x, lo2.y, qh[k][h], ql[k][h]);          // a0 (row hq) / a1 (row hq + 8): columns 2tq, 2tq + 1
+      split2(hi2.x, hi2.y, qh[k][2 + h], ql[k][2 + h]);  // a2 / a3: columns 2tq + 8, 2tq + 9
+    }
+  }
+  float o[HD / 8][4], run_m[2] = {-INFINITY, -INFINITY}, run_l[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int n = 0; n < HD / 8; n++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[n][e] = 0.0f;
+  const int lm = lane >> 3, lr = lane & 7;
+  for (uint32_t it = 0; it < n_tiles; it++) {
+    const int buf = it % NB;
+    const uint32_t tile_lo = it * TILE;
+    __pipeline_wait_prior(NB - 2);
+    __syncthreads();
+    issue(it + NB - 1u);
+    const uint32_t p0 = tile_lo + warp * 16u;  // this warp's 16 positions
+    if (p0 < p_hi) {
+      const __half *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < KS; k++) {
+        uint32_t kb[4];
+        ldsm4(kb, kt + (warp * 16 + (lm >> 1) * 8 + lr) * ROW + 16 * k + (lm & 1) * 8);
+        mma_f16(sa, qh[k][0], qh[k][1], qh[k][2], qh[k][3], kb[0], kb[1]);
+        mma_f16(sa, ql[k][0], ql[k][1], ql[k][2], ql[k][3], kb[0], kb[1]);
+        mma_f16(sb, qh[k][0], qh[k][1], qh[k][2], qh[k][3], kb[2], kb[3]);
+        mma_f16(sb, ql[k][0], ql[k][1], ql[k][2], ql[k][3], kb[2], kb[3]);
+      }
+      uint32_t ph[4], pl[4];  // A fragment of P: a0 / a1 = rows hq / hq + 8 at positions 2tq, +1; a2 / a3 at 8 + 2tq, +1
+      float al[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        float sc[4];
+        sc[0] = p0 + 2 * tq < lim[h] ? sa[2 * h] * a.scale : -INFINITY;
+        sc[1] = p0 + 2 * tq + 1 < lim[h] ? sa[2 * h + 1] * a.scale : -INFINITY;
+        sc[2] = p0 + 8 + 2 * tq < lim[h] ? sb[2 * h] * a.scale : -INFINITY;
+        sc[3] = p0 + 8 + 2 * tq + 1 < lim[h] ? sb[2 * h + 1] * a.scale : -INFINITY;
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        const float m_new = fmaxf(run_m[h], mx), mref = m_new == -INFINITY ? 0.0f : m_new;  // a row may see none of these positions
+        al[h] = expf(run_m[h] - mref);
+        float pv[4], sum = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; e++) pv[e] = expf(sc[e] - mref), sum += pv[e];
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        run_l[h] = run_l[h] * al[h] + sum, run_m[h] = m_new;
+        split2(pv[0], pv[1], ph[h], pl[h]);
+        split2(pv[2], pv[3], ph[2 + h], pl[2 + h]);
+      }
+#pragma unroll
+      for (int u = 0; u < HD / 16; u++) {
+        uint32_t vb[4];
+        ldsm4t(vb, vt + (warp * 16 + (lm & 1) * 8 + lr) * ROW + 16 * u + (lm >> 1) * 8);
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[2 * u][e] *= al[e >> 1], o[2 * u + 1][e] *= al[e >> 1];
+        mma_f16(o[2 * u], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
+        mma_f16(o[2 * u], pl[0], pl[1], pl[2], pl[3], vb[0], vb[1]);
+        mma_f16(o[2 * u + 1], ph[0], ph[1], ph[2], ph[3], vb[2], vb[3]);
+        mma_f16(o[2 * u + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
+      }
+    }
+  }
+  __pipeline_wait_prior(0);
+  __syncthreads();
+  // ---- merge the warps' (max, sum, output) per row in shared memory, reusing the tile buffers
+  float *red = reinterpret_cast<float *>(smem_raw);  // [AM_WARPS][16][HD]
+  float *ml = red + AM_WARPS * 16 * HD;               // [AM_WARPS][16][2]
+  float *fin = ml + AM_WARPS * 16 * 2;                // [16][HD]
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    const int r = hq + 8 * h;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) *reinterpret_cast<float2 *>(red + (warp * 16 + r) * HD + 8 * n + 2 * tq) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    if (tq == 0) ml[(warp * 16 + r) * 2] = run_m[h], ml[(warp * 16 + r) * 2 + 1] = run_l[h];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < ROWS * HD; e += AM_THREADS) {
+    const int r = e / HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; w++) M = fmaxf(M, ml[(w * 16 + r) * 2]);
+    float L = 0.0f, acc = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < AM_WARPS; w++) {
+        const float wk = expf(ml[(w * 16 + r) * 2] - M);
+        L = fmaf(wk, ml[(w * 16 + r) * 2 + 1], L);
+        acc = fmaf(wk, red[(w * 16 + r) * HD + (e % HD)], acc);
+      }
+    }
+    fin[e] = L > 0.0f ? acc * (1.0f / L) : 0.0f;
+  }
+  __syncthreads();
+  // ---- write out: one warp per 32 values of a (token, head) row, which is also a Q8 block of that token's output
+  const uint32_t nbq = a.n_head * HD / 32u;
+  for (int b = warp; b < ROWS * HD / 32; b += AM_WARPS) {
+    const int r = (32 * b) / HD, tk = r / G, hd_ = r % G;
+    if ((uint32_t)tk >= nt) continue;
+    const float v = fin[32 * b + lane];
+    const uint32_t col = ((uint32_t)g * G + hd_) * HD + (32 * b) % HD;
+    reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * (t0 + tk))[col + lane] = v;
+    if (a.oq) quant_block_warp(v, a.oq + a.oq_stride * (t0 + tk), nbq, col / 32u, lane);
+  }
+}
+
+template <int HD, int G>
+static int launch_prefill(const PrefillArgs &a, cudaStream_t st) {
+  constexpr int QT = 16 / G;
+  const size_t tile = (size_t)3 * 2 * ATT_TILE * (HD + AM_PAD) * sizeof(__half);
+  const size_t red = (size_t)((AM_WARPS + 1) * 16 * HD + AM_WARPS * 16 * 2) * sizeof(float);
+  const size_t smem = tile > red ? tile : red;
+  auto k = attn_prefill_mma_kernel<HD, G>;
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  IEB_LAUNCH_PDL("attn_prefill_mma_kernel", k, dim3((a.T + QT - 1) / QT, a.n_kv), dim3(AM_THREADS), smem, st, a);
+  return IE_B200_OK;
+}
+template <int HD>
+static int dispatch_prefill(const PrefillArgs &a, uint32_t G, cudaStream_t st) {
+  switch (G) {
+    case 1: return launch_prefill<HD, 1>(a, st);
+    case 2: return launch_prefill<HD, 2>(a, st);
+    case 4: return launch_prefill<HD, 4>(a, st);
+    case 5: return launch_prefill<HD, 5>(a, st);
+    case 7: return launch_prefill<HD, 7>(a, st);
+    case 8: return launch_prefill<HD, 8>(a, st);
+    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_prefill: %u query heads per KV head unsupported (1, 2, 4, 5, 7, 8)", G);
+  }
+}
+
 // IE_B200_ATTN=scalar keeps the CUDA-core kernel for the half cache as well.
 static bool attn_use_mma() {
   static const bool on = [] {
@@ -868,4 +1066,21 @@ extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, con
   a.k_new = d_k, a.v_new = d_v, a.cs = d_cos, a.sn = d_sin, a.neox = neox;
   a.early_kv = early ? 1 : 0;
   return dispatch_attn<true>(a, hd, kv_f32, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ie_b200_attn_prefill(const float *d_q, const void *d_kc, const void *d_vc, float *d_out, void *d_oq, const uint32_t *d_pos,
+                                    uint32_t n_head, uint32_t n_kv, uint32_t hd, uint32_t kv_len, uint32_t T, size_t q_stride, size_t out_stride,
+                                    size_t oq_stride, void *stream) {
+  if (!d_q || !d_kc || !d_vc || !d_out || !d_pos) return fail(IE_B200_E_ARG, "ie_b200_attn_prefill: NULL pointer");
+  if (n_kv == 0 || n_head % n_kv) return fail(IE_B200_E_SIZE, "ie_b200_attn_prefill: %u heads over %u KV heads", n_head, n_kv);
+  if (hd != 64 && hd != 128) return fail(IE_B200_E_SIZE, "ie_b200_attn_prefill: head dim %u (64, 128; half-precision cache)", hd);
+  if (!aligned16(d_kc) || !aligned16(d_vc) || ((uintptr_t)d_q & 7u) || (q_stride & 7u)) return fail(IE_B200_E_ARG, "ie_b200_attn_prefill: alignment");
+  if (T == 0) return IE_B200_OK;
+  PrefillArgs a;
+  a.q = d_q, a.kc = d_kc, a.vc = d_vc, a.out = d_out, a.oq = static_cast<uint8_t *>(d_oq), a.pos = d_pos;
+  a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.T = T;
+  a.q_stride = q_stride, a.out_stride = out_stride, a.oq_stride = oq_stride;
+  a.scale = 1.0f / sqrtf((float)hd);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return hd == 64 ? dispatch_prefill<64>(a, n_head / n_kv, st) : dispatch_prefill<128>(a, n_head / n_kv, st);
 }

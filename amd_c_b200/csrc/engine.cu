@@ -67,6 +67,7 @@ struct ie_b200_engine {
   uint32_t *hist = nullptr;  // HIST_CAP tokens + the step counter
   uint32_t *err = nullptr;   // device error word: set by a kernel whose bounded wait ran out; err[2..3]: the GEMVs' work and arrival counters
   bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
+  bool no_prefill_attn = false;  // IE_B200_PREFILL_ATTN=0: a chunk's attention through the decode kernel, one CTA set per token
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
@@ -137,6 +138,11 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
     }
     case IE_B200_OP_ATTN: {
       char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+      // a prompt chunk on a half-precision cache: tokens share passes over the cache on the tensor cores
+      if (T > 1 && !d.kv_f32 && (d.hd == 64 || d.hd == 128) && !e->no_prefill_attn)
+        return ie_b200_attn_prefill(static_cast<float *>(at(e, o.a, o.a_stride, t0)), kcl, vcl, static_cast<float *>(at(e, o.b, o.b_stride, t0)),
+                                    at(e, o.qo, o.qo_stride, t0), pos + 1 + t0, d.n_head, d.n_kv, d.hd, d.n_ctx, T, o.a_stride, o.b_stride,
+                                    o.qo_stride, st);
       for (uint32_t s = 0; s < T; s += e->T_att) {  // bounded scratch: at most T_att tokens per launch
         const uint32_t n = T - s < e->T_att ? T - s : e->T_att;
         int r = ie_b200_attn_decode(static_cast<float *>(at(e, o.a, o.a_stride, t0 + s)), kcl, vcl, static_cast<float *>(at(e, o.b, o.b_stride, t0 + s)),
@@ -335,6 +341,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
   if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
+  if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");

@@ -196,6 +196,18 @@ def attn_decode_fused(qkv: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cos
     return out, oq
 
 
+def attn_prefill(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, pos: torch.Tensor, n_head: int, n_kv: int, hd: int, quant: bool = True):
+    """A prompt chunk: q [T, >= n_head hd] f32 rows (rotated), half caches [n_kv, kv_len, hd] that already hold the chunk's rows;
+    returns (out [T, n_head hd], Q8 copies or None)."""
+    T = q.shape[0]
+    out = torch.empty((T, n_head * hd), dtype=torch.float32, device=q.device)
+    nbq = n_head * hd // 32
+    oq = torch.empty((T, q8_bytes(nbq)), dtype=torch.uint8, device=q.device) if quant else None
+    check(_lib.load().ie_b200_attn_prefill(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), _p(oq), pos.data_ptr(), n_head, n_kv, hd,
+                                           kc.shape[1], T, q.stride(0) * 4, n_head * hd * 4, q8_bytes(nbq), _stream()))
+    return out, oq
+
+
 def argmax(x: torch.Tensor) -> torch.Tensor:
     """x: [T, n] f32 -> int32 [T, 2]: (index, float bits of the softmax probability of the maximum)."""
     x2 = x.reshape(-1, x.shape[-1])

@@ -181,6 +181,16 @@ int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, const float *d
                               const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd,
                               int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count, void *stream);
 
+/* Causal attention of a prompt chunk: T tokens at positions *d_pos .. *d_pos + T - 1 whose (rotated) K / V rows are
+ * already in the half-precision cache (ie_b200_rope_kv); token t sees positions 0 .. *d_pos + t. The role of
+ * ie_attn_pfg / ie_attn_fa (kernels/ie_kernels.c:3471-3693; dispatch src/hip.c:1432-1463): 16 / G consecutive tokens
+ * of one KV head share one pass over the cache on the tensor cores (f16 MMA, fp32 softmax and accumulation, q and p
+ * carried as two f16 terms). hd 64 or 128; d_q rows of n_head * hd floats (already rotated), output rows and their
+ * Q8 copies (d_oq may be NULL) as ie_b200_attn_decode; strides in bytes. No scratch. */
+int ie_b200_attn_prefill(const float *d_q, const void *d_kc, const void *d_vc, float *d_out, void *d_oq, const uint32_t *d_pos,
+                         uint32_t n_head, uint32_t n_kv, uint32_t hd, uint32_t kv_len, uint32_t T, size_t q_stride, size_t out_stride,
+                         size_t oq_stride, void *stream);
+
 /* First index of the maximum of each of T rows, and the softmax probability
  * of that maximum: OP_ARGMAX (src/cpu.c:608-614), ie_argmax
  * {x,n,out,part,count,ng} (src/hip.c:1537). out: {u32 index, f32 prob} per row.

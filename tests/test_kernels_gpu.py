@@ -519,3 +519,27 @@ def test_gemm_matches_gemv(ora, cuda, typ, rows, cols, T):
     t = T // 2
     ref = ora.gemv(kind, qw, qs, rows, cols, xq[t].cpu().numpy(), bias=bias.cpu().numpy(), res=res[t].cpu().numpy())
     assert np.abs(got[t] - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("n_head,n_kv,hd,T,pos0", [(8, 2, 128, 9, 70), (28, 4, 128, 5, 200), (8, 8, 64, 19, 0), (10, 2, 64, 4, 129), (16, 2, 128, 3, 63)])
+def test_attention_prefill_chunk(ora, cuda, n_head, n_kv, hd, T, pos0):
+    """A prompt chunk on the tensor cores (tokens of a KV head share passes over the half cache): every token against the
+    oracle's two-pass softmax over the same (half-rounded) cache within 1e-4 of the output scale, the Q8 copies exactly the
+    quantiser of the outputs; token counts that do not fill the last CTA, positions across tile edges, G = 1, 4, 5, 7, 8."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(n_head * 100 + T)
+    n_ctx, kvd = pos0 + T + 5, n_kv * hd
+    kc_ref = rng.standard_normal((n_ctx, kvd)).astype(np.float16).astype(np.float32)
+    vc_ref = rng.standard_normal((n_ctx, kvd)).astype(np.float16).astype(np.float32)
+    kc = torch.from_numpy(kc_ref.reshape(n_ctx, n_kv, hd).transpose(1, 0, 2).copy()).to(cuda).half()
+    vc = torch.from_numpy(vc_ref.reshape(n_ctx, n_kv, hd).transpose(1, 0, 2).copy()).to(cuda).half()
+    q = rng.standard_normal((T, n_head * hd)).astype(np.float32)
+    out, oq = K.attn_prefill(dev(q, cuda), kc, vc, dev(np.array([pos0], np.uint32), cuda), n_head, n_kv, hd)
+    out, oq = out.cpu().numpy(), oq.cpu().numpy()
+    for t in range(T):
+        want = ora.attention(q[t], kc_ref, vc_ref, pos0 + t, n_head, n_kv, hd)
+        assert np.abs(out[t] - want).max() <= 1e-4 * np.abs(want).max(), t
+        assert (oq[t] == ora.quant_q8(out[t])).all(), t
