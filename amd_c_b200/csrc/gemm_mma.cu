@@ -167,7 +167,9 @@ struct GsLay {
   static constexpr int X = HI + HI_BYTES;                       // [TOKS tokens][144 B]: 4 blocks of 32 int8
   static constexpr int DA = X + TOKS * GS_XS;                   // [4 blocks][TOKS tokens] f32
   static constexpr int AS = DA + GS_KB * TOKS * 4;              // [4 blocks][TOKS tokens] i32
-  static constexpr int STAGE = AS + GS_KB * TOKS * 4;
+  static constexpr int SS = AS + GS_KB * TOKS * 4;               // Q4_K: [64 rows][4 blocks] (d sc, dmin mn) f32 pairs, 40-byte rows, worked out once per stage
+  static constexpr int SS_BYTES = KIND == IE_B200_MAT_Q4K ? GM_ROWS * 40 : 0;
+  static constexpr int STAGE = SS + SS_BYTES;
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
@@ -256,7 +258,15 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
     cp_async_wait<GS_STAGES - 2>();
     __syncthreads();  // step's stage is complete for everybody, and everybody is done with the stage refilled next
     issue(step + GS_STAGES - 1);
-    const uint8_t *st = sm + (step % GS_STAGES) * L::STAGE;
+    uint8_t *st = sm + (step % GS_STAGES) * L::STAGE;
+    if (KIND == IE_B200_MAT_Q4K) {  // the 256 (row, block) scale pairs of the stage, one per thread, instead of 4 per lane and block
+      const int row = tid >> 2, kb = tid & 3;
+      const uint4 hd = *reinterpret_cast<const uint4 *>(st + L::SC + row * 16);
+      const uint32_t f = q4k_field(hd, (int)((step * GS_KB + kb) & 7u));
+      *reinterpret_cast<float2 *>(st + L::SS + row * 40 + kb * 8) =
+          make_float2(__fmul_rn(h2f((uint16_t)(hd.x & 0xFFFFu)), (float)(f & 63u)), __fmul_rn(h2f((uint16_t)(hd.x >> 16)), (float)(f >> 6)));
+      __syncthreads();
+    }
     if (KIND == IE_B200_MAT_Q6K && (step & 1u) == 0u) {
 #pragma unroll
       for (int i = 0; i < GM_MT; i++)
@@ -279,10 +289,8 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
             s0[i][h] = h2f(*reinterpret_cast<const uint16_t *>(st + L::SC + rl * 8 + 2 * kb)), s1[i][h] = 0.0f;
           } else if (KIND == IE_B200_MAT_Q4K) {
             wl[i][h] = wv & 0x0F0F0F0Fu, wh[i][h] = (wv >> 4) & 0x0F0F0F0Fu;
-            const uint4 hd = *reinterpret_cast<const uint4 *>(st + L::SC + rl * 16);
-            const uint32_t f = q4k_field(hd, (int)(b & 7u));
-            s0[i][h] = __fmul_rn(h2f((uint16_t)(hd.x & 0xFFFFu)), (float)(f & 63u));
-            s1[i][h] = __fmul_rn(h2f((uint16_t)(hd.x >> 16)), (float)(f >> 6));
+            const float2 ss = *reinterpret_cast<const float2 *>(st + L::SS + rl * 40 + kb * 8);
+            s0[i][h] = ss.x, s1[i][h] = ss.y;
           } else {
             const uint2 hw = *reinterpret_cast<const uint2 *>(st + L::HI + rl * GS_HS + kb * 8);
             wl[i][h] = (uint32_t)q6_sw(wv & 0x0F0F0F0Fu, hw.x, t), wh[i][h] = (uint32_t)q6_sw((wv >> 4) & 0x0F0F0F0Fu, hw.y, t);

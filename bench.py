@@ -319,6 +319,36 @@ def time_prefill_gemm(device) -> dict:
     return out
 
 
+def time_qwen2_prefill(device) -> dict:
+    """The Qwen2-7B-shaped Q4_K_M model (Q4_K attention / FFN, Q6_K for V and down, QKV bias): 4096 seeded uniform prompt
+    ids in chunks of 256 through backend.run (tensor-core GEMM + chunk attention), then 128 greedy tokens on the device."""
+    import numpy as np
+    import torch
+
+    from amd_c_b200 import gguf
+    from amd_c_b200.backend import Backend, prefill
+
+    cfg = gguf.config("qwen2-7b-q4km")
+    tensors = gguf.make_model_device(cfg, seed=0)
+    b = Backend(cfg, 4096 + 136, T=256, device_tensors=tensors, device=device)
+    del tensors
+    torch.cuda.empty_cache()
+    prompt = np.random.default_rng(2).integers(0, cfg.vocab, 4096)
+    prefill(b, prompt[:512], 256)  # warm-up: two chunks
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    tok = prefill(b, prompt, 256)
+    torch.cuda.synchronize(device)
+    dt = time.perf_counter() - t0
+    out, ms = b.decode(tok, 4096, 128)
+    res = {"workload": "Qwen2-7B-shaped random-init Q4_K_M, 28 layers, 4096-token prompt in chunks of 256, then 128 greedy tokens",
+           "prefill_tokens_per_s": 4096 / dt, "prefill_ms_per_chunk": dt * 1e3 / 16, "decode_tokens_per_s": 128 / (ms * 1e-3),
+           "decode_ms_per_step": ms / 128, "weight_gb_per_token": b.weight_bytes_per_token / 1e9}
+    b.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours_single(args, cfg) -> dict:
     import numpy as np
     import torch
@@ -377,6 +407,7 @@ def run_ours_single(args, cfg) -> dict:
     torch.cuda.empty_cache()
     res["roofline"]["gemv_sweep"] = time_gemv_sweep(dev, peak)
     res["prefill_gemm"] = time_prefill_gemm(dev)
+    res["qwen2_7b_q4km"] = time_qwen2_prefill(dev)
     return res
 
 
@@ -393,6 +424,8 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, where exactly one JSON line is expected
     dist.init_process_group("nccl", device_id=dev)
     K, W = args.steps, args.warmup
     n_ctx = PROMPT_LEN + 2 * (K + W) + 8
