@@ -349,6 +349,40 @@ def time_qwen2_prefill(device) -> dict:
     return res
 
 
+def time_long_context(device, positions: int = 32768, n_gen: int = 64) -> dict:
+    """The 27B-class dense Q4_K_M model (64 layers, d_model 5120, 40 / 8 heads of 128, FFN 17408): `positions` seeded
+    prompt ids prefilled in chunks of 256, then greedy decode with the split-KV attention reading the whole cache every
+    step. Run with --long-context (about a minute); not part of the default line."""
+    import numpy as np
+    import torch
+
+    from amd_c_b200 import gguf
+    from amd_c_b200.backend import Backend, prefill
+
+    cfg = gguf.config("dense-27b-q4km")
+    tensors = gguf.make_model_device(cfg, seed=0)
+    b = Backend(cfg, positions + n_gen + 8, T=256, device_tensors=tensors, device=device)
+    del tensors
+    torch.cuda.empty_cache()
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, positions)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    tok = prefill(b, prompt, 256)
+    torch.cuda.synchronize(device)
+    dt = time.perf_counter() - t0
+    out, _ = b.decode(tok, positions, 8)
+    out, ms = b.decode(int(out[-1]), positions + 8, n_gen - 8)
+    n = n_gen - 8
+    kv_bytes = 2.0 * (positions + n_gen // 2) * cfg.n_kv * cfg.hd * 2 * cfg.n_layer
+    res = {"workload": f"27B-class dense Q4_K_M, 64 layers, {positions} positions prefilled in chunks of 256, then {n} timed greedy tokens, f16 KV cache",
+           "prefill_tokens_per_s": positions / dt, "decode_tokens_per_s": n / (ms * 1e-3), "decode_ms_per_step": ms / n,
+           "weight_gb_per_token": b.weight_bytes_per_token / 1e9, "kv_gb_per_token": kv_bytes / 1e9,
+           "step_gb_per_s": (b.weight_bytes_per_token + kv_bytes) / (ms / n * 1e-3) / 1e9}
+    b.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours_single(args, cfg) -> dict:
     import numpy as np
     import torch
@@ -408,6 +442,8 @@ def run_ours_single(args, cfg) -> dict:
     res["roofline"]["gemv_sweep"] = time_gemv_sweep(dev, peak)
     res["prefill_gemm"] = time_prefill_gemm(dev)
     res["qwen2_7b_q4km"] = time_qwen2_prefill(dev)
+    if args.long_context:
+        res["dense_27b_q4km_32k"] = time_long_context(dev)
     return res
 
 
@@ -492,6 +528,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="llama3-8b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--long-context", action="store_true", help="also run the 27B-class model at 32768 positions (one GPU, about a minute)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
