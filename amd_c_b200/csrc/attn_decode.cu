@@ -1,17 +1,18 @@
-// attn_decode.cu -- split-KV decode attention with the K/V of a KV head read
-// once for all of its G query heads (grouped-query attention).
+// attn_decode.cu -- attention over the KV cache, the K / V of a KV head read once for all of its G query heads
+// (grouped-query attention). Three kernels share the geometry:
+//   attn_decode_kernel       one token per CTA set, CUDA cores (float or half cache, any supported head size)
+//   attn_decode_mma_kernel   the same on tensor cores for the half cache (hd 64 / 128): the decode default
+//   attn_prefill_mma_kernel  prompt chunks: 16 / G tokens of a KV head share one pass over the cache
 //
-// Grid: (split s, KV head g, token t). The positions 0 .. np-1 of token t
-// (np = first position + t + 1) are cut into S equal spans, a multiple of the
-// tile (64 positions). A CTA streams its span tile by tile: K and V tiles
-// (contiguous in the head-major cache [kv head][row][hd]) arrive in shared
-// memory through double-buffered 16-byte async copies; 8 lanes share one
-// position for q.k (q in registers, 3 shuffles per head), one warp per head
-// keeps the running max / sum (online softmax), and every lane owns hd/32
-// output dims for p.v. Each CTA writes (max, sum, out[hd]) per head to the
-// partials buffer; the last CTA of a (token, KV head) to arrive merges the S
-// partials in split order, divides, and writes the f32 output and its Q8 copy.
-// Bound by HBM at long context: 2 * np * hd * sizeof(KV) bytes per KV head.
+// Decode grid: (split s, KV head g, token t). The positions 0 .. np-1 of token t (np = first position + t + 1) are
+// cut into up to S spans, multiples of the tile (64 positions), at least ATT_MIN_SPAN long. A CTA streams its span
+// tile by tile: K and V tiles (contiguous in the head-major cache [kv head][row][hd]) arrive in shared memory
+// through 16-byte async copies, two or three tiles ahead; every warp owns some positions of each tile and keeps its
+// own running max / sum / output (online softmax), merged across the warps at the end. With one split the CTA
+// writes the result itself; otherwise it writes (max, sum, out[hd]) per head to the partials buffer and the last
+// CTA of a (token, KV head) to arrive merges the partials in split order, divides, and writes the f32 output and
+// its Q8 copy. The one-token form can also rotate q, rotate and store the step's own K / V row (FUSED).
+// Bound by HBM at long context: 2 * np * hd * sizeof(KV) bytes per KV head; by latency at short.
 #include <cuda_pipeline_primitives.h>
 
 #include <cstdlib>

@@ -275,7 +275,6 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
     }
 #pragma unroll
     for (int kb = 0; kb < GS_KB; kb++) {
-      const uint32_t b = step * GS_KB + kb;
       uint32_t wl[GM_MT][2], wh[GM_MT][2];
       float s0[GM_MT][2], s1[GM_MT][2];
 #pragma unroll

@@ -1,16 +1,18 @@
 // gemv_direct.cu -- the decode (one token) GEMV that streams weights straight
 // from HBM into registers, launched with programmatic dependent launch.
 //
-// Every warp of a persistent grid (two CTAs of eight warps per SM) takes row
-// pairs round-robin (pair g, g + W, ... for W warps in the grid); lane l takes
-// blocks l, l+32, ... of its rows, so each lane keeps up to 8 16-byte loads
-// in flight. The first loads of a warp are issued BEFORE the kernel
-// waits for its predecessor (the weights do not depend on it): the launch
-// latency, the DRAM latency and the predecessor's tail overlap with weight
-// traffic that is already on its way. Only then are the activations staged
-// (optionally computed: fused RMSNorm + Q8, see act_stage.cuh) and consumed.
-// Registers are capped at 80 per thread (three CTAs per SM): a kernel's own
-// two CTAs plus one early CTA of its successor are resident together.
+// Every warp of a persistent grid (exactly the resident CTAs: three of eight
+// warps per SM at 80 registers) takes row pairs round-robin (pair g, g + W, ...
+// for W warps in the grid); lane l takes blocks l, l+32, ... of its rows, so
+// each lane keeps up to 8 16-byte loads in flight (16 in the one-row-per-warp
+// variant for long rows). The first loads of a warp are issued BEFORE the
+// kernel waits for its predecessor (the weights do not depend on it): the
+// launch latency, the DRAM latency and the predecessor's tail overlap with
+// weight traffic that is already on its way. Only then are the activations
+// staged (optionally computed: fused RMSNorm + Q8, see act_stage.cuh) and
+// consumed. Optional tails: RMSNorm + Q8 of the finished vector by the last CTA
+// to arrive; tensor parallel: every finished row pair also stored into the
+// other ranks' slots (peer_ll.cuh).
 //
 // Arithmetic and order are the reference's (one warp per row, blocks
 // l, l+32, ... in order, shuffle-down tree): bit-exact with its CPU GEMV.
@@ -25,7 +27,7 @@
 
 namespace ieb {
 
-constexpr int GD_WARPS = 8, GD_THREADS = GD_WARPS * 32, GD_CTAS_PER_SM = 2;
+constexpr int GD_WARPS = 8, GD_THREADS = GD_WARPS * 32;
 
 struct GdArgs {
   const uint8_t *w;
