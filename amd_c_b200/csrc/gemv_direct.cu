@@ -194,7 +194,10 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
   const unsigned need = (a.rows + R * GD_WARPS - 1) / (R * GD_WARPS);
   unsigned grid = (unsigned)(sm_count() * MINB);
   if (grid > need) grid = need ? need : 1u;
-  // (An L2 bulk prefetch of the warp's further rows ahead of the dependency wait was tried: 4 % slower per step.)
+  // (L2 bulk prefetches were tried three ways and all lost: the warp's own further rows ahead of the dependency wait,
+  // 4 % slower per step; the weights of the first, second or third GEMV after this one, asked for by every CTA before
+  // its own work, 5-7 % slower; the same from a side stream forked inside the step graph, which also broke the
+  // programmatic-launch chain. Weights that come through L2 a little early do not stream faster than from HBM here.)
   IEB_LAUNCH_PDL("gemv_direct_kernel", k, dim3(grid), dim3(GD_THREADS), smem, st, a);
   return IE_B200_OK;
 }
