@@ -88,6 +88,64 @@ gemv_q_kernel(const uint8_t *__restrict__ w, size_t rowb, uint32_t rows, uint32_
   }
 }
 
+// Several tokens per pass over the weights (2..16 tokens: speculative verification, short prompt tails; the role of
+// ie_gemv_q4kq8_tr / _ts2 in the reference, kernels/ie_kernels.c:483-628): a CTA stages the Q8 buffers of TT tokens
+// and every loaded weight block is applied to each of them, every token in exactly the one-token order (lane l:
+// blocks l, l + 32, ... from 0.0f, then the tree), so each row of the result is bit for bit the one-token GEMV's.
+template <int KIND, int U, int TT>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_mt_kernel(const uint8_t *__restrict__ w, size_t rowb, uint32_t rows, uint32_t nb, const uint8_t *__restrict__ x, float *y,
+               const float *__restrict__ bias, const float *res, uint32_t T, size_t xs, size_t ys, size_t rs) {
+  extern __shared__ uint4 smem[];
+  const uint32_t t0 = blockIdx.y * TT, nt = min((uint32_t)TT, T - t0);
+  // per token: A0 plane, A1 plane (nb uint4 each), scales and sums (nb words each)
+  const size_t per_tok = (size_t)nb * 40u / 16u;  // in uint4
+  for (uint32_t t = 0; t < nt; t++) {
+    uint4 *A0 = smem + t * per_tok, *A1 = A0 + nb;
+    stage_q8(x + (size_t)(t0 + t) * xs, nb, A0, A1, reinterpret_cast<float *>(A1 + nb), reinterpret_cast<int *>(reinterpret_cast<float *>(A1 + nb) + nb));
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (uint32_t r = blockIdx.x * GEMV_WARPS + warp; r < rows; r += gridDim.x * GEMV_WARPS) {
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.0f;
+    for (uint32_t c = 0; c < nb; c += 32u * U) {
+      Blk<KIND, false> blk[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t b = c + 32u * u + lane;
+        if (b < nb) blk[u].load(w + (size_t)r * rowb, b, nb);
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t b = c + 32u * u + lane;
+        if (b < nb) {
+#pragma unroll
+          for (int t = 0; t < TT; t++) {
+            if ((uint32_t)t < nt) {
+              const uint4 *A0 = smem + t * per_tok, *A1 = A0 + nb;
+              const float *da = reinterpret_cast<const float *>(A1 + nb);
+              const int *as = reinterpret_cast<const int *>(da + nb);
+              acc[t] = blk[u].accum(acc[t], A0[b], A1[b], da[b], as[b], b);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+      const float v = warp_tree(acc[t]);
+      if (lane == 0 && (uint32_t)t < nt) {
+        float o = v;
+        if (bias) o = __fadd_rn(o, bias[r]);
+        if (res) o = __fadd_rn(reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + (size_t)(t0 + t) * rs)[r], o);
+        reinterpret_cast<float *>(reinterpret_cast<char *>(y) + (size_t)(t0 + t) * ys)[r] = o;
+      }
+    }
+  }
+}
+
 // f32 matrix: lane l sums elements l, l+32, ... in order (product rounded,
 // then added), then the tree. x staged in shared memory; 8 loads in flight per lane.
 __global__ void __launch_bounds__(GEMV_THREADS)
@@ -160,10 +218,27 @@ static unsigned gemv_grid(uint32_t rows, int rows_per_cta, int ctas_per_sm) {
   return need < cap ? (need ? need : 1u) : cap;
 }
 
+template <int KIND, int U, int TT>
+static int launch_mt(const void *w, uint32_t rows, uint32_t cols, const void *x, float *y, const float *bias, const float *res, uint32_t T,
+                     size_t xs, size_t ys, size_t rs, cudaStream_t st) {
+  const uint32_t nb = cols / 32u;
+  const size_t smem = (size_t)nb * 40u * TT;
+  auto k = gemv_mt_kernel<KIND, U, TT>;
+  if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  const dim3 grid(gemv_grid(rows, GEMV_WARPS, smem > 100u * 1024u ? 1 : 2), (T + TT - 1) / TT);
+  k<<<grid, GEMV_THREADS, smem, st>>>(static_cast<const uint8_t *>(w), row_bytes_of(KIND, cols), rows, nb, static_cast<const uint8_t *>(x), y,
+                                      bias, res, T, xs, ys, rs);
+  IEB_LAUNCHED("gemv_mt_kernel");
+  return IE_B200_OK;
+}
+
 template <int KIND, int R, int U>
 static int launch_q(const void *w, uint32_t rows, uint32_t cols, const void *x, float *y, const float *bias, const float *res, uint32_t T,
                     size_t xs, size_t ys, size_t rs, cudaStream_t st) {
   const uint32_t nb = cols / 32u;
+  // several tokens: one pass over the weights for up to 8 (4 when the rows are long) tokens, if their Q8 buffers fit
+  if (T >= 2 && nb % 2u == 0 && (size_t)nb * 40u * 8u <= 200u * 1024u) return launch_mt<KIND, U, 8>(w, rows, cols, x, y, bias, res, T, xs, ys, rs, st);
+  if (T >= 2 && nb % 2u == 0 && (size_t)nb * 40u * 4u <= 200u * 1024u) return launch_mt<KIND, U, 4>(w, rows, cols, x, y, bias, res, T, xs, ys, rs, st);
   const size_t smem = (size_t)nb * 40u;
   auto k = gemv_q_kernel<KIND, R, U>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;

@@ -208,7 +208,12 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
 template <int KIND, bool NORM, bool TP>
 static int pick_direct(const GdArgs &a, cudaStream_t st) {
   constexpr int U2 = KIND == IE_B200_MAT_Q4 ? 4 : 2;
-  const bool few_long = a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
+  static const int long_mode = [] {  // IE_B200_GEMV_LONG: 0 never, 1 (default) 16 lane steps at 2 CTAs/SM, 2: 8 lane steps at 3 CTAs/SM
+    const char *v = getenv("IE_B200_GEMV_LONG");
+    return v ? atoi(v) : 1;
+  }();
+  const bool few_long = long_mode && a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
+  if (few_long && long_mode == 2) return launch_direct<KIND, NORM, 1, 2 * U2, 3, TP>(a, st);
   if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2, TP>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
   return launch_direct<KIND, NORM, 2, U2, 3, TP>(a, st);
 }

@@ -543,3 +543,22 @@ def test_attention_prefill_chunk(ora, cuda, n_head, n_kv, hd, T, pos0):
         want = ora.attention(q[t], kc_ref, vc_ref, pos0 + t, n_head, n_kv, hd)
         assert np.abs(out[t] - want).max() <= 1e-4 * np.abs(want).max(), t
         assert (oq[t] == ora.quant_q8(out[t])).all(), t
+
+
+@pytest.mark.parametrize("typ,rows,cols,T", [(synth.GGML_Q4_0, 130, 1024, 11), (synth.GGML_Q4_K, 77, 512, 16), (synth.GGML_Q6_K, 40, 18944, 5),
+                                             (synth.GGML_Q4_0, 9, 96, 2)])
+def test_gemv_several_tokens_one_pass(ora, cuda, typ, rows, cols, T):
+    """2..16 tokens share one pass over the weights (groups of 8 or 4 tokens per CTA, ragged last group, odd block
+    counts through the per-token kernel): every token's row is bit for bit the oracle's one-token GEMV."""
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows * 3 + T)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    res = rng.standard_normal((T, rows)).astype(np.float32)
+    xq = np.stack([ora.quant_q8(x[t]) for t in range(T)])
+    y = K.gemv(m, dev(xq, cuda), res=dev(res, cuda)).cpu().numpy()
+    for t in range(T):
+        assert (bits(y[t]) == bits(ora.gemv(kind, qw, qs, rows, cols, xq[t], res=res[t]))).all(), t
