@@ -97,6 +97,7 @@ SIGNATURES.update({
     "ie_b200_ar_create": (_int, [_u32, _u32, _u32, C.POINTER(_vp)]),
     "ie_b200_ar_handles": (_int, [_vp, _vp]),
     "ie_b200_ar_connect": (_int, [_vp, _vp]),
+    "ie_b200_ar_connect_local": (_int, [_vp, C.POINTER(_vp)]),
     "ie_b200_ar_allreduce_add": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_allreduce_norm": (_int, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_gemv_allreduce_norm": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),

@@ -316,6 +316,20 @@ extern "C" int ie_b200_ar_connect(ie_b200_allreduce *a, const void *h_all) {
   return IE_B200_OK;
 }
 
+extern "C" int ie_b200_ar_connect_local(ie_b200_allreduce *a, ie_b200_allreduce *const *all) {
+  if (!a || !all) return fail(IE_B200_E_ARG, "ie_b200_ar_connect_local: NULL argument");
+  for (uint32_t j = 0; j < a->d.world; j++) {
+    if (j == a->d.rank) continue;
+    const ie_b200_allreduce *p = all[j];
+    if (!p || p->d.world != a->d.world || p->d.rank != j || p->d.max_n != a->d.max_n)
+      return fail(IE_B200_E_ARG, "ie_b200_ar_connect_local: state %u does not belong to this world", j);
+    a->d.slots[j] = reinterpret_cast<float *>(p->base), a->d.flags[j] = reinterpret_cast<uint32_t *>(p->base + p->off_flags);
+    a->d.ll[j] = reinterpret_cast<unsigned long long *>(p->base + p->off_ll);
+  }
+  a->connected = true;
+  return IE_B200_OK;
+}
+
 extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_out, uint32_t n, uint32_t *d_err,
                                         void *stream) {
   if (!a || !d_part || !d_out) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_add: NULL argument");

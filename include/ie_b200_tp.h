@@ -25,6 +25,10 @@ int ie_b200_ar_create(uint32_t rank, uint32_t world, uint32_t max_floats, ie_b20
 int ie_b200_ar_handles(ie_b200_allreduce *a, void *h_out128);
 /* h_all: the world blobs in rank order (world * 128 bytes). Not needed when world == 1. */
 int ie_b200_ar_connect(ie_b200_allreduce *a, const void *h_all);
+/* The same for states that live in THIS process on GPUs that can address each other (or on one GPU): all[j] is
+ * rank j's state. For hosts that drive several GPUs from one process, and for exercising the bounded waits: a
+ * call made on one rank only finds no partner, gives up after the time limit, sets the error word and returns. */
+int ie_b200_ar_connect_local(ie_b200_allreduce *a, ie_b200_allreduce *const *all);
 /* out = (res ? res : 0) + sum over ranks of part, n floats (a multiple of 4). Every rank must make the same
  * sequence of calls. d_err (may be NULL): set to 3 if a peer did not arrive within the time limit. out may
  * alias res. */

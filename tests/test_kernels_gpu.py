@@ -562,3 +562,41 @@ def test_gemv_several_tokens_one_pass(ora, cuda, typ, rows, cols, T):
     y = K.gemv(m, dev(xq, cuda), res=dev(res, cuda)).cpu().numpy()
     for t in range(T):
         assert (bits(y[t]) == bits(ora.gemv(kind, qw, qs, rows, cols, xq[t], res=res[t]))).all(), t
+
+
+def test_allreduce_missing_rank_gives_up(cuda, lib):
+    """Failure detection without a fault: a world of two ranks whose second rank never calls. The kernel's wait for
+    the peer's words is bounded (2 s): it sets the device error word to 3 and returns, the context stays usable, and
+    the next call on a complete world of one rank works."""
+    import ctypes as C
+    import time
+
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    n = 256
+    hs = (C.c_void_p * 2)()
+    for r in range(2):
+        h = C.c_void_p()
+        K.check(lib.ie_b200_ar_create(r, 2, n, C.byref(h)))
+        hs[r] = h
+    try:
+        for r in range(2):
+            K.check(lib.ie_b200_ar_connect_local(hs[r], hs))
+        x, part = torch.ones(n, device=cuda), torch.ones(n, device=cuda)
+        nw, err = torch.ones(n, device=cuda), torch.zeros(1, dtype=torch.int32, device=cuda)
+        xn, xq = torch.empty(n, device=cuda), torch.empty(40 * (n // 32), dtype=torch.uint8, device=cuda)
+        t0 = time.time()
+        K.check(lib.ie_b200_ar_allreduce_norm(hs[0], part.data_ptr(), x.data_ptr(), nw.data_ptr(), 1e-5, xn.data_ptr(), xq.data_ptr(), n,
+                                              err.data_ptr(), None))
+        torch.cuda.synchronize()
+        waited = time.time() - t0
+        assert int(err.item()) == 3
+        assert 1.5 < waited < 10.0, waited
+        # the context is intact: an ordinary kernel still runs and is right
+        y = K.quant_q8(torch.full((1, 32), 2.0, device=cuda)).cpu().numpy()[0]
+        assert (y[:32].view(np.int8) == 127).all()
+    finally:
+        for r in range(2):
+            lib.ie_b200_ar_destroy(hs[r])
