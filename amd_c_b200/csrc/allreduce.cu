@@ -2,7 +2,7 @@
 // step: the sum over ranks of a dim-float partial (16-20 KB) after every
 // K-split GEMV, fused with the residual add. One process per GPU; every rank
 // maps the other ranks' receive buffers with CUDA IPC and the kernel moves the
-// data itself with plain peer stores over NVLink (no multicast, no TMA):
+// data itself with plain peer stores over NVLink (nothing replicated by the switch, no TMA):
 //
 //   push   each CTA writes its slice of this rank's partial into slot [rank]
 //          of EVERY rank's receive buffer (its own included), then publishes
