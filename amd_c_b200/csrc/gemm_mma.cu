@@ -297,11 +297,21 @@ __global__ void __launch_bounds__(256, 2) gemm_staged_kernel(const GemmArgs a) {
             s0[i][h] = __fmul_rn(dq6[i][h], (float)(int8_t)(sc & 255u)), s1[i][h] = __fmul_rn(dq6[i][h], (float)(int8_t)(sc >> 8));
           }
         }
+      // B fragments of two token tiles per ldmatrix: an 8 x 8 matrix of 16-bit words = 8 tokens x 16 bytes, and lane (g, t)
+      // receives bytes 4t .. 4t + 3 of token g: matrices (tile j, bytes 0..15), (tile j, 16..31), (tile j + 1, 0..15), (.., 16..31)
+      uint32_t bf[NT][2];
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t r4[4];
+        const uint8_t *q = st + L::X + (wn * 8 * NT + 8 * (j + (lane >> 4)) + (lane & 7)) * GS_XS + kb * 32 + ((lane >> 3) & 1) * 16;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r4[0]), "=r"(r4[1]), "=r"(r4[2]), "=r"(r4[3]) : "r"((uint32_t)__cvta_generic_to_shared(q)));
+        bf[j][0] = r4[0], bf[j][1] = r4[1], bf[j + 1][0] = r4[2], bf[j + 1][1] = r4[3];
+      }
 #pragma unroll
       for (int j = 0; j < NT; j++) {
         const int tl = wn * 8 * NT + 8 * j;
-        const uint8_t *q = st + L::X + (tl + g) * GS_XS + kb * 32 + 4 * t;
-        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(q), b1 = *reinterpret_cast<const uint32_t *>(q + 16);
+        const uint32_t b0 = bf[j][0], b1 = bf[j][1];
         const float2 da2 = *reinterpret_cast<const float2 *>(st + L::DA + (kb * TOKS + tl + 2 * t) * 4);
         const float da[2] = {da2.x, da2.y};
         float das[2] = {0.0f, 0.0f};
