@@ -460,8 +460,6 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, where exactly one JSON line is expected
     dist.init_process_group("nccl", device_id=dev)
     K, W = args.steps, args.warmup
     n_ctx = PROMPT_LEN + 2 * (K + W) + 8
@@ -544,7 +542,17 @@ def main() -> None:
         args.gpus = world
     if args.gpus > 1 and world == 1:
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
-    res = run_ours_single(args, cfg) if world == 1 else run_ours_tp(args, cfg, rank, world)
+    # Exactly one JSON line goes to stdout: while the benchmark runs, file descriptor 1 points at stderr, so that
+    # banners that libraries write straight to it (NCCL's version line) do not land in front of the result.
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        res = run_ours_single(args, cfg) if world == 1 else run_ours_tp(args, cfg, rank, world)
+    finally:
+        sys.stdout.flush()
+        os.dup2(out_fd, 1)
+        os.close(out_fd)
     if rank != 0:
         return
     line = {"metric": METRIC, "value": res.pop("value"), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
