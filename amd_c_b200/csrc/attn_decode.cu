@@ -64,6 +64,16 @@ struct AttnArgs {
 
 constexpr uint32_t ATT_MIN_SPAN = 256;  // positions a split covers at least: short contexts stay in one CTA per KV head (no merge)
 
+// The span of one split for np positions over at most S splits: as many splits as spans of ATT_MIN_SPAN positions fit
+// (at least one), and the positions dealt evenly over them (in whole tiles), so that no split is left with a sliver
+// while another holds a full span (300 positions: 192 + 108 rather than 256 + 44).
+__device__ __forceinline__ uint32_t att_span(uint32_t np, uint32_t S) {
+  uint32_t want = (np + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;
+  want = want < 1u ? 1u : (want > S ? S : want);
+  const uint32_t span = (np + want - 1u) / want;
+  return (span + ATT_TILE - 1u) / ATT_TILE * ATT_TILE;
+}
+
 // a * c - b * s and a * s + b * c with every product rounded, as the RoPE kernel and the CPU do
 __device__ __forceinline__ float rope_lo(float a, float b, float c, float s) { return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)); }
 __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)); }
@@ -158,8 +168,7 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
   if (!early) pdl_wait();
   const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
   const uint32_t np = *a.pos + t + 1u;
-  uint32_t span = max((np + S - 1u) / S, ATT_MIN_SPAN);
-  span = (span + TILE - 1u) / TILE * TILE;
+  const uint32_t span = att_span(np, S);
   const uint32_t A = (np + span - 1u) / span;  // splits that hold positions; the others have nothing to do
   if (s >= A) return;
   const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
@@ -483,8 +492,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   if (!early) pdl_wait();
   const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
   const uint32_t np = *a.pos + t + 1u;
-  uint32_t span = max((np + S - 1u) / S, ATT_MIN_SPAN);
-  span = (span + TILE - 1u) / TILE * TILE;
+  const uint32_t span = att_span(np, S);
   const uint32_t A = (np + span - 1u) / span;
   if (s >= A) return;
   const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
