@@ -62,13 +62,13 @@ struct AttnArgs {
   int early_kv;
 };
 
-constexpr uint32_t ATT_MIN_SPAN = 256;  // positions a split covers at least: short contexts stay in one CTA per KV head (no merge)
+constexpr uint32_t ATT_MIN_SPAN = 256;  // about the positions of a split; up to twice as many stay in one CTA per KV head (no merge)
 
 // The span of one split for np positions over at most S splits: as many splits as spans of ATT_MIN_SPAN positions fit
 // (at least one), and the positions dealt evenly over them (in whole tiles), so that no split is left with a sliver
 // while another holds a full span (300 positions: 192 + 108 rather than 256 + 44).
 __device__ __forceinline__ uint32_t att_span(uint32_t np, uint32_t S) {
-  uint32_t want = (np + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;
+  uint32_t want = np <= 2u * ATT_MIN_SPAN ? 1u : (np + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;  // one CTA up to 512 positions: a merge costs more than four tiles
   want = want < 1u ? 1u : (want > S ? S : want);
   const uint32_t span = (np + want - 1u) / want;
   return (span + ATT_TILE - 1u) / ATT_TILE * ATT_TILE;
