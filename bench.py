@@ -11,7 +11,10 @@ line goes to stdout (rank 0):
             memory every step, argmax read back every step
   roofline  the GEMV kernels of the step (the dominant kernel) alone, timed
             with CUDA events on their stream: algorithmic weight bytes / time
-            against the measured HBM copy bandwidth
+            against the measured HBM copy bandwidth; gemv_sweep: the stand-alone
+            GEMV at the Llama-3-8B shapes
+  attention, prefill_gemm, qwen2_7b_q4km  the other kernels and the prompt path
+            (one GPU only)
   cpu_baseline  the reference's own CPU GEMV (oracle/_ref, built from its
             sources) or the oracle port, on a bounded sample, 1 core
 Weights are seeded synthetic (no network, no checkpoint): N(0, 0.02) quantised
@@ -288,6 +291,55 @@ def time_gemv_sweep(device, peak: float) -> list[dict]:
     return out
 
 
+def time_attention(device, peak: float) -> list[dict]:
+    """The decode attention kernel alone (32 query / 8 KV heads of 128, f16 cache, RoPE + KV store fused) at short and
+    long contexts: a graph of 40 launches over rotating caches larger than L2, CUDA events on the capturing stream.
+    Algorithmic bytes: 2 x (positions + 1) x n_kv x hd x 2 B."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    n_head, n_kv, hd = 32, 8, 128
+    out = []
+    for positions in (256, 4096, 32768):
+        n_ctx = positions + 8
+        gen = torch.Generator(device=device).manual_seed(positions)
+        nl = max(2, int(300e6 // (2 * n_kv * n_ctx * hd * 2)) + 1)
+        kc = [(torch.randn(n_kv, n_ctx, hd, device=device, generator=gen) * 0.5).half() for _ in range(nl)]
+        vc = [(torch.randn(n_kv, n_ctx, hd, device=device, generator=gen) * 0.5).half() for _ in range(nl)]
+        cos, sin = torch.ones(n_ctx, hd // 2, device=device), torch.zeros(n_ctx, hd // 2, device=device)
+        qkv = torch.randn((n_head + 2 * n_kv) * hd, device=device, generator=gen)
+        pos = torch.tensor([positions], dtype=torch.int32, device=device)
+        sc = K.AttnScratch(n_head, hd, n_ctx, 1, device)
+        s = torch.cuda.Stream(device=device)
+        n = 40
+
+        def launch(i):
+            K.attn_decode_fused(qkv, kc[i % nl], vc[i % nl], cos, sin, pos, n_head, n_kv, hd, False, n_ctx, sc)
+
+        with torch.cuda.stream(s):
+            for i in range(3):
+                launch(i)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for i in range(n):
+                    launch(i)
+            g.replay()
+            s.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            s.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        gbs = 2.0 * (positions + 1) * n_kv * hd * 2 / us / 1e3
+        out.append({"positions": positions, "us": round(us, 2), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3)})
+        del kc, vc, g
+        torch.cuda.empty_cache()
+    return out
+
+
 def time_prefill_gemm(device) -> dict:
     """The prompt-chunk GEMM on the Qwen2-7B Q4_K_M FFN shapes, one chunk of 256 tokens: int8 tensor-core block dots +
     fp32 scaling. Reported as 2 * rows * cols * T / time; the tensor peak is not the bound of this kernel (the per-block
@@ -440,6 +492,7 @@ def run_ours_single(args, cfg) -> dict:
     b.close()
     torch.cuda.empty_cache()
     res["roofline"]["gemv_sweep"] = time_gemv_sweep(dev, peak)
+    res["attention"] = time_attention(dev, peak)
     res["prefill_gemm"] = time_prefill_gemm(dev)
     res["qwen2_7b_q4km"] = time_qwen2_prefill(dev)
     if args.long_context:
