@@ -79,7 +79,7 @@ __device__ __forceinline__ float rope_lo(float a, float b, float c, float s) { r
 __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)); }
 
 // The last split to arrive merges the A partial records (max, sum, out[hd]) of every head of its KV head, in split
-// order. The weights exp(max_k - max) and the denominators are worked out once in shared memory; the outputs are
+// order. The weights exp(max_k - max) and the denominators are worked out once in shared memory (a warp per head); the outputs are
 // then summed with many independent loads in flight per thread (a plain loop over the splits is one L2 round trip
 // per split and per pass: 16 us at 17 splits).
 // part: the records of this token's first head of the KV head, [G][S][hd + 2]; scr: (2 A + 2) G floats of shared memory.
@@ -92,18 +92,20 @@ __device__ __forceinline__ void merge_partials(const float *part, uint32_t S, ui
     mk[i] = __ldcg(pr), lk[i] = __ldcg(pr + 1);
   }
   __syncthreads();
-  if (threadIdx.x < G) {
+  // one warp per head: its lanes share the splits (maximum, weights exp(max_k - max), denominator), no block-wide steps
+  for (int h = threadIdx.x >> 5; h < G; h += THREADS / 32) {
+    const int lane = threadIdx.x & 31;
     float M = -INFINITY;
-    for (uint32_t k = 0; k < A; k++) M = fmaxf(M, mk[threadIdx.x * A + k]);
-    mh[threadIdx.x] = M;
-  }
-  __syncthreads();
-  for (uint32_t i = threadIdx.x; i < G * A; i += THREADS) mk[i] = expf(mk[i] - mh[i / A]);  // now the weight of split k
-  __syncthreads();
-  if (threadIdx.x < G) {
+    for (uint32_t k = lane; k < A; k += 32u) M = fmaxf(M, mk[h * A + k]);
+    M = warp_max(M);
     float L = 0.0f;
-    for (uint32_t k = 0; k < A; k++) L = fmaf(mk[threadIdx.x * A + k], lk[threadIdx.x * A + k], L);
-    lh[threadIdx.x] = L;
+    for (uint32_t k = lane; k < A; k += 32u) {
+      const float w = expf(mk[h * A + k] - M);
+      mk[h * A + k] = w;  // now the weight of split k
+      L = fmaf(w, lk[h * A + k], L);
+    }
+    L = warp_sum_all(L);
+    if (lane == 0) mh[h] = M, lh[h] = L;
   }
   __syncthreads();
   // all of a thread's elements together, four splits at a time: (elements x 4) independent loads per round trip
