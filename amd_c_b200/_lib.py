@@ -36,6 +36,7 @@ SIGNATURES = {
     "ie_b200_embed": (_int, [_int, _vp, _u32, _vp, _vp, _u32, _sz, _vp]),
     "ie_b200_rmsnorm": (_int, [_vp, _vp, _vp, _u32, _f32, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_swiglu": (_int, [_vp, _vp, _u32, _vp, _u32, _sz, _sz, _vp]),
+    "ie_b200_swiglu_il": (_int, [_vp, _vp, _u32, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_rope_kv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _int, _u32, _u32, _sz, _vp]),
     "ie_b200_attn_part_bytes": (_sz, [_u32, _u32, _u32, _u32]),
     "ie_b200_attn_count_words": (_sz, [_u32, _u32]),

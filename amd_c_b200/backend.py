@@ -114,7 +114,7 @@ class Backend:
         c = self.cfg
         qd, kvd = self.nh * self.hd, self.nkv * self.hd
         sizes = [("x", c.dim * 4), ("xn", c.dim * 4), ("xq", q8_bytes(c.dim // 32)), ("qkv", (qd + 2 * kvd) * 4), ("att", qd * 4),
-                 ("attq", q8_bytes(qd // 32)), ("gu", 2 * self.ffn_l * 4), ("guq", q8_bytes(self.ffn_l // 32)), ("part", c.dim * 4),
+                 ("attq", q8_bytes(qd // 32)), ("gu", 2 * self.ffn_l * 4), ("h", self.ffn_l * 4), ("guq", q8_bytes(self.ffn_l // 32)), ("part", c.dim * 4),
                  ("logits", self.vocab_l * 4), ("argmax", 8)]
         self.bufs, off = {}, 0
         for name, n in sizes:
@@ -130,8 +130,10 @@ class Backend:
             return torch.from_numpy(np.ascontiguousarray(raw).reshape(-1)).to(self.device)
         return raw.contiguous().reshape(-1)
 
-    def _add_mat(self, parts) -> int:
-        """parts: list of (ggml_type, rows, cols, raw bytes) with one type and column count: stacked by rows into one matrix."""
+    def _add_mat(self, parts, interleave: bool = False) -> int:
+        """parts: list of (ggml_type, rows, cols, raw bytes) with one type and column count: stacked by rows into one matrix.
+        interleave (two parts of equal row count): rows alternate part 0, part 1 (gate_i, up_i), so that the warp that owns a
+        row pair of the GEMV owns one SwiGLU output."""
         torch = self.torch
         typ, cols = parts[0][0], parts[0][2]
         kind = GGML_TO_MAT[typ]
@@ -145,6 +147,10 @@ class Backend:
             check(self.lib.ie_b200_repack_gguf(typ, src.data_ptr(), pr, cols, buf.data_ptr() + r * rowb, st))
             r += pr
         torch.cuda.current_stream(self.device).synchronize()
+        if interleave:
+            half = rows // 2
+            two = buf[: rows * rowb].view(2, half, rowb)
+            buf = torch.stack((two[0], two[1]), dim=1).reshape(-1).contiguous()
         self._keep.append(buf)
         h = self.lib.ie_b200_engine_add_mat_device(self.h, kind, rows, cols, buf.data_ptr())
         if h < 0:
@@ -187,7 +193,7 @@ class Backend:
         (ao, as_), (bo, bs), (co, cs), (qoo, qs), (ro, rs) = o(a, aoff), o(b, boff), o(c, coff), o(qo), o(res)
         self.ops.append(Op(kind, mat, vec, layer, n, nh, ao, bo, co, qoo, ro, as_, bs, cs, qs, rs))
 
-    def _gemv_group(self, names_rows, x_q8: str, x_f32: str, out: str, bias_names=None):
+    def _gemv_group(self, names_rows, x_q8: str, x_f32: str, out: str, bias_names=None, interleave: bool = False) -> bool:
         """GEMVs of several row slices into one output buffer: merged into one matrix when the kinds agree
         (as the reference merges q/k/v and gate/up, src/model.c:882-887), else one GEMV per part at its offset."""
         parts = [self._rows(n, r0, r1) for n, r0, r1 in names_rows]
@@ -195,10 +201,11 @@ class Backend:
         if bias_names:
             bias = np.concatenate([self._vec(n)[r0:r1] for (n, r0, r1) in bias_names])
         if len({p[0] for p in parts}) == 1:
-            m = self._add_mat(parts)
             f32 = parts[0][0] == GGML_F32
+            il = interleave and not f32 and len(parts) == 2 and parts[0][1] == parts[1][1] and bias is None
+            m = self._add_mat(parts, interleave=il)
             self._op(OP_GEMV, a=x_f32 if f32 else x_q8, b=out, mat=m, vec=self._add_vec(bias) if bias is not None else -1, n=parts[0][2])
-            return
+            return il
         off = 0
         for p in parts:
             m = self._add_mat([p])
@@ -206,6 +213,7 @@ class Backend:
             v = self._add_vec(bias[off: off + p[1]]) if bias is not None else -1
             self._op(OP_GEMV, a=x_f32 if f32 else x_q8, b=out, boff=off * 4, mat=m, vec=v, n=p[2])
             off += p[1]
+        return False
 
     def _build_ops(self):
         c, tp, r = self.cfg, self.tp, self.rank
@@ -232,8 +240,12 @@ class Backend:
                 self._op(OP_GEMV, a="attq", b="part", mat=wo, n=qd)
                 self._op(OP_ALLREDUCE, a="part", c="x", n=c.dim)  # x = x + sum over ranks of part
                 self._op(OP_RMSNORM, a="x", b="xn", qo="xq", vec=nxt_norm, n=c.dim)
-            self._gemv_group([(p + "ffn_gate.weight", f0, f0 + self.ffn_l), (p + "ffn_up.weight", f0, f0 + self.ffn_l)], "xq", "xn", "gu")
-            self._op(OP_SWIGLU, a="gu", b="gu", boff=self.ffn_l * 4, qo="guq", n=self.ffn_l)
+            il = self._gemv_group([(p + "ffn_gate.weight", f0, f0 + self.ffn_l), (p + "ffn_up.weight", f0, f0 + self.ffn_l)], "xq", "xn", "gu",
+                                  interleave=self.ffn_l % 32 == 0)
+            if il:  # gate_i / up_i in alternating rows: gu holds the pairs, h = silu(gate) * up; one token folds it into the GEMV
+                self._op(OP_SWIGLU, a="gu", b="h", qo="guq", n=self.ffn_l, nh=1)
+            else:
+                self._op(OP_SWIGLU, a="gu", b="gu", boff=self.ffn_l * 4, qo="guq", n=self.ffn_l)
             wd = self._add_mat([self._cols(p + "ffn_down.weight", f0, f0 + self.ffn_l)])
             nname = f"blk.{l + 1}.attn_norm.weight" if l + 1 < c.n_layer else "output_norm.weight"
             nxt_norm = self._add_vec(self._vec(nname))

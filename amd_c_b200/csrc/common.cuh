@@ -26,8 +26,14 @@ int ensure_dynamic_smem(const void *func, size_t bytes);
 //   late_trigger        the kernel lets its dependents start only after its own dependency wait, so a dependent
 //                       that starts knows that everything before this kernel has completed;
 //   after_late_trigger  the kernel before this one was launched with late_trigger.
+//   swi_h               the GEMV's rows are interleaved (gate_i, up_i) pairs: write silu(gate) * up to swi_h[i] instead of
+//                       the two rows, count arrivals per 32 outputs in swi_count (zero between launches), and let the
+//                       warp that completes a block write its Q8 copy into swi_q.
 struct LaunchHints {
   bool late_trigger = false, after_late_trigger = false;
+  float *swi_h = nullptr;
+  uint8_t *swi_q = nullptr;
+  uint32_t *swi_count = nullptr;
 };
 void set_hints(const LaunchHints &h);
 bool gemv_uses_ring();  // IE_B200_GEMV=ring selects the bulk-copy ring kernel instead of the direct one (gemv_stream.cu)

@@ -71,6 +71,10 @@ struct ie_b200_engine {
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
+  uint32_t *swi_count = nullptr;  // arrival counters of the GEMV-fused SwiGLU, one per 32 outputs (zero between launches)
+  uint32_t swi_blocks = 0;
+  bool no_swi_fuse = true;        // IE_B200_SWIGLU_FUSE=1 folds the interleaved SwiGLU into the gate / up GEMV (measured slower: 1.71 against 1.42 ms
+                                  // per token, the fence + arrival counter per row pair stalls the weight stream), default: a kernel of its own
   ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
   uint32_t vocab_off = 0;           // first vocabulary row of this shard's output head
   std::vector<EMat> mats;
@@ -152,7 +156,9 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       }
       return IE_B200_OK;
     }
-    case IE_B200_OP_SWIGLU: return ie_b200_swiglu(static_cast<float *>(a), static_cast<float *>(b), o.n, qo, T, o.a_stride, o.qo_stride, st);
+    case IE_B200_OP_SWIGLU:
+      if (o.nh == 1u) return ie_b200_swiglu_il(static_cast<float *>(a), static_cast<float *>(b), o.n, qo, T, o.a_stride, o.b_stride, o.qo_stride, st);
+      return ie_b200_swiglu(static_cast<float *>(a), static_cast<float *>(b), o.n, qo, T, o.a_stride, o.qo_stride, st);
     case IE_B200_OP_ARGMAX: {
       if (int r = ie_b200_argmax(static_cast<float *>(a), o.n, static_cast<uint32_t *>(b), T, o.a_stride, o.b_stride, e->argmax_part, st)) return r;
       if (!e->ar) return IE_B200_OK;
@@ -222,6 +228,23 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       if (r) return r;
       i++;
       continue;
+    }
+    // gate / up GEMV over interleaved rows + SwiGLU + Q8 in one kernel (one token)
+    if (T == 1 && !e->no_swi_fuse && o.kind == IE_B200_OP_GEMV && i + 1 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
+        o.vec < 0 && o.res == IE_B200_NONE && (kind_mask & (1u << IE_B200_OP_SWIGLU))) {
+      const ie_b200_op &nx = e->ops[i + 1];
+      const EMat &m = e->mats[o.mat];
+      if (nx.kind == IE_B200_OP_SWIGLU && nx.nh == 1u && nx.a == o.b && nx.qo != IE_B200_NONE && m.rows == 2u * nx.n && nx.n % 32u == 0 &&
+          nx.n / 32u <= e->swi_blocks) {
+        LaunchHints hints;
+        hints.swi_h = static_cast<float *>(at(e, nx.b, 0, 0)), hints.swi_q = static_cast<uint8_t *>(at(e, nx.qo, 0, 0)), hints.swi_count = e->swi_count;
+        set_hints(hints);
+        int r = ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)), nullptr, nullptr, e->err,
+                                    e->err + 2, st);
+        if (r) return r;
+        i++;
+        continue;
+      }
     }
     // tensor parallel: a K-split GEMV that stores every finished row to the other ranks as well, then the one-CTA kernel
     // that waits for the peers' rows, reduces onto the residual stream and normalises
@@ -342,6 +365,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
   if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
   if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
+  if (const char *sf = getenv("IE_B200_SWIGLU_FUSE")) e->no_swi_fuse = sf[0] != '1';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");
@@ -363,6 +387,7 @@ extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
     if (m.owned) cudaFree(m.d);
   for (auto &v : e->vecs) cudaFree(v.d);
   cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
+  cudaFree(e->swi_count);
   cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
   if (e->h_scalars) cudaFreeHost(e->h_scalars);
   if (e->h_result) cudaFreeHost(e->h_result);
@@ -480,6 +505,16 @@ extern "C" int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, 
     if ((o.kind == IE_B200_OP_ROPE_KV || o.kind == IE_B200_OP_ATTN) && (o.layer < 0 || (uint32_t)o.layer >= e->d.n_kv_layers))
       return fail(IE_B200_E_ARG, "op %u: KV layer %d of %u", i, o.layer, e->d.n_kv_layers);
     if (o.mat >= (int)e->mats.size() || o.vec >= (int)e->vecs.size()) return fail(IE_B200_E_ARG, "op %u: unknown handle", i);
+  }
+  uint32_t blocks = 0;
+  for (uint32_t i = 0; i < n_ops; i++)
+    if (ops[i].kind == IE_B200_OP_SWIGLU && ops[i].nh == 1u && ops[i].n / 32u > blocks) blocks = ops[i].n / 32u;
+  if (blocks > e->swi_blocks) {
+    cudaFree(e->swi_count);
+    e->swi_count = nullptr;
+    IEB_CUDA(cudaMalloc(&e->swi_count, (size_t)blocks * 4u));
+    IEB_CUDA(cudaMemset(e->swi_count, 0, (size_t)blocks * 4u));
+    e->swi_blocks = blocks;
   }
   e->ops.assign(ops, ops + n_ops);
   e->i_head = i_head;

@@ -42,6 +42,9 @@ struct GdArgs {
   uint32_t late;      // let dependents start only after this kernel's own dependency wait (LaunchHints::late_trigger)
   uint32_t *work;     // two words, zero between launches; word 1 counts the CTAs that have finished (norm tail only)
   ArPush push;        // TP kernels only: every finished row also goes to the other ranks' slots
+  float *swi_h;       // SwiGLU kernels only (LaunchHints::swi_h): outputs, their Q8 copy, arrival counters per 32 outputs
+  uint8_t *swi_q;
+  uint32_t *swi_count;
 };
 
 // R rows of one warp, U lane steps (blocks l, l+32, ... of each row) per chunk: R x U 16-byte loads per lane
@@ -60,8 +63,12 @@ __device__ __forceinline__ void gd_load(Blk<KIND, false> (&blk)[R][U], const uin
   }
 }
 
-template <int KIND, bool NORM, int R, int U, int MINB, bool TP>
+// MODE: 0 plain; 1 tensor-parallel partial (rows also stored to the peers); 2 SwiGLU (R = 2: a warp's row pair is (gate_i,
+// up_i), it writes silu(gate) * up and the warp that completes 32 outputs writes their Q8 block).
+template <int KIND, bool NORM, int R, int U, int MINB, int MODE>
 __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdArgs a) {
+  constexpr bool TP = MODE == 1, SWI = MODE == 2;
+  static_assert(!SWI || R == 2, "a gate / up pair per warp");
   extern __shared__ uint4 smem_gd[];
   const uint32_t nb = a.nb;
   uint4 *A0 = smem_gd, *A1 = smem_gd + nb;
@@ -114,8 +121,29 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   auto finish = [&](float(&acc)[R], uint32_t rr) {
     float v[R];
 #pragma unroll
+    for (int i = 0; i < R; i++) v[i] = warp_tree(acc[i]);
+    if (SWI) {
+      // rows rr, rr + 1 = gate and up of output rr / 2: the same arithmetic as the SwiGLU kernel, then one arrival per
+      // output on the counter of its block of 32; whoever brings it to 32 quantises the block (and clears the counter)
+      const uint32_t i = rr >> 1, blk = i >> 5;
+      uint32_t prev = 0u;
+      if (lane == 0) {
+        const float g = v[0], h = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), v[R - 1]);
+        a.swi_h[i] = h;
+        __threadfence();
+        prev = atomicAdd(a.swi_count + blk, 1u);
+      }
+      prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+      if (prev == 31u) {
+        __threadfence();
+        const float hv = __ldcg(a.swi_h + 32u * blk + lane);
+        quant_block_warp(hv, a.swi_q, a.rows / 64u, blk, lane);
+        if (lane == 0) a.swi_count[blk] = 0u;
+      }
+      return;
+    }
+#pragma unroll
     for (int i = 0; i < R; i++) {
-      v[i] = warp_tree(acc[i]);
       if (lane == 0 && rr + i < r_hi) {
         float o = v[i];
         if (a.bias) o = __fadd_rn(o, a.bias[rr + i]);
@@ -181,10 +209,10 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
   if (threadIdx.x == 0) tl_mark_any(TL_GEMV, 14);  // every CTA's exit (timeline builds)
 }
 
-template <int KIND, bool NORM, int R, int U, int MINB, bool TP>
+template <int KIND, bool NORM, int R, int U, int MINB, int MODE>
 static int launch_direct(const GdArgs &a, cudaStream_t st) {
   const size_t smem = (size_t)a.nb * 40u;
-  auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB, TP>;
+  auto k = gemv_direct_kernel<KIND, NORM, R, U, MINB, MODE>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
   // One group per warp up to a persistent grid of exactly the resident CTAs (MINB per SM), whose warps loop:
   // measured on B200, 3 per SM gives 6.45 TB/s on a 295 MB matrix, 8 per SM 5.98, 4 per SM (1.33 waves) 5.17.
@@ -207,25 +235,25 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
 // Long rows with few of them (the FFN down projection: 4096 x 14336) are a chain of dependent chunks per warp at
 // two rows per warp; one row per warp with the whole row's loads in flight at once (up to 16 lane steps, 2 CTAs
 // per SM for the registers that takes) shortens the chain to one round trip per row.
-template <int KIND, bool NORM, bool TP>
+template <int KIND, bool NORM, int MODE>
 static int pick_direct(const GdArgs &a, cudaStream_t st) {
   constexpr int U2 = KIND == IE_B200_MAT_Q4 ? 4 : 2;
   static const int long_mode = [] {  // IE_B200_GEMV_LONG: 0 never, 1 (default) 16 lane steps at 2 CTAs/SM, 2: 8 lane steps at 3 CTAs/SM
     const char *v = getenv("IE_B200_GEMV_LONG");
     return v ? atoi(v) : 1;
   }();
-  const bool few_long = long_mode && a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
-  if (few_long && long_mode == 2) return launch_direct<KIND, NORM, 1, 2 * U2, 3, TP>(a, st);
-  if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2, TP>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
-  return launch_direct<KIND, NORM, 2, U2, 3, TP>(a, st);
+  const bool few_long = MODE != 2 && long_mode && a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
+  if (few_long && long_mode == 2) return launch_direct<KIND, NORM, 1, 2 * U2, 3, MODE == 2 ? 0 : MODE>(a, st);
+  if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2, MODE == 2 ? 0 : MODE>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
+  return launch_direct<KIND, NORM, 2, U2, 3, MODE>(a, st);
 }
 
-template <bool NORM, bool TP>
+template <bool NORM, int MODE>
 int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
   switch (kind) {
-    case IE_B200_MAT_Q4: return pick_direct<IE_B200_MAT_Q4, NORM, TP>(a, st);
-    case IE_B200_MAT_Q4K: return pick_direct<IE_B200_MAT_Q4K, NORM, TP>(a, st);
-    case IE_B200_MAT_Q6K: return pick_direct<IE_B200_MAT_Q6K, NORM, TP>(a, st);
+    case IE_B200_MAT_Q4: return pick_direct<IE_B200_MAT_Q4, NORM, MODE>(a, st);
+    case IE_B200_MAT_Q4K: return pick_direct<IE_B200_MAT_Q4K, NORM, MODE>(a, st);
+    case IE_B200_MAT_Q6K: return pick_direct<IE_B200_MAT_Q6K, NORM, MODE>(a, st);
     default: return fail(IE_B200_E_ARG, "gemv_direct: matrix kind %d has no streaming kernel", kind);
   }
 }
@@ -234,7 +262,8 @@ int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
                 const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push) {
   GdArgs a = {};
-  a.late = take_hints().late_trigger ? 1u : 0u;
+  const LaunchHints hints = take_hints();
+  a.late = hints.late_trigger ? 1u : 0u;
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.act = act, a.y = d_y, a.bias = d_bias, a.res = d_res;
   a.work = work;
@@ -242,9 +271,15 @@ int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const A
   if (push) {
     if (norm || tail || d_bias || d_res) return fail(IE_B200_E_ARG, "gemv_direct: a tensor-parallel partial takes no norm, bias or residual");
     a.push = *push;
-    return dispatch_direct<false, true>(kind, a, st);
+    return dispatch_direct<false, 1>(kind, a, st);
   }
-  return norm ? dispatch_direct<true, false>(kind, a, st) : dispatch_direct<false, false>(kind, a, st);
+  if (hints.swi_h) {
+    if (norm || tail || d_bias || d_res || !hints.swi_q || !hints.swi_count || rows % 64u)
+      return fail(IE_B200_E_ARG, "gemv_direct: the SwiGLU form takes interleaved gate / up rows (a multiple of 64), no norm, bias or residual");
+    a.swi_h = hints.swi_h, a.swi_q = hints.swi_q, a.swi_count = hints.swi_count;
+    return dispatch_direct<false, 2>(kind, a, st);
+  }
+  return norm ? dispatch_direct<true, 0>(kind, a, st) : dispatch_direct<false, 0>(kind, a, st);
 }
 
 }  // namespace ieb

@@ -127,6 +127,24 @@ __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, u
   tl_mark(TL_SWIGLU, 15);
 }
 
+// The same for interleaved input gu[2i] = gate_i, gu[2i + 1] = up_i (the layout whose GEMV rows come in gate / up
+// pairs): h[i] = silu(gate_i) * up_i into a buffer of its own.
+__global__ void __launch_bounds__(256) swiglu_il_kernel(const float *gu, float *h, uint32_t n, uint8_t *q, size_t gs, size_t hs, size_t qs) {
+  pdl_prologue(TL_SWIGLU);
+  const uint32_t t = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const uint32_t blk = blockIdx.x * 8u + (threadIdx.x >> 5);
+  if (blk >= (n + 31u) / 32u) return;
+  const uint32_t i = 32u * blk + lane;
+  float v = 0.0f;
+  if (i < n) {
+    const float2 p = *reinterpret_cast<const float2 *>(row_ptr(gu, gs, t) + 2u * i);
+    v = __fmul_rn(__fdiv_rn(p.x, __fadd_rn(1.0f, expf(-p.x))), p.y);
+    row_ptr(h, hs, t)[i] = v;
+  }
+  if (q && 32u * blk + 32u <= n) quant_block_warp(v, row_ptr(q, qs, t), n / 32u, blk, lane);
+}
+
 // ---- RoPE of q and k in place, then K/V of the position into the cache ----
 // Cache layout: [kv head][row][hd], row = position % kv_len.
 template <typename KV>
@@ -299,6 +317,19 @@ extern "C" int ie_b200_swiglu(float *d_a, const float *d_b, uint32_t n, void *d_
   const uint32_t nblk = (n + 31u) / 32u;
   IEB_LAUNCH_PDL("swiglu_kernel", swiglu_kernel, dim3((nblk + 7u) / 8u, T), dim3(256), 0, static_cast<cudaStream_t>(stream), d_a, d_b, n,
                  static_cast<uint8_t *>(d_q), a_stride, q_stride);
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_swiglu_il(const float *d_gu, float *d_h, uint32_t n, void *d_q, uint32_t T, size_t gu_stride, size_t h_stride,
+                                 size_t q_stride, void *stream) {
+  if (!d_gu || !d_h) return fail(IE_B200_E_ARG, "ie_b200_swiglu_il: NULL pointer");
+  if (d_q && n % 32u) return fail(IE_B200_E_SIZE, "ie_b200_swiglu_il: the Q8 copy needs n %% 32 == 0 (n = %u)", n);
+  if (((uintptr_t)d_gu & 7u) || (gu_stride & 7u)) return fail(IE_B200_E_ARG, "ie_b200_swiglu_il: the gate / up pairs must be 8-byte aligned");
+  if (n == 0 || T == 0) return IE_B200_OK;
+  if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_swiglu_il: T %u > 65535", T);
+  const uint32_t nblk = (n + 31u) / 32u;
+  IEB_LAUNCH_PDL("swiglu_il_kernel", swiglu_il_kernel, dim3((nblk + 7u) / 8u, T), dim3(256), 0, static_cast<cudaStream_t>(stream), d_gu, d_h, n,
+                 static_cast<uint8_t *>(d_q), gu_stride, h_stride, q_stride);
   return IE_B200_OK;
 }
 

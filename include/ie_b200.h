@@ -150,6 +150,12 @@ int ie_b200_rmsnorm(const float *d_x, const float *d_w, float *d_y, uint32_t n, 
  * kernels/ie_kernels.c:2458). */
 int ie_b200_swiglu(float *d_a, const float *d_b, uint32_t n, void *d_q, uint32_t T, size_t a_stride, size_t q_stride, void *stream);
 
+/* SwiGLU for the interleaved layout gu[2i] = gate_i, gu[2i + 1] = up_i (what a GEMV over a matrix whose rows alternate
+ * gate_i, up_i produces): h[i] = silu(gate_i) * up_i, same arithmetic and Q8 copy as ie_b200_swiglu. The decode engine
+ * folds this into the GEMV itself (a warp owns a gate / up row pair); this entry serves prompt chunks. */
+int ie_b200_swiglu_il(const float *d_gu, float *d_h, uint32_t n, void *d_q, uint32_t T, size_t gu_stride, size_t h_stride, size_t q_stride,
+                      void *stream);
+
 /* RoPE of q (nq heads) and k (nkv heads) in place with the table rows of
  * each token's position, then store k and v of that position into the KV
  * cache (half or float elements): OP_ROPE_KV (src/cpu.c:537-546), ie_rope_kv

@@ -35,7 +35,9 @@ enum {
   IE_B200_OP_ROPE_KV = 4, /* rotate a (q, nh heads) and b (k); store b and c (v) in the
                              KV cache of `layer`                                          (OP_ROPE_KV) */
   IE_B200_OP_ATTN = 5,    /* b = attention(q = a, cache of `layer`), Q8 copy in qo       (OP_ATTN) */
-  IE_B200_OP_SWIGLU = 6,  /* a = silu(a) * b, Q8 copy in qo                               (OP_SWIGLU) */
+  IE_B200_OP_SWIGLU = 6,  /* a = silu(a) * b, Q8 copy in qo                               (OP_SWIGLU);
+                           * nh = 1: a holds interleaved (gate_i, up_i) pairs, b receives silu(gate_i) * up_i: the form
+                           * for a gate / up matrix loaded with alternating rows (one 8-byte load per output) */
   IE_B200_OP_ARGMAX = 7,  /* b = {argmax(a), prob}                                        (OP_ARGMAX) */
   IE_B200_OP_ALLREDUCE = 8, /* c = c + sum over the ranks of a (n floats per token), done by the caller: the
                                engine only stops an enqueue range here (see ie_b200_engine_enqueue) */

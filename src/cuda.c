@@ -177,7 +177,7 @@ static void translate(cuda_backend *B, table *mats, table *vecs, const op *o, ie
       e.layer = (int32_t)m->l[o->layer].kvi;
       if (o->kind == OP_ATTN) e.c = IE_B200_NONE; /* the scores buffer is the CPU's; the engine has its own partials */
       break;
-    case OP_SWIGLU: e.kind = IE_B200_OP_SWIGLU; break;
+    case OP_SWIGLU: e.kind = IE_B200_OP_SWIGLU, e.nh = 0; break; /* planar [gate; up], as graph_build lays it out (src/model.c:882-887) */
     case OP_ARGMAX: e.kind = IE_B200_OP_ARGMAX; break;
     case OP_ADD: e.kind = IE_B200_OP_ADD; break;
     default: ie_die("cuda backend: op kind %d is not built (llama / qwen2 graphs only)", o->kind);

@@ -600,3 +600,21 @@ def test_allreduce_missing_rank_gives_up(cuda, lib):
     finally:
         for r in range(2):
             lib.ie_b200_ar_destroy(hs[r])
+
+
+def test_swiglu_interleaved_equals_planar(cuda, lib):
+    """SwiGLU over interleaved (gate_i, up_i) pairs: the same bits as the planar kernel on the same values, outputs and Q8."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(77)
+    T, n = 3, 768
+    g, u = rng.standard_normal((T, n)).astype(np.float32) * 3, rng.standard_normal((T, n)).astype(np.float32)
+    planar = dev(np.concatenate([g, u], axis=1), cuda)
+    want, want_q = K.swiglu(planar, n)
+    il = dev(np.stack([g, u], axis=2).reshape(T, 2 * n), cuda)
+    h = torch.empty((T, n), dtype=torch.float32, device=cuda)
+    q = torch.empty((T, 40 * (n // 32)), dtype=torch.uint8, device=cuda)
+    K.check(lib.ie_b200_swiglu_il(il.data_ptr(), h.data_ptr(), n, q.data_ptr(), T, 2 * n * 4, n * 4, 40 * (n // 32), None))
+    assert torch.equal(h, want.contiguous()) and torch.equal(q, want_q)
