@@ -29,8 +29,8 @@ SIGNATURES = {
     "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
     "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_gemm": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
-    "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_gemv_norm_tail": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),
     "ie_b200_block_dots": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp]),
     "ie_b200_embed": (_int, [_int, _vp, _u32, _vp, _vp, _u32, _sz, _vp]),
@@ -42,6 +42,8 @@ SIGNATURES = {
     "ie_b200_attn_count_words": (_sz, [_u32, _u32]),
     "ie_b200_attn_decode": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _u32, _u32, _u32, _sz, _sz, _sz, _vp, _vp, _vp]),
     "ie_b200_attn_decode_fused": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _int, _u32, _u32, _vp, _vp, _vp]),
+    "ie_b200_attn_persistent_scratch_bytes": (_sz, [_u32, _u32, _u32]),
+    "ie_b200_attn_persistent": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _u32, _vp, _vp, _vp]),
     "ie_b200_attn_prefill": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_argmax_part_bytes": (_sz, [_u32]),
     "ie_b200_argmax": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp, _vp]),
@@ -76,6 +78,10 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_set_rope": (_int, [_vp, _vp, _vp]),
     "ie_b200_engine_set_ops": (_int, [_vp, C.POINTER(Op), _u32, _u32]),
     "ie_b200_engine_step": (_int, [_vp, _u32, _u32, _vp, C.POINTER(_u32), C.POINTER(C.c_double)]),
+    "ie_b200_engine_clear_error": (_int, [_vp]),
+    "ie_b200_engine_set_step_mode": (_int, [_vp, _int]),
+    "ie_b200_engine_step_is_kernel": (_int, [_vp]),
+    "ie_b200_engine_inject_abort": (_int, [_vp]),
     "ie_b200_engine_decode": (_int, [_vp, _u32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
     "ie_b200_engine_enqueue_kinds": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),

@@ -75,10 +75,14 @@ class Backend:
     device_tensors: optional name -> (ggml_type, rows, cols, torch uint8 CUDA tensor of GGUF bytes) for matrices
     generated on the device; all other tensors come from cfg.tensors (numpy). kv_f32: float KV cache (the reference CPU backend's precision).
     tp / rank: tensor-parallel degree and this engine's slice.
+    step_mode: "auto" (the persistent step kernel where it can run, else the step graph), "graph", "kernel"; None leaves
+    the library's default (auto, or what IE_B200_STEP says).
     """
 
+    STEP_MODES = {"auto": 0, "graph": 1, "kernel": 2}
+
     def __init__(self, cfg: ModelConfig, n_ctx: int, T: int = 1, kv_f32: bool = False, device_tensors: dict | None = None, tp: int = 1,
-                 rank: int = 0, device=None):
+                 rank: int = 0, device=None, step_mode: str | None = None):
         import torch
 
         _lib.require_gpu()
@@ -105,6 +109,8 @@ class Backend:
             cs, sn = rope_tables(n_ctx, self.hd, cfg.rope_base)
             check(self.lib.ie_b200_engine_set_rope(self.h, cs.ctypes.data_as(_vp), sn.ctypes.data_as(_vp)))
             self._build_ops()
+            if step_mode is not None:
+                check(self.lib.ie_b200_engine_set_step_mode(self.h, self.STEP_MODES[step_mode]))
         self.weight_bytes_per_token = int(self.lib.ie_b200_engine_weight_bytes_per_token(self.h))
         self.all_logits = 0
         self.verify_max = 0
@@ -315,6 +321,15 @@ class Backend:
         d = self.bufs[dst]
         s = self.bufs[src] if src is not None else d
         check(self.lib.ie_b200_engine_copy_rows(self.h, d.off, d.stride, d0, s.off, s.stride, r0, n, min(d.stride, s.stride), int(src is None)))
+
+    @property
+    def step_is_kernel(self) -> bool:
+        """Whether one-token steps run as the persistent step kernel (one launch per step or per decode call)."""
+        with self.torch.cuda.device(self.device):
+            return bool(self.lib.ie_b200_engine_step_is_kernel(self.h))
+
+    def clear_error(self) -> None:
+        check(self.lib.ie_b200_engine_clear_error(self.h))
 
     @property
     def launches_per_step(self) -> int:

@@ -23,11 +23,6 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # No fast-math: the quantiser and the GEMV accumulation rely on IEEE division,
 # square root and separately rounded multiply/add (written with intrinsics).
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", str(REPO / "include"), "-I", str(CSRC)]
-# IE_B200_TIMELINE=1 builds the variant whose kernels record a device timeline (ie_b200_timeline_read); use --force
-# when switching, objects are cached by time stamp only.
-if os.environ.get("IE_B200_TIMELINE") == "1":
-    FLAGS.append("-DIEB_TIMELINE")
-
 
 def _newer(target: Path, deps: list[Path]) -> bool:
     if not target.is_file():

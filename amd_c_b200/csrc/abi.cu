@@ -29,14 +29,6 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-static thread_local LaunchHints g_hints;
-void set_hints(const LaunchHints &h) { g_hints = h; }
-LaunchHints take_hints() {
-  const LaunchHints h = g_hints;
-  g_hints = LaunchHints();
-  return h;
-}
-
 bool pdl_enabled() {
   static const bool on = [] {
     const char *v = getenv("IE_B200_PDL");
@@ -86,20 +78,3 @@ extern "C" int ie_b200_device_count(void) {
 }
 
 extern "C" uint64_t ie_b200_launch_count(void) { return ieb::g_launches.load(std::memory_order_relaxed); }
-
-#ifdef IEB_TIMELINE
-// Timeline builds only: gather the (time, tag, cta) records of every source file, 16 bytes each, and clear them.
-namespace ieb {
-static uint32_t (*g_tl_readers[32])(void *, uint32_t);
-static int g_tl_n_readers = 0;
-void tl_register(uint32_t (*reader)(void *, uint32_t)) {
-  if (g_tl_n_readers < 32) g_tl_readers[g_tl_n_readers++] = reader;
-}
-}  // namespace ieb
-extern "C" uint32_t ie_b200_timeline_read(void *out, uint32_t cap) {
-  cudaDeviceSynchronize();
-  uint32_t n = 0;
-  for (int i = 0; i < ieb::g_tl_n_readers; i++) n += ieb::g_tl_readers[i](static_cast<char *>(out) + (size_t)n * 16u, cap - n);
-  return n;
-}
-#endif

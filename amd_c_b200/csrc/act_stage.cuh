@@ -27,13 +27,13 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
   if (!NORM) {
     const uint4 *src = reinterpret_cast<const uint4 *>(a.xq);
     for (uint32_t i = tid; i < 2u * nb; i += NT) {
-      const uint4 v = src[i];
+      const uint4 v = __ldcg(src + i);  // from L2: inside a persistent kernel another SM has just written it
       if (i & 1u) A1[i >> 1] = v;
       else A0[i >> 1] = v;
     }
     const float *d = reinterpret_cast<const float *>(a.xq + 32u * (size_t)nb);
     const int *s = reinterpret_cast<const int *>(a.xq + 36u * (size_t)nb);
-    for (uint32_t i = tid; i < nb; i += NT) da[i] = d[i], as[i] = s[i];
+    for (uint32_t i = tid; i < nb; i += NT) da[i] = __ldcg(d + i), as[i] = __ldcg(s + i);
   } else {
     // Thread t owns half-blocks t, t + NT, ...: 16 consecutive elements each, so the quantiser needs no
     // warp-wide reductions (one exchange with the neighbour lane that holds the other half) and one thread

@@ -24,7 +24,6 @@
 // and a value is complete as soon as its epoch matches ("low-latency" slots, double-buffered by parity):
 //   ar_norm_kernel    x = x + sum over ranks of part, then RMSNorm and the Q8 copy of x for the next GEMVs;
 //   ar_argmax_kernel  the (value, global index) pairs of the ranks' local argmax, best one to every rank.
-#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -49,6 +48,8 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
                                                                    uint32_t *err) {
   pdl_prologue();
   __shared__ uint32_t ok;
+  // an earlier kernel of this step already gave up on a peer: push, advance the epoch, but do not wait again
+  const bool dead = err && *(volatile uint32_t *)err != 0u;
   const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
   const uint32_t per = (n / 4u + gridDim.x - 1u) / gridDim.x * 4u;  // floats per CTA, a multiple of 4
   const uint32_t lo = blockIdx.x * per, hi = min(n, lo + per);
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
     volatile uint32_t *f = s.flags[s.rank] + threadIdx.x * AR_MAX_CTAS + blockIdx.x;
     const uint64_t t0 = ar_now();
     while ((int32_t)(*f - k) < 0) {
-      if (ar_now() - t0 > AR_WAIT_NS) {
+      if (dead || ar_now() - t0 > AR_WAIT_NS) {
         ok = 0u;
         if (err) atomicExch(err, 3u);
         break;
@@ -115,7 +116,6 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   __shared__ float red[32];
   const int tid = threadIdx.x;
   float4 acc[ITERS], mine[ITERS], w4[ITERS];
-  tl_mark(TL_ALLREDUCE, 0);
   pdl_launch_dependents();
   // ahead of the dependency wait: the norm weights (constant) and, when the kernel before this one releases its
   // dependents late (`early`), everything older than that kernel: the epoch and the residual stream
@@ -129,7 +129,6 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   uint32_t k = 0u;
   if (early) k = *(volatile uint32_t *)s.epoch + 1u;
   pdl_wait();
-  tl_mark(TL_ALLREDUCE, 1);
   if (!early) k = *(volatile uint32_t *)s.epoch + 1u;
   const uint32_t par = k & 1u;
 #pragma unroll
@@ -146,8 +145,9 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
       if (!early) acc[it] = *reinterpret_cast<const float4 *>(res + i);
     }
   }
-  // ---- the sum, in rank order; peers' words are polled in place, up to four peers' loads in flight together
-  bool gave_up = false;
+  // ---- the sum, in rank order; peers' words are polled in place, up to four peers' loads in flight together.
+  // If an earlier kernel of this step already gave up on a peer, one look at the slots is all this one takes.
+  bool gave_up = err && *(volatile uint32_t *)err != 0u;
   const uint64_t t0 = ar_now();
   const unsigned long long *my = s.ll[s.rank] + (size_t)par * s.world * s.max_n;
 #pragma unroll
@@ -190,7 +190,6 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
       }
     }
   }
-  tl_mark(TL_ALLREDUCE, 2);
   if (gave_up && err) atomicExch(err, 3u);
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
@@ -199,13 +198,12 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   }
   if (norm_w) norm_quant_vec<ITERS, ARN_THREADS>(acc, w4, n, eps, xn, xq, red);
   if (tid == 0) *(volatile uint32_t *)s.epoch = k;
-  tl_mark(TL_ALLREDUCE, 15);
 }
 
 // One warp: every rank's (logit, global index) of its local argmax to every rank; the largest logit wins, ties
 // go to the smaller index (what one argmax over the whole vocabulary gives). result[0] = the winning index.
 __global__ void __launch_bounds__(32) ar_argmax_kernel(const ArDev s, const float *logits, uint32_t *result, uint32_t vocab_offset, uint32_t *err) {
-  pdl_prologue(TL_ALLREDUCE);
+  pdl_prologue();
   const uint32_t k = *(volatile uint32_t *)s.epoch + 1u, par = k & 1u;
   const uint32_t lane = threadIdx.x;
   const uint32_t li = result[0], lp = result[1];  // local index and its probability within this rank's slice
@@ -219,7 +217,7 @@ __global__ void __launch_bounds__(32) ar_argmax_kernel(const ArDev s, const floa
   }
   float v = -INFINITY, pr = 0.0f;
   uint32_t idx = 0xFFFFFFFFu;
-  bool gave_up = false;
+  bool gave_up = err && *(volatile uint32_t *)err != 0u;
   if (lane == s.rank) {
     v = lv, idx = li + vocab_offset, pr = __uint_as_float(lp);
   } else if (lane < s.world) {
@@ -260,6 +258,17 @@ struct ie_b200_allreduce {
 };
 
 static inline size_t up256(size_t n) { return (n + 255u) & ~(size_t)255u; }
+
+namespace ieb {
+// What a kernel outside this file needs to exchange rows through the state's low-latency slots (step_kernel.cu).
+void ar_push_info(const ie_b200_allreduce *a, ArPush *out) {
+  *out = ArPush();
+  if (!a) return;
+  for (uint32_t j = 0; j < a->d.world; j++) out->ll[j] = a->d.ll[j];
+  out->epoch = a->d.epoch, out->rank = a->d.rank, out->world = a->d.world, out->max_n = a->d.max_n;
+}
+bool ar_connected(const ie_b200_allreduce *a) { return a && a->connected; }
+}  // namespace ieb
 
 extern "C" int ie_b200_ar_create(uint32_t rank, uint32_t world, uint32_t max_floats, ie_b200_allreduce **out) {
   if (!out || world < 1 || world > (uint32_t)AR_MAX_RANKS || rank >= world || max_floats == 0 || max_floats % 4u)
@@ -380,25 +389,11 @@ extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const
   ArPush push = {};
   for (uint32_t j = 0; j < a->d.world; j++) push.ll[j] = a->d.ll[j];
   push.epoch = a->d.epoch, push.rank = a->d.rank, push.world = a->d.world, push.max_n = a->d.max_n;
-  // Who pushes: the GEMV, a warp's two rows at a time while it runs (the transfer overlaps it; a stop costs every
-  // rank rows / 2 x (world - 1) 16-byte packets), or the reduction kernel, in 32-byte pieces per thread after the GEMV
-  // (far fewer packets, no overlap). Measured at 2 / 4 / 8 ranks: 833 / 983 / 959 tok/s against 795 / 903 / 847, so
-  // the GEMV pushes; IE_B200_TP_PUSH=reduce selects the other form.
-  static const int forced = [] {
-    const char *v = getenv("IE_B200_TP_PUSH");
-    return !v ? 0 : v[0] == 'g' ? 1 : v[0] == 'r' ? 2 : 0;
-  }();
-  const bool gemv_pushes = forced != 2;
   // the GEMV releases its dependents only after its own dependency wait: when the reduction kernel starts, everything
   // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
-  LaunchHints hints;
-  hints.late_trigger = true;
-  set_hints(hints);
-  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream),
-                            gemv_pushes ? &push : nullptr);
-  set_hints(LaunchHints());
+  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push, true);
   if (r) return r;
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, gemv_pushes ? 1 : 0, 1);
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
 }
 
 extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {

@@ -56,9 +56,9 @@ struct AttnArgs {
   // and the v of this position, cs / sn the RoPE table rows of all positions
   const float *k_new, *v_new, *cs, *sn;
   int neox;
-  // The launcher guarantees that the kernel before this one in the stream lets its dependents go only after its own
-  // dependency wait, so when this kernel starts everything older than that kernel is complete: the position
-  // scalar and the cache rows of earlier steps may then be read ahead of this kernel's own wait.
+  // Set when the kernel before this one in the stream lets its dependents go only after its own dependency wait:
+  // when this kernel starts, everything older than that kernel is complete, so the position scalar and the cache
+  // rows of earlier steps may be read ahead of this kernel's own wait.
   int early_kv;
 };
 
@@ -164,7 +164,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
   float *Pw = reinterpret_cast<float *>(vbuf + NB * TILE_ELEMS);         // [warp][PPW][GH] probabilities of the warp's positions
   __shared__ uint32_t is_last;
 
-  tl_mark(TL_ATTN, 0);
   pdl_launch_dependents();
   const bool early = FUSED && a.early_kv;
   if (!early) pdl_wait();
@@ -218,7 +217,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
   };
   if (early) load_tables();
   if (early) pdl_wait();
-  tl_mark(TL_ATTN, 1);
 
   // ---- q of this lane for the q.k phase (rotated here when fused), the step's own K / V row
   float qr[GH][DPL];
@@ -272,7 +270,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
       }
     }
   }
-  tl_mark(TL_ATTN, 2);
 
   // ---- the span, tile by tile. Every warp keeps its own running max / sum / output over the positions it owns
   // (PPW per tile), so the only block-wide synchronisation is the hand-over of tile buffers.
@@ -299,7 +296,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     __pipeline_wait_prior(NB - 2);
     __syncthreads();          // tile `it` is complete; everybody is done with tile it - 1, whose buffer is refilled now
     issue(it + NB - 1u);
-    tl_mark(TL_ATTN, 3);
     const uint32_t valid = p_hi - tile_lo;  // positions of this tile that exist (>= 1)
     if ((uint32_t)(wq * PPW) < valid) {
       const KV *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
@@ -368,7 +364,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
   }
   __pipeline_wait_prior(0);
   __syncthreads();
-  tl_mark(TL_ATTN, 4);
 
   // ---- merge the warps' (max, sum, output) in shared memory, reusing the tile buffers
   float *red = reinterpret_cast<float *>(smem_raw);   // [ATT_WARPS][G][HD]
@@ -419,7 +414,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     merge_partials<G, HD, THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
   }
   __syncthreads();
-  tl_mark(TL_ATTN, 5);
   // ---- write out, one warp per block of 32 values (which is also a Q8 block of the output vector)
   float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
   uint8_t *oqt = a.oq ? a.oq + a.oq_stride * t : nullptr;
@@ -429,7 +423,6 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     ot[32 * b + lane] = v;
     if (oqt) quant_block_warp(v, oqt, nbq, g * (G * HD / 32u) + b, lane);
   }
-  tl_mark(TL_ATTN, 15);
 }
 
 template <typename KV, int HD, int G, bool FUSED>
@@ -488,7 +481,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   __half *vbuf = kbuf + NB * TILE_ELEMS;                // [NB][TILE][ROW]
   __shared__ uint32_t is_last;
 
-  tl_mark(TL_ATTN, 0);
   pdl_launch_dependents();
   const bool early = FUSED && a.early_kv;
   if (!early) pdl_wait();
@@ -547,7 +539,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   };
   if (early) load_tables();
   if (early) pdl_wait();
-  tl_mark(TL_ATTN, 1);
 
   // ---- q of head hq in A-fragment order, rotated when fused, split into two f16 terms
   float qf[KS][4];
@@ -611,7 +602,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     split2(qf[k][0], qf[k][1], qh[k][0], ql[k][0]);
     split2(qf[k][2], qf[k][3], qh[k][1], ql[k][1]);
   }
-  tl_mark(TL_ATTN, 2);
 
   float o[HD / 8][4], run_m = -INFINITY, run_l = 0.0f;  // O^T C fragments: o[n][0..1] = head hq, dims 8n + 2tq, + 1
 #pragma unroll
@@ -633,7 +623,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     __pipeline_wait_prior(NB - 2);
     __syncthreads();
     issue(it + NB - 1u);
-    tl_mark(TL_ATTN, 3);
     const uint32_t valid = p_hi - tile_lo;
     const int p0 = warp * 16;  // this warp's positions of the tile
     if ((uint32_t)p0 < valid) {
@@ -684,7 +673,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   }
   __pipeline_wait_prior(0);
   __syncthreads();
-  tl_mark(TL_ATTN, 4);
 
   // ---- merge the warps' (max, sum, output) in shared memory, reusing the tile buffers
   float *red = reinterpret_cast<float *>(smem_raw);  // [AM_WARPS][G][HD]
@@ -731,7 +719,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     merge_partials<G, HD, AM_THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
   }
   __syncthreads();
-  tl_mark(TL_ATTN, 5);
   float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
   uint8_t *oqt = a.oq ? a.oq + a.oq_stride * t : nullptr;
   const uint32_t nbq = a.n_head * HD / 32u;
@@ -740,7 +727,6 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     ot[32 * b + lane] = v;
     if (oqt) quant_block_warp(v, oqt, nbq, g * (G * HD / 32u) + b, lane);
   }
-  tl_mark(TL_ATTN, 15);
 }
 
 template <int HD, int G, bool FUSED, int NB>
@@ -784,7 +770,7 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_prefill_mma_kernel(const P
   __half *kbuf = reinterpret_cast<__half *>(smem_raw);
   __half *vbuf = kbuf + NB * TILE_ELEMS;
 
-  pdl_prologue(TL_ATTN);
+  pdl_prologue();
   const uint32_t t0 = blockIdx.x * QT, g = blockIdx.y;
   const uint32_t nt = min((uint32_t)QT, a.T - t0);            // tokens of this CTA
   const uint32_t pos0 = *a.pos + t0, p_hi = pos0 + nt;         // token i sees positions 0 .. pos0 + i
@@ -949,11 +935,13 @@ static int dispatch_prefill(const PrefillArgs &a, uint32_t G, cudaStream_t st) {
   switch (G) {
     case 1: return launch_prefill<HD, 1>(a, st);
     case 2: return launch_prefill<HD, 2>(a, st);
+    case 3: return launch_prefill<HD, 3>(a, st);
     case 4: return launch_prefill<HD, 4>(a, st);
     case 5: return launch_prefill<HD, 5>(a, st);
+    case 6: return launch_prefill<HD, 6>(a, st);
     case 7: return launch_prefill<HD, 7>(a, st);
     case 8: return launch_prefill<HD, 8>(a, st);
-    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_prefill: %u query heads per KV head unsupported (1, 2, 4, 5, 7, 8)", G);
+    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_prefill: %u query heads per KV head unsupported (1 .. 8)", G);
   }
 }
 
@@ -971,11 +959,13 @@ static int dispatch_g_mma(const AttnArgs &a, uint32_t G, uint32_t T, cudaStream_
   switch (G) {
     case 1: return launch_attn_mma<HD, 1, FUSED>(a, T, st);
     case 2: return launch_attn_mma<HD, 2, FUSED>(a, T, st);
+    case 3: return launch_attn_mma<HD, 3, FUSED>(a, T, st);
     case 4: return launch_attn_mma<HD, 4, FUSED>(a, T, st);
     case 5: return launch_attn_mma<HD, 5, FUSED>(a, T, st);
+    case 6: return launch_attn_mma<HD, 6, FUSED>(a, T, st);
     case 7: return launch_attn_mma<HD, 7, FUSED>(a, T, st);
     case 8: return launch_attn_mma<HD, 8, FUSED>(a, T, st);
-    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: %u query heads per KV head unsupported (1, 2, 4, 5, 7, 8)", G);
+    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: %u query heads per KV head unsupported (1 .. 8)", G);
   }
 }
 
@@ -984,11 +974,13 @@ static int dispatch_g(const AttnArgs &a, uint32_t G, uint32_t T, cudaStream_t st
   switch (G) {
     case 1: return launch_attn<KV, HD, 1, FUSED>(a, T, st);
     case 2: return launch_attn<KV, HD, 2, FUSED>(a, T, st);
+    case 3: return launch_attn<KV, HD, 3, FUSED>(a, T, st);
     case 4: return launch_attn<KV, HD, 4, FUSED>(a, T, st);
     case 5: return launch_attn<KV, HD, 5, FUSED>(a, T, st);
+    case 6: return launch_attn<KV, HD, 6, FUSED>(a, T, st);
     case 7: return launch_attn<KV, HD, 7, FUSED>(a, T, st);
     case 8: return launch_attn<KV, HD, 8, FUSED>(a, T, st);
-    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: %u query heads per KV head unsupported (1, 2, 4, 5, 7, 8)", G);
+    default: return fail(IE_B200_E_SIZE, "ie_b200_attn_decode: %u query heads per KV head unsupported (1 .. 8)", G);
   }
 }
 
@@ -1058,11 +1050,12 @@ extern "C" int ie_b200_attn_decode(const float *d_q, const void *d_kc, const voi
   return dispatch_attn<false>(a, hd, kv_f32, T, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos,
-                                         const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv,
-                                         uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count,
-                                         void *stream) {
-  const bool early = take_hints().after_late_trigger;
+namespace ieb {
+// early: the kernel launched right before this one releases its dependents only after its own dependency wait
+// (gemv_direct's late_trigger), so the position and older cache rows may be read ahead of this kernel's wait.
+int attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin, float *d_out,
+                      void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx,
+                      void *d_part, uint32_t *d_count, cudaStream_t st, bool early) {
   if (!d_q || !d_k || !d_v || !d_kc || !d_vc || !d_cos || !d_sin || !d_out || !d_pos || !d_part || !d_count)
     return fail(IE_B200_E_ARG, "ie_b200_attn_decode_fused: NULL pointer");
   if (n_kv == 0 || n_head % n_kv) return fail(IE_B200_E_SIZE, "ie_b200_attn_decode_fused: %u heads over %u KV heads", n_head, n_kv);
@@ -1076,7 +1069,16 @@ extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, con
   a.scale = 1.0f / sqrtf((float)hd);
   a.k_new = d_k, a.v_new = d_v, a.cs = d_cos, a.sn = d_sin, a.neox = neox;
   a.early_kv = early ? 1 : 0;
-  return dispatch_attn<true>(a, hd, kv_f32, 1, static_cast<cudaStream_t>(stream));
+  return dispatch_attn<true>(a, hd, kv_f32, 1, st);
+}
+}  // namespace ieb
+
+extern "C" int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos,
+                                         const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv,
+                                         uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count,
+                                         void *stream) {
+  return attn_decode_fused(d_q, d_k, d_v, d_kc, d_vc, d_cos, d_sin, d_out, d_oq, d_pos, n_head, n_kv, hd, neox, kv_f32, kv_len, n_ctx, d_part, d_count,
+                           static_cast<cudaStream_t>(stream), false);
 }
 
 extern "C" int ie_b200_attn_prefill(const float *d_q, const void *d_kc, const void *d_vc, float *d_out, void *d_oq, const uint32_t *d_pos,

@@ -22,23 +22,6 @@ bool pdl_enabled();
 // Raise (never lower) a kernel's opt-in dynamic shared memory limit on the current device. Monotone, so that
 // launches already captured into a CUDA graph with a larger size stay valid when a smaller launch follows.
 int ensure_dynamic_smem(const void *func, size_t bytes);
-// Hints from the engine to the next launch made on this thread (read and cleared by take_hints()):
-//   late_trigger        the kernel lets its dependents start only after its own dependency wait, so a dependent
-//                       that starts knows that everything before this kernel has completed;
-//   after_late_trigger  the kernel before this one was launched with late_trigger.
-//   swi_h               the GEMV's rows are interleaved (gate_i, up_i) pairs: write silu(gate) * up to swi_h[i] instead of
-//                       the two rows, count arrivals per 32 outputs in swi_count (zero between launches), and let the
-//                       warp that completes a block write its Q8 copy into swi_q.
-struct LaunchHints {
-  bool late_trigger = false, after_late_trigger = false;
-  float *swi_h = nullptr;
-  uint8_t *swi_q = nullptr;
-  uint32_t *swi_count = nullptr;
-};
-void set_hints(const LaunchHints &h);
-bool gemv_uses_ring();  // IE_B200_GEMV=ring selects the bulk-copy ring kernel instead of the direct one (gemv_stream.cu)
-LaunchHints take_hints();
-
 #define IEB_CUDA(call)                                   \
   do {                                                   \
     cudaError_t e_ = (call);                             \
@@ -91,68 +74,14 @@ __host__ __device__ inline size_t row_bytes_of(int kind, uint32_t cols) {
 // ---- device helpers ----
 #ifdef __CUDACC__
 
-// ---- device timeline (only in builds with -DIEB_TIMELINE; otherwise tl_mark() is nothing) ----
-// The first and the last CTA of a kernel record (global timer, kernel id, phase) into a per-source-file
-// buffer; ie_b200_timeline_read() (abi.cu) gathers the buffers. Phase 0 = entry, 1 = past the dependency
-// wait, 15 = exit; kernels add their own in between.
-enum { TL_GEMV = 1, TL_ATTN, TL_SWIGLU, TL_ROPE, TL_RMSNORM, TL_EMBED, TL_ARGMAX, TL_ARGMAX_MERGE, TL_QUANT, TL_ALLREDUCE, TL_ADVANCE, TL_GEMV_SIMPLE };
-#ifdef IEB_TIMELINE
-struct TlRec {
-  unsigned long long t;
-  uint32_t tag, cta;
-};
-// A record goes to the slot its own time stamp names (32 ns per slot, a window of 8 ms): one plain store, no
-// atomic whose round trip would stretch the phase being measured. Two marks in the same 32 ns lose one.
-constexpr uint32_t TL_CAP = 1u << 18;
-static __device__ TlRec tl_buf[TL_CAP];
-__device__ __forceinline__ void tl_put(uint32_t kernel, uint32_t phase, uint32_t who) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  tl_buf[(uint32_t)(t >> 5) & (TL_CAP - 1u)] = TlRec{t, kernel << 8 | phase, who};
-}
-__device__ __forceinline__ void tl_mark(uint32_t kernel, uint32_t phase) {
-  const bool first = (blockIdx.x | blockIdx.y | blockIdx.z) == 0u;
-  const bool last = blockIdx.x == gridDim.x - 1u && blockIdx.y == gridDim.y - 1u && blockIdx.z == gridDim.z - 1u;
-  if ((threadIdx.x | threadIdx.y) == 0u && (first || last)) tl_put(kernel, phase, first ? 0u : 1u);
-}
-// one record from the calling thread, whatever its CTA
-__device__ __forceinline__ void tl_mark_any(uint32_t kernel, uint32_t phase) { tl_put(kernel, phase, 2u); }
-#else
-__device__ __forceinline__ void tl_mark(uint32_t, uint32_t) {}
-__device__ __forceinline__ void tl_mark_any(uint32_t, uint32_t) {}
-#endif
-
-#ifdef IEB_TIMELINE
-// host side: every source file registers a reader of its own buffer
-void tl_register(uint32_t (*reader)(void *out, uint32_t cap));
-static uint32_t tl_read_tu(void *out, uint32_t cap) {
-  static TlRec *host = nullptr;
-  if (!host) host = static_cast<TlRec *>(malloc(sizeof(TlRec) * TL_CAP));
-  if (!host || cudaMemcpyFromSymbol(host, tl_buf, sizeof(TlRec) * TL_CAP) != cudaSuccess) return 0;
-  uint32_t n = 0;
-  for (uint32_t i = 0; i < TL_CAP && n < cap; i++)
-    if (host[i].t) static_cast<TlRec *>(out)[n++] = host[i];
-  void *dev = nullptr;
-  if (cudaGetSymbolAddress(&dev, tl_buf) == cudaSuccess) cudaMemset(dev, 0, sizeof(TlRec) * TL_CAP);
-  return n;
-}
-namespace {
-struct TlRegistrar {
-  TlRegistrar() { tl_register(&tl_read_tu); }
-} tl_registrar;
-}  // namespace
-#endif
-
 // Programmatic dependent launch: let the next kernel of the stream start (its own pdl_wait keeps it from
 // reading our results early), and wait until the previous kernel has completed and its writes are visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Every kernel launched through launch_pdl starts with this.
-__device__ __forceinline__ void pdl_prologue(uint32_t tl_kernel = 0) {
-  tl_mark(tl_kernel, 0);
+__device__ __forceinline__ void pdl_prologue() {
   pdl_launch_dependents();
   pdl_wait();
-  tl_mark(tl_kernel, 1);
 }
 
 // Ask for the 128-byte line at p to be brought into L2 (no register, no wait).

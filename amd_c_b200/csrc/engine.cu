@@ -9,6 +9,8 @@
 #include "common.cuh"
 #include "ie_b200_engine.h"
 #include "ie_b200_tp.h"
+#include "peer_ll.cuh"
+#include "step_kernel.cuh"
 
 namespace ieb {
 
@@ -71,18 +73,23 @@ struct ie_b200_engine {
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
-  uint32_t *swi_count = nullptr;  // arrival counters of the GEMV-fused SwiGLU, one per 32 outputs (zero between launches)
-  uint32_t swi_blocks = 0;
-  bool no_swi_fuse = true;        // IE_B200_SWIGLU_FUSE=1 folds the interleaved SwiGLU into the gate / up GEMV (measured slower: 1.71 against 1.42 ms
-                                  // per token, the fence + arrival counter per row pair stalls the weight stream), default: a kernel of its own
   ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
   uint32_t vocab_off = 0;           // first vocabulary row of this shard's output head
   std::vector<EMat> mats;
   std::vector<EVec> vecs;
   std::vector<ie_b200_op> ops;
   uint32_t i_head = 0;
+  uint32_t logits_n = 0;  // floats the output head writes per token (a vocabulary-split shard holds fewer than d.vocab)
   cudaGraphExec_t step_graph = nullptr;
   uint32_t step_launches = 0;
+  // the persistent step kernel (step_kernel.cu): the op list translated into phases, and its scratch
+  int step_mode = 0;          // 0: the kernel where the op list and shapes allow it, else the graph; 1: always the graph; 2: the kernel or an error
+  int kernel_state = 0;       // 0: not examined yet, 1: program built, -1: this op list / shape has no program
+  StepPhase *d_prog = nullptr;
+  StepArgs sk = {};
+  float *sk_part = nullptr;
+  void *sk_amax = nullptr;
+  uint32_t *sk_bar = nullptr;  // {arrival counter, abort flag}
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
@@ -90,12 +97,16 @@ static inline void *at(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_
   return off == IE_B200_NONE ? nullptr : e->arena + off + (size_t)stride * t0;
 }
 
-// Can the streaming (bulk-copy ring) GEMV take this matrix? Quantised kinds whose ring fits its shared-memory budget.
-static bool stream_ok(const EMat &m) {
-  if (m.kind == IE_B200_MAT_F32 || m.cols % 32u) return false;
-  const size_t nb = m.cols / 32u;
-  return nb <= 1024u && nb * 40u + 128u + 4u * row_bytes_of(m.kind, m.cols) <= 110u * 1024u;
+namespace ieb {
+void ar_push_info(const ie_b200_allreduce *a, ArPush *out);  // allreduce.cu
+bool ar_connected(const ie_b200_allreduce *a);
+int attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin, float *d_out,
+                      void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd, int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx,
+                      void *d_part, uint32_t *d_count, cudaStream_t st, bool early);  // attn_decode.cu
 }
+
+// Can the one-token decode GEMV take this matrix?
+static bool stream_ok(const EMat &m) { return gemv_direct_ok(m.kind, m.cols); }
 
 // One op for tokens [t0, t0 + T) of a run.
 static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32_t T, cudaStream_t st) {
@@ -125,7 +136,7 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       const EMat &m = e->mats[o.mat];
       const float *bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr;
       if (T == 1 && stream_ok(m))
-        return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), e->err, e->err + 2, st);
+        return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), st);
       // a prompt chunk (the reference's threshold, src/hip.c:965): the tensor-core GEMM reads the weights once per 128 tokens
       if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm)
         return ie_b200_gemm(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
@@ -197,58 +208,36 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
            (kind_mask & (1u << IE_B200_OP_ROPE_KV)) && (kind_mask & (1u << IE_B200_OP_ATTN));
   };
   // The fused attention kernel reads the position and older cache rows ahead of its dependency wait when the
-  // kernel launched right before it is a direct GEMV told to release its dependents late (see LaunchHints).
+  // kernel launched right before it is a decode GEMV told to release its dependents only after its own wait.
   bool prev_late = false;
-  struct HintScope {  // hints never outlive the call they were set for
-    ~HintScope() { set_hints(LaunchHints()); }
-  };
   for (uint32_t i = first; i < last; i++) {
     const ie_b200_op &o = e->ops[i];
     if (!(kind_mask & (1u << o.kind))) continue;
-    HintScope scope;
     const bool was_late = prev_late;
     prev_late = false;
-    if (T == 1 && o.kind == IE_B200_OP_GEMV && o.mat >= 0 && (size_t)o.mat < e->mats.size() && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
-        rope_fuses(i + 1)) {
-      LaunchHints hints;
-      hints.late_trigger = true;
-      set_hints(hints);
+    if (T == 1 && o.kind == IE_B200_OP_GEMV && o.mat >= 0 && (size_t)o.mat < e->mats.size() && stream_ok(e->mats[o.mat]) && rope_fuses(i + 1)) {
+      const EMat &m = e->mats[o.mat];
+      ActSrc act = {};
+      act.xq = static_cast<const uint8_t *>(at(e, o.a, 0, 0));
+      if (int r = gemv_direct(m.kind, m.d, m.rows, m.cols, act, false, static_cast<float *>(at(e, o.b, 0, 0)), o.vec >= 0 ? e->vecs[o.vec].d : nullptr,
+                              static_cast<float *>(at(e, o.res, 0, 0)), nullptr, nullptr, st, nullptr, true))
+        return r;
       prev_late = true;
+      continue;
     }
     if (rope_fuses(i)) {
       const ie_b200_op &nx = e->ops[i + 1];
       char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
-      LaunchHints hints;
-      hints.after_late_trigger = was_late;
-      set_hints(hints);
-      int r = ie_b200_attn_decode_fused(static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.b, 0, 0)),
-                                        static_cast<float *>(at(e, o.c, 0, 0)), kcl, vcl, e->rope_cos, e->rope_sin,
-                                        static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->scalars + e->d.T_max + 1, e->d.n_head,
-                                        e->d.n_kv, e->d.hd, e->d.neox, e->d.kv_f32, e->d.n_ctx, e->d.n_ctx, e->attn_part, e->attn_count, st);
+      int r = attn_decode_fused(static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.b, 0, 0)), static_cast<float *>(at(e, o.c, 0, 0)), kcl,
+                                vcl, e->rope_cos, e->rope_sin, static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->scalars + e->d.T_max + 1,
+                                e->d.n_head, e->d.n_kv, e->d.hd, e->d.neox, e->d.kv_f32, e->d.n_ctx, e->d.n_ctx, e->attn_part, e->attn_count, st, was_late);
       if (r) return r;
       i++;
       continue;
     }
-    // gate / up GEMV over interleaved rows + SwiGLU + Q8 in one kernel (one token)
-    if (T == 1 && !e->no_swi_fuse && o.kind == IE_B200_OP_GEMV && i + 1 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
-        o.vec < 0 && o.res == IE_B200_NONE && (kind_mask & (1u << IE_B200_OP_SWIGLU))) {
-      const ie_b200_op &nx = e->ops[i + 1];
-      const EMat &m = e->mats[o.mat];
-      if (nx.kind == IE_B200_OP_SWIGLU && nx.nh == 1u && nx.a == o.b && nx.qo != IE_B200_NONE && m.rows == 2u * nx.n && nx.n % 32u == 0 &&
-          nx.n / 32u <= e->swi_blocks) {
-        LaunchHints hints;
-        hints.swi_h = static_cast<float *>(at(e, nx.b, 0, 0)), hints.swi_q = static_cast<uint8_t *>(at(e, nx.qo, 0, 0)), hints.swi_count = e->swi_count;
-        set_hints(hints);
-        int r = ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)), nullptr, nullptr, e->err,
-                                    e->err + 2, st);
-        if (r) return r;
-        i++;
-        continue;
-      }
-    }
     // tensor parallel: a K-split GEMV that stores every finished row to the other ranks as well, then the one-CTA kernel
     // that waits for the peers' rows, reduces onto the residual stream and normalises
-    if (T == 1 && e->ar && o.kind == IE_B200_OP_GEMV && i + 2 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) && !gemv_uses_ring() &&
+    if (T == 1 && e->ar && o.kind == IE_B200_OP_GEMV && i + 2 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) &&
         o.vec < 0 && o.res == IE_B200_NONE && (kind_mask & (1u << IE_B200_OP_ALLREDUCE)) && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
       const ie_b200_op &ar = e->ops[i + 1], &nx = e->ops[i + 2];
       const EMat &m = e->mats[o.mat];
@@ -300,7 +289,7 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
           int r = ie_b200_norm_gemv_stream(m.kind, m.d, m.rows, m.cols, static_cast<float *>(at(e, o.a, 0, 0)), e->vecs[o.vec].d, e->d.eps,
                                            firstg ? static_cast<float *>(at(e, o.b, 0, 0)) : nullptr, firstg ? at(e, o.qo, 0, 0) : nullptr,
                                            static_cast<float *>(at(e, g.b, 0, 0)), g.vec >= 0 ? e->vecs[g.vec].d : nullptr,
-                                           static_cast<float *>(at(e, g.res, 0, 0)), e->err, e->err + 2, st);
+                                           static_cast<float *>(at(e, g.res, 0, 0)), st);
           if (r) return r;
         }
         i = j - 1;
@@ -365,8 +354,10 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
   if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
   if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
-  if (const char *sf = getenv("IE_B200_SWIGLU_FUSE")) e->no_swi_fuse = sf[0] != '1';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
+  if (const char *sm = getenv("IE_B200_STEP")) e->step_mode = sm[0] == 'g' ? 1 : sm[0] == 'k' ? 2 : 0;
+  chk(cudaMalloc(&e->sk_bar, 8), "cudaMalloc(barrier words)");
+  if (rc == IE_B200_OK) chk(cudaMemset(e->sk_bar, 0, 8), "cudaMemset");
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->hist, 0, (size_t)(HIST_CAP + 1) * 4), "cudaMemset");
   chk(cudaEventCreate(&e->ev0), "cudaEventCreate");
@@ -387,8 +378,8 @@ extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
     if (m.owned) cudaFree(m.d);
   for (auto &v : e->vecs) cudaFree(v.d);
   cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
-  cudaFree(e->swi_count);
   cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
+  cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax), cudaFree(e->sk_bar);
   if (e->h_scalars) cudaFreeHost(e->h_scalars);
   if (e->h_result) cudaFreeHost(e->h_result);
   if (e->ev0) cudaEventDestroy(e->ev0);
@@ -409,6 +400,7 @@ static size_t gguf_bytes(int t, uint32_t rows, uint32_t cols) {
 // Invalidate the captured step graph: the op list or a handle table changed.
 static void drop_graph(ie_b200_engine *e) {
   if (e->step_graph) cudaGraphExecDestroy(e->step_graph), e->step_graph = nullptr;
+  e->kernel_state = 0;
 }
 
 extern "C" int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uint32_t rows, uint32_t cols, const void *h_bytes) {
@@ -506,18 +498,11 @@ extern "C" int ie_b200_engine_set_ops(ie_b200_engine *e, const ie_b200_op *ops, 
       return fail(IE_B200_E_ARG, "op %u: KV layer %d of %u", i, o.layer, e->d.n_kv_layers);
     if (o.mat >= (int)e->mats.size() || o.vec >= (int)e->vecs.size()) return fail(IE_B200_E_ARG, "op %u: unknown handle", i);
   }
-  uint32_t blocks = 0;
-  for (uint32_t i = 0; i < n_ops; i++)
-    if (ops[i].kind == IE_B200_OP_SWIGLU && ops[i].nh == 1u && ops[i].n / 32u > blocks) blocks = ops[i].n / 32u;
-  if (blocks > e->swi_blocks) {
-    cudaFree(e->swi_count);
-    e->swi_count = nullptr;
-    IEB_CUDA(cudaMalloc(&e->swi_count, (size_t)blocks * 4u));
-    IEB_CUDA(cudaMemset(e->swi_count, 0, (size_t)blocks * 4u));
-    e->swi_blocks = blocks;
-  }
   e->ops.assign(ops, ops + n_ops);
   e->i_head = i_head;
+  e->logits_n = e->d.vocab;
+  for (uint32_t i = 0; i < n_ops; i++)
+    if (ops[i].kind == IE_B200_OP_GEMV && ops[i].b == e->d.logits_off && ops[i].mat >= 0) e->logits_n = e->mats[ops[i].mat].rows;
   drop_graph(e);
   return IE_B200_OK;
 }
@@ -539,6 +524,145 @@ extern "C" int ie_b200_engine_enqueue(ie_b200_engine *e, uint32_t first, uint32_
   if (first > last || last > e->ops.size()) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue: ops [%u, %u) of %zu", first, last, e->ops.size());
   if (T == 0 || T > e->d.T_max) return fail(IE_B200_E_SIZE, "ie_b200_engine_enqueue: %u tokens (1 .. %u)", T, e->d.T_max);
   return enqueue_range(e, first, last, T, ~0u, static_cast<cudaStream_t>(stream));
+}
+
+
+// ---- the persistent step kernel: op list -> phases -----------------------------------------------------------
+// Recognised: EMBED; RMSNORM(+Q8) feeding GEMVs (folded into their prologue); GEMV (+bias, +residual) of the
+// quantised kinds; ROPE_KV + ATTN of one layer on the half cache; interleaved SWIGLU(+Q8) feeding a GEMV (folded into
+// its prologue); ARGMAX; with a collective attached: GEMV -> ALLREDUCE -> RMSNORM. Anything else: no program
+// (returns 0) and the step graph runs instead.
+static int build_program(ie_b200_engine *e) {
+  const ie_b200_engine_desc &d = e->d;
+  e->kernel_state = -1;
+  if (!step_kernel_supports(d.hd, d.n_head, d.n_kv, d.kv_f32) || e->ops.empty() || e->ops[0].kind != IE_B200_OP_EMBED) return 0;
+  const bool tp = e->ar != nullptr;
+  if (tp && !ar_connected(e->ar)) return 0;
+  std::vector<StepPhase> ph;
+  auto A = [&](uint64_t off) -> uint8_t * { return off == IE_B200_NONE ? nullptr : e->arena + off; };
+  const ie_b200_op &emb = e->ops[0];
+  if (emb.mat < 0 || (e->mats[emb.mat].kind != IE_B200_MAT_Q4 && e->mats[emb.mat].kind != IE_B200_MAT_F32) || e->mats[emb.mat].cols != emb.n) return 0;
+  {
+    StepPhase p = {};
+    p.kind = PH_EMBED;
+    ph.push_back(p);
+  }
+  const ie_b200_op *norm = nullptr, *swi = nullptr;
+  uint64_t attq_off = IE_B200_NONE;
+  const void *last_act = nullptr;  // what the previous GEMV phase staged (a following GEMV over the same activations keeps them)
+  bool have_argmax = false;
+  const uint32_t n = (uint32_t)e->ops.size();
+  for (uint32_t i = 1; i < n; i++) {
+    const ie_b200_op &o = e->ops[i];
+    switch (o.kind) {
+      case IE_B200_OP_RMSNORM:
+        if (o.res != IE_B200_NONE || o.qo == IE_B200_NONE || o.vec < 0 || o.n % 32u || o.n / 32u > 1024u) return 0;
+        norm = &o, last_act = nullptr;
+        break;
+      case IE_B200_OP_SWIGLU:
+        if (o.nh != 1u || o.qo == IE_B200_NONE || o.n % 32u || o.n / 32u > 1024u) return 0;
+        swi = &o, last_act = nullptr;
+        break;
+      case IE_B200_OP_GEMV: {
+        if (o.mat < 0) return 0;
+        const EMat &m = e->mats[o.mat];
+        if (!gemv_direct_ok(m.kind, m.cols)) return 0;
+        StepPhase p = {};
+        p.kind = PH_GEMV, p.mkind = m.kind, p.w = static_cast<const uint8_t *>(m.d), p.rowb = row_bytes_of(m.kind, m.cols), p.rows = m.rows, p.nb = m.cols / 32u;
+        p.y = reinterpret_cast<float *>(A(o.b)), p.bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr, p.res = reinterpret_cast<const float *>(A(o.res));
+        const void *act = nullptr;
+        if (norm && o.a == norm->qo && m.cols == norm->n) {
+          p.pro = PRO_NORM, p.src = A(norm->a), p.norm_w = e->vecs[norm->vec].d, act = norm;
+        } else if (swi && o.a == swi->qo && m.cols == swi->n) {
+          p.pro = PRO_SWIGLU, p.src = A(swi->a), act = swi;
+        } else if (attq_off != IE_B200_NONE && o.a == attq_off) {
+          p.pro = PRO_Q8, p.src = A(o.a), act = A(o.a);
+        } else {
+          return 0;
+        }
+        if (act == last_act && !ph.empty() && ph.back().kind == PH_GEMV && !ph.back().push) p.pro = PRO_KEEP, ph.back().nobar = 1;
+        last_act = act;
+        if (tp && i + 1 < n && e->ops[i + 1].kind == IE_B200_OP_ALLREDUCE) {
+          const ie_b200_op &ar = e->ops[i + 1];
+          if (ar.a != o.b || ar.n != m.rows || o.vec >= 0 || o.res != IE_B200_NONE) return 0;
+          p.push = 1, p.nobar = 1;
+          ph.push_back(p);
+          StepPhase r = {};
+          r.kind = PH_REDUCE, r.rows = ar.n, r.res = reinterpret_cast<const float *>(A(ar.c)), r.y = reinterpret_cast<float *>(A(ar.c));
+          ph.push_back(r);
+          last_act = nullptr;
+          i++;
+          break;
+        }
+        ph.push_back(p);
+        break;
+      }
+      case IE_B200_OP_ROPE_KV: {
+        if (i + 1 >= n) return 0;
+        const ie_b200_op &at_ = e->ops[i + 1];
+        if (at_.kind != IE_B200_OP_ATTN || at_.layer != o.layer || at_.a != o.a || at_.qo == IE_B200_NONE || o.nh != d.n_head) return 0;
+        if (o.b != o.a + (uint64_t)d.n_head * d.hd * 4u || o.c != o.a + (uint64_t)(d.n_head + d.n_kv) * d.hd * 4u) return 0;
+        StepPhase p = {};
+        p.kind = PH_ATTN, p.q = reinterpret_cast<const float *>(A(o.a));
+        p.kc = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, p.vc = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
+        ph.push_back(p);
+        StepPhase q = {};
+        q.kind = PH_MERGE, q.att = reinterpret_cast<float *>(A(at_.b)), q.attq = A(at_.qo);
+        ph.push_back(q);
+        attq_off = at_.qo, last_act = nullptr;
+        i++;
+        break;
+      }
+      case IE_B200_OP_ARGMAX: {
+        if (o.a != d.logits_off || o.b != d.argmax_off) return 0;
+        StepPhase p = {};
+        p.kind = PH_ARGMAX;
+        ph.push_back(p);
+        StepPhase f = {};
+        f.kind = tp ? PH_XARGMAX : PH_FINISH;
+        ph.push_back(f);
+        have_argmax = true;
+        e->sk.logits = reinterpret_cast<const float *>(A(o.a)), e->sk.n_logits = o.n;
+        break;
+      }
+      default: return 0;
+    }
+  }
+  if (!have_argmax || ph.back().kind == PH_ARGMAX) return 0;
+  // weights for idle warps to pull into L2: during a layer's attention the matrix of the GEMV that follows it
+  for (size_t k = 0; k + 2 < ph.size(); k++)
+    if (ph[k].kind == PH_ATTN && ph[k + 2].kind == PH_GEMV) ph[k].pf = ph[k + 2].w, ph[k].pf_bytes = ph[k + 2].rowb * ph[k + 2].rows;
+  StepArgs &a = e->sk;
+  a.smax = step_kernel_smax(d.n_kv);
+  cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax);
+  e->d_prog = nullptr, e->sk_part = nullptr, e->sk_amax = nullptr;
+  IEB_CUDA(cudaMalloc(&e->d_prog, ph.size() * sizeof(StepPhase)));
+  IEB_CUDA(cudaMemcpy(e->d_prog, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+  IEB_CUDA(cudaMalloc(&e->sk_part, (size_t)d.n_head * a.smax * (d.hd + 2u) * sizeof(float)));
+  IEB_CUDA(cudaMalloc(&e->sk_amax, step_kernel_amax_bytes()));
+  a.prog = e->d_prog, a.n_phases = (uint32_t)ph.size(), a.n_steps = 1;
+  a.scalars = e->scalars, a.Tm = d.T_max, a.hist = e->hist, a.hist_cap = HIST_CAP, a.bar = e->sk_bar, a.err = e->err, a.eps = d.eps;
+  a.n_head = d.n_head, a.n_kv = d.n_kv, a.kv_len = d.n_ctx, a.neox = d.neox ? 1u : 0u, a.cs = e->rope_cos, a.sn = e->rope_sin;
+  a.part = e->sk_part, a.amax_part = e->sk_amax, a.result = reinterpret_cast<uint32_t *>(e->arena + d.argmax_off);
+  a.emb = static_cast<const uint8_t *>(e->mats[emb.mat].d), a.emb_kind = e->mats[emb.mat].kind, a.dim = emb.n, a.x = reinterpret_cast<float *>(A(emb.a));
+  ar_push_info(e->ar, &a.push);
+  a.vocab_off = e->vocab_off, a.wait_ns = AR_WAIT_NS;
+  e->kernel_state = 1;
+  return 1;
+}
+
+// Does a one-token step run as the persistent kernel? Builds the program on first use.
+static int use_step_kernel(ie_b200_engine *e, bool *yes) {
+  *yes = false;
+  if (e->step_mode == 1) return IE_B200_OK;
+  if (e->kernel_state == 0) {
+    const int r = build_program(e);
+    if (r < 0) return r;
+  }
+  if (e->kernel_state != 1 && e->step_mode == 2)
+    return fail(IE_B200_E_STATE, "the persistent step kernel was requested, but this op list / shape has no program (half cache, heads of 64 or 128, llama / qwen2 ops)");
+  *yes = e->kernel_state == 1;
+  return IE_B200_OK;
 }
 
 // Capture ops [0, n_ops) for one token into an executable graph.
@@ -569,16 +693,23 @@ extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos
   if (!e || !next) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
   if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_step: no op list");
   IEB_CUDA(cudaSetDevice(e->device));
-  if (!e->step_graph)
+  bool kernel = false;
+  if (int r = use_step_kernel(e, &kernel)) return r;
+  if (!kernel && !e->step_graph)
     if (int r = capture_step(e)) return r;
   cudaStream_t st = e->stream;
   if (ms) IEB_CUDA(cudaEventRecord(e->ev0, st));
   if (int r = upload_input(e, &tok, 1, pos, st)) return r;
-  IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
-  count_launch(e->step_launches);
+  if (kernel) {
+    e->sk.n_steps = 1;
+    if (int r = step_kernel_launch(e->sk, e->d.hd, st)) return r;
+  } else {
+    IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
+    count_launch(e->step_launches);
+  }
   IEB_CUDA(cudaMemcpyAsync(e->h_result, e->arena + e->d.argmax_off, 8, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
-  if (h_logits) IEB_CUDA(cudaMemcpyAsync(h_logits, e->arena + e->d.logits_off, (size_t)e->d.vocab * 4, cudaMemcpyDeviceToHost, st));
+  if (h_logits) IEB_CUDA(cudaMemcpyAsync(h_logits, e->arena + e->d.logits_off, (size_t)e->logits_n * 4, cudaMemcpyDeviceToHost, st));
   if (ms) IEB_CUDA(cudaEventRecord(e->ev1, st));
   IEB_CUDA(cudaStreamSynchronize(st));
   if (ms) {
@@ -598,15 +729,22 @@ extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t p
   if (K > HIST_CAP) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: %u steps > %u per call", K, HIST_CAP);
   if ((uint64_t)pos + K > e->d.n_ctx) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: positions %u .. %u exceed the context %u", pos, pos + K - 1, e->d.n_ctx);
   IEB_CUDA(cudaSetDevice(e->device));
-  if (!e->step_graph)
+  bool kernel = false;
+  if (int r = use_step_kernel(e, &kernel)) return r;
+  if (!kernel && !e->step_graph)
     if (int r = capture_step(e)) return r;
   cudaStream_t st = e->stream;
   if (int r = upload_input(e, &tok, 1, pos, st)) return r;
   IEB_CUDA(cudaMemsetAsync(e->hist + HIST_CAP, 0, 4, st));
   IEB_CUDA(cudaEventRecord(e->ev0, st));
-  for (uint32_t k = 0; k < K; k++) IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
+  if (kernel) {  // one launch: the kernel loops over the K tokens itself
+    e->sk.n_steps = K;
+    if (int r = step_kernel_launch(e->sk, e->d.hd, st)) return r;
+  } else {
+    for (uint32_t k = 0; k < K; k++) IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
+    count_launch(e->step_launches * K);
+  }
   IEB_CUDA(cudaEventRecord(e->ev1, st));
-  count_launch(e->step_launches * K);
   IEB_CUDA(cudaMemcpyAsync(h_out, e->hist, (size_t)K * 4, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaStreamSynchronize(st));
@@ -638,7 +776,9 @@ extern "C" int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint3
   for (uint32_t i = ih; i < n_ops; i++)  // the output head for the last token only
     if (int r = launch_op(e, e->ops[i], T - 1, 1, st)) return r;
   IEB_CUDA(cudaMemcpy2DAsync(e->h_result, 8, e->arena + e->d.argmax_off, e->d.argmax_stride ? e->d.argmax_stride : 8, 8, T, cudaMemcpyDeviceToHost, st));
+  IEB_CUDA(cudaMemcpyAsync(e->h_result + 2 * e->d.T_max, e->err, 4, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaStreamSynchronize(st));
+  if (e->h_result[2 * e->d.T_max]) return fail(IE_B200_E_DEVICE, "a kernel gave up a bounded wait (device error word %u)", e->h_result[2 * e->d.T_max]);
   for (uint32_t t = 0; t < T; t++) {
     out[t] = e->h_result[2 * t];
     if (prob) std::memcpy(&prob[t], &e->h_result[2 * t + 1], 4);
@@ -671,6 +811,37 @@ extern "C" int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uin
   return IE_B200_OK;
 }
 
+extern "C" int ie_b200_engine_clear_error(ie_b200_engine *e) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_clear_error: NULL engine");
+  IEB_CUDA(cudaSetDevice(e->device));
+  IEB_CUDA(cudaMemsetAsync(e->err, 0, 4, e->stream));
+  IEB_CUDA(cudaMemsetAsync(e->sk_bar, 0, 8, e->stream));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_set_step_mode(ie_b200_engine *e, int mode) {
+  if (!e || mode < 0 || mode > 2) return fail(IE_B200_E_ARG, "ie_b200_engine_set_step_mode: mode %d (0 auto, 1 graph, 2 kernel)", mode);
+  e->step_mode = mode;
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_step_is_kernel(ie_b200_engine *e) {
+  if (!e || e->ops.empty()) return 0;
+  bool kernel = false;
+  if (cudaSetDevice(e->device) != cudaSuccess || use_step_kernel(e, &kernel) != IE_B200_OK) return 0;
+  return kernel ? 1 : 0;
+}
+
+extern "C" int ie_b200_engine_inject_abort(ie_b200_engine *e) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_inject_abort: NULL engine");
+  IEB_CUDA(cudaSetDevice(e->device));
+  const uint32_t one = 1u;
+  IEB_CUDA(cudaMemcpyAsync(e->sk_bar + 1, &one, 4, cudaMemcpyHostToDevice, e->stream));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return IE_B200_OK;
+}
+
 extern "C" void *ie_b200_engine_arena(ie_b200_engine *e) { return e ? e->arena : nullptr; }
 extern "C" void *ie_b200_engine_input_scalars(ie_b200_engine *e) { return e ? e->scalars : nullptr; }
 
@@ -687,7 +858,10 @@ extern "C" uint64_t ie_b200_engine_weight_bytes_per_token(ie_b200_engine *e) {
 }
 
 extern "C" uint32_t ie_b200_engine_launches_per_step(ie_b200_engine *e) {
-  if (!e) return 0;
-  if (!e->step_graph && !e->ops.empty()) capture_step(e);
+  if (!e || e->ops.empty()) return 0;
+  bool kernel = false;
+  if (cudaSetDevice(e->device) != cudaSuccess || use_step_kernel(e, &kernel) != IE_B200_OK) return 0;
+  if (kernel) return 1;
+  if (!e->step_graph) capture_step(e);
   return e->step_launches;
 }

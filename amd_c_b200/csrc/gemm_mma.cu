@@ -13,8 +13,6 @@
 // the A fragment needs exactly nibble word t of the block (low nibbles = the first, high nibbles = the second),
 // one 4-byte load; the B fragment is two 4-byte loads from a token's Q8 row. CTA = 8 warps as 2 (rows) x 4
 // (tokens), warp tile 32 rows x 32 tokens, CTA tile 64 rows x 128 tokens.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace ieb {
@@ -399,11 +397,9 @@ extern "C" int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t c
   a.xs = x_stride, a.ys = y_stride, a.rs = res_stride;
   const dim3 grid((rows + GM_ROWS - 1) / GM_ROWS, (T + GM_TOKS - 1) / GM_TOKS);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static const bool direct_only = [] {
-    const char *v = getenv("IE_B200_GEMM_KERNEL");
-    return v && v[0] == 'd';
-  }();
-  if (!direct_only && a.nb % GS_KB == 0 && aligned16(d_xq) && x_stride % 16u == 0) {
+  // rows of whole stages (4 blocks) and 16-byte aligned token rows go through the shared-memory staged kernel,
+  // every other shape through the kernel that reads its fragments straight from global memory
+  if (a.nb % GS_KB == 0 && aligned16(d_xq) && x_stride % 16u == 0) {
     switch (kind) {
       case IE_B200_MAT_Q4: return launch_staged<IE_B200_MAT_Q4>(a, st);
       case IE_B200_MAT_Q4K: return launch_staged<IE_B200_MAT_Q4K>(a, st);

@@ -19,7 +19,7 @@ __device__ __forceinline__ T *row_ptr(T *p, size_t stride, uint32_t t) {
 
 // ---- Q8 quantiser: one warp per block of 32 ----
 __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *q, uint32_t nb, size_t xs, size_t qs) {
-  pdl_prologue(TL_QUANT);
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t b = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) quant_q8_kernel(const float *x, uint8_t *
 
 // ---- embedding row ----
 __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t rowb, uint32_t nb, const uint32_t *tok, float *out, size_t os) {
-  pdl_prologue(TL_EMBED);
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const uint8_t *rp = w + (size_t)tok[t] * rowb;
   float *o = row_ptr(out, os, t);
@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t 
   }
 }
 __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t cols, const uint32_t *tok, float *out, size_t os) {
-  pdl_prologue(TL_EMBED);
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const float *rp = w + (size_t)tok[t] * cols;
   float *o = row_ptr(out, os, t);
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t
 // ---- RMSNorm (+Q8): one CTA of 1024 threads per token ----
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *x, const float *__restrict__ w, float *y, uint32_t n, float eps, uint8_t *q,
                                                       size_t xs, size_t ys, size_t qs) {
-  pdl_prologue(TL_RMSNORM);
+  pdl_prologue();
   __shared__ float red[32];
   const uint32_t t = blockIdx.x;
   const float *xt = row_ptr(x, xs, t);
@@ -87,7 +87,6 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float *x, const
   __shared__ float red[32];
   const uint32_t t = blockIdx.x;
   float4 x4[ITERS], w4[ITERS];
-  tl_mark(TL_RMSNORM, 0);
   pdl_launch_dependents();
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
@@ -96,7 +95,6 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float *x, const
     if (i < n) w4[it] = *reinterpret_cast<const float4 *>(w + i);
   }
   pdl_wait();
-  tl_mark(TL_RMSNORM, 1);
   const float *xt = row_ptr(x, xs, t);
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
@@ -104,12 +102,11 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float *x, const
     if (i < n) x4[it] = *reinterpret_cast<const float4 *>(xt + i);
   }
   norm_quant_vec<ITERS, 1024>(x4, w4, n, eps, row_ptr(y, ys, t), q ? row_ptr(q, qs, t) : nullptr, red);
-  tl_mark(TL_RMSNORM, 15);
 }
 
 // ---- SwiGLU (+Q8): one warp per 32 elements ----
 __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, uint32_t n, uint8_t *q, size_t as, size_t qs) {
-  pdl_prologue(TL_SWIGLU);
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t blk = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -124,13 +121,12 @@ __global__ void __launch_bounds__(256) swiglu_kernel(float *a, const float *b, u
     at[i] = v;
   }
   if (q && 32u * blk + 32u <= n) quant_block_warp(v, row_ptr(q, qs, t), n / 32u, blk, lane);
-  tl_mark(TL_SWIGLU, 15);
 }
 
 // The same for interleaved input gu[2i] = gate_i, gu[2i + 1] = up_i (the layout whose GEMV rows come in gate / up
 // pairs): h[i] = silu(gate_i) * up_i into a buffer of its own.
 __global__ void __launch_bounds__(256) swiglu_il_kernel(const float *gu, float *h, uint32_t n, uint8_t *q, size_t gs, size_t hs, size_t qs) {
-  pdl_prologue(TL_SWIGLU);
+  pdl_prologue();
   const uint32_t t = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const uint32_t blk = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -151,7 +147,7 @@ template <typename KV>
 __global__ void __launch_bounds__(256)
 rope_kv_kernel(float *q, float *k, const float *v, KV *kc, KV *vc, const float *__restrict__ cs, const float *__restrict__ sn,
                const uint32_t *pos0, uint32_t nq, uint32_t nkv, uint32_t hd, int neox, uint32_t kv_len, size_t stride) {
-  pdl_prologue(TL_ROPE);
+  pdl_prologue();
   const uint32_t t = blockIdx.y, pos = *pos0 + t, h2 = hd / 2u;
   const uint32_t npair = (nq + nkv) * h2, total = npair + nkv * hd;
   float *qt = row_ptr(q, stride, t), *kt = row_ptr(k, stride, t);
@@ -186,7 +182,7 @@ struct ArgPart {
   uint32_t pad;
 };
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32_t n, ArgPart *part, size_t xs) {
-  pdl_prologue(TL_ARGMAX);
+  pdl_prologue();
   __shared__ float smx[8], ssum[8];
   __shared__ uint32_t sidx[8];
   const uint32_t t = blockIdx.y;
@@ -223,7 +219,7 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float *x, uint32
   }
 }
 __global__ void __launch_bounds__(32) argmax_merge_kernel(const ArgPart *part, uint32_t *out, size_t os) {
-  pdl_prologue(TL_ARGMAX_MERGE);
+  pdl_prologue();
   const uint32_t t = blockIdx.x;
   const int lane = threadIdx.x;
   float mx = -INFINITY, sum = 0.0f;

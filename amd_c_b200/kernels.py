@@ -97,23 +97,21 @@ def gemm(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.T
     return y
 
 
-def gemv_stream(w: Mat, xq: torch.Tensor, bias=None, res=None, err: torch.Tensor | None = None, work: torch.Tensor | None = None) -> torch.Tensor:
-    """The one-token decode GEMV (same result as gemv with one row). work: two zeroed int32 for dynamic row scheduling."""
+def gemv_stream(w: Mat, xq: torch.Tensor, bias=None, res=None) -> torch.Tensor:
+    """The one-token decode GEMV (same result as gemv with one row)."""
     y = torch.empty((1, w.rows), dtype=torch.float32, device=xq.device)
-    check(_lib.load().ie_b200_gemv_stream(w.kind, w.data.data_ptr(), w.rows, w.cols, xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _p(err),
-                                          _p(work), _stream()))
+    check(_lib.load().ie_b200_gemv_stream(w.kind, w.data.data_ptr(), w.rows, w.cols, xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _stream()))
     return y
 
 
-def norm_gemv_stream(w: Mat, x: torch.Tensor, norm_w: torch.Tensor, eps: float, bias=None, res=None, err: torch.Tensor | None = None,
-                     work: torch.Tensor | None = None):
+def norm_gemv_stream(w: Mat, x: torch.Tensor, norm_w: torch.Tensor, eps: float, bias=None, res=None):
     """y = W Q8(rmsnorm(x) * norm_w) with the norm folded into the GEMV; returns (y, xn, xq)."""
     n = w.cols
     y = torch.empty((1, w.rows), dtype=torch.float32, device=x.device)
     xn = torch.empty(n, dtype=torch.float32, device=x.device)
     xq = torch.empty(q8_bytes(n // 32), dtype=torch.uint8, device=x.device)
     check(_lib.load().ie_b200_norm_gemv_stream(w.kind, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), norm_w.data_ptr(), eps, xn.data_ptr(),
-                                               xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _p(err), _p(work), _stream()))
+                                               xq.data_ptr(), y.data_ptr(), _p(bias), _p(res), _stream()))
     return y, xn, xq
 
 
@@ -194,6 +192,21 @@ def attn_decode_fused(qkv: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cos
                                                 int(kc.dtype == torch.float32), kc.shape[1], n_ctx, scratch.part.data_ptr(),
                                                 scratch.count.data_ptr(), _stream()))
     return out, oq
+
+
+def attn_persistent(qkv: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
+                    n_head: int, n_kv: int, hd: int, neox: bool, quant: bool = True):
+    """One token's RoPE + cache store + attention as the persistent step kernel runs it (half caches). `pos` must be the second
+    element of an int32 tensor of at least two (the kernel addresses it as scalars[1]). Returns (out, Q8 copy, error word)."""
+    lib = _lib.load()
+    out = torch.empty((1, n_head * hd), dtype=torch.float32, device=qkv.device)
+    nbq = n_head * hd // 32
+    oq = torch.empty((1, q8_bytes(nbq)), dtype=torch.uint8, device=qkv.device) if quant else None
+    scratch = torch.empty(lib.ie_b200_attn_persistent_scratch_bytes(n_head, n_kv, hd), dtype=torch.uint8, device=qkv.device)
+    err = torch.zeros(4, dtype=torch.int32, device=qkv.device)
+    check(lib.ie_b200_attn_persistent(qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), _p(oq),
+                                      pos.data_ptr(), n_head, n_kv, hd, int(neox), kc.shape[1], scratch.data_ptr(), err.data_ptr(), _stream()))
+    return out, oq, err
 
 
 def attn_prefill(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, pos: torch.Tensor, n_head: int, n_kv: int, hd: int, quant: bool = True):

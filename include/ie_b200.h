@@ -103,27 +103,24 @@ int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const 
 int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
                  const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
 
-/* The one-token GEMV of a decode step, same result as ie_b200_gemv with T = 1: the row panels stream through a
- * shared-memory ring filled by bulk asynchronous copies, and the launch uses programmatic dependent launch, so
- * the ring fills while the previous kernel of the stream still runs (the weights do not depend on it; the
- * activations are read only after the previous kernel has completed). d_err (may be NULL): a device word set to
- * 1 if a bounded wait inside the kernel ran out. d_work (may be NULL): two u32 in device memory, zero before the
- * first launch and left zero by every launch; reserved for work bookkeeping (the norm-tail variant counts finished
- * CTAs there); launches that share them must not overlap on the GPU. Replaces ie_gemv_q4q8 / _q4kq8 / _q6kq8 at decode
- * (kernels/ie_kernels.c:310, :401, :675). */
+/* The one-token GEMV of a decode step, same result as ie_b200_gemv with T = 1: every warp of a persistent grid
+ * streams its rows straight from HBM into registers with 16-byte loads (up to 16 per lane in flight), and the
+ * launch uses programmatic dependent launch: the first loads are issued before the kernel waits for its
+ * predecessor in the stream (the weights do not depend on it; the activations are read only after the previous
+ * kernel has completed). Replaces ie_gemv_q4q8 / _q4kq8 / _q6kq8 at decode (kernels/ie_kernels.c:310, :401, :675). */
 int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
-                        const float *d_res, uint32_t *d_err, uint32_t *d_work, void *stream);
+                        const float *d_res, void *stream);
 /* The same with RMSNorm + the Q8 quantiser of the f32 vector d_x (cols floats) folded into the prologue: the role
  * of the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285; src/model.c:1265-1293) moved
  * to the consumer side. d_xn_out / d_xq_out (may be NULL): the normalised vector and its Q8 copy, written once. */
 int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, const float *d_norm_w, float eps,
-                             float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, uint32_t *d_err,
-                             uint32_t *d_work, void *stream);
+                             float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, void *stream);
 
 /* The one-token GEMV with the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285;
  * IE_NORM_FUSE, src/model.c:1265-1293): after y = W x (+bias) (+res) is complete, the last CTA to finish writes
- * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: the
- * two work words of ie_b200_gemv_stream (required here: they also count the CTAs that have finished). */
+ * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: two
+ * u32 in device memory, zero before the first launch and left zero by every launch (they count the CTAs that
+ * have finished); launches that share them must not overlap on the GPU. */
 int ie_b200_gemv_norm_tail(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
                            const float *d_res, const float *d_norm_w, float eps, float *d_xn_out, void *d_xq_out, uint32_t *d_counter,
                            void *stream);
@@ -152,7 +149,7 @@ int ie_b200_swiglu(float *d_a, const float *d_b, uint32_t n, void *d_q, uint32_t
 
 /* SwiGLU for the interleaved layout gu[2i] = gate_i, gu[2i + 1] = up_i (what a GEMV over a matrix whose rows alternate
  * gate_i, up_i produces): h[i] = silu(gate_i) * up_i, same arithmetic and Q8 copy as ie_b200_swiglu. The decode engine
- * folds this into the GEMV itself (a warp owns a gate / up row pair); this entry serves prompt chunks. */
+ * and the prompt chunks both use it after a GEMV over the interleaved matrix. */
 int ie_b200_swiglu_il(const float *d_gu, float *d_h, uint32_t n, void *d_q, uint32_t T, size_t gu_stride, size_t h_stride, size_t q_stride,
                       void *stream);
 
@@ -186,6 +183,19 @@ int ie_b200_attn_decode(const float *d_q, const void *d_kc, const void *d_vc, fl
 int ie_b200_attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos,
                               const float *d_sin, float *d_out, void *d_oq, const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd,
                               int neox, int kv_f32, uint32_t kv_len, uint32_t n_ctx, void *d_part, uint32_t *d_count, void *stream);
+
+/* The same step (OP_ROPE_KV + OP_ATTN of one token on the half-precision cache) as the persistent step kernel runs it
+ * per layer (include/ie_b200_engine.h, ie_b200_engine_set_step_mode): a cooperative launch of one CTA per SM whose groups
+ * of four warps each take a (KV head, split) item -- one 64-position tile per item while there are more groups than tiles --
+ * followed, behind a grid barrier, by the merge of the splits' records (one warp per head) into d_out and its Q8 copy d_oq.
+ * The role of ie_attn_kv inside the reference's megakernel (kernels/ie_mk.c:43-95, kernels/ie_kernels.c:2721-2868). d_qkv: the
+ * un-rotated q | k | v of position *d_pos (n_head + 2 n_kv heads of hd floats); hd 64 or 128, at most 8 query heads per KV head.
+ * d_scratch: ie_b200_attn_persistent_scratch_bytes() bytes, 16-byte aligned, any contents; d_err: the device error word
+ * (set if a bounded wait of the kernel ran out). */
+size_t ie_b200_attn_persistent_scratch_bytes(uint32_t n_head, uint32_t n_kv, uint32_t hd);
+int ie_b200_attn_persistent(const float *d_qkv, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin, float *d_out, void *d_oq,
+                            const uint32_t *d_pos, uint32_t n_head, uint32_t n_kv, uint32_t hd, int neox, uint32_t kv_len, void *d_scratch,
+                            uint32_t *d_err, void *stream);
 
 /* Causal attention of a prompt chunk: T tokens at positions *d_pos .. *d_pos + T - 1 whose (rotated) K / V rows are
  * already in the half-precision cache (ie_b200_rope_kv); token t sees positions 0 .. *d_pos + t. The role of

@@ -102,6 +102,24 @@ int ie_b200_engine_set_collective(ie_b200_engine *e, struct ie_b200_allreduce *a
 /* backend.step (src/backend.h:10): one token at position pos; h_logits (vocab floats) may be NULL;
  * *next = the argmax token; *ms (may be NULL) = device time of the step. Host buffers in and out. */
 int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms);
+/* A bounded wait that ran out leaves the device error word set, and every later step / decode / run reports
+ * IE_B200_E_DEVICE (the all-reduce kernels then stop waiting: they look once and go on). Once the caller has dealt
+ * with the failure (the ranks of a tensor-parallel run are back in step: same number of calls made on each), this
+ * clears the word. */
+int ie_b200_engine_clear_error(ie_b200_engine *e);
+/* How a one-token step (step, decode) runs. 0 (default): as one persistent cooperative kernel that walks the whole
+ * op list with grid barriers between dependent ops -- the role of the reference's megakernel (kernels/ie_mk.c:43-95,
+ * recorder src/hip.c:445-566) -- wherever the op list and shapes allow it (half-precision cache, heads of 64 or 128,
+ * the llama / qwen2 op patterns), else as a CUDA graph of one kernel per op; 1: always the graph; 2: the kernel, or
+ * IE_B200_E_STATE where it cannot run. The environment variable IE_B200_STEP=graph|kernel sets the default.
+ * ie_b200_engine_step_is_kernel: 1 if steps of the current op list run as the persistent kernel. */
+int ie_b200_engine_set_step_mode(ie_b200_engine *e, int mode);
+int ie_b200_engine_step_is_kernel(ie_b200_engine *e);
+/* Failure injection from the host (for tests of the recovery path; nothing on the GPU faults): raises the abort
+ * flag that a CTA of the persistent kernel raises when one of its bounded waits runs out. The next step / decode
+ * then ends at once with the device error word set and returns IE_B200_E_DEVICE; ie_b200_engine_clear_error
+ * lowers the flag again. */
+int ie_b200_engine_inject_abort(ie_b200_engine *e);
 /* K greedy tokens without a host round trip per token: the step graph is replayed K times and a one-CTA
  * kernel feeds each argmax back as the next token on the device (what the decode loop of src/main.c:192-225
  * does on the host). h_out: the K generated tokens; *ms: device time of the K steps. K <= 4096 per call. */

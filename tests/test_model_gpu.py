@@ -109,6 +109,101 @@ def test_prefill_chunks_match_single_steps(cuda):
     assert got == want
 
 
+@pytest.mark.parametrize("name", ["tiny", "tiny-k", "tiny-128"])
+def test_prompt_chunks_on_the_half_cache(cuda, ora, name):
+    """The prompt path of the performance configuration: chunks of 32 tokens (the tensor-core GEMM takes 17 tokens and
+    more; with heads of 64 / 128 the chunk's attention runs on the tensor cores over the half cache), a prompt of two full
+    chunks and a tail of 6. The first generated token's logits against the oracle with the same half rounding at the cache
+    store (1e-2 of the logit scale: see test_half_cache_matches_oracle_with_half_cache for why not 1e-4), the greedy
+    continuation against token-by-token steps of the same engine wherever the oracle's top-two gap allows."""
+    from oracle.oracle import OracleModel
+
+    cfg = gguf.make_model(gguf.config(name), seed=0)
+    rng = np.random.default_rng(11)
+    prompt = [int(t) for t in rng.integers(0, cfg.vocab, 70)]
+    n_ctx, n_gen = 128, 10
+    om = OracleModel(ora, cfg, n_ctx, kv_f16=True)
+    want_logits = []
+    tok = prompt[0]
+    for pos in range(len(prompt) + n_gen - 1):
+        nxt, lg = om.step(tok, pos)
+        if pos >= len(prompt) - 1:
+            want_logits.append(lg)
+        tok = prompt[pos + 1] if pos + 1 < len(prompt) else nxt
+    om.close()
+    b = Backend(cfg, n_ctx, T=32, kv_f32=False)
+    for p0 in range(0, len(prompt), 32):
+        out = b.run(0, prompt[p0: p0 + 32], p0, last_only=True)
+    first = int(out[-1])
+    logits = b.read_rows("logits", len(prompt) % 32 - 1, 1).view(np.float32)[0, : cfg.vocab]
+    w0 = want_logits[0]
+    d0 = float(np.abs(logits - w0).max())
+    assert d0 <= 1e-2 * float(np.abs(w0).max()), d0
+    top2 = np.sort(w0)[-2:]
+    if top2[1] - top2[0] > 2 * d0:
+        assert first == int(np.argmax(w0))
+    # continue greedily from the chunk-written cache, logits against the oracle at every step
+    lg = np.zeros(cfg.vocab, np.float32)
+    tok, ids = first, [first]
+    for i in range(1, n_gen):
+        tok, _ = b.step(tok, len(prompt) + i - 1, lg)
+        ids.append(tok)
+        w = want_logits[i]
+        d = float(np.abs(lg - w).max())
+        assert d <= 1e-2 * float(np.abs(w).max()), (i, d)
+        top2 = np.sort(w)[-2:]
+        if top2[1] - top2[0] <= 2 * d or tok != int(np.argmax(w)):
+            break  # a near-tie: the two runs may part here, and the oracle's later logits follow its own token
+    b.close()
+    # the same prompt token by token through the step graph: same cache contents up to rounding flips, so the same
+    # first token wherever the gap allows
+    b1 = Backend(cfg, n_ctx, kv_f32=False)
+    tok = prompt[0]
+    for pos in range(len(prompt)):
+        nxt, _ = b1.step(prompt[pos], pos, lg if pos == len(prompt) - 1 else None)
+    b1.close()
+    d1 = float(np.abs(lg - w0).max())
+    assert d1 <= 1e-2 * float(np.abs(w0).max())
+    if top2[1] - top2[0] > 2 * max(d0, d1):
+        assert nxt == first
+
+
+VARIANTS = [{"IE_B200_PDL": "0"}, {"IE_B200_ATTN_FUSE": "0"}, {"IE_B200_NORM": "tail"}, {"IE_B200_NORM": "prologue"}, {"IE_B200_ATTN": "scalar"},
+            {"IE_B200_GEMM": "0"}, {"IE_B200_PREFILL_ATTN": "0"}]
+
+
+@pytest.mark.parametrize("env", VARIANTS, ids=lambda e: "-".join(f"{k}={v}" for k, v in e.items()))
+def test_switchable_variants(cuda, env, tmp_path_factory):
+    """Every environment switch of the library selects code that must give the same model: a child process with the
+    switch set runs the tiny models (float cache: the golden greedy ids of the reference CPU backend must come out; half
+    cache with the prompt as chunks: logits against the default configuration's)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    worker = Path(__file__).resolve().parent / "variant_worker.py"
+    base_path = tmp_path_factory.getbasetemp() / "variants_default.npz"
+    if not base_path.is_file():  # the default configuration once per session
+        base = subprocess.run([sys.executable, str(worker), str(base_path)], capture_output=True, text=True, timeout=600,
+                              env={k: v for k, v in os.environ.items() if not k.startswith("IE_B200_")})
+        assert base.returncode == 0, base.stdout[-1500:] + base.stderr[-3000:]
+    mine = tmp_path_factory.mktemp("variant") / "v.npz"
+    r = subprocess.run([sys.executable, str(worker), str(mine)], capture_output=True, text=True, timeout=600, env={**os.environ, **env})
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    want, got = np.load(base_path), np.load(mine)
+    for name in ("tiny", "tiny-k", "tiny-128"):
+        for i, key in enumerate(("_l0", "_l1")):
+            w, g = want[name + key], got[name + key]
+            d = float(np.abs(g - w).max())
+            # bit-exact kernels swapped for each other leave the logits unchanged; a different summation order (the GEMM
+            # against the GEMV, tree against sequential norm sums) may flip an int8 or half rounding: 1e-2 of the scale
+            assert d <= 1e-2 * float(np.abs(w).max()), (name, key, d)
+            top2 = np.sort(w)[-2:]
+            if top2[1] - top2[0] > 2 * d:
+                assert int(got[name + "_t"][i]) == int(want[name + "_t"][i]), (name, key)
+
+
 def test_step_argument_checks(cuda):
     from amd_c_b200._lib import IeB200Error
 
