@@ -82,6 +82,7 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_set_step_mode": (_int, [_vp, _int]),
     "ie_b200_engine_step_is_kernel": (_int, [_vp]),
     "ie_b200_engine_inject_abort": (_int, [_vp]),
+    "ie_b200_engine_phase_times": (_int, [_vp, _int, _vp]),
     "ie_b200_engine_decode": (_int, [_vp, _u32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
     "ie_b200_engine_enqueue_kinds": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
@@ -108,6 +109,8 @@ SIGNATURES.update({
     "ie_b200_ar_allreduce_add": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_allreduce_norm": (_int, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_gemv_allreduce_norm": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),
+    "ie_b200_gemv_push": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _vp, _vp]),
+    "ie_b200_ar_reduce_norm": (_int, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_argmax": (_int, [_vp, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_destroy": (None, [_vp]),
 })

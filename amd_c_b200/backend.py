@@ -75,8 +75,9 @@ class Backend:
     device_tensors: optional name -> (ggml_type, rows, cols, torch uint8 CUDA tensor of GGUF bytes) for matrices
     generated on the device; all other tensors come from cfg.tensors (numpy). kv_f32: float KV cache (the reference CPU backend's precision).
     tp / rank: tensor-parallel degree and this engine's slice.
-    step_mode: "auto" (the persistent step kernel where it can run, else the step graph), "graph", "kernel"; None leaves
-    the library's default (auto, or what IE_B200_STEP says).
+    step_mode: "graph" (a CUDA graph of one kernel per op: the library's default), "kernel" (the persistent step kernel, an error
+    where it cannot run), "auto" (the kernel where it can run, else the graph); None leaves the library's default (graph, or what
+    IE_B200_STEP says).
     """
 
     STEP_MODES = {"auto": 0, "graph": 1, "kernel": 2}
@@ -327,6 +328,15 @@ class Backend:
         """Whether one-token steps run as the persistent step kernel (one launch per step or per decode call)."""
         with self.torch.cuda.device(self.device):
             return bool(self.lib.ie_b200_engine_step_is_kernel(self.h))
+
+    PHASE_KINDS = ("embed", "gemv", "attention", "merge", "argmax", "finish", "reduce", "argmax_exchange", "gemv_from_q8", "gemv_with_norm",
+                   "gemv_with_swiglu", "gemv_same_activations")
+
+    def phase_times(self, enable: bool = True) -> dict:
+        """Per phase kind of the persistent step kernel: {kind: (work ms, barrier ms, barriers)} summed by CTA 0 since the last call."""
+        buf = (C.c_double * 36)()
+        check(self.lib.ie_b200_engine_phase_times(self.h, int(enable), buf))
+        return {k: (buf[3 * i], buf[3 * i + 1], int(buf[3 * i + 2])) for i, k in enumerate(self.PHASE_KINDS) if buf[3 * i + 2]}
 
     def clear_error(self) -> None:
         check(self.lib.ie_b200_engine_clear_error(self.h))

@@ -105,12 +105,14 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
 }
 
 
-constexpr int ARN_THREADS = 1024;
+constexpr int ARN_MAX_THREADS = 1024;
 
 // One CTA: x (= res, may alias out) + the ranks' partials in rank order, then y = x * rsqrt(mean x^2 + eps) * w
 // and the Q8 copy of y (the same arithmetic as the RMSNorm kernel and the norm tail of the GEMV).
 // Thread t owns elements 4 (t + 1024 it) .. + 3; eight neighbouring threads hold one Q8 block.
-template <int ITERS>
+// PEERS: how many ranks' words a thread polls together (4: worlds of up to four ranks at 1024 threads; 8: larger worlds at 512
+// threads, whose 128 registers hold all seven peers' loads in flight at once: one trip to L2 per poll instead of two).
+template <int ITERS, int ARN_THREADS, int PEERS>
 __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, const float *part, const float *res, float *out, const float *norm_w, float eps,
                                                               float *xn, uint8_t *xq, uint32_t n, uint32_t *err, int pushed, int early) {
   __shared__ float red[32];
@@ -154,17 +156,17 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   for (int it = 0; it < ITERS; it++) {
     const uint32_t i = 4u * (tid + ARN_THREADS * it);
     if (i >= n) continue;
-    for (uint32_t j0 = 0; j0 < s.world; j0 += 4u) {
-      unsigned long long v[4][4];
+    for (uint32_t j0 = 0; j0 < s.world; j0 += PEERS) {
+      unsigned long long v[PEERS][4];
       for (;;) {
         bool all = true;
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
+        for (int q = 0; q < PEERS; q++) {
           const uint32_t j = j0 + q;
           if (j < s.world && j != s.rank) ll_load4(my + (size_t)j * s.max_n + i, v[q]);
         }
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
+        for (int q = 0; q < PEERS; q++) {
           const uint32_t j = j0 + q;
           if (j < s.world && j != s.rank) {
 #pragma unroll
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
         }
       }
 #pragma unroll
-      for (int q = 0; q < 4; q++) {
+      for (int q = 0; q < PEERS; q++) {
         const uint32_t j = j0 + q;
         if (j >= s.world) continue;
         float4 pv = mine[it];
@@ -356,18 +358,28 @@ static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x,
                           uint32_t *d_err, void *stream, int pushed, int early = 0) {
   if (!a || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: NULL argument");
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_allreduce_norm: peers not connected");
-  if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_THREADS)
+  if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_MAX_THREADS)
     return fail(IE_B200_E_SIZE, "ie_b200_ar_allreduce_norm: %u floats (a multiple of 32, at most %u)", n, a->d.max_n < 16384u ? a->d.max_n : 16384u);
   if (!aligned16(d_part) || !aligned16(d_x) || !aligned16(d_norm_w) || (d_xn && !aligned16(d_xn)) || (d_xq && !aligned16(d_xq)))
     return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: 16-byte alignment");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t *xq = static_cast<uint8_t *>(d_xq);
-  const uint32_t iters = (n + 4u * ARN_THREADS - 1u) / (4u * ARN_THREADS);
-  switch (iters) {
-    case 1: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<1>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
-    case 2: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<2>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
-    default: IEB_LAUNCH_PDL("ar_norm_kernel", ar_norm_kernel<4>, dim3(1), dim3(ARN_THREADS), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early); break;
+#define IEB_ARN(IT, TH, PE)                                                                                                                  \
+  IEB_LAUNCH_PDL("ar_norm_kernel", (ar_norm_kernel<IT, TH, PE>), dim3(1), dim3(TH), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, \
+                 pushed, early)
+  if (a->d.world > 4u) {  // 512 threads, all peers polled together
+    const uint32_t iters = (n + 4u * 512u - 1u) / (4u * 512u);
+    if (iters <= 1) IEB_ARN(1, 512, 8);
+    else if (iters <= 2) IEB_ARN(2, 512, 8);
+    else if (iters <= 4) IEB_ARN(4, 512, 8);
+    else IEB_ARN(8, 512, 8);
+  } else {
+    const uint32_t iters = (n + 4u * 1024u - 1u) / (4u * 1024u);
+    if (iters <= 1) IEB_ARN(1, 1024, 4);
+    else if (iters <= 2) IEB_ARN(2, 1024, 4);
+    else IEB_ARN(4, 1024, 4);
   }
+#undef IEB_ARN
   return IE_B200_OK;
 }
 
@@ -376,23 +388,31 @@ extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_pa
   return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 0);
 }
 
-extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
-                                           float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream) {
-  if (!a || !d_w || !d_xq || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: NULL argument");
-  if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_gemv_allreduce_norm: peers not connected");
-  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: matrix kind %d", kind);
-  if (rows == 0 || rows % 32u || rows > a->d.max_n) return fail(IE_B200_E_SIZE, "ie_b200_gemv_allreduce_norm: %u rows (a multiple of 32, at most %u)", rows, a->d.max_n);
-  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u) || cols / 32u > 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_allreduce_norm: %u columns", cols);
-  if (!aligned16(d_w) || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: 16-byte alignment");
+extern "C" int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part, void *stream) {
+  if (!a || !d_w || !d_xq || !d_part) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: NULL argument");
+  if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_gemv_push: peers not connected");
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: matrix kind %d", kind);
+  if (rows == 0 || rows % 32u || rows > a->d.max_n) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u rows (a multiple of 32, at most %u)", rows, a->d.max_n);
+  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u) || cols / 32u > 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u columns", cols);
+  if (!aligned16(d_w) || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: 16-byte alignment");
   ActSrc act = {};
   act.xq = static_cast<const uint8_t *>(d_xq);
-  ArPush push = {};
-  for (uint32_t j = 0; j < a->d.world; j++) push.ll[j] = a->d.ll[j];
-  push.epoch = a->d.epoch, push.rank = a->d.rank, push.world = a->d.world, push.max_n = a->d.max_n;
+  ArPush push;
+  ar_push_info(a, &push);
   // the GEMV releases its dependents only after its own dependency wait: when the reduction kernel starts, everything
   // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
-  const int r = gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push, true);
-  if (r) return r;
+  return gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push, true);
+}
+
+extern "C" int ie_b200_ar_reduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                                      uint32_t n, uint32_t *d_err, void *stream) {
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 1, 0);
+}
+
+extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
+                                           float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream) {
+  if (!d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: NULL argument");
+  if (int r = ie_b200_gemv_push(a, kind, d_w, rows, cols, d_xq, d_part, stream)) return r;
   return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
 }
 

@@ -83,13 +83,16 @@ struct ie_b200_engine {
   cudaGraphExec_t step_graph = nullptr;
   uint32_t step_launches = 0;
   // the persistent step kernel (step_kernel.cu): the op list translated into phases, and its scratch
-  int step_mode = 0;          // 0: the kernel where the op list and shapes allow it, else the graph; 1: always the graph; 2: the kernel or an error
+  int step_mode = 1;          // 1: the step graph (default: measured faster on B200, see ie_b200_engine_set_step_mode); 2: the persistent kernel, or
+                              // an error where it cannot run; 0: the kernel where the op list and shapes allow it, else the graph
   int kernel_state = 0;       // 0: not examined yet, 1: program built, -1: this op list / shape has no program
   StepPhase *d_prog = nullptr;
   StepArgs sk = {};
+  int sk_kset = 0;            // matrix kinds of the program's GEMVs (0 Q4_0, 1 Q4_K / Q6_K, 2 mixed)
   float *sk_part = nullptr;
   void *sk_amax = nullptr;
   uint32_t *sk_bar = nullptr;  // {arrival counter, abort flag}
+  unsigned long long *sk_trace = nullptr;  // per phase kind {work ns, barrier ns, barriers} of CTA 0 (ie_b200_engine_phase_times)
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
@@ -355,7 +358,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
   if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
-  if (const char *sm = getenv("IE_B200_STEP")) e->step_mode = sm[0] == 'g' ? 1 : sm[0] == 'k' ? 2 : 0;
+  if (const char *sm = getenv("IE_B200_STEP")) e->step_mode = sm[0] == 'g' ? 1 : sm[0] == 'k' ? 2 : sm[0] == 'a' ? 0 : 1;
   chk(cudaMalloc(&e->sk_bar, 8), "cudaMalloc(barrier words)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->sk_bar, 0, 8), "cudaMemset");
   chk(cudaMalloc(&e->hist, (size_t)(HIST_CAP + 1) * 4), "cudaMalloc(history)");
@@ -379,7 +382,7 @@ extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
   for (auto &v : e->vecs) cudaFree(v.d);
   cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
   cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
-  cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax), cudaFree(e->sk_bar);
+  cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax), cudaFree(e->sk_bar), cudaFree(e->sk_trace);
   if (e->h_scalars) cudaFreeHost(e->h_scalars);
   if (e->h_result) cudaFreeHost(e->h_result);
   if (e->ev0) cudaEventDestroy(e->ev0);
@@ -548,6 +551,7 @@ static int build_program(ie_b200_engine *e) {
     ph.push_back(p);
   }
   const ie_b200_op *norm = nullptr, *swi = nullptr;
+  bool swi_in_gemv = false;
   uint64_t attq_off = IE_B200_NONE;
   const void *last_act = nullptr;  // what the previous GEMV phase staged (a following GEMV over the same activations keeps them)
   bool have_argmax = false;
@@ -561,7 +565,11 @@ static int build_program(ie_b200_engine *e) {
         break;
       case IE_B200_OP_SWIGLU:
         if (o.nh != 1u || o.qo == IE_B200_NONE || o.n % 32u || o.n / 32u > 1024u) return 0;
-        swi = &o, last_act = nullptr;
+        swi = &o, last_act = nullptr, swi_in_gemv = false;
+        // the GEMV right before it produced the (gate, up) pairs: it writes silu(gate) * up itself (a warp owns whole pairs)
+        if (!ph.empty() && ph.back().kind == PH_GEMV && ph.back().y == reinterpret_cast<float *>(A(o.a)) && !ph.back().bias && !ph.back().res &&
+            !ph.back().push && ph.back().rows == 2u * o.n && o.b != IE_B200_NONE)
+          ph.back().swi = 1u, ph.back().y = reinterpret_cast<float *>(A(o.b)), swi_in_gemv = true;
         break;
       case IE_B200_OP_GEMV: {
         if (o.mat < 0) return 0;
@@ -574,7 +582,7 @@ static int build_program(ie_b200_engine *e) {
         if (norm && o.a == norm->qo && m.cols == norm->n) {
           p.pro = PRO_NORM, p.src = A(norm->a), p.norm_w = e->vecs[norm->vec].d, act = norm;
         } else if (swi && o.a == swi->qo && m.cols == swi->n) {
-          p.pro = PRO_SWIGLU, p.src = A(swi->a), act = swi;
+          p.pro = swi_in_gemv ? PRO_QUANT : PRO_SWIGLU, p.src = A(swi_in_gemv ? swi->b : swi->a), act = swi;
         } else if (attq_off != IE_B200_NONE && o.a == attq_off) {
           p.pro = PRO_Q8, p.src = A(o.a), act = A(o.a);
         } else {
@@ -629,9 +637,38 @@ static int build_program(ie_b200_engine *e) {
     }
   }
   if (!have_argmax || ph.back().kind == PH_ARGMAX) return 0;
-  // weights for idle warps to pull into L2: during a layer's attention the matrix of the GEMV that follows it
-  for (size_t k = 0; k + 2 < ph.size(); k++)
-    if (ph[k].kind == PH_ATTN && ph[k + 2].kind == PH_GEMV) ph[k].pf = ph[k + 2].w, ph[k].pf_bytes = ph[k + 2].rowb * ph[k + 2].rows;
+  // Which phase pulls the head of which later matrix into L2: the weights form one stream in program order (cyclic: after
+  // the output head comes layer 0 of the next token); every phase claims the next unclaimed matrix (its first 24 MB) while
+  // less than 40 MB are claimed and not yet consumed, so the fetch from HBM runs ahead of the GEMVs through attention,
+  // merge and barriers, and never ahead by more than the L2 can hold. Two laps: the second one is the steady state.
+  {
+    std::vector<size_t> g;
+    for (size_t k = 0; k < ph.size(); k++)
+      if (ph[k].kind == PH_GEMV) g.push_back(k);
+    const uint64_t WINDOW = 40ull << 20, CAP = 24ull << 20;
+    std::vector<uint64_t> claimed(ph.size(), 0);
+    uint64_t ahead = 0;
+    size_t next = 0, outstanding = 0;
+    for (int lap = 0; lap < 2 && g.size() > 1; lap++)
+      for (size_t k = 0; k < ph.size(); k++) {
+        if (ph[k].kind == PH_GEMV) {
+          if (claimed[k]) ahead -= claimed[k] < ahead ? claimed[k] : ahead, claimed[k] = 0, outstanding--;
+          else if (g[next] == k) next = (next + 1) % g.size();  // nobody fetched it ahead: its own loads do
+        }
+        ph[k].pf = nullptr, ph[k].pf_bytes = 0;
+        if (ahead < WINDOW && outstanding + 1 < g.size() && g[next] != k && !claimed[g[next]]) {
+          const size_t j = g[next];
+          const uint64_t bytes = ph[j].rowb * ph[j].rows, take = bytes < CAP ? bytes : CAP;
+          ph[k].pf = ph[j].w, ph[k].pf_bytes = take;
+          claimed[j] = take, ahead += take, outstanding++;
+          next = (next + 1) % g.size();
+        }
+      }
+  }
+  bool has_q4 = false, has_k = false;
+  for (const StepPhase &q : ph)
+    if (q.kind == PH_GEMV) (q.mkind == IE_B200_MAT_Q4 ? has_q4 : has_k) = true;
+  e->sk_kset = has_q4 && has_k ? 2 : has_k ? 1 : 0;
   StepArgs &a = e->sk;
   a.smax = step_kernel_smax(d.n_kv);
   cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax);
@@ -646,7 +683,9 @@ static int build_program(ie_b200_engine *e) {
   a.part = e->sk_part, a.amax_part = e->sk_amax, a.result = reinterpret_cast<uint32_t *>(e->arena + d.argmax_off);
   a.emb = static_cast<const uint8_t *>(e->mats[emb.mat].d), a.emb_kind = e->mats[emb.mat].kind, a.dim = emb.n, a.x = reinterpret_cast<float *>(A(emb.a));
   ar_push_info(e->ar, &a.push);
-  a.vocab_off = e->vocab_off, a.wait_ns = AR_WAIT_NS;
+  a.vocab_off = e->vocab_off, a.wait_ns = AR_WAIT_NS, a.trace = e->sk_trace;
+  a.knobs = 3u;
+  if (const char *kn = getenv("IE_B200_SK_KNOBS")) a.knobs = (uint32_t)atoi(kn);
   e->kernel_state = 1;
   return 1;
 }
@@ -702,7 +741,7 @@ extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos
   if (int r = upload_input(e, &tok, 1, pos, st)) return r;
   if (kernel) {
     e->sk.n_steps = 1;
-    if (int r = step_kernel_launch(e->sk, e->d.hd, st)) return r;
+    if (int r = step_kernel_launch(e->sk, e->d.hd, e->sk_kset, st)) return r;
   } else {
     IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
     count_launch(e->step_launches);
@@ -739,7 +778,7 @@ extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t p
   IEB_CUDA(cudaEventRecord(e->ev0, st));
   if (kernel) {  // one launch: the kernel loops over the K tokens itself
     e->sk.n_steps = K;
-    if (int r = step_kernel_launch(e->sk, e->d.hd, st)) return r;
+    if (int r = step_kernel_launch(e->sk, e->d.hd, e->sk_kset, st)) return r;
   } else {
     for (uint32_t k = 0; k < K; k++) IEB_CUDA(cudaGraphLaunch(e->step_graph, st));
     count_launch(e->step_launches * K);
@@ -831,6 +870,22 @@ extern "C" int ie_b200_engine_step_is_kernel(ie_b200_engine *e) {
   bool kernel = false;
   if (cudaSetDevice(e->device) != cudaSuccess || use_step_kernel(e, &kernel) != IE_B200_OK) return 0;
   return kernel ? 1 : 0;
+}
+
+extern "C" int ie_b200_engine_phase_times(ie_b200_engine *e, int enable, double *h_ms36) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_phase_times: NULL engine");
+  IEB_CUDA(cudaSetDevice(e->device));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  if (h_ms36) {
+    unsigned long long raw[36] = {};
+    if (e->sk_trace) IEB_CUDA(cudaMemcpy(raw, e->sk_trace, sizeof raw, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < 36; i++) h_ms36[i] = i % 3 == 2 ? (double)raw[i] : (double)raw[i] * 1e-6;
+  }
+  if (enable && !e->sk_trace) IEB_CUDA(cudaMalloc(&e->sk_trace, 36 * sizeof(unsigned long long)));
+  if (e->sk_trace) IEB_CUDA(cudaMemset(e->sk_trace, 0, 36 * sizeof(unsigned long long)));
+  if (!enable && e->sk_trace) cudaFree(e->sk_trace), e->sk_trace = nullptr;
+  e->sk.trace = e->sk_trace;
+  return IE_B200_OK;
 }
 
 extern "C" int ie_b200_engine_inject_abort(ie_b200_engine *e) {

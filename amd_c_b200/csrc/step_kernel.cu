@@ -32,7 +32,10 @@
 
 namespace ieb {
 
-constexpr int SK_WARPS = 16, SK_THREADS = SK_WARPS * 32;
+// 8 warps per CTA, one CTA per SM: 255 registers per thread, so that neither the GEMV loop with 24 loads per lane in flight
+// nor the attention tile loop (64 accumulator registers) spills. (16 warps at 128 registers spilled about 1 KB per thread;
+// with the kernel's shared memory leaving an L1 of a few tens of KB, that traffic went to L2 and tripled the step time.)
+constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32;
 constexpr int SK_GROUPS = 2, SK_GW = 4, SK_GT = SK_GW * 32;  // attention: two groups of four warps per CTA
 constexpr int SK_TILE = 64, SK_PAD = 8, SK_NB = 3;            // 64-position tiles, rows padded by 8 halves, 3 tile buffers per group
 
@@ -66,8 +69,10 @@ struct SkBar {
   uint32_t *count, *abort, *err;
   uint32_t target;
   uint64_t wait_ns;
+  unsigned long long *trace;  // CTA 0 only: time from the last release to this arrival and from arrival to release, per phase kind
+  uint64_t t_rel;
 };
-__device__ __forceinline__ bool grid_sync(SkBar &b, uint32_t *s_ok) {
+__device__ __forceinline__ bool grid_sync(SkBar &b, uint32_t *s_ok, int kind) {
   __syncthreads();
   b.target += gridDim.x;
   if (threadIdx.x == 0) {
@@ -88,15 +93,20 @@ __device__ __forceinline__ bool grid_sync(SkBar &b, uint32_t *s_ok) {
       }
     }
     *s_ok = ok;
+    if (b.trace) {
+      const uint64_t t1 = ar_now();
+      b.trace[3 * kind] += t0 - b.t_rel, b.trace[3 * kind + 1] += t1 - t0, b.trace[3 * kind + 2] += 1ull;
+      b.t_rel = t1;
+    }
   }
   __syncthreads();
   return *s_ok != 0u;
 }
 
-// Lines of [p, p + bytes) that belong to this CTA's share, into L2, by the `nthr` threads numbered `t`.
-__device__ __forceinline__ void prefetch_share(const uint8_t *p, uint64_t bytes, uint32_t t, uint32_t nthr) {
+// Part `part` of `nparts` of the lines of [p, p + bytes) into L2, by the `nthr` threads numbered `t`.
+__device__ __forceinline__ void prefetch_part(const uint8_t *p, uint64_t bytes, uint32_t part, uint32_t nparts, uint32_t t, uint32_t nthr) {
   const uint64_t lines = (bytes + 127u) >> 7;
-  const uint64_t per = (lines + gridDim.x - 1u) / gridDim.x, lo = per * blockIdx.x;
+  const uint64_t per = (lines + nparts - 1u) / nparts, lo = per * part;
   const uint64_t hi = lo + per < lines ? lo + per : lines;
   for (uint64_t i = lo + t; i < hi; i += nthr) prefetch_l2(p + (i << 7));
 }
@@ -108,11 +118,13 @@ struct SkRows {
   uint32_t W, gw, full, base, rp;
 };
 template <int R>
-__device__ __forceinline__ SkRows sk_rows(uint32_t rows, int warp) {
+__device__ __forceinline__ SkRows sk_rows(uint32_t rows, int warp, bool pairs) {
+  static_assert(R % 2 == 0, "row pairs stay in one group");
   SkRows s;
   s.W = gridDim.x * SK_WARPS, s.gw = (uint32_t)warp * gridDim.x + blockIdx.x;
   s.full = rows / (R * s.W), s.base = s.full * s.W * R;
   s.rp = (rows - s.base + s.W - 1u) / s.W;
+  if (pairs) s.rp = (s.rp + 1u) & ~1u;  // (gate, up) pairs are not split between warps
   return s;
 }
 
@@ -157,6 +169,17 @@ __device__ __forceinline__ void sk_group(const StepPhase &ph, const StepArgs &a,
   float v[R];
 #pragma unroll
   for (int i = 0; i < R; i++) v[i] = __shfl_sync(0xFFFFFFFFu, warp_tree(acc[i]), 0);
+  if (ph.swi) {
+    // rows r0 + 2j, r0 + 2j + 1 are gate and up of output (r0 >> 1) + j (r0 and nr are even): the SwiGLU kernel's arithmetic
+#pragma unroll
+    for (int j = 0; j < R / 2; j++) {
+      if (lane == j && (uint32_t)(2 * j + 1) < nr) {
+        const float g = v[2 * j];
+        ph.y[(r0 >> 1) + j] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), v[2 * j + 1]);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < R; i++) {
     if (lane == i && (uint32_t)i < nr) {
@@ -176,34 +199,96 @@ __device__ __forceinline__ void sk_group(const StepPhase &ph, const StepArgs &a,
   }
 }
 
-// Not inlined on purpose: each instantiation gets the kernel's whole register budget for its hot loop, and the kernel's
-// own long-lived state is saved around the call instead of being squeezed out of the loop.
+// The rows [r0, r0 + nr) of a matrix into L2 (whole rows, at most 16 KB each), by one warp.
+__device__ __forceinline__ void sk_prefetch_rows(const uint8_t *w, size_t rowb, uint32_t r0, uint32_t nr, int lane) {
+  const uint32_t lines = (uint32_t)((rowb + 127u) >> 7);
+  for (uint32_t i = 0; i < nr; i++) {
+    const uint8_t *rp = w + (size_t)(r0 + i) * rowb;
+    for (uint32_t l = lane; l < lines && l < 128u; l += 32u) prefetch_l2(rp + ((size_t)l << 7));
+  }
+}
+
+// One copy of the group code per instantiation (whole rounds and the evenly spread rest share it): two inlined copies cost
+// some 30 registers more. Before a group is worked on, the rows of the warp's next group are asked into L2, so that only the
+// first group of a phase pays the full trip to HBM.
 template <int KIND, int R, int U>
-__device__ __noinline__ void sk_gemv(const StepPhase &ph, const StepArgs &a, const uint4 *A0, const uint4 *A1, const float *da, const int *as, int warp,
+__device__ __forceinline__ void sk_gemv(const StepPhase &ph, const StepArgs &a, const uint4 *A0, const uint4 *A1, const float *da, const int *as, int warp,
                                         int lane, uint32_t ep) {
-  const SkRows s = sk_rows<R>(ph.rows, warp);
-  for (uint32_t k = 0; k < s.full; k++) sk_group<KIND, R, U>(ph, a, (k * s.W + s.gw) * R, R, A0, A1, da, as, lane, ep);
-  const uint32_t r0 = s.base + s.gw * s.rp;
-  if (s.rp && r0 < ph.rows) sk_group<KIND, R, U>(ph, a, r0, min(s.rp, ph.rows - r0), A0, A1, da, as, lane, ep);
+  const SkRows s = sk_rows<R>(ph.rows, warp, ph.swi != 0u);
+  const uint32_t rows = ph.rows;
+  auto group_of = [&](uint32_t k, uint32_t &r0, uint32_t &nr) {
+    r0 = (k * s.W + s.gw) * R, nr = R;
+    if (k == s.full) {
+      r0 = s.base + s.gw * s.rp;
+      nr = (s.rp && r0 < rows) ? min(s.rp, rows - r0) : 0u;
+    }
+  };
+  for (uint32_t k = 0; k <= s.full; k++) {
+    uint32_t r0, nr;
+    group_of(k, r0, nr);
+    if ((a.knobs & 1u) && k < s.full) {
+      uint32_t rn, nn;
+      group_of(k + 1u, rn, nn);
+      sk_prefetch_rows(ph.w, ph.rowb, rn, nn, lane);
+    }
+    if (nr) sk_group<KIND, R, U>(ph, a, r0, nr, A0, A1, da, as, lane, ep);
+  }
+}
+
+// Rows per group of the instantiation that takes a matrix (must agree with the dispatch in the kernel).
+__device__ __forceinline__ int sk_rows_per_group(int mkind, uint32_t nb) {
+  (void)nb;
+  return mkind == IE_B200_MAT_Q4 ? 4 : 2;
 }
 
 // The rows of this warp's first group of a GEMV phase into L2 (called before the barrier in front of the phase).
 __device__ __forceinline__ void sk_gemv_prefetch(const StepPhase &ph, int warp, int lane) {
-  const bool wide = ph.nb <= 128u;
-  const int R = ph.mkind == IE_B200_MAT_Q4 ? (wide ? 4 : 2) : (wide ? 2 : 1);
+  const int R = sk_rows_per_group(ph.mkind, ph.nb);
   const uint32_t W = gridDim.x * SK_WARPS, gw = (uint32_t)warp * gridDim.x + blockIdx.x;
   const uint32_t full = ph.rows / (R * W);
   uint32_t r0, nr;
   if (full) {
     r0 = gw * R, nr = R;
   } else {
-    const uint32_t rp = (ph.rows + W - 1u) / W;
+    uint32_t rp = (ph.rows + W - 1u) / W;
+    if (ph.swi) rp = (rp + 1u) & ~1u;
     r0 = gw * rp, nr = rp;
   }
-  const uint32_t lines = (uint32_t)((ph.rowb + 127u) >> 7);
-  for (uint32_t i = 0; i < nr && r0 + i < ph.rows; i++) {
-    const uint8_t *rp_ = ph.w + (size_t)(r0 + i) * ph.rowb;
-    for (uint32_t l = lane; l < lines && l < 128u; l += 32u) prefetch_l2(rp_ + ((size_t)l << 7));
+  if (r0 < ph.rows) sk_prefetch_rows(ph.w, ph.rowb, r0, min(nr, ph.rows - r0), lane);
+}
+
+// Q8 of an f32 vector into the activation planes: thread t owns half-blocks t, t + SK_THREADS, ... (16 values each).
+__device__ __forceinline__ void sk_stage_quant(const float *x, uint32_t nb, uint4 *A0, uint4 *A1, float *da, int *as) {
+  const uint32_t HB = 2u * nb;
+  for (uint32_t k0 = 0; k0 < HB; k0 += SK_THREADS) {  // uniform trip count: the shuffles need every lane
+    const uint32_t hb = k0 + threadIdx.x, b = hb >> 1, h = hb & 1u;
+    const bool valid = hb < HB;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+      float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid) p = __ldcg(reinterpret_cast<const float4 *>(x + 16u * (size_t)hb + j));
+      v[j] = p.x, v[j + 1] = p.y, v[j + 2] = p.z, v[j + 3] = p.w;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; j++) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    const float d = __fdiv_rn(amax, 127.0f), rinv = __frcp_rn(d);
+    uint32_t pk[4] = {0u, 0u, 0u, 0u};
+    int s = 0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      int q = 0;
+      if (d != 0.0f) q = q8_round(v[j], d, rinv);
+      s += q;
+      pk[j >> 2] |= (uint32_t)(q & 255) << (8 * (j & 3));
+    }
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    if (valid) {
+      (h ? A1 : A0)[b] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      if (h == 0u) da[b] = d, as[b] = s;
+    }
   }
 }
 
@@ -285,7 +370,7 @@ struct SkAttnSmem {
 };
 
 template <int HD>
-__device__ __noinline__ void sk_attn_item(const StepArgs &a, const StepPhase &ph, uint32_t g, uint32_t s, uint32_t A, uint32_t span, uint32_t np,
+__device__ __forceinline__ void sk_attn_item(const StepArgs &a, const StepPhase &ph, uint32_t g, uint32_t s, uint32_t A, uint32_t span, uint32_t np,
                                              uint8_t *gsm, int gtid, int bar_id) {
   using SM = SkAttnSmem<HD>;
   constexpr int ROW = SM::ROW, TILE_ELEMS = SM::TILE_ELEMS, KS = HD / 16;
@@ -490,28 +575,40 @@ __device__ __forceinline__ void sk_merge_head(const StepArgs &a, const StepPhase
   constexpr int DPL = HD / 32;
   const size_t rec = HD + 2;
   const float *pr = a.part + (size_t)head * a.smax * rec;
-  float M = -INFINITY;
-  for (uint32_t k = lane; k < A; k += 32u) M = fmaxf(M, __ldcg(pr + k * rec));
-  M = warp_max(M);
-  float L = 0.0f;
-  for (uint32_t k = lane; k < A; k += 32u) L = fmaf(expf(__ldcg(pr + k * rec) - M), __ldcg(pr + k * rec + 1), L);
-  L = warp_sum_all(L);
+  // every load of the first eight splits goes out before anything is used: one trip to L2 for a short context
+  float mk[2] = {-INFINITY, -INFINITY}, lk[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int j = 0; j < 2; j++) {
+    const uint32_t k = lane + 32u * j;
+    if (k < A) mk[j] = __ldcg(pr + k * rec), lk[j] = __ldcg(pr + k * rec + 1);
+  }
+  float v0[8][DPL];
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+#pragma unroll
+    for (int d = 0; d < DPL; d++) v0[j][d] = (uint32_t)j < A ? __ldcg(pr + (size_t)j * rec + 2 + lane + 32 * d) : 0.0f;
+  const float M = warp_max(fmaxf(mk[0], mk[1]));
+  const float w0 = expf(mk[0] - M), w1 = expf(mk[1] - M);  // lane k holds the weight of split k (and k + 32)
+  const float L = warp_sum_all(fmaf(w0, lk[0], w1 * lk[1]));
   float acc[DPL];
 #pragma unroll
   for (int d = 0; d < DPL; d++) acc[d] = 0.0f;
-  for (uint32_t k0 = 0; k0 < A; k0 += 4u) {
-    float w[4], v[4][DPL];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float wk = __shfl_sync(0xFFFFFFFFu, w0, j);
+#pragma unroll
+    for (int d = 0; d < DPL; d++) acc[d] = fmaf(wk, v0[j][d], acc[d]);  // a missing split: weight exp(-inf) = 0, value 0
+  }
+  for (uint32_t k0 = 8u; k0 < A; k0 += 4u) {
+    float v[4][DPL];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int d = 0; d < DPL; d++) v[j][d] = k0 + j < A ? __ldcg(pr + (size_t)(k0 + j) * rec + 2 + lane + 32 * d) : 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const bool ok = k0 + j < A;
-      const float *p = pr + (size_t)(ok ? k0 + j : k0) * rec;
-      w[j] = ok ? __ldcg(p) : -INFINITY;
-#pragma unroll
-      for (int d = 0; d < DPL; d++) v[j][d] = __ldcg(p + 2 + lane + 32 * d);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const float wk = expf(w[j] - M);  // -inf for a missing split: weight 0
+      const uint32_t k = k0 + j;
+      const float wk = __shfl_sync(0xFFFFFFFFu, k < 32u ? w0 : w1, k & 31u);
 #pragma unroll
       for (int d = 0; d < DPL; d++) acc[d] = fmaf(wk, v[j][d], acc[d]);
     }
@@ -527,14 +624,15 @@ __device__ __forceinline__ void sk_merge_head(const StepArgs &a, const StepPhase
 }
 
 // ---- the kernel --------------------------------------------------------------------------------------------------
-template <int HD>
+// KSET: the matrix kinds of the model's GEMVs the instantiation carries code for: 0 Q4_0, 1 Q4_K + Q6_K, 2 all three.
+template <int HD, int KSET>
 __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_constant__ StepArgs a) {
   extern __shared__ uint4 smem_sk[];
   __shared__ float red[SK_WARPS];
   __shared__ uint32_t s_ok;
   __shared__ float s_mx[SK_WARPS], s_sum[SK_WARPS];
   __shared__ uint32_t s_idx[SK_WARPS];
-  __shared__ StepPhase s_ph;  // the phase being executed (the functions below read it from here)
+  __shared__ StepPhase s_ph[2];  // the phase being executed and the next one (fetched while this one runs)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   if (threadIdx.x == 0) {
@@ -544,17 +642,24 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_consta
   }
   __syncthreads();
   if (!s_ok) return;
-  SkBar bar = {a.bar, a.bar + 1, a.err, 0u, a.wait_ns};
+  SkBar bar = {a.bar, a.bar + 1, a.err, 0u, a.wait_ns, blockIdx.x == 0 ? a.trace : nullptr, ar_now()};
   uint32_t ep = 0u;  // tensor parallel: the epoch of the last exchange
   if (a.push.world > 1u) ep = __ldcg(a.push.epoch);
 
+  constexpr uint32_t PH_WORDS = sizeof(StepPhase) / 8u;
+  if (threadIdx.x < PH_WORDS) reinterpret_cast<uint64_t *>(&s_ph[0])[threadIdx.x] = reinterpret_cast<const uint64_t *>(a.prog)[threadIdx.x];
+  uint32_t cur = 0u;
   for (uint32_t step = 0; step < a.n_steps; step++) {
-    for (uint32_t p = 0; p < a.n_phases; p++) {
-      __syncthreads();  // (also: nobody still reads the previous phase's record or its staged activations)
-      if (threadIdx.x < sizeof(StepPhase) / 8u) reinterpret_cast<uint64_t *>(&s_ph)[threadIdx.x] = reinterpret_cast<const uint64_t *>(a.prog + p)[threadIdx.x];
-      __syncthreads();
-      const StepPhase &ph = s_ph;
+    for (uint32_t p = 0; p < a.n_phases; p++, cur ^= 1u) {
+      __syncthreads();  // the record of phase p is in s_ph[cur]; nobody still reads the previous phase's staged activations
+      // the next phase's record travels from global memory while this phase runs
+      const uint32_t pn = p + 1u < a.n_phases ? p + 1u : 0u;
+      uint64_t nxt_word = 0ull;
+      if (threadIdx.x < PH_WORDS) nxt_word = reinterpret_cast<const uint64_t *>(a.prog + pn)[threadIdx.x];
+      const StepPhase &ph = s_ph[cur];
       const int32_t ph_kind = ph.kind, ph_nobar = ph.nobar;
+      // the head of a matrix that a later phase streams, into L2 while this phase runs (the attention phase leaves that to its idle groups)
+      if ((a.knobs & 2u) && ph.pf && ph_kind != PH_ATTN) prefetch_part(ph.pf, ph.pf_bytes, blockIdx.x, gridDim.x, threadIdx.x, SK_THREADS);
       switch (ph_kind) {
         case PH_EMBED: {
           if (blockIdx.x == 0) {
@@ -578,6 +683,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_consta
         }
         case PH_GEMV: {
           const uint32_t nb = ph.nb;
+          const bool tr = bar.trace != nullptr && threadIdx.x == 0;
+          const uint64_t tg0 = tr ? ar_now() : 0ull;
           uint4 *A0 = smem_sk, *A1 = smem_sk + nb;
           float *da = reinterpret_cast<float *>(smem_sk + 2u * nb);
           int *as = reinterpret_cast<int *>(da + nb);
@@ -592,22 +699,22 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_consta
           } else if (ph.pro == PRO_SWIGLU) {
             sk_stage_swiglu(static_cast<const float *>(ph.src), nb, A0, A1, da, as);
             __syncthreads();
+          } else if (ph.pro == PRO_QUANT) {
+            sk_stage_quant(static_cast<const float *>(ph.src), nb, A0, A1, da, as);
+            __syncthreads();
           }
           if (ph.push) ep++;
-          const bool wide = nb <= 128u;  // a lane's blocks of a row fit 4 lane steps: 4 rows per group; else 2 rows x 8 steps
-          switch (ph.mkind) {
-            case IE_B200_MAT_Q4:
-              if (wide) sk_gemv<IE_B200_MAT_Q4, 4, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
-              else sk_gemv<IE_B200_MAT_Q4, 2, 8>(ph, a, A0, A1, da, as, warp, lane, ep);
-              break;
-            case IE_B200_MAT_Q4K:
-              if (wide) sk_gemv<IE_B200_MAT_Q4K, 2, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
-              else sk_gemv<IE_B200_MAT_Q4K, 1, 8>(ph, a, A0, A1, da, as, warp, lane, ep);
-              break;
-            default:
-              if (wide) sk_gemv<IE_B200_MAT_Q6K, 2, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
-              else sk_gemv<IE_B200_MAT_Q6K, 1, 8>(ph, a, A0, A1, da, as, warp, lane, ep);
-              break;
+          const uint64_t tg1 = tr ? ar_now() : 0ull;
+          // rows per group x lane steps per chunk = 16-byte loads a lane keeps in flight: 16 for Q4_0 (4 rows x 4 steps), 8 for
+          // the K kinds (8 registers per block). One instantiation per kind: rows longer than 128 blocks loop over chunks (their
+          // later chunks are in L2 by then: whole rows are asked for ahead).
+          if (KSET != 1 && ph.mkind == IE_B200_MAT_Q4) sk_gemv<IE_B200_MAT_Q4, 4, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
+          else if (KSET != 0 && ph.mkind == IE_B200_MAT_Q4K) sk_gemv<IE_B200_MAT_Q4K, 2, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
+          else if (KSET != 0 && ph.mkind == IE_B200_MAT_Q6K) sk_gemv<IE_B200_MAT_Q6K, 2, 4>(ph, a, A0, A1, da, as, warp, lane, ep);
+          if (tr) {  // slots 8 + prologue kind: {prologue ns, rows loop ns of warp 0, phases}
+            const uint64_t tg2 = ar_now();
+            unsigned long long *t = bar.trace + 3 * (8 + (ph.pro == PRO_QUANT ? PRO_SWIGLU : ph.pro));
+            t[0] += tg1 - tg0, t[1] += tg2 - tg1, t[2] += 1ull;
           }
           break;
         }
@@ -615,14 +722,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_consta
           const uint32_t np = ld_cg_u32(a.scalars + a.Tm + 1u) + 1u;
           uint32_t span, A;
           sk_splits(np, a.smax, span, A);
-          if (warp < SK_GROUPS * SK_GW) {
+          {
             const int grp = warp / SK_GW;
             uint8_t *gsm = reinterpret_cast<uint8_t *>(smem_sk) + (size_t)grp * SkAttnSmem<HD>::BYTES;
             const uint32_t n_items = a.n_kv * A, n_slots = gridDim.x * SK_GROUPS;
-            for (uint32_t item = (uint32_t)grp * gridDim.x + blockIdx.x; item < n_items; item += n_slots)
+            const uint32_t first = (uint32_t)grp * gridDim.x + blockIdx.x;
+            // a group without an item pulls its share of the next matrix into L2 instead (most groups, at a short context)
+            if ((a.knobs & 2u) && first >= n_items && ph.pf)
+              prefetch_part(ph.pf, ph.pf_bytes, blockIdx.x * SK_GROUPS + grp, gridDim.x * SK_GROUPS, threadIdx.x - grp * SK_GT, SK_GT);
+            for (uint32_t item = first; item < n_items; item += n_slots)
               sk_attn_item<HD>(a, ph, item % a.n_kv, item / a.n_kv, A, span, np, gsm, threadIdx.x - grp * SK_GT, 1 + grp);
-          } else if (ph.pf) {
-            prefetch_share(ph.pf, ph.pf_bytes, threadIdx.x - SK_GROUPS * SK_GT, SK_THREADS - SK_GROUPS * SK_GT);
           }
           break;
         }
@@ -798,14 +907,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const __grid_consta
         }
         default: break;
       }
+      if (threadIdx.x < PH_WORDS) reinterpret_cast<uint64_t *>(&s_ph[cur ^ 1u])[threadIdx.x] = nxt_word;
       if (!ph_nobar) {
         // ask for what the next phase streams first, then arrive: the weights are on their way while the CTAs gather
-        uint32_t pn = p + 1u;
-        if (pn == a.n_phases && step + 1u < a.n_steps) pn = 0u;
-        if (pn < a.n_phases) {
-          if (a.prog[pn].kind == PH_GEMV) sk_gemv_prefetch(a.prog[pn], warp, lane);
-        }
-        if (!grid_sync(bar, &s_ok)) return;
+        __syncthreads();
+        if ((p + 1u < a.n_phases || step + 1u < a.n_steps) && s_ph[cur ^ 1u].kind == PH_GEMV) sk_gemv_prefetch(s_ph[cur ^ 1u], warp, lane);
+        if (!grid_sync(bar, &s_ok, ph_kind)) return;
       }
     }
   }
@@ -830,8 +937,10 @@ uint32_t step_kernel_smax(uint32_t n_kv) {
 
 size_t step_kernel_amax_bytes() { return (size_t)sm_count() * sizeof(SkArgPart); }
 
-int step_kernel_launch(const StepArgs &a, uint32_t hd, cudaStream_t st) {
-  const void *k = hd == 64 ? reinterpret_cast<const void *>(step_kernel<64>) : reinterpret_cast<const void *>(step_kernel<128>);
+int step_kernel_launch(const StepArgs &a, uint32_t hd, int kset, cudaStream_t st) {
+  const void *k = nullptr;
+  if (hd == 64) k = kset == 0 ? reinterpret_cast<const void *>(step_kernel<64, 0>) : kset == 1 ? reinterpret_cast<const void *>(step_kernel<64, 1>) : reinterpret_cast<const void *>(step_kernel<64, 2>);
+  else k = kset == 0 ? reinterpret_cast<const void *>(step_kernel<128, 0>) : kset == 1 ? reinterpret_cast<const void *>(step_kernel<128, 1>) : reinterpret_cast<const void *>(step_kernel<128, 2>);
   const size_t smem = sk_smem_bytes(hd);
   if (int r = ensure_dynamic_smem(k, smem)) return r;
   static thread_local int coop_dev = -1, coop = 0;
@@ -881,5 +990,5 @@ extern "C" int ie_b200_attn_persistent(const float *d_qkv, void *d_kc, void *d_v
   a.n_head = n_head, a.n_kv = n_kv, a.kv_len = kv_len, a.neox = neox ? 1u : 0u, a.cs = d_cos, a.sn = d_sin;
   a.part = reinterpret_cast<float *>(sc + sizeof ph + 32), a.smax = step_kernel_smax(n_kv);
   a.wait_ns = AR_WAIT_NS;
-  return step_kernel_launch(a, hd, st);
+  return step_kernel_launch(a, hd, 0, st);
 }

@@ -22,7 +22,8 @@ enum {
   PRO_Q8 = 0,      // src: a Q8 buffer
   PRO_NORM = 1,    // src: f32 vector; act = Q8(rmsnorm(src) * norm_w)
   PRO_SWIGLU = 2,  // src: interleaved (gate_i, up_i) f32 pairs; act = Q8(silu(gate) * up)
-  PRO_KEEP = 3     // the activations the previous phase staged are still in shared memory
+  PRO_KEEP = 3,    // the activations the previous phase staged are still in shared memory
+  PRO_QUANT = 4    // src: f32 vector; act = Q8(src)
 };
 
 struct StepPhase {
@@ -40,7 +41,8 @@ struct StepPhase {
   uint8_t *attq;
   const uint8_t *pf;          // weights that idle warps of this phase pull into L2 (the matrices of the next phases)
   uint64_t pf_bytes;
-  uint32_t push, pad;         // PH_GEMV under tensor parallelism: finished rows also go to the peers' slots
+  uint32_t push;              // PH_GEMV under tensor parallelism: finished rows also go to the peers' slots
+  uint32_t swi;               // PH_GEMV over interleaved (gate_i, up_i) rows: y[i] = silu(gate_i) * up_i instead of the two rows
 };
 
 struct StepArgs {
@@ -67,6 +69,9 @@ struct StepArgs {
   ArPush push;                // tensor parallel (world > 1): the peers' low-latency slots
   uint32_t vocab_off;
   uint64_t wait_ns;           // limit of every wait inside the kernel
+  uint32_t knobs;             // bit 0: a warp asks its next row group into L2 before it works on the current one; bit 1: phases pull the head of
+                              // a later phase's matrix (StepPhase::pf) into L2
+  unsigned long long *trace;  // NULL, or 8 x {work ns, barrier ns, barriers} summed by CTA 0 per kind of the phase a barrier closes
 };
 
 // Head sizes and cache type the kernel is built for.
@@ -75,7 +80,8 @@ bool step_kernel_supports(uint32_t hd, uint32_t n_head, uint32_t n_kv, int kv_f3
 uint32_t step_kernel_smax(uint32_t n_kv);
 // Bytes of one PH_ARGMAX record times the CTAs of the kernel.
 size_t step_kernel_amax_bytes();
-// One cooperative launch of n_steps steps; a.bar must be zero (the launcher clears it on the stream).
-int step_kernel_launch(const StepArgs &a, uint32_t hd, cudaStream_t st);
+// One cooperative launch of n_steps steps (the launcher clears the arrival counter on the stream). kset: the matrix kinds of
+// the program's GEMVs: 0 Q4_0 only, 1 Q4_K / Q6_K only, 2 any.
+int step_kernel_launch(const StepArgs &a, uint32_t hd, int kset, cudaStream_t st);
 
 }  // namespace ieb

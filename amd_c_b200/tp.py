@@ -49,10 +49,11 @@ class TensorParallelBackend:
         with self.torch.cuda.device(self.dev):
             self.dist.barrier(group=self.group)
 
-    def step(self, tok: int, pos: int) -> int:
-        """backend.step for the sharded model: host token in, host token out (identical on every rank)."""
+    def step(self, tok: int, pos: int, logits=None) -> int:
+        """backend.step for the sharded model: host token in, host token out (identical on every rank). logits: optional
+        float32[vocab / world] that receives this rank's slice of the logits."""
         self._align()
-        return self.b.step(tok, pos)[0]
+        return self.b.step(tok, pos, logits)[0]
 
     def decode(self, tok: int, pos: int, K: int, timed: bool = False):
         """K greedy tokens, the argmax fed back on the device. timed: also return the device milliseconds."""

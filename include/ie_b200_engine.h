@@ -107,14 +107,26 @@ int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_
  * with the failure (the ranks of a tensor-parallel run are back in step: same number of calls made on each), this
  * clears the word. */
 int ie_b200_engine_clear_error(ie_b200_engine *e);
-/* How a one-token step (step, decode) runs. 0 (default): as one persistent cooperative kernel that walks the whole
- * op list with grid barriers between dependent ops -- the role of the reference's megakernel (kernels/ie_mk.c:43-95,
- * recorder src/hip.c:445-566) -- wherever the op list and shapes allow it (half-precision cache, heads of 64 or 128,
- * the llama / qwen2 op patterns), else as a CUDA graph of one kernel per op; 1: always the graph; 2: the kernel, or
- * IE_B200_E_STATE where it cannot run. The environment variable IE_B200_STEP=graph|kernel sets the default.
+/* How a one-token step (step, decode) runs. 1 (default): as a CUDA graph of one kernel per op, chained by programmatic
+ * dependent launch. 2: as ONE persistent cooperative kernel that walks the whole op list with grid barriers between dependent
+ * ops and loops over the K tokens of a decode call by itself -- the role of the reference's megakernel (kernels/ie_mk.c:43-95,
+ * grid barrier kernels/ie_kernels.c:417-463, recorder src/hip.c:445-566); IE_B200_E_STATE where the op list or the shapes have
+ * no program (it needs the half-precision cache, heads of 64 or 128 and the llama / qwen2 op patterns). 0: the kernel where
+ * it can run, else the graph. On B200 the graph is the faster of the two (a kernel boundary under programmatic dependent launch
+ * costs less than a software barrier over 148 CTAs), which is why it is the default; the environment variable
+ * IE_B200_STEP=graph|kernel|auto sets the default of new engines.
  * ie_b200_engine_step_is_kernel: 1 if steps of the current op list run as the persistent kernel. */
 int ie_b200_engine_set_step_mode(ie_b200_engine *e, int mode);
 int ie_b200_engine_step_is_kernel(ie_b200_engine *e);
+/* Where the persistent kernel's time goes: with enable != 0, CTA 0 of the kernel sums, per kind of phase (the PH_* numbering
+ * of the kernel: 0 embed, 1 GEMV, 2 attention, 3 merge, 4 argmax, 5 finish, 6 reduce, 7 argmax exchange), the time it spent
+ * between leaving one grid barrier and arriving at the next (its own work in the phase) and the time between arriving and
+ * leaving (waiting for the slowest CTA). h_ms36 (may be NULL) receives the sums since the last call as 12 x {ms, ms, count}:
+ * entries 0..7 per phase kind {work, barrier wait, barriers}; entries 8..11 the GEMV phases by the way their activations are
+ * staged (8 a Q8 buffer, 9 RMSNorm + Q8, 10 SwiGLU + Q8, 11 kept from the phase before) {staging, rows loop of warp 0, phases}.
+ * Every call clears the sums; enable = 0 switches the record off. The role of the reference's
+ * per-op profile of its megakernel (src/hip.c:1840-1900, IE_PROFILE). */
+int ie_b200_engine_phase_times(ie_b200_engine *e, int enable, double *h_ms36);
 /* Failure injection from the host (for tests of the recovery path; nothing on the GPU faults): raises the abort
  * flag that a CTA of the persistent kernel raises when one of its bounded waits runs out. The next step / decode
  * then ends at once with the device error word set and returns IE_B200_E_DEVICE; ie_b200_engine_clear_error

@@ -48,6 +48,14 @@ int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *
  * the exchange (a multiple of 32, at most max_floats). */
 int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
                                 float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream);
+/* The two halves of ie_b200_gemv_allreduce_norm as calls of their own, for a host that drives several ranks from one
+ * thread (it must launch every rank's GEMV before any rank's reduction, or the first reduction waits for rows nobody has
+ * sent yet) and for tests that run the ranks of a world one after the other on one GPU: ie_b200_gemv_push is the K-split
+ * GEMV that writes its partial to d_part and stores every finished row into the other ranks' slots; ie_b200_ar_reduce_norm
+ * waits for the peers' rows of that exchange (already pushed), adds the partials in rank order onto d_x and normalises. */
+int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part, void *stream);
+int ie_b200_ar_reduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
+                           uint32_t *d_err, void *stream);
 /* The output head split by vocabulary rows: d_result = {local argmax index, its probability within the local
  * slice (f32 bits)} as ie_b200_argmax leaves them, d_logits the local logits. On return d_result = {global
  * index of the largest logit over all ranks (ties: the smaller index), its probability over the whole

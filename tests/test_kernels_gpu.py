@@ -662,11 +662,85 @@ def test_allreduce_missing_rank_gives_up(cuda, lib):
         waited = time.time() - t0
         assert int(err.item()) == 3
         assert 1.5 < waited < 10.0, waited
+        # with the error word up, later stops of the same step do not wait again: each looks once and goes on
+        t0 = time.time()
+        for _ in range(3):
+            K.check(lib.ie_b200_ar_allreduce_norm(hs[0], part.data_ptr(), x.data_ptr(), nw.data_ptr(), 1e-5, xn.data_ptr(), xq.data_ptr(), n,
+                                                  err.data_ptr(), None))
+            K.check(lib.ie_b200_ar_allreduce_add(hs[0], part.data_ptr(), x.data_ptr(), x.data_ptr(), n, err.data_ptr(), None))
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 0.5 and int(err.item()) == 3
         # the context is intact: an ordinary kernel still runs and is right
         y = K.quant_q8(torch.full((1, 32), 2.0, device=cuda)).cpu().numpy()[0]
         assert (y[:32].view(np.int8) == 127).all()
     finally:
         for r in range(2):
+            lib.ie_b200_ar_destroy(hs[r])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world):
+    """The tensor-parallel stop with real partners, the ranks of a world run one after the other on one GPU (their states
+    connected in-process): every rank's K-split GEMV first (each stores its rows into the others' slots and waits for
+    nobody), then every rank's reduction (all rows are there: no kernel waits for a later one). x + p_0 + p_1 + ... in rank
+    order, bit for bit against the oracle's partial GEMVs added in that order on the host; the same bits on every rank;
+    RMSNorm 1e-5 and its Q8 copy exact; twice, so that both slot parities and the epoch hand-over are used."""
+    import ctypes as C
+
+    import torch
+
+    from amd_c_b200 import kernels as K
+    from amd_c_b200.backend import shard_cols
+
+    rows, cols = 512, 256 * world
+    rng = np.random.default_rng(world)
+    raw = synth.q4_0_normal(rng, rows, cols)
+    nw = (1 + 0.1 * rng.standard_normal(rows)).astype(np.float32)
+    hs = (C.c_void_p * world)()
+    for r in range(world):
+        h = C.c_void_p()
+        K.check(lib.ie_b200_ar_create(r, world, rows, C.byref(h)))
+        hs[r] = h
+    try:
+        for r in range(world):
+            K.check(lib.ie_b200_ar_connect_local(hs[r], hs))
+        shards, mats = [], []
+        for r in range(world):
+            sub = np.ascontiguousarray(shard_cols(raw, synth.GGML_Q4_0, rows, cols, r * 256, (r + 1) * 256)).reshape(-1)
+            shards.append(ora.repack(synth.GGML_Q4_0, sub, rows, 256))
+            mats.append(K.Mat.from_gguf(synth.GGML_Q4_0, dev(sub, cuda), rows, 256))
+        d_nw = dev(nw, cuda)
+        err = torch.zeros(1, dtype=torch.int32, device=cuda)
+        x0 = rng.standard_normal(rows).astype(np.float32)
+        d_x = [dev(x0.copy(), cuda) for _ in range(world)]
+        want_x = x0.copy()
+        for rep in range(2):
+            act = rng.standard_normal(cols).astype(np.float32)
+            xqs = [ora.quant_q8(act[r * 256: (r + 1) * 256]) for r in range(world)]
+            d_xq = [dev(q, cuda) for q in xqs]
+            part = [torch.empty(rows, dtype=torch.float32, device=cuda) for _ in range(world)]
+            xn = [torch.empty(rows, dtype=torch.float32, device=cuda) for _ in range(world)]
+            xnq = [torch.empty(40 * (rows // 32), dtype=torch.uint8, device=cuda) for _ in range(world)]
+            for r in range(world):
+                K.check(lib.ie_b200_gemv_push(hs[r], mats[r].kind, mats[r].data.data_ptr(), rows, 256, d_xq[r].data_ptr(), part[r].data_ptr(), None))
+            for r in range(world):
+                K.check(lib.ie_b200_ar_reduce_norm(hs[r], part[r].data_ptr(), d_x[r].data_ptr(), d_nw.data_ptr(), 1e-5, xn[r].data_ptr(),
+                                                   xnq[r].data_ptr(), rows, err.data_ptr(), None))
+            torch.cuda.synchronize()
+            assert int(err.item()) == 0
+            for r in range(world):
+                kind, qw, qs = shards[r]
+                p = ora.gemv(kind, qw, qs, rows, 256, xqs[r])
+                assert (bits(part[r].cpu().numpy()) == bits(p)).all(), (rep, r)
+                want_x = (want_x + p).astype(np.float32)
+            for r in range(world):
+                assert (bits(d_x[r].cpu().numpy()) == bits(want_x)).all(), (rep, r)
+                got_n = xn[r].cpu().numpy()
+                want_n = ora.rmsnorm(want_x, nw, 1e-5)
+                assert np.abs(got_n - want_n).max() <= 1e-5 * np.abs(want_n).max()
+                assert (xnq[r].cpu().numpy() == ora.quant_q8(got_n)).all()
+    finally:
+        for r in range(world):
             lib.ie_b200_ar_destroy(hs[r])
 
 

@@ -1,5 +1,8 @@
-"""Worker of the tensor-parallel GPU test (launched by torch.distributed.run, one process per GPU): decode the
-tiny model sharded over the ranks and compare with the unsharded engine on rank 0's GPU."""
+"""Worker of the tensor-parallel GPU tests (launched by torch.distributed.run, one process per GPU): decode a small
+model sharded over the ranks, in the step mode given as the first argument (graph | kernel), and compare with the
+unsharded engine on rank 0's GPU: the gathered logits of the first steps within 1e-4 of the logit scale (the cross-rank
+sum adds the ranks' partials in rank order instead of one row sum: a different float order, nothing else), the greedy
+tokens identical on every rank and equal to the unsharded engine's wherever its top-two gap allows."""
 import os
 import sys
 from pathlib import Path
@@ -10,37 +13,64 @@ import torch.distributed as dist
 
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 from amd_c_b200 import gguf  # noqa: E402
-from amd_c_b200.backend import Backend, greedy  # noqa: E402
+from amd_c_b200.backend import Backend  # noqa: E402
 from amd_c_b200.tp import TensorParallelBackend  # noqa: E402
 
 
 def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "graph"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', rank))}")
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    cfg = gguf.make_model(gguf.config("tiny"), seed=0)
-    n_ctx, n_gen, prompt = 96, 24, [1, 2, 3]
-    tpb = TensorParallelBackend(Backend(cfg, n_ctx, kv_f32=True, tp=world, rank=rank, device=dev), dist.group.WORLD)
-    tok, ids = prompt[0], list(prompt)
-    for pos in range(len(prompt) - 1):
-        tpb.step(prompt[pos], pos)
-    out = tpb.decode(prompt[-1], len(prompt) - 1, n_gen)
-    ids += [int(t) for t in out]
-    # every rank must hold the same tokens
-    t = torch.tensor(ids, dtype=torch.int64, device=dev)
+    cfg = gguf.make_model(gguf.config("tiny-tp"), seed=0)
+    kv_f32 = mode == "graph"  # the persistent kernel runs on the half cache
+    n_ctx, n_gen, prompt = 160, 40, [1, 2, 3]
+    tpb = TensorParallelBackend(Backend(cfg, n_ctx, kv_f32=kv_f32, tp=world, rank=rank, device=dev, step_mode=mode), dist.group.WORLD)
+    assert tpb.b.step_is_kernel == (mode == "kernel")
+    single = Backend(cfg, n_ctx, kv_f32=kv_f32, device=dev, step_mode=mode) if rank == 0 else None
+    mine = np.zeros(cfg.vocab // world, np.float32)
+    want = np.zeros(cfg.vocab, np.float32)
+    tok, n_checked, worst = prompt[0], 0, 0.0
+    for pos in range(len(prompt) + 12):
+        nxt = tpb.step(tok, pos, mine)
+        parts = [torch.empty(mine.size, dtype=torch.float32, device=dev) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(mine).to(dev))
+        got = torch.cat(parts).cpu().numpy()
+        agree = torch.tensor([nxt], dtype=torch.int64, device=dev)
+        every = [torch.empty_like(agree) for _ in range(world)]
+        dist.all_gather(every, agree)
+        assert all(int(e) == nxt for e in every), "ranks disagree on the token"
+        assert int(np.argmax(got)) == nxt, "the exchanged argmax is not the argmax of the gathered logits"
+        if rank == 0:
+            w_tok, _ = single.step(tok, pos, want)
+            d = float(np.abs(got - want).max()) / float(np.abs(want).max())
+            worst = max(worst, d)
+            # 1e-4 until a rounding flips (see tests/test_model_gpu.py); flips stay in the cache
+            assert d <= (1e-4 if pos < 2 else 3e-2), (pos, d)
+            top2 = np.sort(want)[-2:]
+            if top2[1] - top2[0] > 2 * float(np.abs(got - want).max()):
+                assert nxt == w_tok, pos
+            n_checked += 1
+            nxt = w_tok
+        t = torch.tensor([nxt], dtype=torch.int64, device=dev)
+        dist.broadcast(t, 0)  # teacher-forced by the unsharded engine
+        nxt = int(t.item())
+        tok = prompt[pos + 1] if pos + 1 < len(prompt) else nxt
+    # the device-chained decode: identical tokens on every rank
+    out = tpb.decode(tok, len(prompt) + 12, n_gen)
+    t = torch.tensor([int(x) for x in out], dtype=torch.int64, device=dev)
     gathered = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(gathered, t)
     assert all(torch.equal(gathered[0], g) for g in gathered), "ranks disagree on the decoded tokens"
     if rank == 0:
-        single = Backend(cfg, n_ctx, kv_f32=True, device=dev)
-        want = greedy(single, prompt, n_gen)
+        w = []
+        for i in range(n_gen):
+            tok, _ = single.step(tok, len(prompt) + 12 + i)
+            w.append(tok)
+        common = next((i for i, (a, b) in enumerate(zip(out, w)) if int(a) != int(b)), n_gen)
+        print(f"TP{world} {mode}: logits of {n_checked} steps within {worst:.1e} of the unsharded engine, {common} of {n_gen} chained tokens identical", flush=True)
         single.close()
-        # the cross-rank sum changes the float order of two sums per layer, so a near-tie may flip: require a
-        # long common prefix and report it
-        common = next((i for i, (a, b) in enumerate(zip(ids, want)) if a != b), len(want))
-        print(f"TP{world}: {common} of {len(want)} tokens identical to the unsharded engine", flush=True)
-        assert common >= len(prompt) + 8, (ids, want)
     tpb.close()
     dist.barrier()
     dist.destroy_process_group()
