@@ -29,6 +29,9 @@ SIGNATURES = {
     "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
     "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_gemm": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
+    "ie_b200_gemm_tc_scratch_bytes": (_sz, [_u32, _u32, _u32]),
+    "ie_b200_mat_tc_exp": (_int, [_int, _vp, _u32, _u32, C.POINTER(_int), _vp]),
+    "ie_b200_gemm_tc": (_int, [_int, _vp, _u32, _u32, _int, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp, _sz, _vp, _vp]),
     "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_gemv_norm_tail": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),
@@ -47,6 +50,8 @@ SIGNATURES = {
     "ie_b200_attn_prefill": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_argmax_part_bytes": (_sz, [_u32]),
     "ie_b200_argmax": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp, _vp]),
+    "ie_b200_topk_scratch_bytes": (_sz, [_u32, _u32, _u32]),
+    "ie_b200_topk": (_int, [_vp, _u32, _u32, _u32, _sz, _vp, _vp, _vp, _vp]),
     "ie_b200_argmax_static_max_rows": (_u32, []),
     "ie_b200_argmax_static": (_int, [_vp, _u32, _vp, _u32, _sz, _sz, _vp]),
 }
@@ -88,6 +93,8 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
     "ie_b200_engine_read_rows": (_int, [_vp, _u64, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_copy_rows": (_int, [_vp, _u64, _u32, _u32, _u64, _u32, _u32, _u32, _u32, _int]),
+    "ie_b200_engine_topk": (_int, [_vp, _u64, _u32, _u32, _u32, _u32, _u32, _vp, _vp]),
+    "ie_b200_engine_write_rows": (_int, [_vp, _u64, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_set_collective": (_int, [_vp, _vp, _u32]),
     "ie_b200_engine_set_input": (_int, [_vp, _vp, _u32, _u32, _vp]),
     "ie_b200_engine_enqueue": (_int, [_vp, _u32, _u32, _u32, _vp]),

@@ -2,6 +2,7 @@
 // one GPU; runs a static op list with the kernels of this library. A
 // one-token step is one CUDA-graph launch bracketed by an 8-byte upload
 // (token, position) and an 8-byte download (argmax, probability).
+#include <climits>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -19,6 +20,7 @@ struct EMat {
   uint32_t rows, cols;
   void *d;
   bool owned;
+  int tc_exp = INT32_MIN;  // power-of-two scale of the weights for the tcgen05 GEMM (worked out at first use)
 };
 struct EVec {
   float *d;
@@ -71,6 +73,11 @@ struct ie_b200_engine {
   bool no_attn_fuse = false; // IE_B200_ATTN_FUSE=0: RoPE + KV store as a kernel of its own
   bool no_prefill_attn = false;  // IE_B200_PREFILL_ATTN=0: a chunk's attention through the decode kernel, one CTA set per token
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
+  bool gemm_mma = false;     // IE_B200_GEMM=mma: the int8 mma.sync GEMM instead of the tcgen05 one
+  void *topk_scratch = nullptr;  // candidates and results of ie_b200_engine_topk
+  size_t topk_bytes = 0;
+  void *gemm_scratch = nullptr;  // expanded activations and K-split partials of the tcgen05 GEMM
+  size_t gemm_scratch_bytes = 0;
   int norm_mode = 2;         // IE_B200_NORM: 2 (default) a kernel of its own, 0 "tail": in the producing GEMV's last CTA, 1 "prologue": in the consuming GEMVs
   uint32_t T_att = 1;
   ie_b200_allreduce *ar = nullptr;  // tensor parallel: serves the ALLREDUCE ops and the argmax exchange (not owned)
@@ -141,9 +148,24 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       if (T == 1 && stream_ok(m))
         return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), st);
       // a prompt chunk (the reference's threshold, src/hip.c:965): the tensor-core GEMM reads the weights once per 128 tokens
-      if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm)
+      if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm) {
+        if (!e->gemm_mma && o.a_stride % 16u == 0) {  // tcgen05 / tensor memory
+          EMat &mm = e->mats[o.mat];
+          if (mm.tc_exp == INT32_MIN)
+            if (int r = ie_b200_mat_tc_exp(mm.kind, mm.d, mm.rows, mm.cols, &mm.tc_exp, st)) return r;
+          const size_t need = ie_b200_gemm_tc_scratch_bytes(mm.rows, mm.cols, e->d.T_max);
+          if (need > e->gemm_scratch_bytes) {
+            IEB_CUDA(cudaStreamSynchronize(st));
+            cudaFree(e->gemm_scratch), e->gemm_scratch = nullptr, e->gemm_scratch_bytes = 0;
+            IEB_CUDA(cudaMalloc(&e->gemm_scratch, need));
+            e->gemm_scratch_bytes = need;
+          }
+          return ie_b200_gemm_tc(mm.kind, mm.d, mm.rows, mm.cols, mm.tc_exp, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride,
+                                 o.b_stride, o.res_stride, e->gemm_scratch, e->gemm_scratch_bytes, e->err, st);
+        }
         return ie_b200_gemm(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
                             o.res_stride, st);
+      }
       return ie_b200_gemv(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), T, o.a_stride, o.b_stride,
                           o.res_stride, st);
     }
@@ -355,7 +377,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   chk(cudaMalloc(&e->err, 16), "cudaMalloc(error word)");
   if (rc == IE_B200_OK) chk(cudaMemset(e->err, 0, 16), "cudaMemset");
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
-  if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0';
+  if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0', e->gemm_mma = gm[0] == 'm';
   if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   if (const char *sm = getenv("IE_B200_STEP")) e->step_mode = sm[0] == 'g' ? 1 : sm[0] == 'k' ? 2 : sm[0] == 'a' ? 0 : 1;
@@ -382,6 +404,7 @@ extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
   for (auto &v : e->vecs) cudaFree(v.d);
   cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
   cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
+  cudaFree(e->gemm_scratch), cudaFree(e->topk_scratch);
   cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax), cudaFree(e->sk_bar), cudaFree(e->sk_trace);
   if (e->h_scalars) cudaFreeHost(e->h_scalars);
   if (e->h_result) cudaFreeHost(e->h_result);
@@ -426,7 +449,7 @@ extern "C" int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uin
       return r;
     }
   }
-  e->mats.push_back({kind, rows, cols, dst, true});
+  e->mats.push_back(EMat{kind, rows, cols, dst, true});
   return (int)e->mats.size() - 1;
 }
 
@@ -460,14 +483,14 @@ extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t 
       return r;
     }
   }
-  e->mats.push_back({kind, rows, cols, dst, true});
+  e->mats.push_back(EMat{kind, rows, cols, dst, true});
   return (int)e->mats.size() - 1;
 }
 
 extern "C" int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *d_data) {
   if (!e || !d_data) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: NULL argument");
   if (!aligned16(d_data)) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: the matrix must be 16-byte aligned");
-  e->mats.push_back({kind, rows, cols, const_cast<void *>(d_data), false});
+  e->mats.push_back(EMat{kind, rows, cols, const_cast<void *>(d_data), false});
   return (int)e->mats.size() - 1;
 }
 
@@ -671,6 +694,7 @@ static int build_program(ie_b200_engine *e) {
   e->sk_kset = has_q4 && has_k ? 2 : has_k ? 1 : 0;
   StepArgs &a = e->sk;
   a.smax = step_kernel_smax(d.n_kv);
+  cudaFree(e->gemm_scratch), cudaFree(e->topk_scratch);
   cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax);
   e->d_prog = nullptr, e->sk_part = nullptr, e->sk_amax = nullptr;
   IEB_CUDA(cudaMalloc(&e->d_prog, ph.size() * sizeof(StepPhase)));
@@ -832,6 +856,39 @@ extern "C" int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_
   IEB_CUDA(cudaMemcpyAsync(h_dst, e->arena + lo, len, cudaMemcpyDeviceToHost, e->stream));
   IEB_CUDA(cudaStreamSynchronize(e->stream));
   return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_write_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, const void *h_src) {
+  if (!e || !h_src) return fail(IE_B200_E_ARG, "ie_b200_engine_write_rows: NULL argument");
+  const uint64_t lo = off + (uint64_t)stride * r0, len = (uint64_t)stride * n;
+  if (lo + len > e->d.arena_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_write_rows: rows outside the arena");
+  IEB_CUDA(cudaMemcpyAsync(e->arena + lo, h_src, len, cudaMemcpyHostToDevice, e->stream));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_topk(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, uint32_t nv, uint32_t K, float *h_val,
+                                   uint32_t *h_idx) {
+  if (!e || !h_val || !h_idx) return fail(IE_B200_E_ARG, "ie_b200_engine_topk: NULL argument");
+  if (n == 0) return 1;
+  if (K == 0 || K > 64u || K > nv || (uint64_t)((nv + 2047u) / 2048u) * K > 6144u) return 0;  // the caller selects on the host
+  if (off + (uint64_t)stride * (r0 + n - 1) + (uint64_t)nv * 4u > e->d.arena_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_topk: rows outside the arena");
+  IEB_CUDA(cudaSetDevice(e->device));
+  const size_t need = ie_b200_topk_scratch_bytes(nv, K, n) + (size_t)n * K * 8u;
+  if (need > e->topk_bytes) {
+    IEB_CUDA(cudaStreamSynchronize(e->stream));
+    cudaFree(e->topk_scratch), e->topk_scratch = nullptr, e->topk_bytes = 0;
+    IEB_CUDA(cudaMalloc(&e->topk_scratch, need));
+    e->topk_bytes = need;
+  }
+  float *d_val = static_cast<float *>(e->topk_scratch);
+  uint32_t *d_idx = reinterpret_cast<uint32_t *>(d_val + (size_t)n * K);
+  void *scratch = d_idx + (size_t)n * K;
+  if (int r = ie_b200_topk(reinterpret_cast<const float *>(e->arena + off + (uint64_t)stride * r0), nv, K, n, stride, d_val, d_idx, scratch, e->stream)) return r;
+  IEB_CUDA(cudaMemcpyAsync(h_val, d_val, (size_t)n * K * 4u, cudaMemcpyDeviceToHost, e->stream));
+  IEB_CUDA(cudaMemcpyAsync(h_idx, d_idx, (size_t)n * K * 4u, cudaMemcpyDeviceToHost, e->stream));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  return 1;
 }
 
 extern "C" int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uint32_t dst_stride, uint32_t d0, uint64_t src_off, uint32_t src_stride,

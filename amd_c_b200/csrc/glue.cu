@@ -252,9 +252,95 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const ArgPart *part, u
   }
 }
 
+// ---- top K of a row: K <= 64 largest values, descending, equal values by rising index ----
+// Two launches: every CTA of the first keeps a slice of 2048 values in registers (8 per thread) and takes its K best one at
+// a time (the thread's own best, a shuffle tree over the warp, eight warp winners through shared memory; the owner of the
+// winner strikes it out); the second does the same over the slices' K candidates of a row.
+constexpr int TK_THREADS = 256, TK_SLICE = 2048, TK_MAXK = 64, TK_MERGE_PER = 24;
+constexpr uint32_t TK_NONE = 0xFFFFFFFFu;
+__device__ __forceinline__ bool tk_better(float v, uint32_t i, float bv, uint32_t bi) {
+  return i != TK_NONE && (bi == TK_NONE || v > bv || (v == bv && i < bi));
+}
+template <int PER>
+__device__ __forceinline__ void tk_select(float (&v)[PER], uint32_t (&id)[PER], uint32_t K, float *out_v, uint32_t *out_i) {
+  __shared__ float wv[TK_THREADS / 32];
+  __shared__ uint32_t wi[TK_THREADS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (uint32_t k = 0; k < K; k++) {
+    float bv = 0.0f;
+    uint32_t bi = TK_NONE;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+      if (tk_better(v[j], id[j], bv, bi)) bv = v[j], bi = id[j];
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+      const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      if (tk_better(ov, oi, bv, bi)) bv = ov, bi = oi;
+    }
+    if (lane == 0) wv[warp] = bv, wi[warp] = bi;
+    __syncthreads();
+    bv = wv[0], bi = wi[0];
+#pragma unroll
+    for (int w = 1; w < TK_THREADS / 32; w++)
+      if (tk_better(wv[w], wi[w], bv, bi)) bv = wv[w], bi = wi[w];
+    __syncthreads();
+    if (threadIdx.x == 0) out_v[k] = bi == TK_NONE ? -INFINITY : bv, out_i[k] = bi;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+      if (id[j] == bi) id[j] = TK_NONE;  // indices are unique within a row: only the owner strikes
+  }
+}
+__global__ void __launch_bounds__(TK_THREADS) topk_part_kernel(const float *x, uint32_t nv, size_t xs, uint32_t K, uint32_t ng, float *cv, uint32_t *ci) {
+  pdl_prologue();
+  const uint32_t g = blockIdx.x, t = blockIdx.y;
+  const float *row = row_ptr(x, xs, t);
+  float v[TK_SLICE / TK_THREADS];
+  uint32_t id[TK_SLICE / TK_THREADS];
+#pragma unroll
+  for (int j = 0; j < TK_SLICE / TK_THREADS; j++) {
+    const uint32_t i = g * TK_SLICE + j * TK_THREADS + threadIdx.x;
+    v[j] = i < nv ? row[i] : 0.0f, id[j] = i < nv ? i : TK_NONE;
+  }
+  tk_select(v, id, K, cv + ((size_t)t * ng + g) * K, ci + ((size_t)t * ng + g) * K);
+}
+__global__ void __launch_bounds__(TK_THREADS) topk_merge_kernel(const float *cv, const uint32_t *ci, uint32_t nc, uint32_t K, float *ov, uint32_t *oi) {
+  pdl_prologue();
+  const uint32_t t = blockIdx.x;
+  float v[TK_MERGE_PER];
+  uint32_t id[TK_MERGE_PER];
+#pragma unroll
+  for (int j = 0; j < TK_MERGE_PER; j++) {
+    const uint32_t p = j * TK_THREADS + threadIdx.x;
+    v[j] = p < nc ? cv[(size_t)t * nc + p] : 0.0f, id[j] = p < nc ? ci[(size_t)t * nc + p] : TK_NONE;
+  }
+  tk_select(v, id, K, ov + (size_t)t * K, oi + (size_t)t * K);
+}
+
 }  // namespace ieb
 
 using namespace ieb;
+
+extern "C" size_t ie_b200_topk_scratch_bytes(uint32_t nv, uint32_t K, uint32_t T) {
+  const size_t ng = (nv + TK_SLICE - 1) / TK_SLICE;
+  return (size_t)T * ng * K * 8u + 256u;
+}
+
+extern "C" int ie_b200_topk(const float *d_x, uint32_t nv, uint32_t K, uint32_t T, size_t x_stride, float *d_val, uint32_t *d_idx, void *d_scratch,
+                            void *stream) {
+  if (!d_x || !d_val || !d_idx || !d_scratch) return fail(IE_B200_E_ARG, "ie_b200_topk: NULL pointer");
+  const uint32_t ng = (nv + TK_SLICE - 1) / TK_SLICE;
+  if (K == 0 || K > (uint32_t)TK_MAXK || K > nv || (uint64_t)ng * K > (uint64_t)TK_MERGE_PER * TK_THREADS)
+    return fail(IE_B200_E_SIZE, "ie_b200_topk: K = %u of %u values (1 .. %d, at most %d candidates per row)", K, nv, TK_MAXK, TK_MERGE_PER * TK_THREADS);
+  if (T == 0) return IE_B200_OK;
+  if (T > 65535u) return fail(IE_B200_E_SIZE, "ie_b200_topk: T %u > 65535", T);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float *cv = static_cast<float *>(d_scratch);
+  uint32_t *ci = reinterpret_cast<uint32_t *>(cv + (size_t)T * ng * K);
+  IEB_LAUNCH_PDL("topk_part_kernel", topk_part_kernel, dim3(ng, T), dim3(TK_THREADS), 0, st, d_x, nv, x_stride, K, ng, cv, ci);
+  IEB_LAUNCH_PDL("topk_merge_kernel", topk_merge_kernel, dim3(T), dim3(TK_THREADS), 0, st, static_cast<const float *>(cv), static_cast<const uint32_t *>(ci),
+                 ng * K, K, d_val, d_idx);
+  return IE_B200_OK;
+}
 
 extern "C" int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_t x_stride, size_t q_stride, void *stream) {
   if (!d_x || !d_q) return fail(IE_B200_E_ARG, "ie_b200_quant_q8: NULL pointer");

@@ -5,6 +5,8 @@ call into libie_b200.so on the current torch CUDA stream.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -94,6 +96,25 @@ def gemm(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.T
     rs = 0 if res is None else res.reshape(T, -1).stride(0) * 4
     check(_lib.load().ie_b200_gemm(w.kind, w.data.data_ptr(), w.rows, w.cols, x2.data_ptr(), y.data_ptr(), _p(bias), _p(res), T,
                                    x2.stride(0) * x2.element_size(), w.rows * 4, rs, _stream()))
+    return y
+
+
+def gemm_tc(w: Mat, x: torch.Tensor, bias: torch.Tensor | None = None, res: torch.Tensor | None = None, err: torch.Tensor | None = None) -> torch.Tensor:
+    """The prompt-chunk GEMM on tcgen05 / tensor memory (equal to gemv to fp32 rounding). x: Q8 buffers [T, 40 nb] uint8."""
+    lib = _lib.load()
+    x2 = x.reshape(-1, x.shape[-1])
+    T = x2.shape[0]
+    y = torch.empty((T, w.rows), dtype=torch.float32, device=x.device)
+    rs = 0 if res is None else res.reshape(T, -1).stride(0) * 4
+    nbytes = lib.ie_b200_gemm_tc_scratch_bytes(w.rows, w.cols, T)
+    scratch = torch.empty(nbytes + 256, dtype=torch.uint8, device=x.device)
+    base = (scratch.data_ptr() + 255) // 256 * 256
+    if getattr(w, "tc_exp", None) is None:
+        e = ctypes.c_int(0)
+        check(lib.ie_b200_mat_tc_exp(w.kind, w.data.data_ptr(), w.rows, w.cols, ctypes.byref(e), _stream()))
+        w.tc_exp = e.value
+    check(lib.ie_b200_gemm_tc(w.kind, w.data.data_ptr(), w.rows, w.cols, w.tc_exp, x2.data_ptr(), y.data_ptr(), _p(bias), _p(res), T,
+                              x2.stride(0) * x2.element_size(), w.rows * 4, rs, base, nbytes, _p(err), _stream()))
     return y
 
 
@@ -219,6 +240,18 @@ def attn_prefill(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, pos: torch
     check(_lib.load().ie_b200_attn_prefill(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), _p(oq), pos.data_ptr(), n_head, n_kv, hd,
                                            kc.shape[1], T, q.stride(0) * 4, n_head * hd * 4, q8_bytes(nbq), _stream()))
     return out, oq
+
+
+def topk(x: torch.Tensor, K: int):
+    """x: [T, n] f32 -> (values [T, K], indices [T, K] int32): per row descending, equal values by rising index."""
+    x2 = x.reshape(-1, x.shape[-1])
+    T, n = x2.shape
+    lib = _lib.load()
+    scratch = torch.empty(lib.ie_b200_topk_scratch_bytes(n, K, T), dtype=torch.uint8, device=x.device)
+    val = torch.empty((T, K), dtype=torch.float32, device=x.device)
+    idx = torch.empty((T, K), dtype=torch.int32, device=x.device)
+    check(lib.ie_b200_topk(x2.data_ptr(), n, K, T, x2.stride(0) * 4, val.data_ptr(), idx.data_ptr(), scratch.data_ptr(), _stream()))
+    return val, idx
 
 
 def argmax(x: torch.Tensor) -> torch.Tensor:

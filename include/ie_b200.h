@@ -94,7 +94,8 @@ int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_
 int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_x, float *d_y, const float *d_bias,
                  const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
 
-/* The prompt-chunk GEMM: y[T][rows] = W Q8(x) (+bias) (+res) for T >= 17 tokens with the weights read once
+/* The prompt-chunk GEMM on the int8 mma.sync path (kept beside ie_b200_gemm_tc, which replaced it as the default:
+ * it needs no scratch and takes any alignment): y[T][rows] = W Q8(x) (+bias) (+res) for T >= 17 tokens with the weights read once
  * per 128 tokens; the role of ie_gemm_q4kr / ie_gemm_q6kr (kernels/ie_kernels.c:1315-1465, :2015-2158;
  * dispatch src/hip.c:965-1003), for MAT_Q4 as well. Every 32-weight block dot is one int8 tensor-core product
  * (exact int32, as the reference's MMA trick), scaled in fp32 block after block; the result equals
@@ -102,6 +103,22 @@ int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t cols, const 
  * reference. Same operands as ie_b200_gemv (Q8 buffers per token; strides in bytes, multiples of 4). */
 int ie_b200_gemm(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_y, const float *d_bias,
                  const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *stream);
+
+/* The same GEMM on the tcgen05 tensor cores with the accumulators in tensor memory: the prompt-chunk default. Nothing is
+ * scaled inside the main loop: a pre-pass expands the Q8 rows to f16 pairs x = x_hi + x_lo once per call, producer warps
+ * dequantise each 256-row x 32-column weight block to f16 pairs w = w_hi + w_lo in shared memory, and one thread issues
+ * w_hi x_hi + w_hi x_lo + w_lo x_hi as tcgen05.mma kind::f16 (M 128, N up to 256 tokens, fp32 accumulation over the whole K);
+ * matrices with few rows are split along K, the partial sums added in split order by a second kernel. Equal to ie_b200_gemv
+ * to fp32 rounding. d_scratch: ie_b200_gemm_tc_scratch_bytes() bytes, 256-byte aligned (the expanded activations and the
+ * K-split partials); d_err (may be NULL): set to 5 if a bounded wait inside the kernel ran out. x_stride a multiple of 16.
+ * w_exp: the power of two the weights are scaled by before they are split into half-precision terms, as ie_b200_mat_tc_exp
+ * gives it for the matrix (once, at load time: it reads the matrix's scale fields and synchronises the stream): the largest
+ * possible weight times 2^w_exp stays below 8192, and small weights keep their low term out of the subnormal range. */
+int ie_b200_mat_tc_exp(int kind, const void *d_w, uint32_t rows, uint32_t cols, int *h_exp, void *stream);
+size_t ie_b200_gemm_tc_scratch_bytes(uint32_t rows, uint32_t cols, uint32_t T);
+int ie_b200_gemm_tc(int kind, const void *d_w, uint32_t rows, uint32_t cols, int w_exp, const void *d_xq, float *d_y, const float *d_bias,
+                    const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *d_scratch, size_t scratch_bytes,
+                    uint32_t *d_err, void *stream);
 
 /* The one-token GEMV of a decode step, same result as ie_b200_gemv with T = 1: every warp of a persistent grid
  * streams its rows straight from HBM into registers with 16-byte loads (up to 16 per lane in flight), and the
@@ -214,6 +231,14 @@ int ie_b200_attn_prefill(const float *d_q, const void *d_kc, const void *d_vc, f
 size_t ie_b200_argmax_part_bytes(uint32_t T);
 int ie_b200_argmax(const float *d_x, uint32_t n, uint32_t *d_out, uint32_t T, size_t x_stride, size_t out_stride, void *d_part,
                    void *stream);
+
+/* The K largest values of each of T rows and their indices, per row value descending, equal values smaller index first:
+ * backend.topk (src/backend.h:33-37; ie_topk_part / ie_topk_merge, kernels/ie_kernels.c:4018-4035, launcher src/hip.c:1762-1782).
+ * K <= 64 and at most 6144 candidates per row (K times the 2048-value slices of a row); otherwise IE_B200_E_SIZE, and the
+ * caller selects on the host as the reference does when its backend returns 0. d_val / d_idx: T * K entries;
+ * d_scratch: ie_b200_topk_scratch_bytes() bytes. */
+size_t ie_b200_topk_scratch_bytes(uint32_t nv, uint32_t K, uint32_t T);
+int ie_b200_topk(const float *d_x, uint32_t nv, uint32_t K, uint32_t T, size_t x_stride, float *d_val, uint32_t *d_idx, void *d_scratch, void *stream);
 
 /* ie_b200_argmax for callers that cannot allocate device memory. It has no counterpart in the reference; it
  * exists for hosts that have already committed all device memory (arena and KV cache sized to fill the GPU at

@@ -144,6 +144,13 @@ int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, u
 int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uint32_t dst_stride, uint32_t d0, uint64_t src_off, uint32_t src_stride,
                              uint32_t r0, uint32_t n, uint32_t row_bytes, int zero);
 
+/* backend.topk (src/backend.h:33-37) on arena offsets: the K largest of the first nv floats of n rows from row r0, to the
+ * host; returns 1 if done, 0 if K is too large for the kernel (the caller then selects on the host), negative on an error.
+ * backend.snap's row copy (src/backend.h:42-48) uses read_rows and write_rows: llama / qwen2 keep no state outside the KV
+ * cache, so a snapshot is row 0 of the hbuf buffer, if any. */
+int ie_b200_engine_topk(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, uint32_t nv, uint32_t K, float *h_val, uint32_t *h_idx);
+int ie_b200_engine_write_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, const void *h_src);
+
 /* For callers that interleave their own work (collectives of a tensor-parallel run) with the ops:
  * write token ids and the first position to the device scalars on `stream`, then enqueue ops
  * [first, last) for T tokens on `stream`. OP_ALLREDUCE ops inside the range are skipped. */

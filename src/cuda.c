@@ -33,6 +33,8 @@ typedef struct {
   const graph *g;
   ie_b200_engine *e;
   uint32_t *out_tmp;
+  void *snap_row[2]; /* prompt-cache snapshots: row 0 of the hbuf buffer (llama / qwen2 keep nothing else outside the KV cache) */
+  int snap_buf[2];
 } cuda_backend;
 
 #define CHECK(call)                                                          \
@@ -140,10 +142,41 @@ static void cuda_copy_rows(backend *bk, int dst, uint32_t d0, int src, uint32_t 
   CHECK(ie_b200_engine_copy_rows(B->e, d->off, d->stride, d0, s->off, s->stride, r0, n, bytes, src < 0));
 }
 
+/* backend.topk (src/backend.h:33-37): 1 if done on the GPU, 0 if K is too large (gen.c then selects on the host). */
+static int cuda_topk(backend *bk, int id, uint32_t r0, uint32_t n, uint32_t nv, uint32_t K, float *val, uint32_t *idx) {
+  cuda_backend *B = (cuda_backend *)bk;
+  if (id < 0 || (uint32_t)id >= B->g->n_bufs) ie_die("topk: buffer %d", id);
+  const buf *b = &B->g->bufs[id];
+  const int r = ie_b200_engine_topk(B->e, b->off, b->stride, r0, n, nv, K, val, idx);
+  CHECK(r);
+  return r;
+}
+
+/* backend.snap (src/backend.h:42-48). llama / qwen2 have no linear-attention state and no conv ring: what is not kept per
+ * position is nothing, so a snapshot is row 0 of buffer hbuf (if any), held on the host; the KV caches are not copied. */
+static void cuda_snap(backend *bk, int save, int k, int hbuf) {
+  cuda_backend *B = (cuda_backend *)bk;
+  if (k < 0 || k > 1) ie_die("snap: snapshot %d", k);
+  if (save) {
+    B->snap_buf[k] = hbuf;
+    if (hbuf < 0) return;
+    if ((uint32_t)hbuf >= B->g->n_bufs) ie_die("snap: buffer %d", hbuf);
+    const buf *b = &B->g->bufs[hbuf];
+    B->snap_row[k] = realloc(B->snap_row[k], b->stride ? b->stride : 4);
+    if (!B->snap_row[k]) ie_die("out of memory");
+    CHECK(ie_b200_engine_read_rows(B->e, b->off, b->stride, 0, 1, B->snap_row[k]));
+  } else {
+    const int id = B->snap_buf[k];
+    if (id < 0 || !B->snap_row[k]) return;
+    const buf *b = &B->g->bufs[id];
+    CHECK(ie_b200_engine_write_rows(B->e, b->off, b->stride, 0, 1, B->snap_row[k]));
+  }
+}
+
 static void cuda_close(backend *bk) {
   cuda_backend *B = (cuda_backend *)bk;
   ie_b200_engine_destroy(B->e);
-  free(B->out_tmp);
+  free(B->out_tmp), free(B->snap_row[0]), free(B->snap_row[1]);
   free(B);
 }
 
@@ -227,8 +260,8 @@ backend *gpu_open(const model *m, const graph *g, const char *hsaco) {
   B->out_tmp = calloc(g->T ? g->T : 1, sizeof(uint32_t));
   B->base.step = cuda_step, B->base.close = cuda_close, B->base.run = cuda_run, B->base.accept = cuda_accept;
   B->base.read_rows = cuda_read_rows, B->base.copy_rows = cuda_copy_rows;
-  B->base.topk = NULL; /* sampling falls back to host top-k over read_rows (src/gen.c:57) */
-  B->base.snap = NULL; /* no state outside the KV cache: the prompt cache is off (src/gen.c:566) */
+  B->base.topk = cuda_topk, B->base.snap = cuda_snap;
+  B->snap_buf[0] = B->snap_buf[1] = -1;
   B->base.verify_max = 0;
   fprintf(stderr, "cuda: %u ops, %u matrices, arena %.2f MB, KV %s, weights %.2f MB/token, %u launches/step\n", n, (unsigned)mats.n,
           g->arena / 1e6, d.kv_f32 ? "f32" : "f16", ie_b200_engine_weight_bytes_per_token(B->e) / 1e6, ie_b200_engine_launches_per_step(B->e));

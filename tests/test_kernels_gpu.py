@@ -588,6 +588,62 @@ def test_gemm_matches_gemv(ora, cuda, typ, rows, cols, T):
     assert np.abs(got[t] - ref).max() <= 1e-5 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("typ,rows,cols,T", [(synth.GGML_Q4_0, 256, 256, 17), (synth.GGML_Q4_0, 1000, 4096, 100), (synth.GGML_Q4_K, 3584, 3584, 256),
+                                             (synth.GGML_Q6_K, 512, 1024, 131), (synth.GGML_Q4_K, 96, 512, 40), (synth.GGML_Q4_0, 77, 192, 33),
+                                             (synth.GGML_Q4_0, 130, 320, 20), (synth.GGML_Q4_0, 5000, 4096, 300), (synth.GGML_Q6_K, 300, 18944, 64),
+                                             (synth.GGML_Q4_K, 9000, 3584, 256), (synth.GGML_Q4_0, 1, 64, 1)])
+def test_gemm_tc_matches_gemv(ora, cuda, typ, rows, cols, T):
+    """The prompt-chunk GEMM on tcgen05 / tensor memory (both operands as two half-precision terms, fp32 accumulation over the
+    whole K in tensor memory) against the multi-token GEMV, which is bit-exact with the CPU reference: 1e-5 of the largest
+    output, with bias and residual; ragged rows (the second 128-row tile partly or wholly empty), ragged tokens (N rounded up to
+    16, more than one token tile), K split over several CTAs for matrices of few rows (partials added in split order)."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(rows * 7 + cols + T)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    m = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    x = dev((rng.standard_normal((T, cols)) * rng.choice([1e-3, 1.0, 40.0], size=(T, 1))).astype(np.float32), cuda)
+    xq = K.quant_q8(x)
+    bias = dev(rng.standard_normal(rows).astype(np.float32), cuda)
+    res = dev(rng.standard_normal((T, rows)).astype(np.float32), cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    plain = K.gemv(m, xq).cpu().numpy()
+    got0 = K.gemm_tc(m, xq, err=err).cpu().numpy()
+    assert int(err.item()) == 0
+    # every token row on its own scale (the rows differ by orders of magnitude)
+    for t in range(T):
+        assert np.abs(got0[t] - plain[t]).max() <= 1e-5 * np.abs(plain[t]).max(), t
+    want = K.gemv(m, xq, bias=bias, res=res).cpu().numpy()
+    got = K.gemm_tc(m, xq, bias=bias, res=res, err=err).cpu().numpy()
+    assert int(err.item()) == 0
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    kind, qw, qs = ora.repack(typ, raw, rows, cols)
+    t = T // 2
+    ref = ora.gemv(kind, qw, qs, rows, cols, xq[t].cpu().numpy())
+    assert np.abs(got0[t] - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_gemm_tc_small_and_large_weights(ora, cuda):
+    """Weights far below and above the half-precision sweet spot: the per-matrix power-of-two scale keeps the two-term split
+    exact to 22 bits (Q4_0 scales of 2e-6 and of 300)."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(12)
+    rows, cols, T = 300, 512, 40
+    for sigma in (2e-6, 300.0):
+        raw = synth.q4_0_normal(rng, rows, cols, sigma=sigma)
+        m = K.Mat.from_gguf(synth.GGML_Q4_0, dev(raw, cuda), rows, cols)
+        xq = K.quant_q8(dev(rng.standard_normal((T, cols)).astype(np.float32), cuda))
+        want = K.gemv(m, xq).cpu().numpy()
+        got = K.gemm_tc(m, xq).cpu().numpy()
+        assert np.isfinite(got).all()
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max(), sigma
+
+
 @pytest.mark.parametrize("n_head,n_kv,hd,T,pos0", [(8, 2, 128, 9, 70), (28, 4, 128, 5, 200), (8, 8, 64, 19, 0), (10, 2, 64, 4, 129), (16, 2, 128, 3, 63),
                                                           (24, 8, 128, 11, 100), (12, 2, 64, 7, 300)])
 def test_attention_prefill_chunk(ora, cuda, n_head, n_kv, hd, T, pos0):
@@ -742,6 +798,34 @@ def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world):
     finally:
         for r in range(world):
             lib.ie_b200_ar_destroy(hs[r])
+
+
+@pytest.mark.parametrize("n,K,T", [(1024, 1, 2), (1024, 40, 3), (128256, 64, 2), (152064, 50, 1), (5000, 64, 4), (70, 64, 1)])
+def test_topk(cuda, n, K, T):
+    """The K largest of each row, descending, equal values by rising index (what a stable sort of (-value, index) gives),
+    with many exact ties in the rows (values rounded to a coarse grid) and -inf entries."""
+    import torch
+
+    from amd_c_b200 import kernels as K_
+
+    rng = np.random.default_rng(n + K)
+    x = np.round(rng.standard_normal((T, n)) * 8).astype(np.float32) / 8  # a coarse grid: thousands of equal values
+    x[0, : min(n, 7)] = -np.inf
+    val, idx = K_.topk(dev(x, cuda), K)
+    val, idx = val.cpu().numpy(), idx.cpu().numpy()
+    for t in range(T):
+        order = np.lexsort((np.arange(n), -x[t]))[:K]
+        assert (idx[t] == order).all(), t
+        assert (val[t] == x[t][order]).all(), t
+
+
+def test_topk_refuses_large_k(cuda, lib):
+    import torch
+
+    x = torch.zeros(1, 200000, device=cuda)
+    out = torch.zeros(256, device=cuda)
+    assert lib.ie_b200_topk(x.data_ptr(), 200000, 65, 1, 800000, out.data_ptr(), out.data_ptr(), out.data_ptr(), None) == -2
+    assert lib.ie_b200_topk(x.data_ptr(), 200000, 64, 1, 800000, out.data_ptr(), out.data_ptr(), out.data_ptr(), None) == -2  # 98 slices x 64 candidates
 
 
 def test_swiglu_interleaved_equals_planar(cuda, lib):
