@@ -34,6 +34,8 @@ SIGNATURES = {
     "ie_b200_gemm_tc": (_int, [_int, _vp, _u32, _u32, _int, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp, _sz, _vp, _vp]),
     "ie_b200_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_norm_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ie_b200_gemv_swiglu": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp]),
+    "ie_b200_quant_gemv_stream": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ie_b200_gemv_norm_tail": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp]),
     "ie_b200_block_dots": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp]),
     "ie_b200_embed": (_int, [_int, _vp, _u32, _vp, _vp, _u32, _sz, _vp]),

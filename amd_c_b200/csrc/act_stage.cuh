@@ -12,7 +12,7 @@ namespace ieb {
 struct ActSrc {
   const uint8_t *xq;    // Q8 buffer (NORM = false)
   const float *xf;      // f32 vector (NORM = true)
-  const float *norm_w;
+  const float *norm_w;  // NULL with NORM: no norm, the Q8 quantiser of xf alone (y = x)
   float eps;
   float *xn_out;        // optional outputs of the fused norm
   uint8_t *xq_out;
@@ -48,7 +48,7 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
         float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
         if (own) {
           x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + 16u * tid + j));  // L2: other CTAs may just have written it
-          w4 = *reinterpret_cast<const float4 *>(a.norm_w + 16u * tid + j);
+          if (a.norm_w) w4 = *reinterpret_cast<const float4 *>(a.norm_w + 16u * tid + j);
         }
         x0[j] = x4.x, x0[j + 1] = x4.y, x0[j + 2] = x4.z, x0[j + 3] = x4.w;
         w0[j] = w4.x, w0[j + 1] = w4.y, w0[j + 2] = w4.z, w0[j + 3] = w4.w;
@@ -70,6 +70,7 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
     float tot = lane < WARPS ? red[lane] : 0.0f;
     tot = warp_sum_all(tot);
     const float sc = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)n), a.eps)));
+    const bool plain = a.norm_w == nullptr;
     for (uint32_t k0 = 0; k0 < HB; k0 += NT) {  // uniform trip count: the shuffles below need every lane
       const uint32_t hb = k0 + tid, b = hb >> 1, h = hb & 1u, base = 16u * hb;
       const bool valid = hb < HB;
@@ -78,7 +79,10 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
 #pragma unroll
         for (int j = 0; j < 16; j += 4) {
           float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = x4;
-          if (valid) x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + base + j)), w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
+          if (valid) {
+            x4 = __ldcg(reinterpret_cast<const float4 *>(a.xf + base + j));
+            if (!plain) w4 = *reinterpret_cast<const float4 *>(a.norm_w + base + j);
+          }
           x0[j] = x4.x, x0[j + 1] = x4.y, x0[j + 2] = x4.z, x0[j + 3] = x4.w;
           w0[j] = w4.x, w0[j + 1] = w4.y, w0[j + 2] = w4.z, w0[j + 3] = w4.w;
         }
@@ -86,7 +90,7 @@ __device__ __forceinline__ void stage_activations(const ActSrc &a, uint32_t nb, 
       float amax = 0.0f;
 #pragma unroll
       for (int j = 0; j < 16; j++) {
-        v[j] = __fmul_rn(__fmul_rn(x0[j], sc), w0[j]);
+        v[j] = plain ? x0[j] : __fmul_rn(__fmul_rn(x0[j], sc), w0[j]);
         amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));  // the other half of the block

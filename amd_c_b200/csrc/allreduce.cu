@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   }
   // ---- the sum, in rank order; peers' words are polled in place, up to four peers' loads in flight together.
   // If an earlier kernel of this step already gave up on a peer, one look at the slots is all this one takes.
-  bool gave_up = err && *(volatile uint32_t *)err != 0u;
+  // (the error word is looked at only once a poll has come back empty: nothing on the path of a step that runs well)
+  bool gave_up = false, looked = false;
   const uint64_t t0 = ar_now();
   const unsigned long long *my = s.ll[s.rank] + (size_t)par * s.world * s.max_n;
 #pragma unroll
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
           }
         }
         if (all) break;
+        if (!looked) looked = true, gave_up = err && *(volatile uint32_t *)err != 0u;
         if (gave_up || ar_now() - t0 > AR_WAIT_NS) {
           gave_up = true;
           break;
@@ -388,21 +390,38 @@ extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_pa
   return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 0);
 }
 
-extern "C" int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part, void *stream) {
-  if (!a || !d_w || !d_xq || !d_part) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: NULL argument");
+namespace ieb {
+// The K-split GEMV that pushes its rows, with the activations either a Q8 buffer (act.xq) or an f32 vector quantised in the
+// prologue (act.xf, plain = true).
+int gemv_push_act(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool plain, float *d_part, cudaStream_t st) {
+  if (!a || !d_w || !d_part || !(plain ? (const void *)act.xf : (const void *)act.xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: NULL argument");
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_gemv_push: peers not connected");
   if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: matrix kind %d", kind);
   if (rows == 0 || rows % 32u || rows > a->d.max_n) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u rows (a multiple of 32, at most %u)", rows, a->d.max_n);
   if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u) || cols / 32u > 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u columns", cols);
-  if (!aligned16(d_w) || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: 16-byte alignment");
-  ActSrc act = {};
-  act.xq = static_cast<const uint8_t *>(d_xq);
+  if (!aligned16(d_w) || !aligned16(plain ? (const void *)act.xf : (const void *)act.xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: 16-byte alignment");
   ArPush push;
   ar_push_info(a, &push);
   // the GEMV releases its dependents only after its own dependency wait: when the reduction kernel starts, everything
   // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
-  return gemv_direct(kind, d_w, rows, cols, act, false, d_part, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &push, true);
+  return gemv_direct(kind, d_w, rows, cols, act, plain, d_part, nullptr, nullptr, nullptr, nullptr, st, &push, true);
 }
+int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
+                       uint32_t *d_err, cudaStream_t st);
+}  // namespace ieb
+
+extern "C" int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part, void *stream) {
+  ActSrc act0 = {};
+  act0.xq = static_cast<const uint8_t *>(d_xq);
+  return gemv_push_act(a, kind, d_w, rows, cols, act0, false, d_part, static_cast<cudaStream_t>(stream));
+}
+
+namespace ieb {
+int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
+                       uint32_t *d_err, cudaStream_t st) {
+  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, st, 1, 1);
+}
+}  // namespace ieb
 
 extern "C" int ie_b200_ar_reduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
                                       uint32_t n, uint32_t *d_err, void *stream) {

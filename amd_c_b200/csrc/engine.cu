@@ -74,6 +74,9 @@ struct ie_b200_engine {
   bool no_prefill_attn = false;  // IE_B200_PREFILL_ATTN=0: a chunk's attention through the decode kernel, one CTA set per token
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   bool gemm_mma = false;     // IE_B200_GEMM=mma: the int8 mma.sync GEMM instead of the tcgen05 one
+  int swi_epi = -1;          // IE_B200_SWIGLU=gemv|kernel: SwiGLU in the gate / up GEMV's epilogue and the Q8 quantiser in the down GEMV's
+                             // prologue (one launch less per layer), or a kernel of its own; -1: in the GEMV for a tensor-parallel shard
+                             // (small vectors, launch-bound), its own kernel on one GPU (where the prologue's extra L2 reads cost more)
   void *topk_scratch = nullptr;  // candidates and results of ie_b200_engine_topk
   size_t topk_bytes = 0;
   void *gemm_scratch = nullptr;  // expanded activations and K-split partials of the tcgen05 GEMM
@@ -108,6 +111,9 @@ static inline void *at(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_
 }
 
 namespace ieb {
+int gemv_push_act(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool plain, float *d_part, cudaStream_t st);
+int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
+                       uint32_t *d_err, cudaStream_t st);  // allreduce.cu
 void ar_push_info(const ie_b200_allreduce *a, ArPush *out);  // allreduce.cu
 bool ar_connected(const ie_b200_allreduce *a);
 int attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin, float *d_out,
@@ -206,6 +212,15 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
     }
     case IE_B200_OP_ALLREDUCE: {
       if (!e->ar) return IE_B200_OK;  // no collective attached: the caller serves these stops between enqueue calls
+      // a prompt chunk whose token rows lie back to back: one exchange over T x n floats (the state's buffers permitting)
+      if (T > 1 && o.a_stride == o.n * 4u && o.c_stride == o.n * 4u) {
+        ArPush info;
+        ar_push_info(e->ar, &info);
+        if ((uint64_t)o.n * T <= info.max_n) {
+          float *x = static_cast<float *>(at(e, o.c, o.c_stride, t0));
+          return ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0)), x, x, o.n * T, e->err, st);
+        }
+      }
       for (uint32_t t = 0; t < T; t++) {
         float *x = static_cast<float *>(at(e, o.c, o.c_stride, t0 + t));
         if (int r = ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0 + t)), x, x, o.n, e->err, st)) return r;
@@ -235,11 +250,52 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
   // The fused attention kernel reads the position and older cache rows ahead of its dependency wait when the
   // kernel launched right before it is a decode GEMV told to release its dependents only after its own wait.
   bool prev_late = false;
+  const bool swi_epi = T == 1 && e->swi_epi == 1 && (kind_mask & (1u << IE_B200_OP_SWIGLU)) && (kind_mask & (1u << IE_B200_OP_GEMV));
+  uint64_t h_q8 = IE_B200_NONE, h_f32 = IE_B200_NONE;  // the Q8 buffer a skipped SWIGLU op would have written, and the f32 vector that stands for it
   for (uint32_t i = first; i < last; i++) {
     const ie_b200_op &o = e->ops[i];
     if (!(kind_mask & (1u << o.kind))) continue;
     const bool was_late = prev_late;
     prev_late = false;
+    // gate / up GEMV over interleaved rows: SwiGLU in its epilogue (a warp owns a pair), the op after it is skipped
+    if (swi_epi && o.kind == IE_B200_OP_GEMV && i + 2 < last && o.mat >= 0 && stream_ok(e->mats[o.mat]) && o.vec < 0 && o.res == IE_B200_NONE) {
+      const ie_b200_op &sw = e->ops[i + 1], &dn = e->ops[i + 2];
+      const EMat &m = e->mats[o.mat];
+      if (sw.kind == IE_B200_OP_SWIGLU && sw.nh == 1u && sw.a == o.b && sw.qo != IE_B200_NONE && sw.b != IE_B200_NONE && m.rows == 2u * sw.n && sw.n % 32u == 0 &&
+          dn.kind == IE_B200_OP_GEMV && dn.a == sw.qo && dn.mat >= 0 && stream_ok(e->mats[dn.mat]) && e->mats[dn.mat].cols == sw.n) {
+        ActSrc act = {};
+        act.xq = static_cast<const uint8_t *>(at(e, o.a, 0, 0));
+        if (int r = gemv_direct(m.kind, m.d, m.rows, m.cols, act, false, static_cast<float *>(at(e, sw.b, 0, 0)), nullptr, nullptr, nullptr, nullptr, st, nullptr,
+                                false, true))
+          return r;
+        h_q8 = sw.qo, h_f32 = sw.b;
+        i++;
+        continue;
+      }
+    }
+    // the GEMV that reads the skipped op's Q8 buffer: it quantises the f32 vector in its own prologue (CTA 0 also writes the Q8 buffer)
+    if (T == 1 && h_q8 != IE_B200_NONE && o.kind == IE_B200_OP_GEMV && o.a == h_q8) {
+      const EMat &m = e->mats[o.mat];
+      ActSrc act = {};
+      act.xf = static_cast<const float *>(at(e, h_f32, 0, 0)), act.xq_out = static_cast<uint8_t *>(at(e, h_q8, 0, 0));
+      h_q8 = IE_B200_NONE;
+      if (e->ar && i + 2 < last && o.vec < 0 && o.res == IE_B200_NONE && (kind_mask & (1u << IE_B200_OP_ALLREDUCE)) && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
+        const ie_b200_op &ar = e->ops[i + 1], &nx = e->ops[i + 2];
+        if (ar.kind == IE_B200_OP_ALLREDUCE && ar.a == o.b && ar.n == m.rows && nx.kind == IE_B200_OP_RMSNORM && nx.a == ar.c && nx.res == IE_B200_NONE &&
+            nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
+          if (int r = gemv_push_act(e->ar, m.kind, m.d, m.rows, m.cols, act, true, static_cast<float *>(at(e, o.b, 0, 0)), st)) return r;
+          if (int r = ar_norm_after_push(e->ar, static_cast<float *>(at(e, o.b, 0, 0)), static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
+                                         static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), m.rows, e->err, st))
+            return r;
+          i += 2;
+          continue;
+        }
+      }
+      if (int r = gemv_direct(m.kind, m.d, m.rows, m.cols, act, true, static_cast<float *>(at(e, o.b, 0, 0)), o.vec >= 0 ? e->vecs[o.vec].d : nullptr,
+                              static_cast<float *>(at(e, o.res, 0, 0)), nullptr, nullptr, st))
+        return r;
+      continue;
+    }
     if (T == 1 && o.kind == IE_B200_OP_GEMV && o.mat >= 0 && (size_t)o.mat < e->mats.size() && stream_ok(e->mats[o.mat]) && rope_fuses(i + 1)) {
       const EMat &m = e->mats[o.mat];
       ActSrc act = {};
@@ -379,6 +435,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   if (const char *af = getenv("IE_B200_ATTN_FUSE")) e->no_attn_fuse = af[0] == '0';
   if (const char *gm = getenv("IE_B200_GEMM")) e->no_gemm = gm[0] == '0', e->gemm_mma = gm[0] == 'm';
   if (const char *pa = getenv("IE_B200_PREFILL_ATTN")) e->no_prefill_attn = pa[0] == '0';
+  if (const char *sw = getenv("IE_B200_SWIGLU")) e->swi_epi = sw[0] == 'g' ? 1 : sw[0] == 'k' ? 0 : -1;
   if (const char *nm = getenv("IE_B200_NORM")) e->norm_mode = nm[0] == 'p' ? 1 : nm[0] == 't' ? 0 : 2;
   if (const char *sm = getenv("IE_B200_STEP")) e->step_mode = sm[0] == 'g' ? 1 : sm[0] == 'k' ? 2 : sm[0] == 'a' ? 0 : 1;
   chk(cudaMalloc(&e->sk_bar, 8), "cudaMalloc(barrier words)");

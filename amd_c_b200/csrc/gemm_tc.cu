@@ -8,13 +8,13 @@
 // whole K in tensor memory:
 //   activations  a pre-pass expands each token's Q8 row to x = d_a * q (f32) and splits it into two f16 terms
 //                x = x_hi + x_lo (22 significant bits), stored in the order the MMA wants (cost ~ T x K, once per chunk);
-//   weights      four producer warps dequantise the CTA's 256 rows of the current 32-column block (d (q - 8); d sc q -
+//   weights      sixteen producer warps dequantise the CTA's 256 rows of the current 32-column block (d (q - 8); d sc q -
 //                dmin mn; d sc (q - 32)) to f32 and split them the same way, w = w_hi + w_lo, straight into shared
 //                memory in the canonical K-major core-matrix layout (cost ~ rows x K, once per 256 tokens);
 //   MMA          one thread issues, per 16 columns, w_hi x_hi + w_hi x_lo + w_lo x_hi (the dropped w_lo x_lo term is
 //                below 2^-22 of a product) as tcgen05.mma kind::f16, M = 128, N = up to 256 tokens, two 128-row tiles per
 //                CTA, accumulators in tensor memory (2 x 256 columns);
-//   epilogue     the producer warps read the accumulators back (tcgen05.ld, one row per thread), add bias / residual
+//   epilogue     the producer warps read the accumulators back (tcgen05.ld, one row and 128 tokens per thread), add bias / residual
 //                and store token rows (32 consecutive rows per warp store: coalesced).
 // A three-stage ring (64 KB per stage: 32 KB of weights, 32 KB of activations brought by one bulk copy) is handed over
 // through mbarriers; tcgen05.commit frees a stage when the MMAs that read it have completed. Matrices with few rows
@@ -37,7 +37,7 @@
 
 namespace ieb {
 
-constexpr int TC_ROWS = 256, TC_TOK = 256, TC_KS = 32, TC_STAGES = 3, TC_THREADS = 192;
+constexpr int TC_ROWS = 256, TC_TOK = 256, TC_KS = 32, TC_STAGES = 3, TC_PROD_WARPS = 16, TC_THREADS = (TC_PROD_WARPS + 2) * 32;
 constexpr int TC_A_TILE = 128 * TC_KS * 2;       // one 128-row tile, one f16 term, one stage: 8 KB
 constexpr int TC_A_STAGE = 4 * TC_A_TILE;        // two tiles x (hi, lo)
 constexpr int TC_B_TERM = TC_TOK * TC_KS * 2;    // 16 KB
@@ -201,14 +201,12 @@ struct TcBlk<IE_B200_MAT_Q4> {
     w = __ldg(reinterpret_cast<const uint4 *>(rp + 16u * (size_t)b));
     d = __ldg(reinterpret_cast<const uint16_t *>(rp + 16u * (size_t)nb + 2u * b));
   }
-  __device__ __forceinline__ void values(float (&f)[32], uint32_t) const {
+  // columns 16 hf .. 16 hf + 15 of the block: the low (hf = 0) or high nibbles of the four words
+  __device__ __forceinline__ void values16(float (&f)[16], uint32_t, uint32_t hf) const {
     const float df = h2f(d);
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t ww[4] = {w.x >> (4u * hf), w.y >> (4u * hf), w.z >> (4u * hf), w.w >> (4u * hf)};
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      const int q = (int)((ww[(j & 15) >> 2] >> (8 * (j & 3) + 4 * (j >> 4))) & 15u);
-      f[j] = __fmul_rn(df, (float)(q - 8));
-    }
+    for (int j = 0; j < 16; j++) f[j] = __fmul_rn(df, (float)((int)((ww[j >> 2] >> (8 * (j & 3))) & 15u) - 8));
   }
 };
 template <>
@@ -218,16 +216,13 @@ struct TcBlk<IE_B200_MAT_Q4K> {
     w = __ldg(reinterpret_cast<const uint4 *>(rp + 16u * (size_t)b));
     h = __ldg(reinterpret_cast<const uint4 *>(rp + 16u * (size_t)nb + 16u * (b >> 3)));
   }
-  __device__ __forceinline__ void values(float (&f)[32], uint32_t b) const {
+  __device__ __forceinline__ void values16(float (&f)[16], uint32_t b, uint32_t hf) const {
     const uint32_t fld = q4k_field(h, (int)(b & 7u));
     const float s = __fmul_rn(h2f((uint16_t)(h.x & 0xFFFFu)), (float)(fld & 63u));
     const float mm = __fmul_rn(h2f((uint16_t)(h.x >> 16)), (float)(fld >> 6));
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t ww[4] = {w.x >> (4u * hf), w.y >> (4u * hf), w.z >> (4u * hf), w.w >> (4u * hf)};
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      const int q = (int)((ww[(j & 15) >> 2] >> (8 * (j & 3) + 4 * (j >> 4))) & 15u);
-      f[j] = __fmaf_rn(s, (float)q, -mm);
-    }
+    for (int j = 0; j < 16; j++) f[j] = __fmaf_rn(s, (float)((ww[j >> 2] >> (8 * (j & 3))) & 15u), -mm);
   }
 };
 template <>
@@ -241,16 +236,15 @@ struct TcBlk<IE_B200_MAT_Q6K> {
     sc = __ldg(reinterpret_cast<const uint16_t *>(rp + 24u * (size_t)nb + 2u * b));
     d = __ldg(reinterpret_cast<const uint16_t *>(rp + 26u * (size_t)nb + 2u * (b >> 3)));
   }
-  __device__ __forceinline__ void values(float (&f)[32], uint32_t) const {
-    const float df = h2f(d);
-    const float s[2] = {__fmul_rn(df, (float)(int8_t)(sc & 255u)), __fmul_rn(df, (float)(int8_t)(sc >> 8))};
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w}, hh[2] = {hw.x, hw.y};
+  __device__ __forceinline__ void values16(float (&f)[16], uint32_t, uint32_t hf) const {
+    const float s = __fmul_rn(h2f(d), (float)(int8_t)(hf ? sc >> 8 : sc & 255u));
+    const uint32_t ww[4] = {w.x >> (4u * hf), w.y >> (4u * hf), w.z >> (4u * hf), w.w >> (4u * hf)}, hh = hf ? hw.y : hw.x;
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      // weight j = 16 h + 4 k + i: low nibble / high nibble h of byte i of word k; its two high bits at bits 8 i + 2 k of hw[h]
-      const int h = j >> 4, k = (j & 15) >> 2, i = j & 3;
-      const uint32_t lo4 = (ww[k] >> (8 * i + 4 * h)) & 15u, hi2 = (hh[h] >> (8 * i + 2 * k)) & 3u;
-      f[j] = __fmul_rn(s[h], (float)((int)(lo4 | (hi2 << 4)) - 32));
+    for (int j = 0; j < 16; j++) {
+      // weight 16 hf + 4 k + i: nibble hf of byte i of word k; its two high bits at bits 8 i + 2 k of the half's high-bit word
+      const int k = j >> 2, i = j & 3;
+      const uint32_t lo4 = (ww[k] >> (8 * i)) & 15u, hi2 = (hh >> (8 * i + 2 * k)) & 3u;
+      f[j] = __fmul_rn(s, (float)((int)(lo4 | (hi2 << 4)) - 32));
     }
   }
 };
@@ -273,11 +267,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
   if (tid == 0) {
     s_abort = 0u;
-    for (int s = 0; s < TC_STAGES; s++) mbar_init(&full_a[s], 4u), mbar_init(&full_b[s], 1u), mbar_init(&empty[s], 1u);
+    for (int s = 0; s < TC_STAGES; s++) mbar_init(&full_a[s], (uint32_t)TC_PROD_WARPS), mbar_init(&full_b[s], 1u), mbar_init(&empty[s], 1u);
     mbar_init(done, 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {  // tensor memory: all 512 columns (two accumulators of up to 256 columns), by one warp
+  if (warp == TC_PROD_WARPS) {  // tensor memory: all 512 columns (two accumulators of up to 256 columns), by one warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -290,59 +284,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   for (uint32_t j = tid; j < TC_TOK; j += TC_THREADS) s_inv[j] = nt * TC_TOK + j < a.T ? a.tok_inv[nt * TC_TOK + j] : 0.0f;
   __syncthreads();
 
-  if (warp < 4) {
-    // ---------------- producers: dequantise rows m0 + tid and m0 + 128 + tid, block by block ----------------
-    const uint32_t rl = (uint32_t)tid;  // row within the tile
-    const bool ok0 = m0 + rl < a.rows, ok1 = m0 + 128u + rl < a.rows;
-    const uint8_t *rp0 = a.w + (size_t)(m0 + rl) * a.rowb, *rp1 = a.w + (size_t)(m0 + 128u + rl) * a.rowb;
-    TcBlk<KIND> cur[2], nxt[2];
-    if (n_it) {
-      if (ok0) cur[0].load(rp0, kb0, a.nb);
-      if (ok1) cur[1].load(rp1, kb0, a.nb);
+  if (warp < TC_PROD_WARPS) {
+    // ---------------- producers: warp w dequantises half h = w & 1 (16 columns) of the block for 32 rows of tile w >> 3 ----------------
+    // (16 warps of one half block per thread: four warps per scheduler hide the conversion latency behind each other; with
+    // four warps of two whole blocks per thread the tensor pipe waited for the producers)
+    const uint32_t t = (uint32_t)warp >> 3, hf = (uint32_t)warp & 1u, rl = (((uint32_t)warp >> 1) & 3u) * 32u + lane;  // tile, column half, row in the tile
+    const bool ok = m0 + t * 128u + rl < a.rows;
+    const uint8_t *rp = a.w + (size_t)(m0 + t * 128u + rl) * a.rowb;
+    TcBlk<KIND> cur, nxt, nx2;  // the blocks of this stage and of the two after it: their bytes are on the way while this one is converted
+    if (ok) {
+      if (n_it > 0u) cur.load(rp, kb0, a.nb);
+      if (n_it > 1u) nxt.load(rp, kb0 + 1u, a.nb);
     }
     for (uint32_t it = 0; it < n_it; it++) {
       const uint32_t s = it % TC_STAGES, round = it / TC_STAGES, b = kb0 + it;
-      if (it + 1u < n_it) {  // the next block's bytes travel while this one is converted
-        if (ok0) nxt[0].load(rp0, b + 1u, a.nb);
-        if (ok1) nxt[1].load(rp1, b + 1u, a.nb);
-      }
+      if (it + 2u < n_it && ok) nx2.load(rp, b + 2u, a.nb);
       if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u, &s_abort)) break;
+      float f[16];
+      if (ok) {
+        cur.values16(f, b, hf);
 #pragma unroll
-      for (int t = 0; t < 2; t++) {
-        float f[32];
-        if (t == 0 ? ok0 : ok1) {
-          cur[t].values(f, b);
+        for (int j = 0; j < 16; j++) f[j] = __fmul_rn(f[j], a.w_scale);  // exact: a power of two
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; j++) f[j] = __fmul_rn(f[j], a.w_scale);  // exact: a power of two
-        } else {
+        for (int j = 0; j < 16; j++) f[j] = 0.0f;
+      }
+      uint8_t *dst = sA + s * TC_A_STAGE + t * 2 * TC_A_TILE + (rl >> 3) * 128u + (rl & 7u) * 16u + hf * 2u * 2048u;
 #pragma unroll
-          for (int j = 0; j < 32; j++) f[j] = 0.0f;
-        }
-        uint8_t *dst = sA + s * TC_A_STAGE + t * 2 * TC_A_TILE + (rl >> 3) * 128u + (rl & 7u) * 16u;
+      for (int c = 0; c < 2; c++) {  // 8-column chunks 2 hf + c of the block
+        uint32_t h[4], l[4];
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          uint32_t h[4], l[4];
-#pragma unroll
-          for (int p = 0; p < 4; p++) tc_split2(f[8 * c + 2 * p], f[8 * c + 2 * p + 1], h[p], l[p]);
-          *reinterpret_cast<uint4 *>(dst + c * 2048u) = make_uint4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<uint4 *>(dst + TC_A_TILE + c * 2048u) = make_uint4(l[0], l[1], l[2], l[3]);
-        }
+        for (int p = 0; p < 4; p++) tc_split2(f[8 * c + 2 * p], f[8 * c + 2 * p + 1], h[p], l[p]);
+        *reinterpret_cast<uint4 *>(dst + c * 2048u) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4 *>(dst + TC_A_TILE + c * 2048u) = make_uint4(l[0], l[1], l[2], l[3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read shared memory through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
-      cur[0] = nxt[0], cur[1] = nxt[1];
+      cur = nxt, nxt = nx2;
     }
     // ---------------- epilogue: accumulators -> token rows ----------------
     const bool finished = mbar_wait(done, 0u, &s_abort);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (finished && !s_abort) {
-      for (uint32_t t = 0; t < n_tiles; t++) {
-        const uint32_t row = m0 + t * 128u + (uint32_t)warp * 32u + lane;
-        const float bias = (a.bias && row < a.rows && !a.partial) ? a.bias[row] : 0.0f;
-        for (uint32_t c0 = 0; c0 < n_eff; c0 += 32u) {
+      // warp w reads lanes 32 (w & 3) .. + 31 of tensor memory (a warp reaches the quarter w mod 4 only): tile (w >> 2) & 1,
+      // token columns [128 (w >> 3), + 128)
+      const uint32_t q = (uint32_t)warp & 3u, te = ((uint32_t)warp >> 2) & 1u, ch = (uint32_t)warp >> 3;
+      const uint32_t row = m0 + te * 128u + q * 32u + lane;
+      const float bias = (a.bias && row < a.rows && !a.partial) ? a.bias[row] : 0.0f;
+      if (te < n_tiles) {
+        for (uint32_t c0 = ch * 128u; c0 < min(n_eff, ch * 128u + 128u); c0 += 32u) {
           uint32_t v[32];
-          tc_ld32(tmem + (((uint32_t)warp * 32u) << 16) + t * TC_TOK + c0, v);
+          tc_ld32(tmem + ((q * 32u) << 16) + te * TC_TOK + c0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (row < a.rows) {
 #pragma unroll
@@ -363,7 +356,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == TC_PROD_WARPS) {
     // ---------------- MMA issue: one thread ----------------
     if (lane == 0) {
       // instruction descriptor: D f32, A and B f16, both K-major, N = n_eff, M = 128
@@ -416,7 +409,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   __syncthreads();
   if (tid == 0 && s_abort && a.err) atomicExch(a.err, 5u);
   __syncwarp();
-  if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  if (warp == TC_PROD_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
 // y[n][row] = sum over the splits (in order) of partial[split][n][row] (+ bias) (+ res).

@@ -42,6 +42,7 @@ struct GdArgs {
                       // everything older than this kernel has completed
   uint32_t *work;     // two words, zero between launches; word 1 counts the CTAs that have finished (norm tail only)
   ArPush push;        // TP kernels only: every finished row also goes to the other ranks' slots
+  uint32_t swi;       // rows are interleaved (gate_i, up_i) pairs (two rows per warp): y[i] = silu(gate_i) * up_i instead of the rows
 };
 
 // R rows of one warp, U lane steps (blocks l, l+32, ... of each row) per chunk: R x U 16-byte loads per lane
@@ -83,7 +84,8 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
 
   // the norm weights (a constant vector) into L2 while waiting: the norm after the wait then pays one L2 round trip
   if (NORM) {
-    for (uint32_t i = 32u * threadIdx.x; i < 32u * nb; i += 32u * GD_THREADS) prefetch_l2(a.act.norm_w + i);
+    if (a.act.norm_w)
+      for (uint32_t i = 32u * threadIdx.x; i < 32u * nb; i += 32u * GD_THREADS) prefetch_l2(a.act.norm_w + i);
   } else if (a.tail.norm_w && blockIdx.x == 0) {
     for (uint32_t i = 32u * threadIdx.x; i < a.rows; i += 32u * GD_THREADS) prefetch_l2(a.tail.norm_w + i);
   }
@@ -111,6 +113,13 @@ __global__ void __launch_bounds__(GD_THREADS, MINB) gemv_direct_kernel(const GdA
     float v[R];
 #pragma unroll
     for (int i = 0; i < R; i++) v[i] = warp_tree(acc[i]);
+    if (R == 2 && a.swi) {  // the SwiGLU kernel's arithmetic on the pair this warp owns
+      if (lane == 0 && rr + 1 < r_hi) {
+        const float g = v[0];
+        a.y[rr >> 1] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), v[R - 1]);
+      }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < R; i++) {
       if (lane == 0 && rr + i < r_hi) {
@@ -191,7 +200,7 @@ static int launch_direct(const GdArgs &a, cudaStream_t st) {
 template <int KIND, bool NORM, bool TP>
 static int pick_direct(const GdArgs &a, cudaStream_t st) {
   constexpr int U2 = KIND == IE_B200_MAT_Q4 ? 4 : 2;
-  const bool few_long = a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
+  const bool few_long = !a.swi && a.nb >= 256u && (uint64_t)a.rows * 2u <= (uint64_t)sm_count() * 3u * GD_WARPS * 4u;
   if (few_long) return launch_direct<KIND, NORM, 1, 4 * U2, 2, TP>(a, st);  // Q4_0: 16 lane steps = rows of up to 512 blocks in one chunk
   return launch_direct<KIND, NORM, 2, U2, 3, TP>(a, st);
 }
@@ -207,17 +216,21 @@ int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
 }
 
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push, bool late_trigger) {
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push, bool late_trigger, bool swiglu_pairs) {
   GdArgs a = {};
   a.late = late_trigger ? 1u : 0u;
+  if (swiglu_pairs) {
+    if (tail || push || d_bias || d_res || rows % 2u) return fail(IE_B200_E_ARG, "gemv_direct: the SwiGLU form takes interleaved gate / up rows, no bias, residual or tail");
+    a.swi = 1u;
+  }
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = cols / 32u;
   a.act = act, a.y = d_y, a.bias = d_bias, a.res = d_res;
   a.work = work;
   if (tail) a.tail = *tail, a.tail.xf = d_y;
   if (push) {
-    if (norm || tail || d_bias || d_res) return fail(IE_B200_E_ARG, "gemv_direct: a tensor-parallel partial takes no norm, bias or residual");
+    if ((norm && act.norm_w) || tail || d_bias || d_res) return fail(IE_B200_E_ARG, "gemv_direct: a tensor-parallel partial takes no norm, bias or residual");
     a.push = *push;
-    return dispatch_direct<false, true>(kind, a, st);
+    return norm ? dispatch_direct<true, true>(kind, a, st) : dispatch_direct<false, true>(kind, a, st);
   }
   return norm ? dispatch_direct<true, false>(kind, a, st) : dispatch_direct<false, false>(kind, a, st);
 }
@@ -258,6 +271,25 @@ extern "C" int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows
   if (rows == 0) return IE_B200_OK;
   ActSrc act = {};
   act.xf = d_x, act.norm_w = d_norm_w, act.eps = eps, act.xn_out = d_xn_out, act.xq_out = static_cast<uint8_t *>(d_xq_out);
+  return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ie_b200_gemv_swiglu(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_h, void *stream) {
+  if (int e = check_common("ie_b200_gemv_swiglu", kind, d_w, rows, cols, d_h)) return e;
+  if (!d_xq || !aligned16(d_xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_swiglu: activations must be a 16-byte aligned Q8 buffer");
+  if (rows == 0) return IE_B200_OK;
+  ActSrc act = {};
+  act.xq = static_cast<const uint8_t *>(d_xq);
+  return gemv_direct(kind, d_w, rows, cols, act, false, d_h, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), nullptr, false, true);
+}
+
+extern "C" int ie_b200_quant_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, void *d_xq_out, float *d_y,
+                                         const float *d_bias, const float *d_res, void *stream) {
+  if (int e = check_common("ie_b200_quant_gemv_stream", kind, d_w, rows, cols, d_y)) return e;
+  if (!d_x || !aligned16(d_x)) return fail(IE_B200_E_ARG, "ie_b200_quant_gemv_stream: the vector must be 16-byte aligned");
+  if (rows == 0) return IE_B200_OK;
+  ActSrc act = {};
+  act.xf = d_x, act.norm_w = nullptr, act.eps = 0.0f, act.xq_out = static_cast<uint8_t *>(d_xq_out);
   return gemv_direct(kind, d_w, rows, cols, act, true, d_y, d_bias, d_res, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 

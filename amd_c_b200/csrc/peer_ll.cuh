@@ -70,9 +70,11 @@ struct ArPush {
 
 // The direct decode GEMV (gemv_direct.cu). tail: RMSNorm + Q8 of the finished vector by the last CTA; push (no
 // tail / bias / res): a tensor-parallel partial whose rows are also stored into the other ranks' slots;
-// late_trigger: the kernel lets its dependents start only after its own dependency wait.
+// late_trigger: the kernel lets its dependents start only after its own dependency wait; swiglu_pairs: the rows are
+// interleaved (gate_i, up_i) pairs and d_y receives silu(gate_i) * up_i (rows / 2 values).
 int gemv_direct(int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool norm, float *d_y, const float *d_bias,
-                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push = nullptr, bool late_trigger = false);
+                const float *d_res, const ActSrc *tail, uint32_t *work, cudaStream_t st, const ArPush *push = nullptr, bool late_trigger = false,
+                bool swiglu_pairs = false);
 // Whether the direct decode GEMV takes this matrix (a quantised kind, at most 1024 blocks per row).
 bool gemv_direct_ok(int kind, uint32_t cols);
 

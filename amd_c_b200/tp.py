@@ -32,7 +32,8 @@ class TensorParallelBackend:
         c = shard.cfg
         h = _vp()
         with torch.cuda.device(self.dev):
-            check(self.lib.ie_b200_ar_create(self.rank, self.world, c.dim, C.byref(h)))
+            # room for a whole prompt chunk per exchange (T x dim floats), so that a chunk's stop is one launch
+            check(self.lib.ie_b200_ar_create(self.rank, self.world, c.dim * max(1, shard.T), C.byref(h)))
             self.ar = h
             blob = (C.c_uint8 * 128)()
             check(self.lib.ie_b200_ar_handles(self.ar, blob))
@@ -43,6 +44,9 @@ class TensorParallelBackend:
             check(self.lib.ie_b200_ar_connect(self.ar, raw))
             check(self.lib.ie_b200_engine_set_collective(shard.h, self.ar, self.rank * shard.vocab_l))
         shard.collective = True
+        # capture the step graph (or build the persistent kernel's program) now: the first step should not spend its time on
+        # that after the ranks have been aligned (the kernels wait for a peer for 2 s at most)
+        _ = shard.launches_per_step
 
     def _align(self):
         """The kernels' waits for a peer are bounded (2 s): make sure no rank launches long before the others."""
@@ -54,6 +58,12 @@ class TensorParallelBackend:
         float32[vocab / world] that receives this rank's slice of the logits."""
         self._align()
         return self.b.step(tok, pos, logits)[0]
+
+    def run(self, toks, pos: int, last_only: bool = True):
+        """backend.run for the sharded model: a prompt chunk of up to T tokens at positions pos..; a stop of the chunk is one
+        exchange over T x dim floats. Returns the argmax tokens (identical on every rank)."""
+        self._align()
+        return self.b.run(0, toks, pos, last_only=last_only)
 
     def decode(self, tok: int, pos: int, K: int, timed: bool = False):
         """K greedy tokens, the argmax fed back on the device. timed: also return the device milliseconds."""

@@ -133,6 +133,15 @@ int ie_b200_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols,
 int ie_b200_norm_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, const float *d_norm_w, float eps,
                              float *d_xn_out, void *d_xq_out, float *d_y, const float *d_bias, const float *d_res, void *stream);
 
+/* SwiGLU moved into the GEMVs around it (one launch less per layer; the tensor-parallel step uses it): ie_b200_gemv_swiglu is
+ * the gate / up GEMV over a matrix whose rows alternate gate_i, up_i -- the warp that owns a pair writes d_h[i] = silu(gate_i) *
+ * up_i (rows / 2 floats, the arithmetic of ie_b200_swiglu_il) instead of the two rows; ie_b200_quant_gemv_stream is the GEMV
+ * that follows, with the Q8 quantiser of the f32 vector d_x (cols floats) in its prologue (d_xq_out, may be NULL: the Q8 copy,
+ * written once). Together they give the bits of GEMV, ie_b200_swiglu_il, GEMV (src/cpu.c:579-582 between two cpu_gemv_q4). */
+int ie_b200_gemv_swiglu(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_h, void *stream);
+int ie_b200_quant_gemv_stream(int kind, const void *d_w, uint32_t rows, uint32_t cols, const float *d_x, void *d_xq_out, float *d_y, const float *d_bias,
+                              const float *d_res, void *stream);
+
 /* The one-token GEMV with the reference's fused norm tail (gemv_norm_tail, kernels/ie_kernels.c:274-285;
  * IE_NORM_FUSE, src/model.c:1265-1293): after y = W x (+bias) (+res) is complete, the last CTA to finish writes
  * d_xn_out = rmsnorm(y) * d_norm_w and its Q8 copy d_xq_out (either may be NULL). rows % 32 == 0. d_counter: two

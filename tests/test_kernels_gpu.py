@@ -828,6 +828,44 @@ def test_topk_refuses_large_k(cuda, lib):
     assert lib.ie_b200_topk(x.data_ptr(), 200000, 64, 1, 800000, out.data_ptr(), out.data_ptr(), out.data_ptr(), None) == -2  # 98 slices x 64 candidates
 
 
+@pytest.mark.parametrize("typ,ffn,dim", [(synth.GGML_Q4_0, 768, 256), (synth.GGML_Q4_0, 14336, 4096), (synth.GGML_Q4_K, 1024, 1024), (synth.GGML_Q6_K, 1792, 512)])
+def test_swiglu_inside_the_gemvs(ora, cuda, lib, typ, ffn, dim):
+    """SwiGLU moved into the GEMVs around it: the gate / up GEMV over interleaved rows writes silu(gate) * up itself, the GEMV
+    after it quantises that vector in its prologue. Against the oracle's GEMV, SwiGLU, quantiser, GEMV: the two GEMVs bit for
+    bit, the SwiGLU values within 1e-6 (expf), the Q8 copy exactly the quantiser of the values."""
+    import torch
+
+    from amd_c_b200 import kernels as K
+
+    rng = np.random.default_rng(ffn + dim)
+    gate, up = synth.make_gguf_bytes(typ, rng, ffn, dim), synth.make_gguf_bytes(typ, rng, ffn, dim)
+    down = synth.make_gguf_bytes(synth.GGML_Q4_0, rng, dim, ffn)
+    mg, mu = K.Mat.from_gguf(typ, dev(gate, cuda), ffn, dim), K.Mat.from_gguf(typ, dev(up, cuda), ffn, dim)
+    rowb = lib.ie_b200_row_bytes(mg.kind, dim)
+    il = torch.stack((mg.data[: ffn * rowb].view(ffn, rowb), mu.data[: ffn * rowb].view(ffn, rowb)), dim=1).reshape(-1).contiguous()
+    md = K.Mat.from_gguf(synth.GGML_Q4_0, dev(down, cuda), dim, ffn)
+    x = rng.standard_normal(dim).astype(np.float32)
+    xq = ora.quant_q8(x)
+    d_xq = dev(xq, cuda)
+    h = torch.empty(ffn, dtype=torch.float32, device=cuda)
+    K.check(lib.ie_b200_gemv_swiglu(mg.kind, il.data_ptr(), 2 * ffn, dim, d_xq.data_ptr(), h.data_ptr(), None))
+    kg, gw, gs = ora.repack(typ, gate, ffn, dim)
+    ku, uw, us = ora.repack(typ, up, ffn, dim)
+    g_ref, u_ref = ora.gemv(kg, gw, gs, ffn, dim, xq), ora.gemv(ku, uw, us, ffn, dim, xq)
+    h_ref = ora.swiglu(g_ref, u_ref)
+    got_h = h.cpu().numpy()
+    assert np.abs(got_h - h_ref).max() <= 1e-6 * np.abs(h_ref).max()
+    res = rng.standard_normal(dim).astype(np.float32)
+    d_res = dev(res, cuda)
+    hq = torch.empty(40 * (ffn // 32), dtype=torch.uint8, device=cuda)
+    y = torch.empty(dim, dtype=torch.float32, device=cuda)
+    K.check(lib.ie_b200_quant_gemv_stream(md.kind, md.data.data_ptr(), dim, ffn, h.data_ptr(), hq.data_ptr(), y.data_ptr(), None, d_res.data_ptr(), None))
+    want_q = ora.quant_q8(got_h)
+    assert (hq.cpu().numpy() == want_q).all()
+    kd, dw, ds = ora.repack(synth.GGML_Q4_0, down, dim, ffn)
+    assert (bits(y.cpu().numpy()) == bits(ora.gemv(kd, dw, ds, dim, ffn, want_q, res=res))).all()
+
+
 def test_swiglu_interleaved_equals_planar(cuda, lib):
     """SwiGLU over interleaved (gate_i, up_i) pairs: the same bits as the planar kernel on the same values, outputs and Q8."""
     import torch

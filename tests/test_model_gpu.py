@@ -169,7 +169,7 @@ def test_prompt_chunks_on_the_half_cache(cuda, ora, name):
 
 
 VARIANTS = [{"IE_B200_PDL": "0"}, {"IE_B200_ATTN_FUSE": "0"}, {"IE_B200_NORM": "tail"}, {"IE_B200_NORM": "prologue"}, {"IE_B200_ATTN": "scalar"},
-            {"IE_B200_GEMM": "0"}, {"IE_B200_GEMM": "mma"}, {"IE_B200_PREFILL_ATTN": "0"}, {"IE_B200_STEP": "auto"}]
+            {"IE_B200_GEMM": "0"}, {"IE_B200_GEMM": "mma"}, {"IE_B200_PREFILL_ATTN": "0"}, {"IE_B200_STEP": "auto"}, {"IE_B200_SWIGLU": "gemv"}]
 
 
 @pytest.mark.parametrize("env", VARIANTS, ids=lambda e: "-".join(f"{k}={v}" for k, v in e.items()))

@@ -26,9 +26,9 @@ def main():
     cfg = gguf.make_model(gguf.config("tiny-tp"), seed=0)
     kv_f32 = mode == "graph"  # the persistent kernel runs on the half cache
     n_ctx, n_gen, prompt = 160, 40, [1, 2, 3]
-    tpb = TensorParallelBackend(Backend(cfg, n_ctx, kv_f32=kv_f32, tp=world, rank=rank, device=dev, step_mode=mode), dist.group.WORLD)
+    tpb = TensorParallelBackend(Backend(cfg, n_ctx, T=24, kv_f32=kv_f32, tp=world, rank=rank, device=dev, step_mode=mode), dist.group.WORLD)
     assert tpb.b.step_is_kernel == (mode == "kernel")
-    single = Backend(cfg, n_ctx, kv_f32=kv_f32, device=dev, step_mode=mode) if rank == 0 else None
+    single = Backend(cfg, n_ctx, T=24, kv_f32=kv_f32, device=dev, step_mode=mode) if rank == 0 else None
     mine = np.zeros(cfg.vocab // world, np.float32)
     want = np.zeros(cfg.vocab, np.float32)
     tok, n_checked, worst = prompt[0], 0, 0.0
@@ -69,6 +69,26 @@ def main():
             tok, _ = single.step(tok, len(prompt) + 12 + i)
             w.append(tok)
         common = next((i for i, (a, b) in enumerate(zip(out, w)) if int(a) != int(b)), n_gen)
+    # a prompt chunk (T tokens per call, each stop one exchange over T x dim floats) against the unsharded engine's chunk
+    T = tpb.b.T
+    pos0 = len(prompt) + 12  # over the same history on both sides: the teacher-forced steps above (the chained tokens may have parted)
+    chunk = (np.arange(T, dtype=np.uint32) * 7 + 3) % cfg.vocab
+    got_t = tpb.run(chunk, pos0, last_only=False)
+    rows = np.ascontiguousarray(tpb.b.read_rows("logits", 0, T)[:, : 4 * tpb.b.vocab_l]).view(np.float32)
+    parts = [torch.empty(rows.shape, dtype=torch.float32, device=dev) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(rows).to(dev))
+    got = torch.cat(parts, dim=1).cpu().numpy()
+    t = torch.tensor([int(x) for x in got_t], dtype=torch.int64, device=dev)
+    gathered = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(gathered, t)
+    assert all(torch.equal(gathered[0], g) for g in gathered), "ranks disagree on the chunk's tokens"
+    assert [int(x) for x in got_t] == [int(x) for x in got.argmax(axis=1)], "the exchanged argmax is not the argmax of the gathered logits"
+    if rank == 0:
+        single.run(0, chunk, pos0, last_only=False)
+        want_rows = np.ascontiguousarray(single.read_rows("logits", 0, T)[:, : 4 * cfg.vocab]).view(np.float32)
+        d_chunk = float(np.abs(got - want_rows).max()) / float(np.abs(want_rows).max())
+        assert d_chunk <= 3e-2, d_chunk
+        print(f"TP{world} {mode}: a chunk of {T} prompt tokens within {d_chunk:.1e} of the unsharded engine", flush=True)
         print(f"TP{world} {mode}: logits of {n_checked} steps within {worst:.1e} of the unsharded engine, {common} of {n_gen} chained tokens identical", flush=True)
         single.close()
     tpb.close()
