@@ -26,6 +26,7 @@ SIGNATURES = {
     "ie_b200_mat_bytes": (_sz, [_int, _u32, _u32]),
     "ie_b200_repack_gguf": (_int, [_int, _vp, _u32, _u32, _vp, _vp]),
     "ie_b200_repack_ref": (_int, [_int, _vp, _vp, _u32, _u32, _vp, _vp]),
+    "ie_b200_mat_part": (_int, [_int, _vp, _u32, _u32, _u32, _vp, _vp, _u32, _u32, _vp, _vp]),
     "ie_b200_quant_q8": (_int, [_vp, _vp, _u32, _u32, _sz, _sz, _vp]),
     "ie_b200_gemv": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
     "ie_b200_gemm": (_int, [_int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _sz, _sz, _sz, _vp]),
@@ -80,6 +81,7 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_destroy": (None, [_vp]),
     "ie_b200_engine_add_mat_gguf": (_int, [_vp, _int, _u32, _u32, _vp]),
     "ie_b200_engine_add_mat_ref": (_int, [_vp, _int, _u32, _u32, _vp, _vp]),
+    "ie_b200_engine_add_mat_ref_part": (_int, [_vp, _int, _u32, _u32, _vp, _vp, _u32, _vp, _vp, _u32, _u32]),
     "ie_b200_engine_add_mat_device": (_int, [_vp, _int, _u32, _u32, _vp]),
     "ie_b200_engine_add_vec": (_int, [_vp, _vp, _u32]),
     "ie_b200_engine_set_rope": (_int, [_vp, _vp, _vp]),
@@ -93,6 +95,12 @@ ENGINE_SIGNATURES = {
     "ie_b200_engine_decode": (_int, [_vp, _u32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
     "ie_b200_engine_enqueue_kinds": (_int, [_vp, _u32, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
+    "ie_b200_engine_step_begin": (_int, [_vp, _u32, _u32, _int]),
+    "ie_b200_engine_step_end": (_int, [_vp, _vp, C.POINTER(_u32), C.POINTER(C.c_double)]),
+    "ie_b200_engine_decode_begin": (_int, [_vp, _u32, _u32, _u32]),
+    "ie_b200_engine_decode_end": (_int, [_vp, _vp, C.POINTER(C.c_double)]),
+    "ie_b200_engine_run_begin": (_int, [_vp, _vp, _u32, _u32, _int]),
+    "ie_b200_engine_run_end": (_int, [_vp, _vp, _vp]),
     "ie_b200_engine_read_rows": (_int, [_vp, _u64, _u32, _u32, _u32, _vp]),
     "ie_b200_engine_copy_rows": (_int, [_vp, _u64, _u32, _u32, _u64, _u32, _u32, _u32, _u32, _int]),
     "ie_b200_engine_topk": (_int, [_vp, _u64, _u32, _u32, _u32, _u32, _u32, _vp, _vp]),
@@ -122,6 +130,13 @@ SIGNATURES.update({
     "ie_b200_ar_reduce_norm": (_int, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_argmax": (_int, [_vp, _vp, _vp, _u32, _vp, _vp]),
     "ie_b200_ar_destroy": (None, [_vp]),
+    "ie_b200_tp_group_create": (_int, [_u32, _vp, _u32, C.POINTER(_vp)]),
+    "ie_b200_tp_group_use": (_int, [_vp, _u32]),
+    "ie_b200_tp_group_attach": (_int, [_vp, _u32, _vp, _u32, _u32]),
+    "ie_b200_tp_group_step": (_int, [_vp, _u32, _u32, _vp, C.POINTER(_u32), C.POINTER(C.c_double)]),
+    "ie_b200_tp_group_run": (_int, [_vp, _vp, _u32, _u32, _int, _vp, _vp]),
+    "ie_b200_tp_group_decode": (_int, [_vp, _u32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
+    "ie_b200_tp_group_destroy": (None, [_vp]),
 })
 
 

@@ -356,18 +356,20 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
   return IE_B200_OK;
 }
 
-static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
-                          uint32_t *d_err, void *stream, int pushed, int early = 0) {
+// d_res: what the ranks' partials are added to (NULL: d_x itself, in place); d_x receives the sum.
+static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_x, const float *d_norm_w, float eps, float *d_xn,
+                          void *d_xq, uint32_t n, uint32_t *d_err, void *stream, int pushed, int early = 0) {
   if (!a || !d_part || !d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: NULL argument");
+  if (!d_res) d_res = d_x;
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_ar_allreduce_norm: peers not connected");
   if (n == 0 || n % 32u || n > a->d.max_n || n > 4u * 4u * ARN_MAX_THREADS)
     return fail(IE_B200_E_SIZE, "ie_b200_ar_allreduce_norm: %u floats (a multiple of 32, at most %u)", n, a->d.max_n < 16384u ? a->d.max_n : 16384u);
-  if (!aligned16(d_part) || !aligned16(d_x) || !aligned16(d_norm_w) || (d_xn && !aligned16(d_xn)) || (d_xq && !aligned16(d_xq)))
+  if (!aligned16(d_part) || !aligned16(d_x) || !aligned16(d_res) || !aligned16(d_norm_w) || (d_xn && !aligned16(d_xn)) || (d_xq && !aligned16(d_xq)))
     return fail(IE_B200_E_ARG, "ie_b200_ar_allreduce_norm: 16-byte alignment");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t *xq = static_cast<uint8_t *>(d_xq);
 #define IEB_ARN(IT, TH, PE)                                                                                                                  \
-  IEB_LAUNCH_PDL("ar_norm_kernel", (ar_norm_kernel<IT, TH, PE>), dim3(1), dim3(TH), 0, st, a->d, d_part, d_x, d_x, d_norm_w, eps, d_xn, xq, n, d_err, \
+  IEB_LAUNCH_PDL("ar_norm_kernel", (ar_norm_kernel<IT, TH, PE>), dim3(1), dim3(TH), 0, st, a->d, d_part, d_res, d_x, d_norm_w, eps, d_xn, xq, n, d_err, \
                  pushed, early)
   if (a->d.world > 4u) {  // 512 threads, all peers polled together
     const uint32_t iters = (n + 4u * 512u - 1u) / (4u * 512u);
@@ -387,7 +389,7 @@ static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, float *d_x,
 
 extern "C" int ie_b200_ar_allreduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
                                          uint32_t n, uint32_t *d_err, void *stream) {
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 0);
+  return ar_norm_launch(a, d_part, nullptr, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 0);
 }
 
 namespace ieb {
@@ -406,8 +408,6 @@ int gemv_push_act(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows
   // before the GEMV is complete, and it may fetch the epoch and the residual stream while the GEMV still runs
   return gemv_direct(kind, d_w, rows, cols, act, plain, d_part, nullptr, nullptr, nullptr, nullptr, st, &push, true);
 }
-int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
-                       uint32_t *d_err, cudaStream_t st);
 }  // namespace ieb
 
 extern "C" int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part, void *stream) {
@@ -417,22 +417,24 @@ extern "C" int ie_b200_gemv_push(ie_b200_allreduce *a, int kind, const void *d_w
 }
 
 namespace ieb {
-int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
-                       uint32_t *d_err, cudaStream_t st) {
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, st, 1, 1);
+// The reduction behind a GEMV that pushed its rows (pushed) or behind anything else (the kernel pushes d_part itself);
+// d_res NULL: onto d_x in place.
+int ar_norm_reduce(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                   uint32_t n, uint32_t *d_err, cudaStream_t st, bool pushed) {
+  return ar_norm_launch(a, d_part, d_res, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, st, pushed ? 1 : 0, pushed ? 1 : 0);
 }
 }  // namespace ieb
 
 extern "C" int ie_b200_ar_reduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
                                       uint32_t n, uint32_t *d_err, void *stream) {
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 1, 0);
+  return ar_norm_launch(a, d_part, nullptr, d_x, d_norm_w, eps, d_xn, d_xq, n, d_err, stream, 1, 0);
 }
 
 extern "C" int ie_b200_gemv_allreduce_norm(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, float *d_part,
                                            float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq_out, uint32_t *d_err, void *stream) {
   if (!d_x || !d_norm_w) return fail(IE_B200_E_ARG, "ie_b200_gemv_allreduce_norm: NULL argument");
   if (int r = ie_b200_gemv_push(a, kind, d_w, rows, cols, d_xq, d_part, stream)) return r;
-  return ar_norm_launch(a, d_part, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
+  return ar_norm_launch(a, d_part, nullptr, d_x, d_norm_w, eps, d_xn, d_xq_out, rows, d_err, stream, 1, 1);
 }
 
 extern "C" int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream) {

@@ -472,7 +472,29 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t &hi, uint32_t 
   hi = *reinterpret_cast<const uint32_t *>(&h), lo = *reinterpret_cast<const uint32_t *>(&l);
 }
 
-template <int HD, int G, bool FUSED, int NB>
+// Shared memory of the cluster form behind the tile buffers / merge scratch: the records (max, sum, out[hd]) of the CL CTAs of a
+// split, written into the leader's memory by every CTA of the cluster.
+__host__ __device__ constexpr size_t am_main_bytes(int HD, int G, int NB, uint32_t S) {
+  const size_t tile = (size_t)NB * 2 * ATT_TILE * (HD + AM_PAD) * sizeof(__half);
+  const size_t red = (size_t)((AM_WARPS + 1) * G * HD + AM_WARPS * G * 2 + (2 * S + 2) * G) * sizeof(float);
+  return ((tile > red ? tile : red) + 15u) & ~(size_t)15u;
+}
+
+__device__ __forceinline__ uint32_t cluster_map_shared(const void *p, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(cta_rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CL: CTAs per split. 1: a CTA streams its whole split. 4: a thread-block cluster shares the split, a CTA takes every
+// CL-th part of its tiles, and the parts meet in the leader's shared memory (distributed shared memory, one cluster
+// barrier): for short contexts, where one CTA per KV head leaves the fetch of the cache rows to a single SM.
+template <int HD, int G, bool FUSED, int NB, int CL>
 __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_kernel(const AttnArgs a) {
   constexpr int TILE = ATT_TILE, ROW = HD + AM_PAD, TILE_ELEMS = TILE * ROW, KS = HD / 16;
   static_assert(G <= 8, "the heads of a KV head fill the first 8 rows of the 16-row MMA");
@@ -484,13 +506,18 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   pdl_launch_dependents();
   const bool early = FUSED && a.early_kv;
   if (!early) pdl_wait();
-  const uint32_t s = blockIdx.x, g = blockIdx.y, t = blockIdx.z, S = a.S;
+  const uint32_t s = blockIdx.x / CL, cr = blockIdx.x % CL, g = blockIdx.y, t = blockIdx.z, S = a.S;
   const uint32_t np = *a.pos + t + 1u;
   const uint32_t span = att_span(np, S);
   const uint32_t A = (np + span - 1u) / span;
-  if (s >= A) return;
-  const uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
-  const bool owns_new = FUSED && s == A - 1u;
+  if (s >= A) return;  // (the whole cluster of such a split returns here)
+  uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
+  if (CL > 1) {  // this CTA's tiles of the split: ceil(tiles / CL) consecutive ones; the last CTAs may hold none
+    const uint32_t tiles = (p_hi - p_lo + TILE - 1u) / TILE, per = (tiles + CL - 1u) / CL;
+    const uint32_t lo2 = min(p_hi, p_lo + cr * per * TILE);
+    p_hi = min(p_hi, lo2 + per * TILE), p_lo = lo2;
+  }
+  const bool owns_new = FUSED && s == A - 1u && p_lo < np && np <= p_hi;  // the CTA whose positions end with this step's own
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hq = lane >> 2, tq = lane & 3;  // hq: the head (MMA row), tq: the column pair
   const float *qt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * t) + (size_t)g * G * HD;
   const __half *kh = static_cast<const __half *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const __half *>(a.vc) + (size_t)g * a.kv_len * HD;
@@ -685,17 +712,51 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   }
   __syncthreads();
   const size_t rec = HD + 2;
+  float *recv = reinterpret_cast<float *>(reinterpret_cast<char *>(smem_raw) + am_main_bytes(HD, G, NB, S));  // [CL][G][HD + 2], used in the leader
+  if (CL > 1) {
+    // every CTA's record into the leader's memory, then one cluster barrier; a CTA without positions sends (max -inf, sum 0)
+    const uint32_t base = cluster_map_shared(recv + (size_t)cr * G * rec, 0u);
+    for (int e = threadIdx.x; e < G * HD; e += AM_THREADS) {
+      const int h = e / HD;
+      float M = -INFINITY, L = 0.0f, acc = 0.0f;
+      if (p_lo < p_hi) {
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; w++) M = fmaxf(M, ml[(w * G + h) * 2]);
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; w++) {
+          const float wk = expf(ml[(w * G + h) * 2] - M);
+          L = fmaf(wk, ml[(w * G + h) * 2 + 1], L);
+          acc = fmaf(wk, red[(w * G + h) * HD + (e % HD)], acc);
+        }
+      }
+      cluster_st_f32(base + (uint32_t)((h * rec + 2 + (e % HD)) * sizeof(float)), acc);
+      if (e % HD == 0) cluster_st_f32(base + (uint32_t)(h * rec * sizeof(float)), M), cluster_st_f32(base + (uint32_t)((h * rec + 1) * sizeof(float)), L);
+    }
+    cluster_sync_all();
+    if (cr != 0u) return;
+  }
   for (int e = threadIdx.x; e < G * HD; e += AM_THREADS) {
     const int h = e / HD;
     float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < AM_WARPS; w++) M = fmaxf(M, ml[(w * G + h) * 2]);
     float L = 0.0f, acc = 0.0f;
+    if (CL > 1) {  // the leader: the cluster's records in rank order (rank 0 always holds positions: M is finite)
 #pragma unroll
-    for (int w = 0; w < AM_WARPS; w++) {
-      const float wk = expf(ml[(w * G + h) * 2] - M);  // a warp without positions has max -inf: weight 0
-      L = fmaf(wk, ml[(w * G + h) * 2 + 1], L);
-      acc = fmaf(wk, red[(w * G + h) * HD + (e % HD)], acc);
+      for (int c = 0; c < CL; c++) M = fmaxf(M, recv[(c * G + h) * rec]);
+#pragma unroll
+      for (int c = 0; c < CL; c++) {
+        const float wk = expf(recv[(c * G + h) * rec] - M);
+        L = fmaf(wk, recv[(c * G + h) * rec + 1], L);
+        acc = fmaf(wk, recv[(c * G + h) * rec + 2 + (e % HD)], acc);
+      }
+    } else {
+#pragma unroll
+      for (int w = 0; w < AM_WARPS; w++) M = fmaxf(M, ml[(w * G + h) * 2]);
+#pragma unroll
+      for (int w = 0; w < AM_WARPS; w++) {
+        const float wk = expf(ml[(w * G + h) * 2] - M);  // a warp without positions has max -inf: weight 0
+        L = fmaf(wk, ml[(w * G + h) * 2 + 1], L);
+        acc = fmaf(wk, red[(w * G + h) * HD + (e % HD)], acc);
+      }
     }
     if (A == 1u) {
       fin[e] = acc * (1.0f / L);
@@ -729,20 +790,37 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   }
 }
 
-template <int HD, int G, bool FUSED, int NB>
+// IE_B200_ATTN=single: one CTA per split at every length (the form without clusters).
+static bool attn_cluster_on() {
+  static const bool on = [] {
+    const char *v = getenv("IE_B200_ATTN");
+    return !(v && v[0] == 's' && v[1] == 'i');
+  }();
+  return on;
+}
+
+template <int HD, int G, bool FUSED, int NB, int CL>
 static int launch_attn_mma_nb(const AttnArgs &a, uint32_t T, cudaStream_t st) {
-  const size_t tile = (size_t)NB * 2 * ATT_TILE * (HD + AM_PAD) * sizeof(__half);
-  const size_t red = (size_t)((AM_WARPS + 1) * G * HD + AM_WARPS * G * 2 + (2 * a.S + 2) * G) * sizeof(float);
-  const size_t smem = tile > red ? tile : red;
-  auto k = attn_decode_mma_kernel<HD, G, FUSED, NB>;
+  const size_t smem = am_main_bytes(HD, G, NB, a.S) + (CL > 1 ? (size_t)CL * G * (HD + 2) * sizeof(float) : 0);
+  auto k = attn_decode_mma_kernel<HD, G, FUSED, NB, CL>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), smem)) return r;
+  if (CL > 1) {
+    cudaError_t e_ = launch_pdl_cluster(k, dim3(a.S * CL, a.n_kv, T), dim3(AM_THREADS), smem, st, CL, a);
+    count_launch();
+    if (e_ != cudaSuccess) return cuda_fail(e_, "attn_decode_mma_kernel (cluster)");
+    return IE_B200_OK;
+  }
   IEB_LAUNCH_PDL("attn_decode_mma_kernel", k, dim3(a.S, a.n_kv, T), dim3(AM_THREADS), smem, st, a);
   return IE_B200_OK;
 }
+constexpr int AM_CLUSTER = 4;
 template <int HD, int G, bool FUSED>
 static int launch_attn_mma(const AttnArgs &a, uint32_t T, cudaStream_t st) {
-  if ((uint64_t)a.S * a.n_kv * T > (uint64_t)sm_count()) return launch_attn_mma_nb<HD, G, FUSED, 3>(a, T, st);
-  return launch_attn_mma_nb<HD, G, FUSED, 4>(a, T, st);
+  const uint64_t ctas = (uint64_t)a.S * a.n_kv * T;
+  if (ctas > (uint64_t)sm_count()) return launch_attn_mma_nb<HD, G, FUSED, 3, 1>(a, T, st);
+  // few splits (short contexts): four CTAs per split while every CTA still has an SM of its own
+  if (ctas * AM_CLUSTER <= (uint64_t)sm_count() && attn_cluster_on()) return launch_attn_mma_nb<HD, G, FUSED, 4, AM_CLUSTER>(a, T, st);
+  return launch_attn_mma_nb<HD, G, FUSED, 4, 1>(a, T, st);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -949,7 +1027,7 @@ static int dispatch_prefill(const PrefillArgs &a, uint32_t G, cudaStream_t st) {
 static bool attn_use_mma() {
   static const bool on = [] {
     const char *v = getenv("IE_B200_ATTN");
-    return !(v && v[0] == 's');
+    return !(v && v[0] == 's' && v[1] == 'c');
   }();
   return on;
 }

@@ -74,9 +74,12 @@ struct ie_b200_engine {
   bool no_prefill_attn = false;  // IE_B200_PREFILL_ATTN=0: a chunk's attention through the decode kernel, one CTA set per token
   bool no_gemm = false;      // IE_B200_GEMM=0: prompt chunks through the multi-token GEMV (bit-exact with the one-token path)
   bool gemm_mma = false;     // IE_B200_GEMM=mma: the int8 mma.sync GEMM instead of the tcgen05 one
-  int swi_epi = -1;          // IE_B200_SWIGLU=gemv|kernel: SwiGLU in the gate / up GEMV's epilogue and the Q8 quantiser in the down GEMV's
-                             // prologue (one launch less per layer), or a kernel of its own; -1: in the GEMV for a tensor-parallel shard
-                             // (small vectors, launch-bound), its own kernel on one GPU (where the prologue's extra L2 reads cost more)
+  uint32_t ctx_bound = 0;    // positions the captured step graph's attention grid is sized for (0: the whole context)
+  bool timed = false;        // the step begun last records its device time
+  uint32_t run_T = 0;        // tokens of the chunk (or steps of the decode run) begun last
+  int swi_epi = -1;          // IE_B200_SWIGLU=gemv: SwiGLU in the gate / up GEMV's epilogue and the Q8 quantiser in the down GEMV's
+                             // prologue (one launch less per layer). Off unless asked for: every CTA of the down GEMV then quantises
+                             // the whole vector itself, which costs more than the launch it saves (measured at 1 and 2 GPUs)
   void *topk_scratch = nullptr;  // candidates and results of ie_b200_engine_topk
   size_t topk_bytes = 0;
   void *gemm_scratch = nullptr;  // expanded activations and K-split partials of the tcgen05 GEMM
@@ -110,10 +113,17 @@ static inline void *at(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_
   return off == IE_B200_NONE ? nullptr : e->arena + off + (size_t)stride * t0;
 }
 
+// Host to device on the engine's stream, then wait: a plain cudaMemcpy from pageable memory may return while its last piece
+// is still on the way, and the engine's stream (non-blocking) does not order itself behind the default stream.
+static cudaError_t h2d(ie_b200_engine *e, void *dst, const void *src, size_t n) {
+  cudaError_t r = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, e->stream);
+  return r == cudaSuccess ? cudaStreamSynchronize(e->stream) : r;
+}
+
 namespace ieb {
 int gemv_push_act(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool plain, float *d_part, cudaStream_t st);
-int ar_norm_after_push(ie_b200_allreduce *a, const float *d_part, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq, uint32_t n,
-                       uint32_t *d_err, cudaStream_t st);  // allreduce.cu
+int ar_norm_reduce(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_x, const float *d_norm_w, float eps, float *d_xn, void *d_xq,
+                   uint32_t n, uint32_t *d_err, cudaStream_t st, bool pushed);
 void ar_push_info(const ie_b200_allreduce *a, ArPush *out);  // allreduce.cu
 bool ar_connected(const ie_b200_allreduce *a);
 int attn_decode_fused(const float *d_q, const float *d_k, const float *d_v, void *d_kc, void *d_vc, const float *d_cos, const float *d_sin, float *d_out,
@@ -210,20 +220,23 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
           return r;
       return IE_B200_OK;
     }
-    case IE_B200_OP_ALLREDUCE: {
+    case IE_B200_OP_ALLREDUCE: {  // c = (res, or c itself) + the sum over the ranks of a
       if (!e->ar) return IE_B200_OK;  // no collective attached: the caller serves these stops between enqueue calls
+      const bool own_res = o.res != IE_B200_NONE;
       // a prompt chunk whose token rows lie back to back: one exchange over T x n floats (the state's buffers permitting)
-      if (T > 1 && o.a_stride == o.n * 4u && o.c_stride == o.n * 4u) {
+      if (T > 1 && o.a_stride == o.n * 4u && o.c_stride == o.n * 4u && (!own_res || o.res_stride == o.n * 4u)) {
         ArPush info;
         ar_push_info(e->ar, &info);
         if ((uint64_t)o.n * T <= info.max_n) {
           float *x = static_cast<float *>(at(e, o.c, o.c_stride, t0));
-          return ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0)), x, x, o.n * T, e->err, st);
+          const float *rs = own_res ? static_cast<const float *>(at(e, o.res, o.res_stride, t0)) : x;
+          return ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0)), rs, x, o.n * T, e->err, st);
         }
       }
       for (uint32_t t = 0; t < T; t++) {
         float *x = static_cast<float *>(at(e, o.c, o.c_stride, t0 + t));
-        if (int r = ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0 + t)), x, x, o.n, e->err, st)) return r;
+        const float *rs = own_res ? static_cast<const float *>(at(e, o.res, o.res_stride, t0 + t)) : x;
+        if (int r = ie_b200_ar_allreduce_add(e->ar, static_cast<float *>(at(e, o.a, o.a_stride, t0 + t)), rs, x, o.n, e->err, st)) return r;
       }
       return IE_B200_OK;
     }
@@ -284,8 +297,9 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
         if (ar.kind == IE_B200_OP_ALLREDUCE && ar.a == o.b && ar.n == m.rows && nx.kind == IE_B200_OP_RMSNORM && nx.a == ar.c && nx.res == IE_B200_NONE &&
             nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
           if (int r = gemv_push_act(e->ar, m.kind, m.d, m.rows, m.cols, act, true, static_cast<float *>(at(e, o.b, 0, 0)), st)) return r;
-          if (int r = ar_norm_after_push(e->ar, static_cast<float *>(at(e, o.b, 0, 0)), static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
-                                         static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), m.rows, e->err, st))
+          if (int r = ar_norm_reduce(e->ar, static_cast<float *>(at(e, o.b, 0, 0)), static_cast<const float *>(at(e, ar.res, 0, 0)),
+                                     static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps, static_cast<float *>(at(e, nx.b, 0, 0)),
+                                     at(e, nx.qo, 0, 0), m.rows, e->err, st, true))
             return r;
           i += 2;
           continue;
@@ -311,7 +325,8 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       char *kcl = static_cast<char *>(e->kc) + e->kv_layer_bytes * o.layer, *vcl = static_cast<char *>(e->vc) + e->kv_layer_bytes * o.layer;
       int r = attn_decode_fused(static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.b, 0, 0)), static_cast<float *>(at(e, o.c, 0, 0)), kcl,
                                 vcl, e->rope_cos, e->rope_sin, static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), e->scalars + e->d.T_max + 1,
-                                e->d.n_head, e->d.n_kv, e->d.hd, e->d.neox, e->d.kv_f32, e->d.n_ctx, e->d.n_ctx, e->attn_part, e->attn_count, st, was_late);
+                                e->d.n_head, e->d.n_kv, e->d.hd, e->d.neox, e->d.kv_f32, e->d.n_ctx, e->ctx_bound ? e->ctx_bound : e->d.n_ctx, e->attn_part, e->attn_count, st,
+                                was_late);
       if (r) return r;
       i++;
       continue;
@@ -324,10 +339,13 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
       const EMat &m = e->mats[o.mat];
       if (ar.kind == IE_B200_OP_ALLREDUCE && ar.a == o.b && ar.n == m.rows && nx.kind == IE_B200_OP_RMSNORM && nx.a == ar.c && nx.res == IE_B200_NONE &&
           nx.vec >= 0 && nx.n == m.rows && m.rows % 32u == 0) {
-        int r = ie_b200_gemv_allreduce_norm(e->ar, m.kind, m.d, m.rows, m.cols, at(e, o.a, 0, 0), static_cast<float *>(at(e, o.b, 0, 0)),
-                                            static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps, static_cast<float *>(at(e, nx.b, 0, 0)),
-                                            at(e, nx.qo, 0, 0), e->err, st);
-        if (r) return r;
+        ActSrc act = {};
+        act.xq = static_cast<const uint8_t *>(at(e, o.a, 0, 0));
+        if (int r = gemv_push_act(e->ar, m.kind, m.d, m.rows, m.cols, act, false, static_cast<float *>(at(e, o.b, 0, 0)), st)) return r;
+        if (int r = ar_norm_reduce(e->ar, static_cast<float *>(at(e, o.b, 0, 0)), static_cast<const float *>(at(e, ar.res, 0, 0)),
+                                   static_cast<float *>(at(e, ar.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps, static_cast<float *>(at(e, nx.b, 0, 0)),
+                                   at(e, nx.qo, 0, 0), m.rows, e->err, st, true))
+          return r;
         i += 2;
         continue;
       }
@@ -336,8 +354,9 @@ static int enqueue_range(ie_b200_engine *e, uint32_t first, uint32_t last, uint3
     if (T == 1 && e->ar && o.kind == IE_B200_OP_ALLREDUCE && i + 1 < last && (kind_mask & (1u << IE_B200_OP_RMSNORM))) {
       const ie_b200_op &nx = e->ops[i + 1];
       if (nx.kind == IE_B200_OP_RMSNORM && nx.a == o.c && nx.res == IE_B200_NONE && nx.vec >= 0 && nx.n == o.n && o.n % 32u == 0 && o.n <= 16384u) {
-        int r = ie_b200_ar_allreduce_norm(e->ar, static_cast<float *>(at(e, o.a, 0, 0)), static_cast<float *>(at(e, o.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps,
-                                          static_cast<float *>(at(e, nx.b, 0, 0)), at(e, nx.qo, 0, 0), o.n, e->err, st);
+        int r = ar_norm_reduce(e->ar, static_cast<float *>(at(e, o.a, 0, 0)), static_cast<const float *>(at(e, o.res, 0, 0)),
+                               static_cast<float *>(at(e, o.c, 0, 0)), e->vecs[nx.vec].d, e->d.eps, static_cast<float *>(at(e, nx.b, 0, 0)),
+                               at(e, nx.qo, 0, 0), o.n, e->err, st, false);
         if (r) return r;
         i++;
         continue;
@@ -454,6 +473,7 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
 
 extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
   if (!e) return;
+  cudaSetDevice(e->device);
   if (e->stream) cudaStreamSynchronize(e->stream);
   if (e->step_graph) cudaGraphExecDestroy(e->step_graph);
   for (auto &m : e->mats)
@@ -488,13 +508,14 @@ static void drop_graph(ie_b200_engine *e) {
 
 extern "C" int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uint32_t rows, uint32_t cols, const void *h_bytes) {
   if (!e || !h_bytes) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_gguf: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
   const int kind = kind_of_ggml(ggml_type);
   if (kind < 0) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_gguf: GGML type %d unsupported", ggml_type);
   const size_t src_n = gguf_bytes(ggml_type, rows, cols), dst_n = ie_b200_mat_bytes(kind, rows, cols);
   void *tmp = nullptr, *dst = nullptr;
   IEB_CUDA(cudaMalloc(&dst, dst_n ? dst_n : 16));
   if (kind == IE_B200_MAT_F32) {
-    IEB_CUDA(cudaMemcpy(dst, h_bytes, src_n, cudaMemcpyHostToDevice));
+    IEB_CUDA(h2d(e, dst, h_bytes, src_n));
   } else {
     IEB_CUDA(cudaMalloc(&tmp, src_n ? src_n : 16));
     IEB_CUDA(cudaMemcpyAsync(tmp, h_bytes, src_n, cudaMemcpyHostToDevice, e->stream));
@@ -512,6 +533,7 @@ extern "C" int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uin
 
 extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs) {
   if (!e || !h_qw) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
   const size_t nb = cols / 32u, n = (size_t)rows * nb;
   size_t qw_n, qs_n;
   switch (kind) {
@@ -526,7 +548,7 @@ extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t 
   const size_t dst_n = ie_b200_mat_bytes(kind, rows, cols);
   IEB_CUDA(cudaMalloc(&dst, dst_n ? dst_n : 16));
   if (kind == IE_B200_MAT_F32) {
-    IEB_CUDA(cudaMemcpy(dst, h_qw, qw_n, cudaMemcpyHostToDevice));
+    IEB_CUDA(h2d(e, dst, h_qw, qw_n));
   } else {
     IEB_CUDA(cudaMalloc(&dqw, qw_n ? qw_n : 16));
     IEB_CUDA(cudaMalloc(&dqs, qs_n ? qs_n : 16));
@@ -544,6 +566,30 @@ extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t 
   return (int)e->mats.size() - 1;
 }
 
+extern "C" int ie_b200_engine_add_mat_ref_part(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs,
+                                               uint32_t n_ranges, const uint32_t *row0, const uint32_t *n_rows, uint32_t col0, uint32_t n_cols) {
+  if (!e || !row0 || !n_rows || n_ranges == 0) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref_part: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
+  const int whole = ie_b200_engine_add_mat_ref(e, kind, rows, cols, h_qw, h_qs);
+  if (whole < 0) return whole;
+  uint32_t part_rows = 0;
+  for (uint32_t k = 0; k < n_ranges; k++) part_rows += n_rows[k];
+  void *dst = nullptr;
+  const size_t dst_n = ie_b200_mat_bytes(kind, part_rows, n_cols);
+  cudaError_t ce = cudaMalloc(&dst, dst_n ? dst_n : 16);
+  int r = ce == cudaSuccess ? ie_b200_mat_part(kind, e->mats[whole].d, rows, cols, n_ranges, row0, n_rows, col0, n_cols, dst, e->stream)
+                            : cuda_fail(ce, "cudaMalloc(matrix part)");
+  cudaStreamSynchronize(e->stream);
+  cudaFree(e->mats[whole].d);  // the whole matrix was only the source of the part
+  if (r) {
+    cudaFree(dst);
+    e->mats.pop_back();
+    return r;
+  }
+  e->mats[whole] = EMat{kind, part_rows, n_cols, dst, true};
+  return whole;
+}
+
 extern "C" int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *d_data) {
   if (!e || !d_data) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: NULL argument");
   if (!aligned16(d_data)) return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_device: the matrix must be 16-byte aligned");
@@ -553,9 +599,10 @@ extern "C" int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32
 
 extern "C" int ie_b200_engine_add_vec(ie_b200_engine *e, const float *h_f, uint32_t n) {
   if (!e || !h_f) return fail(IE_B200_E_ARG, "ie_b200_engine_add_vec: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
   float *dptr = nullptr;
   IEB_CUDA(cudaMalloc(&dptr, (size_t)(n ? n : 1) * 4));
-  IEB_CUDA(cudaMemcpy(dptr, h_f, (size_t)n * 4, cudaMemcpyHostToDevice));
+  IEB_CUDA(h2d(e, dptr, h_f, (size_t)n * 4));
   e->vecs.push_back({dptr, n});
   return (int)e->vecs.size() - 1;
 }
@@ -563,8 +610,8 @@ extern "C" int ie_b200_engine_add_vec(ie_b200_engine *e, const float *h_f, uint3
 extern "C" int ie_b200_engine_set_rope(ie_b200_engine *e, const float *h_cos, const float *h_sin) {
   if (!e || !h_cos || !h_sin) return fail(IE_B200_E_ARG, "ie_b200_engine_set_rope: NULL argument");
   const size_t n = (size_t)e->d.n_ctx * (e->d.hd / 2u) * 4u;
-  IEB_CUDA(cudaMemcpy(e->rope_cos, h_cos, n, cudaMemcpyHostToDevice));
-  IEB_CUDA(cudaMemcpy(e->rope_sin, h_sin, n, cudaMemcpyHostToDevice));
+  IEB_CUDA(h2d(e, e->rope_cos, h_cos, n));
+  IEB_CUDA(h2d(e, e->rope_sin, h_sin, n));
   return IE_B200_OK;
 }
 
@@ -676,7 +723,7 @@ static int build_program(ie_b200_engine *e) {
           p.push = 1, p.nobar = 1;
           ph.push_back(p);
           StepPhase r = {};
-          r.kind = PH_REDUCE, r.rows = ar.n, r.res = reinterpret_cast<const float *>(A(ar.c)), r.y = reinterpret_cast<float *>(A(ar.c));
+          r.kind = PH_REDUCE, r.rows = ar.n, r.res = reinterpret_cast<const float *>(A(ar.res != IE_B200_NONE ? ar.res : ar.c)), r.y = reinterpret_cast<float *>(A(ar.c));
           ph.push_back(r);
           last_act = nullptr;
           i++;
@@ -755,7 +802,7 @@ static int build_program(ie_b200_engine *e) {
   cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax);
   e->d_prog = nullptr, e->sk_part = nullptr, e->sk_amax = nullptr;
   IEB_CUDA(cudaMalloc(&e->d_prog, ph.size() * sizeof(StepPhase)));
-  IEB_CUDA(cudaMemcpy(e->d_prog, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+  IEB_CUDA(h2d(e, e->d_prog, ph.data(), ph.size() * sizeof(StepPhase)));
   IEB_CUDA(cudaMalloc(&e->sk_part, (size_t)d.n_head * a.smax * (d.hd + 2u) * sizeof(float)));
   IEB_CUDA(cudaMalloc(&e->sk_amax, step_kernel_amax_bytes()));
   a.prog = e->d_prog, a.n_phases = (uint32_t)ph.size(), a.n_steps = 1;
@@ -809,16 +856,34 @@ static int capture_step(ie_b200_engine *e) {
   return IE_B200_OK;
 }
 
-extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms) {
-  if (!e || !next) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
+// The step graph's attention grid is sized for a bound on the positions, not for the whole context: a chat at position 200
+// of an 8192-position context would otherwise launch the splits of 8192 positions every step (and miss the short-context
+// form of the kernel). The bound doubles from 512; the graph is captured again when the positions outgrow it, or fall to a
+// quarter of it. (Correctness does not hang on it: a split simply grows past the bound.)
+static int step_graph_for(ie_b200_engine *e, uint32_t positions) {
+  uint32_t want = 512u;
+  while (want < positions && want < e->d.n_ctx) want *= 2u;
+  if (want > e->d.n_ctx) want = e->d.n_ctx;
+  if (e->step_graph && (want > e->ctx_bound || want * 4u <= e->ctx_bound)) cudaGraphExecDestroy(e->step_graph), e->step_graph = nullptr;
+  if (e->step_graph) return IE_B200_OK;
+  if (want > e->ctx_bound || want * 4u <= e->ctx_bound || e->ctx_bound == 0) e->ctx_bound = want;
+  return capture_step(e);
+}
+
+// A step, a decode run and a prompt chunk each come as two halves: everything up to and including the copies of the results
+// (asynchronous, on the engine's stream) and the wait for them. A host that drives the shards of one model on several GPUs
+// from one thread enqueues every shard's first half before it waits for any of them.
+extern "C" int ie_b200_engine_step_begin(ie_b200_engine *e, uint32_t tok, uint32_t pos, int timed) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
   if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_step: no op list");
   IEB_CUDA(cudaSetDevice(e->device));
   bool kernel = false;
   if (int r = use_step_kernel(e, &kernel)) return r;
-  if (!kernel && !e->step_graph)
-    if (int r = capture_step(e)) return r;
+  if (!kernel)
+    if (int r = step_graph_for(e, pos + 1u)) return r;
   cudaStream_t st = e->stream;
-  if (ms) IEB_CUDA(cudaEventRecord(e->ev0, st));
+  e->timed = timed != 0;
+  if (timed) IEB_CUDA(cudaEventRecord(e->ev0, st));
   if (int r = upload_input(e, &tok, 1, pos, st)) return r;
   if (kernel) {
     e->sk.n_steps = 1;
@@ -829,10 +894,18 @@ extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos
   }
   IEB_CUDA(cudaMemcpyAsync(e->h_result, e->arena + e->d.argmax_off, 8, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
-  if (h_logits) IEB_CUDA(cudaMemcpyAsync(h_logits, e->arena + e->d.logits_off, (size_t)e->logits_n * 4, cudaMemcpyDeviceToHost, st));
-  if (ms) IEB_CUDA(cudaEventRecord(e->ev1, st));
-  IEB_CUDA(cudaStreamSynchronize(st));
-  if (ms) {
+  if (timed) IEB_CUDA(cudaEventRecord(e->ev1, st));
+  return IE_B200_OK;
+}
+
+// (The first half copies into the engine's own pinned memory only: a copy into the caller's pageable memory would make the
+// host wait for the step, and with it for ranks whose work this thread has not enqueued yet.)
+extern "C" int ie_b200_engine_step_end(ie_b200_engine *e, float *h_logits, uint32_t *next, double *ms) {
+  if (!e || !next) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  if (h_logits) IEB_CUDA(cudaMemcpy(h_logits, e->arena + e->d.logits_off, (size_t)e->logits_n * 4, cudaMemcpyDeviceToHost));
+  if (ms && e->timed) {
     float f = 0;
     IEB_CUDA(cudaEventElapsedTime(&f, e->ev0, e->ev1));
     *ms = f;
@@ -842,17 +915,22 @@ extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos
   return IE_B200_OK;
 }
 
-extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K, uint32_t *h_out, double *ms) {
-  if (!e || !h_out) return fail(IE_B200_E_ARG, "ie_b200_engine_decode: NULL argument");
+extern "C" int ie_b200_engine_step(ie_b200_engine *e, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms) {
+  if (!e || !next) return fail(IE_B200_E_ARG, "ie_b200_engine_step: NULL argument");
+  if (int r = ie_b200_engine_step_begin(e, tok, pos, ms != nullptr)) return r;
+  return ie_b200_engine_step_end(e, h_logits, next, ms);
+}
+
+extern "C" int ie_b200_engine_decode_begin(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K) {
+  if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_decode: NULL argument");
   if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_decode: no op list");
-  if (K == 0) return IE_B200_OK;
-  if (K > HIST_CAP) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: %u steps > %u per call", K, HIST_CAP);
+  if (K == 0 || K > HIST_CAP) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: %u steps (1 .. %u per call)", K, HIST_CAP);
   if ((uint64_t)pos + K > e->d.n_ctx) return fail(IE_B200_E_SIZE, "ie_b200_engine_decode: positions %u .. %u exceed the context %u", pos, pos + K - 1, e->d.n_ctx);
   IEB_CUDA(cudaSetDevice(e->device));
   bool kernel = false;
   if (int r = use_step_kernel(e, &kernel)) return r;
-  if (!kernel && !e->step_graph)
-    if (int r = capture_step(e)) return r;
+  if (!kernel)
+    if (int r = step_graph_for(e, pos + K)) return r;
   cudaStream_t st = e->stream;
   if (int r = upload_input(e, &tok, 1, pos, st)) return r;
   IEB_CUDA(cudaMemsetAsync(e->hist + HIST_CAP, 0, 4, st));
@@ -865,9 +943,16 @@ extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t p
     count_launch(e->step_launches * K);
   }
   IEB_CUDA(cudaEventRecord(e->ev1, st));
-  IEB_CUDA(cudaMemcpyAsync(h_out, e->hist, (size_t)K * 4, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaMemcpyAsync(e->h_result + 2, e->err, 4, cudaMemcpyDeviceToHost, st));
-  IEB_CUDA(cudaStreamSynchronize(st));
+  e->run_T = K;
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_decode_end(ie_b200_engine *e, uint32_t *h_out, double *ms) {
+  if (!e || !h_out) return fail(IE_B200_E_ARG, "ie_b200_engine_decode: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
+  IEB_CUDA(cudaMemcpy(h_out, e->hist, (size_t)e->run_T * 4, cudaMemcpyDeviceToHost));
   if (e->h_result[2]) return fail(IE_B200_E_DEVICE, "a kernel gave up a bounded wait (device error word %u)", e->h_result[2]);
   if (ms) {
     float f = 0;
@@ -877,6 +962,13 @@ extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t p
   return IE_B200_OK;
 }
 
+extern "C" int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K, uint32_t *h_out, double *ms) {
+  if (!e || !h_out) return fail(IE_B200_E_ARG, "ie_b200_engine_decode: NULL argument");
+  if (K == 0) return e->ops.empty() ? fail(IE_B200_E_STATE, "ie_b200_engine_decode: no op list") : IE_B200_OK;
+  if (int r = ie_b200_engine_decode_begin(e, tok, pos, K)) return r;
+  return ie_b200_engine_decode_end(e, h_out, ms);
+}
+
 extern "C" int ie_b200_engine_enqueue_kinds(ie_b200_engine *e, uint32_t first, uint32_t last, uint32_t kind_mask, uint32_t T, void *stream) {
   if (!e) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue_kinds: NULL engine");
   if (first > last || last > e->ops.size()) return fail(IE_B200_E_ARG, "ie_b200_engine_enqueue_kinds: ops [%u, %u) of %zu", first, last, e->ops.size());
@@ -884,8 +976,8 @@ extern "C" int ie_b200_engine_enqueue_kinds(ie_b200_engine *e, uint32_t first, u
   return enqueue_range(e, first, last, T, kind_mask, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob) {
-  if (!e || !toks || !out) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
+extern "C" int ie_b200_engine_run_begin(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only) {
+  if (!e || !toks) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
   if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_run: no op list");
   IEB_CUDA(cudaSetDevice(e->device));
   cudaStream_t st = e->stream;
@@ -897,13 +989,26 @@ extern "C" int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint3
     if (int r = launch_op(e, e->ops[i], T - 1, 1, st)) return r;
   IEB_CUDA(cudaMemcpy2DAsync(e->h_result, 8, e->arena + e->d.argmax_off, e->d.argmax_stride ? e->d.argmax_stride : 8, 8, T, cudaMemcpyDeviceToHost, st));
   IEB_CUDA(cudaMemcpyAsync(e->h_result + 2 * e->d.T_max, e->err, 4, cudaMemcpyDeviceToHost, st));
-  IEB_CUDA(cudaStreamSynchronize(st));
+  e->run_T = T;
+  return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_run_end(ie_b200_engine *e, uint32_t *out, float *prob) {
+  if (!e || !out) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
+  IEB_CUDA(cudaSetDevice(e->device));
+  IEB_CUDA(cudaStreamSynchronize(e->stream));
   if (e->h_result[2 * e->d.T_max]) return fail(IE_B200_E_DEVICE, "a kernel gave up a bounded wait (device error word %u)", e->h_result[2 * e->d.T_max]);
-  for (uint32_t t = 0; t < T; t++) {
+  for (uint32_t t = 0; t < e->run_T; t++) {
     out[t] = e->h_result[2 * t];
     if (prob) std::memcpy(&prob[t], &e->h_result[2 * t + 1], 4);
   }
   return IE_B200_OK;
+}
+
+extern "C" int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob) {
+  if (!e || !toks || !out) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
+  if (int r = ie_b200_engine_run_begin(e, toks, T, pos, last_only)) return r;
+  return ie_b200_engine_run_end(e, out, prob);
 }
 
 extern "C" int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, void *h_dst) {
@@ -1031,6 +1136,6 @@ extern "C" uint32_t ie_b200_engine_launches_per_step(ie_b200_engine *e) {
   bool kernel = false;
   if (cudaSetDevice(e->device) != cudaSuccess || use_step_kernel(e, &kernel) != IE_B200_OK) return 0;
   if (kernel) return 1;
-  if (!e->step_graph) capture_step(e);
+  if (!e->step_graph) step_graph_for(e, e->ctx_bound ? e->ctx_bound : 1u);
   return e->step_launches;
 }

@@ -182,3 +182,70 @@ extern "C" int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, 
   IEB_LAUNCHED("repack_ref");
   return IE_B200_OK;
 }
+
+// ---- a part of a matrix in the streaming layout (tensor-parallel shards): row ranges one after the other, one column range ----
+namespace {
+struct PartAreas {
+  uint32_t n;             // areas per row
+  uint32_t src[4], dst[4], len[4];  // byte offsets within the source / destination row, bytes (all multiples of 2)
+};
+
+// One CTA per destination row.
+__global__ void mat_part_kernel(const uint8_t *src, size_t src_rowb, uint8_t *dst, size_t dst_rowb, uint32_t src_row0, uint32_t dst_row0, PartAreas a) {
+  const uint8_t *s = src + (size_t)(src_row0 + blockIdx.x) * src_rowb;
+  uint8_t *d = dst + (size_t)(dst_row0 + blockIdx.x) * dst_rowb;
+  for (uint32_t k = 0; k < a.n; k++) {
+    const uint16_t *sp = reinterpret_cast<const uint16_t *>(s + a.src[k]);
+    uint16_t *dp = reinterpret_cast<uint16_t *>(d + a.dst[k]);
+    for (uint32_t i = threadIdx.x; i < a.len[k] / 2u; i += blockDim.x) dp[i] = sp[i];
+  }
+  // the padding of a row (rows are rounded up to 16 bytes) stays defined
+  const uint32_t end = a.dst[a.n - 1] + a.len[a.n - 1];
+  for (uint32_t i = end + threadIdx.x; i < dst_rowb; i += blockDim.x) d[i] = 0;
+}
+}  // namespace
+
+extern "C" int ie_b200_mat_part(int kind, const void *d_src, uint32_t rows, uint32_t cols, uint32_t n_ranges, const uint32_t *row0, const uint32_t *n_rows,
+                                uint32_t col0, uint32_t n_cols, void *d_dst, void *stream) {
+  if (!d_src || !d_dst || !row0 || !n_rows || n_ranges == 0) return fail(IE_B200_E_ARG, "ie_b200_mat_part: NULL argument");
+  if (kind != IE_B200_MAT_F32 && kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
+    return fail(IE_B200_E_ARG, "ie_b200_mat_part: matrix kind %d", kind);
+  const uint32_t unit = kind == IE_B200_MAT_F32 ? 1u : kind == IE_B200_MAT_Q4 ? 32u : 256u;
+  if (n_cols == 0 || col0 % unit || n_cols % unit || (uint64_t)col0 + n_cols > cols)
+    return fail(IE_B200_E_SIZE, "ie_b200_mat_part: columns [%u, %u) of %u (whole blocks of %u)", col0, col0 + n_cols, cols, unit);
+  if (kind != IE_B200_MAT_F32)
+    if (int e = check_shape("ie_b200_mat_part", kind, rows, cols)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint32_t nb = cols / 32u, b0 = col0 / 32u, nbl = n_cols / 32u;
+  PartAreas a = {};
+  switch (kind) {
+    case IE_B200_MAT_F32: a.n = 1, a.src[0] = col0 * 4u, a.dst[0] = 0, a.len[0] = n_cols * 4u; break;
+    case IE_B200_MAT_Q4:
+      a.n = 2;
+      a.src[0] = b0 * 16u, a.dst[0] = 0, a.len[0] = nbl * 16u;
+      a.src[1] = nb * 16u + b0 * 2u, a.dst[1] = nbl * 16u, a.len[1] = nbl * 2u;
+      break;
+    case IE_B200_MAT_Q4K:
+      a.n = 2;
+      a.src[0] = b0 * 16u, a.dst[0] = 0, a.len[0] = nbl * 16u;
+      a.src[1] = nb * 16u + (b0 / 8u) * 16u, a.dst[1] = nbl * 16u, a.len[1] = (nbl / 8u) * 16u;
+      break;
+    default:  // Q6_K
+      a.n = 4;
+      a.src[0] = b0 * 16u, a.dst[0] = 0, a.len[0] = nbl * 16u;
+      a.src[1] = nb * 16u + b0 * 8u, a.dst[1] = nbl * 16u, a.len[1] = nbl * 8u;
+      a.src[2] = nb * 24u + b0 * 2u, a.dst[2] = nbl * 24u, a.len[2] = nbl * 2u;
+      a.src[3] = nb * 26u + (b0 / 8u) * 2u, a.dst[3] = nbl * 26u, a.len[3] = (nbl / 8u) * 2u;
+      break;
+  }
+  const size_t src_rowb = row_bytes_of(kind, cols), dst_rowb = row_bytes_of(kind, n_cols);
+  uint32_t out_row = 0;
+  for (uint32_t k = 0; k < n_ranges; k++) {
+    if ((uint64_t)row0[k] + n_rows[k] > rows) return fail(IE_B200_E_SIZE, "ie_b200_mat_part: rows [%u, %u) of %u", row0[k], row0[k] + n_rows[k], rows);
+    if (n_rows[k] == 0) continue;
+    mat_part_kernel<<<n_rows[k], 128, 0, st>>>(static_cast<const uint8_t *>(d_src), src_rowb, static_cast<uint8_t *>(d_dst), dst_rowb, row0[k], out_row, a);
+    IEB_LAUNCHED("mat_part_kernel");
+    out_row += n_rows[k];
+  }
+  return IE_B200_OK;
+}

@@ -65,6 +65,21 @@ class Mat:
         return Mat(kind, rows, cols, dst)
 
 
+def mat_part(w: Mat, row_ranges, col0: int, n_cols: int) -> Mat:
+    """The part of w that a tensor-parallel shard holds: row_ranges = [(first row, rows), ...] one after the other, columns
+    [col0, col0 + n_cols) in whole blocks."""
+    import ctypes as C
+
+    lib = _lib.load()
+    n = len(row_ranges)
+    r0 = (C.c_uint32 * n)(*[int(a) for a, _ in row_ranges])
+    nr = (C.c_uint32 * n)(*[int(b) for _, b in row_ranges])
+    rows = sum(int(b) for _, b in row_ranges)
+    dst = torch.empty(max(lib.ie_b200_mat_bytes(w.kind, rows, n_cols), 16), dtype=torch.uint8, device=w.data.device)
+    check(lib.ie_b200_mat_part(w.kind, w.data.data_ptr(), w.rows, w.cols, n, r0, nr, col0, n_cols, dst.data_ptr(), _stream()))
+    return Mat(w.kind, rows, n_cols, dst)
+
+
 def quant_q8(x: torch.Tensor) -> torch.Tensor:
     """x: [T, n] or [n] f32 -> uint8 [T, 40 n/32] Q8 buffers."""
     x2 = x.reshape(-1, x.shape[-1]).contiguous()

@@ -74,6 +74,12 @@ int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t rows, uint32_
 /* The reference's repacked arrays qw / qs (on the device, as ie_mat_sink
  * receives them from model_load, src/model.c:649-658) -> streaming layout. */
 int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, uint32_t rows, uint32_t cols, void *d_dst, void *stream);
+/* A part of a matrix that is already in the streaming layout, again in the streaming layout: n_ranges row ranges
+ * [row0[k], row0[k] + n_rows[k]) one after the other, columns [col0, col0 + n_cols) (whole blocks: 32 columns for
+ * MAT_Q4, 256 for the K kinds, any for MAT_F32). row0 / n_rows are host arrays. What a tensor-parallel shard holds of a
+ * matrix; the reference, which runs on one device, has no counterpart. */
+int ie_b200_mat_part(int kind, const void *d_src, uint32_t rows, uint32_t cols, uint32_t n_ranges, const uint32_t *row0, const uint32_t *n_rows,
+                     uint32_t col0, uint32_t n_cols, void *d_dst, void *stream);
 
 /* ------------------------------------------------------------- kernels */
 

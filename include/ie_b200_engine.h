@@ -39,8 +39,9 @@ enum {
                            * nh = 1: a holds interleaved (gate_i, up_i) pairs, b receives silu(gate_i) * up_i: the form
                            * for a gate / up matrix loaded with alternating rows (one 8-byte load per output) */
   IE_B200_OP_ARGMAX = 7,  /* b = {argmax(a), prob}                                        (OP_ARGMAX) */
-  IE_B200_OP_ALLREDUCE = 8, /* c = c + sum over the ranks of a (n floats per token), done by the caller: the
-                               engine only stops an enqueue range here (see ie_b200_engine_enqueue) */
+  IE_B200_OP_ALLREDUCE = 8, /* c = (res if given, else c) + sum over the ranks of a (n floats per token): served by the
+                               engine once a collective is attached (ie_b200_engine_set_collective); without one the
+                               caller does it and an enqueue range only stops here (ie_b200_engine_enqueue) */
   IE_B200_OP_ADD = 9      /* c = a + b, n floats                                          (OP_ADD) */
 };
 
@@ -84,6 +85,11 @@ void ie_b200_engine_destroy(ie_b200_engine *e);
 int ie_b200_engine_add_mat_gguf(ie_b200_engine *e, int ggml_type, uint32_t rows, uint32_t cols, const void *h_bytes);
 int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs);
 int ie_b200_engine_add_mat_device(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *d_data);
+/* A tensor-parallel shard's part of a matrix given as _ref gives the whole one: the row ranges [row0[k], row0[k] + n_rows[k])
+ * one after the other (q / k / v heads or the gate / up slices of a merged matrix: src/model.h:55-58) and the columns
+ * [col0, col0 + n_cols) (whole blocks: 32 columns for MAT_Q4, 256 for the K kinds). No reference counterpart. */
+int ie_b200_engine_add_mat_ref_part(ie_b200_engine *e, int kind, uint32_t rows, uint32_t cols, const void *h_qw, const void *h_qs, uint32_t n_ranges,
+                                    const uint32_t *row0, const uint32_t *n_rows, uint32_t col0, uint32_t n_cols);
 /* A float vector (norm weight, bias); returns its handle. */
 int ie_b200_engine_add_vec(ie_b200_engine *e, const float *h_f, uint32_t n);
 /* RoPE tables [n_ctx][hd / 2] (graph.rope_cos / rope_sin, src/model.c:1655-1664). */
@@ -139,6 +145,16 @@ int ie_b200_engine_decode(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_
 /* backend.run (src/backend.h:20), section 0: T tokens at positions pos .. pos + T - 1; out: T argmax
  * tokens (only out[T-1] is meaningful when last_only), prob: T floats or NULL. */
 int ie_b200_engine_run(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob);
+/* step, decode and run in two halves each: _begin enqueues the work and the copies of its results into the engine's own
+ * pinned memory and returns without waiting; _end waits and hands the results out (step = step_begin + step_end, and so
+ * on). For a host thread that drives the shards of one model on several GPUs (ie_b200_tp_group in ie_b200_tp.h): it
+ * begins every shard before it ends any, since each shard's kernels wait for the others' rows. No reference counterpart. */
+int ie_b200_engine_step_begin(ie_b200_engine *e, uint32_t tok, uint32_t pos, int timed);
+int ie_b200_engine_step_end(ie_b200_engine *e, float *h_logits, uint32_t *next, double *ms);
+int ie_b200_engine_decode_begin(ie_b200_engine *e, uint32_t tok, uint32_t pos, uint32_t K);
+int ie_b200_engine_decode_end(ie_b200_engine *e, uint32_t *h_out, double *ms);
+int ie_b200_engine_run_begin(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only);
+int ie_b200_engine_run_end(ie_b200_engine *e, uint32_t *out, float *prob);
 /* backend.read_rows / copy_rows (src/backend.h:27-31) on arena offsets: n rows of `stride` bytes. */
 int ie_b200_engine_read_rows(ie_b200_engine *e, uint64_t off, uint32_t stride, uint32_t r0, uint32_t n, void *h_dst);
 int ie_b200_engine_copy_rows(ie_b200_engine *e, uint64_t dst_off, uint32_t dst_stride, uint32_t d0, uint64_t src_off, uint32_t src_stride,

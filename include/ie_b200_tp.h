@@ -63,6 +63,25 @@ int ie_b200_ar_reduce_norm(ie_b200_allreduce *a, const float *d_part, float *d_x
 int ie_b200_ar_argmax(ie_b200_allreduce *a, const float *d_logits, uint32_t *d_result, uint32_t vocab_offset, uint32_t *d_err, void *stream);
 void ie_b200_ar_destroy(ie_b200_allreduce *a);
 
+/* ---- one host thread, several GPUs ----
+ * The form a single-process host program needs (the reference's ie-run is one; src/cuda.c uses this under IE_TP=N): the
+ * group owns the all-reduce states of `world` distinct GPUs of this process (devices: world device ordinals, NULL for
+ * 0 .. world-1; peer access is enabled both ways and the states are connected in place, no IPC). The caller makes the
+ * rank's device current with _use, builds that rank's shard engine (ie_b200_engine.h) and attaches it; step / run /
+ * decode then have backend.step / run semantics (src/backend.h:10, :20) for the whole sharded model: every rank's work is
+ * enqueued before any rank is waited for, h_logits receives the ranks' vocabulary slices side by side, and the ranks'
+ * tokens are checked to be identical. max_floats: the largest exchange (dim floats, times the chunk length T if prompt
+ * chunks should take one exchange per stop). _destroy detaches the engines; they stay the caller's to destroy. */
+struct ie_b200_engine;
+typedef struct ie_b200_tp_group ie_b200_tp_group;
+int ie_b200_tp_group_create(uint32_t world, const int *devices, uint32_t max_floats, ie_b200_tp_group **out);
+int ie_b200_tp_group_use(ie_b200_tp_group *g, uint32_t rank);
+int ie_b200_tp_group_attach(ie_b200_tp_group *g, uint32_t rank, struct ie_b200_engine *e, uint32_t vocab_offset, uint32_t vocab_local);
+int ie_b200_tp_group_step(ie_b200_tp_group *g, uint32_t tok, uint32_t pos, float *h_logits, uint32_t *next, double *ms);
+int ie_b200_tp_group_run(ie_b200_tp_group *g, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only, uint32_t *out, float *prob);
+int ie_b200_tp_group_decode(ie_b200_tp_group *g, uint32_t tok, uint32_t pos, uint32_t K, uint32_t *h_out, double *ms);
+void ie_b200_tp_group_destroy(ie_b200_tp_group *g);
+
 #ifdef __cplusplus
 }
 #endif

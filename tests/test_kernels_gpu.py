@@ -118,6 +118,37 @@ def test_repack_layout_and_gemv_bit_exact(ora, cuda, golden_kernels, lib, typ, s
             assert (d == ora.block_dots_q4(qw, rows, nb, xq)).all(), key
 
 
+@pytest.mark.parametrize("typ,rows,cols,ranges,c0,c1", [
+    (synth.GGML_Q4_0, 96, 1024, [(8, 16), (40, 8), (72, 24)], 0, 1024),    # q / k / v heads of a merged matrix
+    (synth.GGML_Q4_0, 64, 1024, [(0, 64)], 352, 352 + 160),                # a column slice that is not a multiple of 8 blocks
+    (synth.GGML_Q4_K, 48, 1536, [(0, 48)], 512, 1280),
+    (synth.GGML_Q6_K, 40, 2048, [(0, 40)], 1024, 2048),
+    (synth.GGML_Q6_K, 40, 1024, [(4, 9), (20, 20)], 256, 768),             # rows and columns at once
+    (synth.GGML_F32, 512, 512, [(256, 256)], 0, 512),                      # a vocabulary slice of an f32 head
+])
+def test_mat_part_is_the_repack_of_the_slice(cuda, lib, typ, rows, cols, ranges, c0, c1):
+    """A shard's part of a matrix, cut from the streaming layout on the device, equals the streaming layout of the same rows and
+    columns cut from the GGUF tensor on the host, byte for byte (row padding included)."""
+    from amd_c_b200 import kernels as K
+    from amd_c_b200.backend import shard_cols
+
+    rng = np.random.default_rng(rows * 7 + cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
+    whole = K.Mat.from_gguf(typ, dev(raw, cuda), rows, cols)
+    part = K.mat_part(whole, ranges, c0, c1 - c0)
+    per_row = raw.reshape(rows, -1)
+    sub = np.concatenate([shard_cols(per_row[r0: r0 + n].reshape(-1), typ, n, cols, c0, c1).reshape(n, -1) for r0, n in ranges])
+    n_rows = sum(n for _, n in ranges)
+    want = K.Mat.from_gguf(typ, dev(np.ascontiguousarray(sub).reshape(-1), cuda), n_rows, c1 - c0)
+    assert part.rows == n_rows and part.cols == c1 - c0
+    nbytes = lib.ie_b200_mat_bytes(part.kind, n_rows, c1 - c0)
+    rowb = lib.ie_b200_row_bytes(part.kind, c1 - c0)
+    used = {MAT_Q4: 18, MAT_Q4K: 18, MAT_Q6K: 26, MAT_F32: 128}[part.kind] * ((c1 - c0) // 32) + (((c1 - c0) // 128) if part.kind == MAT_Q6K else 0)
+    got_b, want_b = part.data.cpu().numpy()[:nbytes].reshape(n_rows, rowb), want.data.cpu().numpy()[:nbytes].reshape(n_rows, rowb)
+    assert (got_b[:, :used] == want_b[:, :used]).all()
+    assert (got_b[:, used:] == 0).all()
+
+
 @pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 1000, 4096), (synth.GGML_Q4_0, 260, 14336), (synth.GGML_Q4_K, 520, 3584),
                                            (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944), (synth.GGML_Q4_K, 96, 5120)])
 def test_gemv_model_shapes_with_epilogue(ora, cuda, typ, rows, cols):

@@ -109,6 +109,32 @@ def test_prefill_chunks_match_single_steps(cuda):
     assert got == want
 
 
+def test_step_graph_follows_the_positions(cuda):
+    """The step graph sizes its attention for a bound on the positions (512, 1024, ...) and is captured again when the
+    positions outgrow it: steps across the bounds of a 2304-position context (half cache, heads of 128: the tensor-core
+    attention, its short-context cluster form below 512 positions) give the logits of one-token runs, which launch every op
+    for the whole context, on a second engine fed the same tokens."""
+    cfg = gguf.make_model(gguf.config("tiny-128"), seed=0)
+    rng = np.random.default_rng(11)
+    n_ctx = 2304
+    toks = [int(t) for t in rng.integers(0, cfg.vocab, 1100)]
+    a, b = Backend(cfg, n_ctx, T=64), Backend(cfg, n_ctx, T=64)
+    la, lb = np.zeros(cfg.vocab, np.float32), np.zeros(cfg.vocab, np.float32)
+    for lo, hi in ((0, 448), (448, 960)):  # most of the way in chunks, the same on both engines
+        for p0 in range(lo, hi, 64):
+            a.run(0, toks[p0: p0 + 64], p0)
+            b.run(0, toks[p0: p0 + 64], p0)
+        worst = 0.0
+        for pos in range(hi, hi + 70):  # 448 .. 517 crosses 512, 960 .. 1029 crosses 1024
+            a.step(toks[pos], pos, la)
+            b.run(0, [toks[pos]], pos)
+            lb[:] = np.ascontiguousarray(b.read_rows("logits", 0, 1)[0, : 4 * cfg.vocab]).view(np.float32)
+            worst = max(worst, rel_err(la, lb))
+        assert worst <= 3e-2, worst  # both run on the half cache: 1e-6 until a rounding flips
+    a.close()
+    b.close()
+
+
 @pytest.mark.parametrize("name", ["tiny", "tiny-k", "tiny-128"])
 def test_prompt_chunks_on_the_half_cache(cuda, ora, name):
     """The prompt path of the performance configuration: chunks of 32 tokens (the tensor-core GEMM takes 17 tokens and
@@ -168,7 +194,7 @@ def test_prompt_chunks_on_the_half_cache(cuda, ora, name):
         assert nxt == first
 
 
-VARIANTS = [{"IE_B200_PDL": "0"}, {"IE_B200_ATTN_FUSE": "0"}, {"IE_B200_NORM": "tail"}, {"IE_B200_NORM": "prologue"}, {"IE_B200_ATTN": "scalar"},
+VARIANTS = [{"IE_B200_PDL": "0"}, {"IE_B200_ATTN_FUSE": "0"}, {"IE_B200_NORM": "tail"}, {"IE_B200_NORM": "prologue"}, {"IE_B200_ATTN": "scalar"}, {"IE_B200_ATTN": "single"},
             {"IE_B200_GEMM": "0"}, {"IE_B200_GEMM": "mma"}, {"IE_B200_PREFILL_ATTN": "0"}, {"IE_B200_STEP": "auto"}, {"IE_B200_SWIGLU": "gemv"}]
 
 
@@ -219,7 +245,8 @@ def test_step_argument_checks(cuda):
     b.close()
 
 
-def test_ie_run_drop_in(cuda, tmp_path):
+@pytest.mark.parametrize("model", ["tiny", "tiny-k"])
+def test_ie_run_drop_in(cuda, tmp_path, model):
     """The reference's own ie-run host program (main.c, gen.c, model.c, plan.c compiled unchanged) linked with
     src/cuda.c: `--backend gpu` prints the same greedy ids as `--backend cpu`, token by token (--dump-logits
     forces one-token steps) and with the prompt run as a chunk. Skipped where the binary was never built."""
@@ -230,13 +257,13 @@ def test_ie_run_drop_in(cuda, tmp_path):
     exe = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "ie-run-cuda"
     if not exe.is_file():
         pytest.skip("oracle/_ref/ie-run-cuda not built (reference tree absent at build time)")
-    cfg = gguf.make_model(gguf.config("tiny"), seed=0)
+    cfg = gguf.make_model(gguf.config(model), seed=0)  # tiny: llama, Q4_0; tiny-k: qwen2 (biases, the other RoPE pairing), K-quants
     path = tmp_path / "tiny.gguf"
     gguf.write_gguf(path, cfg)
     env = {**os.environ, "IE_KV_F32": "1"}
 
     def run(*extra):
-        r = subprocess.run([str(exe), str(path), "--tokens", "1,2,3,7,900,12", "--n", "24", "--ctx", "64", *extra], capture_output=True, text=True,
+        r = subprocess.run([str(exe), str(path), "--tokens", "1,2,3,7,300,12", "--n", "24", "--ctx", "64", *extra], capture_output=True, text=True,
                            timeout=300, env=env)
         assert r.returncode == 0, r.stderr[-2000:]
         line = [ln for ln in r.stdout.splitlines() if ln.startswith("ids:")][0]
@@ -252,14 +279,15 @@ def test_ie_run_drop_in(cuda, tmp_path):
     # Teacher-forced by their own tokens, the two runs agree to ~1e-7 until a rounding step flips somewhere (one
     # int8 of a Q8 activation: about 1e-3 of a 256-wide vector); the flipped value stays in the KV cache, so from
     # there on the logits differ by a few 1e-3 and the runs may part at a close call. Require: 1e-4 on at least
-    # the first 8 positions, the same tokens there, and bounded drift (2e-2) while the tokens still agree.
+    # the first 8 positions (4 for the K-quant model), the same tokens there, and bounded drift (2e-2) while the tokens still agree.
     errs = []
     for pos, ((tc, c), (tg, g)) in enumerate(zip(lc, lg)):
         if tc != tg:
             break
         errs.append(rel_err(g, c))
     print("ie-run cpu vs gpu, relative logit error per position:", " ".join(f"{e:.1e}" for e in errs))
-    assert len(errs) >= 9 and max(errs[:8]) <= REL, errs
+    n_tight = 8 if model == "tiny" else 4  # tiny-k's first flip comes at the fifth position
+    assert len(errs) >= 9 and max(errs[:n_tight]) <= REL, errs
     assert max(errs) <= 2e-2, errs
     assert got[:9] == want[:9]
     chunked = run("--backend", "gpu", "--chunk", "4")  # the prompt in chunks of 4 through backend.run

@@ -1,5 +1,5 @@
 """Worker of the tensor-parallel GPU tests (launched by torch.distributed.run, one process per GPU): decode a small
-model sharded over the ranks, in the step mode given as the first argument (graph | kernel), and compare with the
+model (second argument, default tiny-tp) sharded over the ranks, in the step mode given as the first argument (graph | kernel), and compare with the
 unsharded engine on rank 0's GPU: the gathered logits of the first steps within 1e-4 of the logit scale (the cross-rank
 sum adds the ranks' partials in rank order instead of one row sum: a different float order, nothing else), the greedy
 tokens identical on every rank and equal to the unsharded engine's wherever its top-two gap allows."""
@@ -19,11 +19,12 @@ from amd_c_b200.tp import TensorParallelBackend  # noqa: E402
 
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "graph"
+    model = sys.argv[2] if len(sys.argv) > 2 else "tiny-tp"  # tiny-tp: llama, Q4_0; tiny-k: qwen2 with biases, Q4_K / Q6_K matrices, f32 head
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', rank))}")
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    cfg = gguf.make_model(gguf.config("tiny-tp"), seed=0)
+    cfg = gguf.make_model(gguf.config(model), seed=0)
     kv_f32 = mode == "graph"  # the persistent kernel runs on the half cache
     n_ctx, n_gen, prompt = 160, 40, [1, 2, 3]
     tpb = TensorParallelBackend(Backend(cfg, n_ctx, T=24, kv_f32=kv_f32, tp=world, rank=rank, device=dev, step_mode=mode), dist.group.WORLD)
