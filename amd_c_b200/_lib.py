@@ -11,9 +11,9 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libie_b200.so"
 
-MAT_Q4, MAT_F32, MAT_Q4K, MAT_Q6K = 0, 1, 3, 4
-GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
-GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
+MAT_Q4, MAT_F32, MAT_Q8, MAT_Q4K, MAT_Q6K = 0, 1, 2, 3, 4
+GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q8_0: MAT_Q8, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
 
 _vp, _u32, _sz, _int, _f32 = C.c_void_p, C.c_uint32, C.c_size_t, C.c_int, C.c_float
 

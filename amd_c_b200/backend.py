@@ -20,7 +20,7 @@ import numpy as np
 from . import _lib
 from ._lib import GGML_TO_MAT, MAT_F32, check
 from .gguf import ModelConfig
-from .synth import GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K
+from .synth import GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0
 
 NONE = 0xFFFFFFFFFFFFFFFF
 OP_EMBED, OP_RMSNORM, OP_QUANT, OP_GEMV, OP_ROPE_KV, OP_ATTN, OP_SWIGLU, OP_ARGMAX, OP_ALLREDUCE, OP_ADD = range(10)
@@ -62,7 +62,7 @@ def shard_rows(raw: np.ndarray, typ: int, rows: int, cols: int, r0: int, r1: int
 
 def shard_cols(raw, typ: int, rows: int, cols: int, c0: int, c1: int):
     """Columns [c0, c1) of a GGUF tensor: whole 32-blocks (Q4_0) or 256 super-blocks (K kinds). Works on numpy or torch uint8."""
-    gran, bb = {GGML_Q4_0: (32, 18), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210), GGML_F32: (1, 4)}[typ]
+    gran, bb = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210), GGML_F32: (1, 4)}[typ]
     if c0 % gran or c1 % gran:
         raise ValueError(f"column split [{c0}, {c1}) is not a multiple of the {gran}-weight block of GGML type {typ}")
     v = raw.reshape(rows, cols // gran, bb)

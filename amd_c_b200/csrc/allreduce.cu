@@ -398,9 +398,11 @@ namespace ieb {
 int gemv_push_act(ie_b200_allreduce *a, int kind, const void *d_w, uint32_t rows, uint32_t cols, const ActSrc &act, bool plain, float *d_part, cudaStream_t st) {
   if (!a || !d_w || !d_part || !(plain ? (const void *)act.xf : (const void *)act.xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: NULL argument");
   if (!a->connected) return fail(IE_B200_E_STATE, "ie_b200_gemv_push: peers not connected");
-  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: matrix kind %d", kind);
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q8 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
+    return fail(IE_B200_E_ARG, "ie_b200_gemv_push: matrix kind %d", kind);
   if (rows == 0 || rows % 32u || rows > a->d.max_n) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u rows (a multiple of 32, at most %u)", rows, a->d.max_n);
-  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u) || cols / 32u > 1024u) return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u columns", cols);
+  if (cols == 0 || cols % ((kind == IE_B200_MAT_Q4 || kind == IE_B200_MAT_Q8) ? 32u : 256u) || cols / 32u > 1024u)
+    return fail(IE_B200_E_SIZE, "ie_b200_gemv_push: %u columns", cols);
   if (!aligned16(d_w) || !aligned16(plain ? (const void *)act.xf : (const void *)act.xq)) return fail(IE_B200_E_ARG, "ie_b200_gemv_push: 16-byte alignment");
   ArPush push;
   ar_push_info(a, &push);

@@ -78,6 +78,7 @@ __host__ __device__ inline size_t row_bytes_of(int kind, uint32_t cols) {
   const size_t nb = cols / 32u;
   switch (kind) {
     case IE_B200_MAT_Q4: return round16(nb * 18u);
+    case IE_B200_MAT_Q8: return round16(nb * 34u);
     case IE_B200_MAT_Q4K: return nb * 16u + (nb / 8u) * 16u;
     case IE_B200_MAT_Q6K: return round16(nb * 26u + (nb / 8u) * 2u);
     default: return (size_t)cols * 4u;

@@ -5,6 +5,7 @@
 #include <climits>
 #include <cstdlib>
 #include <cstring>
+#include <cstdio>
 #include <vector>
 
 #include "common.cuh"
@@ -164,8 +165,10 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       if (T == 1 && stream_ok(m))
         return ie_b200_gemv_stream(m.kind, m.d, m.rows, m.cols, a, static_cast<float *>(b), bias, static_cast<float *>(res), st);
       // a prompt chunk (the reference's threshold, src/hip.c:965): the tensor-core GEMM reads the weights once per 128 tokens
-      if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm) {
-        if (!e->gemm_mma && o.a_stride % 16u == 0) {  // tcgen05 / tensor memory
+      const bool tc_ok = !e->gemm_mma && o.a_stride % 16u == 0;
+      // (Q8_0 has no mma.sync form: where the tcgen05 kernel cannot run it takes the multi-token GEMV below, 8 tokens per pass)
+      if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm && (tc_ok || m.kind != IE_B200_MAT_Q8)) {
+        if (tc_ok) {  // tcgen05 / tensor memory
           EMat &mm = e->mats[o.mat];
           if (mm.tc_exp == INT32_MIN)
             if (int r = ie_b200_mat_tc_exp(mm.kind, mm.d, mm.rows, mm.cols, &mm.tc_exp, st)) return r;
@@ -471,33 +474,47 @@ extern "C" int ie_b200_engine_create(const ie_b200_engine_desc *desc, ie_b200_en
   return IE_B200_OK;
 }
 
+// A release that fails must not leave its error behind for the next launch check to find (cudaPeekAtLastError): note it in
+// the library's error text, on stderr, and clear it.
+static void released(cudaError_t r, const char *what) {
+  if (r == cudaSuccess) return;
+  fprintf(stderr, "libie_b200: %s while releasing an engine: %s\n", what, cudaGetErrorString(r));
+  cuda_fail(r, what);
+  (void)cudaGetLastError();
+}
+#define IEB_RELEASE(call) released((call), #call)
+
 extern "C" void ie_b200_engine_destroy(ie_b200_engine *e) {
   if (!e) return;
-  cudaSetDevice(e->device);
-  if (e->stream) cudaStreamSynchronize(e->stream);
-  if (e->step_graph) cudaGraphExecDestroy(e->step_graph);
+  IEB_RELEASE(cudaSetDevice(e->device));
+  if (e->stream) IEB_RELEASE(cudaStreamSynchronize(e->stream));
+  if (e->step_graph) IEB_RELEASE(cudaGraphExecDestroy(e->step_graph));
   for (auto &m : e->mats)
-    if (m.owned) cudaFree(m.d);
-  for (auto &v : e->vecs) cudaFree(v.d);
-  cudaFree(e->arena), cudaFree(e->kc), cudaFree(e->vc), cudaFree(e->rope_cos), cudaFree(e->rope_sin), cudaFree(e->scalars);
-  cudaFree(e->attn_part), cudaFree(e->attn_count), cudaFree(e->argmax_part), cudaFree(e->hist), cudaFree(e->err);
-  cudaFree(e->gemm_scratch), cudaFree(e->topk_scratch);
-  cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax), cudaFree(e->sk_bar), cudaFree(e->sk_trace);
-  if (e->h_scalars) cudaFreeHost(e->h_scalars);
-  if (e->h_result) cudaFreeHost(e->h_result);
-  if (e->ev0) cudaEventDestroy(e->ev0);
-  if (e->ev1) cudaEventDestroy(e->ev1);
-  if (e->stream) cudaStreamDestroy(e->stream);
+    if (m.owned) IEB_RELEASE(cudaFree(m.d));
+  for (auto &v : e->vecs) IEB_RELEASE(cudaFree(v.d));
+  IEB_RELEASE(cudaFree(e->arena)), IEB_RELEASE(cudaFree(e->kc)), IEB_RELEASE(cudaFree(e->vc)), IEB_RELEASE(cudaFree(e->rope_cos));
+  IEB_RELEASE(cudaFree(e->rope_sin)), IEB_RELEASE(cudaFree(e->scalars));
+  IEB_RELEASE(cudaFree(e->attn_part)), IEB_RELEASE(cudaFree(e->attn_count)), IEB_RELEASE(cudaFree(e->argmax_part)), IEB_RELEASE(cudaFree(e->hist));
+  IEB_RELEASE(cudaFree(e->err));
+  IEB_RELEASE(cudaFree(e->gemm_scratch)), IEB_RELEASE(cudaFree(e->topk_scratch));
+  IEB_RELEASE(cudaFree(e->d_prog)), IEB_RELEASE(cudaFree(e->sk_part)), IEB_RELEASE(cudaFree(e->sk_amax)), IEB_RELEASE(cudaFree(e->sk_bar));
+  IEB_RELEASE(cudaFree(e->sk_trace));
+  if (e->h_scalars) IEB_RELEASE(cudaFreeHost(e->h_scalars));
+  if (e->h_result) IEB_RELEASE(cudaFreeHost(e->h_result));
+  if (e->ev0) IEB_RELEASE(cudaEventDestroy(e->ev0));
+  if (e->ev1) IEB_RELEASE(cudaEventDestroy(e->ev1));
+  if (e->stream) IEB_RELEASE(cudaStreamDestroy(e->stream));
   delete e;
 }
 
 static int kind_of_ggml(int t) {
-  return t == IE_B200_GGML_F32 ? IE_B200_MAT_F32 : t == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : t == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K
-         : t == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
+  return t == IE_B200_GGML_F32 ? IE_B200_MAT_F32 : t == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : t == IE_B200_GGML_Q8_0 ? IE_B200_MAT_Q8
+         : t == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K : t == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
 }
 static size_t gguf_bytes(int t, uint32_t rows, uint32_t cols) {
   const size_t n = (size_t)rows * cols;
-  return t == IE_B200_GGML_F32 ? n * 4u : t == IE_B200_GGML_Q4_0 ? n / 32u * 18u : t == IE_B200_GGML_Q4_K ? n / 256u * 144u : n / 256u * 210u;
+  return t == IE_B200_GGML_F32 ? n * 4u : t == IE_B200_GGML_Q4_0 ? n / 32u * 18u : t == IE_B200_GGML_Q8_0 ? n / 32u * 34u
+         : t == IE_B200_GGML_Q4_K ? n / 256u * 144u : n / 256u * 210u;
 }
 
 // Invalidate the captured step graph: the op list or a handle table changed.
@@ -539,6 +556,7 @@ extern "C" int ie_b200_engine_add_mat_ref(ie_b200_engine *e, int kind, uint32_t 
   switch (kind) {
     case IE_B200_MAT_F32: qw_n = (size_t)rows * cols * 4u, qs_n = 0; break;
     case IE_B200_MAT_Q4: qw_n = n * 16u, qs_n = n * 2u; break;
+    case IE_B200_MAT_Q8: qw_n = n * 32u, qs_n = n * 2u; break;
     case IE_B200_MAT_Q4K: qw_n = n * 16u, qs_n = (n + (size_t)rows * (nb / 8u) * 2u) * 2u; break;
     case IE_B200_MAT_Q6K: qw_n = n * 24u, qs_n = (n + (size_t)rows * (nb / 8u)) * 2u; break;
     default: return fail(IE_B200_E_ARG, "ie_b200_engine_add_mat_ref: kind %d unsupported", kind);
@@ -701,7 +719,7 @@ static int build_program(ie_b200_engine *e) {
       case IE_B200_OP_GEMV: {
         if (o.mat < 0) return 0;
         const EMat &m = e->mats[o.mat];
-        if (!gemv_direct_ok(m.kind, m.cols)) return 0;
+        if (!gemv_direct_ok(m.kind, m.cols) || m.kind == IE_B200_MAT_Q8) return 0;  // (no Q8_0 instantiation in the persistent kernel)
         StepPhase p = {};
         p.kind = PH_GEMV, p.mkind = m.kind, p.w = static_cast<const uint8_t *>(m.d), p.rowb = row_bytes_of(m.kind, m.cols), p.rows = m.rows, p.nb = m.cols / 32u;
         p.y = reinterpret_cast<float *>(A(o.b)), p.bias = o.vec >= 0 ? e->vecs[o.vec].d : nullptr, p.res = reinterpret_cast<const float *>(A(o.res));
@@ -798,7 +816,6 @@ static int build_program(ie_b200_engine *e) {
   e->sk_kset = has_q4 && has_k ? 2 : has_k ? 1 : 0;
   StepArgs &a = e->sk;
   a.smax = step_kernel_smax(d.n_kv);
-  cudaFree(e->gemm_scratch), cudaFree(e->topk_scratch);
   cudaFree(e->d_prog), cudaFree(e->sk_part), cudaFree(e->sk_amax);
   e->d_prog = nullptr, e->sk_part = nullptr, e->sk_amax = nullptr;
   IEB_CUDA(cudaMalloc(&e->d_prog, ph.size() * sizeof(StepPhase)));
@@ -813,7 +830,6 @@ static int build_program(ie_b200_engine *e) {
   ar_push_info(e->ar, &a.push);
   a.vocab_off = e->vocab_off, a.wait_ns = AR_WAIT_NS, a.trace = e->sk_trace;
   a.knobs = 3u;
-  if (const char *kn = getenv("IE_B200_SK_KNOBS")) a.knobs = (uint32_t)atoi(kn);
   e->kernel_state = 1;
   return 1;
 }
@@ -1126,7 +1142,7 @@ extern "C" uint64_t ie_b200_engine_weight_bytes_per_token(ie_b200_engine *e) {
     if (o.kind != IE_B200_OP_GEMV || o.mat < 0) continue;
     const EMat &m = e->mats[o.mat];
     const uint64_t nblk = (uint64_t)m.rows * (m.cols / 32u);
-    wb += m.kind == IE_B200_MAT_F32 ? (uint64_t)m.rows * m.cols * 4u : m.kind == IE_B200_MAT_Q6K ? nblk * 210u / 8u : nblk * 18u;
+    wb += m.kind == IE_B200_MAT_F32 ? (uint64_t)m.rows * m.cols * 4u : m.kind == IE_B200_MAT_Q6K ? nblk * 210u / 8u : m.kind == IE_B200_MAT_Q8 ? nblk * 34u : nblk * 18u;
   }
   return wb;
 }

@@ -210,6 +210,24 @@ struct TcBlk<IE_B200_MAT_Q4> {
   }
 };
 template <>
+struct TcBlk<IE_B200_MAT_Q8> {
+  uint4 w0, w1;
+  uint16_t d;
+  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
+    w0 = __ldg(reinterpret_cast<const uint4 *>(rp + 32u * (size_t)b));
+    w1 = __ldg(reinterpret_cast<const uint4 *>(rp + 32u * (size_t)b + 16u));
+    d = __ldg(reinterpret_cast<const uint16_t *>(rp + 32u * (size_t)nb + 2u * b));
+  }
+  // columns 16 hf .. 16 hf + 15: the signed bytes of the first (hf = 0) or second four words
+  __device__ __forceinline__ void values16(float (&f)[16], uint32_t, uint32_t hf) const {
+    const float df = h2f(d);
+    const uint4 v = hf ? w1 : w0;
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 16; j++) f[j] = __fmul_rn(df, (float)(int8_t)(ww[j >> 2] >> (8 * (j & 3))));
+  }
+};
+template <>
 struct TcBlk<IE_B200_MAT_Q4K> {
   uint4 w, h;
   __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
@@ -452,13 +470,15 @@ namespace ieb {
 template <int KIND>
 __global__ void __launch_bounds__(256) tc_wbound_kernel(const uint8_t *w, size_t rowb, uint32_t rows, uint32_t nb, uint32_t *out_bits) {
   float m = 0.0f;
-  const uint32_t per = KIND == IE_B200_MAT_Q4 ? nb : nb / 8u;
+  const uint32_t per = (KIND == IE_B200_MAT_Q4 || KIND == IE_B200_MAT_Q8) ? nb : nb / 8u;
   for (size_t i = (size_t)blockIdx.x * 256u + threadIdx.x; i < (size_t)rows * per; i += (size_t)gridDim.x * 256u) {
     const uint8_t *rp = w + (i / per) * rowb;
     const uint32_t b = (uint32_t)(i % per);
     float v;
     if (KIND == IE_B200_MAT_Q4) {
       v = 8.0f * fabsf(h2f(*reinterpret_cast<const uint16_t *>(rp + 16u * (size_t)nb + 2u * b)));
+    } else if (KIND == IE_B200_MAT_Q8) {
+      v = 128.0f * fabsf(h2f(*reinterpret_cast<const uint16_t *>(rp + 32u * (size_t)nb + 2u * b)));
     } else if (KIND == IE_B200_MAT_Q4K) {
       const uint32_t dd = *reinterpret_cast<const uint32_t *>(rp + 16u * (size_t)nb + 16u * b);
       v = 63.0f * (15.0f * fabsf(h2f((uint16_t)(dd & 0xFFFFu))) + fabsf(h2f((uint16_t)(dd >> 16))));
@@ -474,7 +494,8 @@ __global__ void __launch_bounds__(256) tc_wbound_kernel(const uint8_t *w, size_t
 
 extern "C" int ie_b200_mat_tc_exp(int kind, const void *d_w, uint32_t rows, uint32_t cols, int *h_exp, void *stream) {
   if (!d_w || !h_exp) return fail(IE_B200_E_ARG, "ie_b200_mat_tc_exp: NULL pointer");
-  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_mat_tc_exp: matrix kind %d", kind);
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q8 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
+    return fail(IE_B200_E_ARG, "ie_b200_mat_tc_exp: matrix kind %d", kind);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint32_t *d_bits = nullptr, bits = 0;
   IEB_CUDA(cudaMalloc(&d_bits, 4));
@@ -483,6 +504,7 @@ extern "C" int ie_b200_mat_tc_exp(int kind, const void *d_w, uint32_t rows, uint
   const size_t rowb = row_bytes_of(kind, cols);
   const uint32_t nb = cols / 32u, grid = 592;
   if (kind == IE_B200_MAT_Q4) tc_wbound_kernel<IE_B200_MAT_Q4><<<grid, 256, 0, st>>>(w, rowb, rows, nb, d_bits);
+  else if (kind == IE_B200_MAT_Q8) tc_wbound_kernel<IE_B200_MAT_Q8><<<grid, 256, 0, st>>>(w, rowb, rows, nb, d_bits);
   else if (kind == IE_B200_MAT_Q4K) tc_wbound_kernel<IE_B200_MAT_Q4K><<<grid, 256, 0, st>>>(w, rowb, rows, nb, d_bits);
   else tc_wbound_kernel<IE_B200_MAT_Q6K><<<grid, 256, 0, st>>>(w, rowb, rows, nb, d_bits);
   count_launch();
@@ -506,8 +528,9 @@ extern "C" int ie_b200_gemm_tc(int kind, const void *d_w, uint32_t rows, uint32_
                                const float *d_res, uint32_t T, size_t x_stride, size_t y_stride, size_t res_stride, void *d_scratch, size_t scratch_bytes,
                                uint32_t *d_err, void *stream) {
   if (!d_w || !d_xq || !d_y || !d_scratch) return fail(IE_B200_E_ARG, "ie_b200_gemm_tc: NULL pointer");
-  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K) return fail(IE_B200_E_ARG, "ie_b200_gemm_tc: matrix kind %d (Q4_0, Q4_K, Q6_K)", kind);
-  if (cols == 0 || cols % (kind == IE_B200_MAT_Q4 ? 32u : 256u)) return fail(IE_B200_E_SIZE, "ie_b200_gemm_tc: %u columns", cols);
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q8 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
+    return fail(IE_B200_E_ARG, "ie_b200_gemm_tc: matrix kind %d (Q4_0, Q8_0, Q4_K, Q6_K)", kind);
+  if (cols == 0 || cols % ((kind == IE_B200_MAT_Q4 || kind == IE_B200_MAT_Q8) ? 32u : 256u)) return fail(IE_B200_E_SIZE, "ie_b200_gemm_tc: %u columns", cols);
   if (rows == 0 || T == 0) return IE_B200_OK;
   if (!aligned16(d_w) || !aligned16(d_xq) || (x_stride & 15u) || (y_stride & 3u) || (res_stride & 3u) || ((uintptr_t)d_scratch & 255u))
     return fail(IE_B200_E_ARG, "ie_b200_gemm_tc: the matrix and the Q8 rows must be 16-byte aligned, strides multiples of 4, the scratch 256-byte aligned");
@@ -526,12 +549,13 @@ extern "C" int ie_b200_gemm_tc(int kind, const void *d_w, uint32_t rows, uint32_
   TcArgs a = {};
   a.w = static_cast<const uint8_t *>(d_w), a.rowb = row_bytes_of(kind, cols), a.rows = rows, a.nb = nb, a.T = T;
   a.blocks_per_split = (nb + splits - 1u) / splits;
-  if (kind != IE_B200_MAT_Q4) a.blocks_per_split = (a.blocks_per_split + 7u) & ~7u;
+  if (kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q8) a.blocks_per_split = (a.blocks_per_split + 7u) & ~7u;
   a.bp = bp, a.y = d_y, a.bias = d_bias, a.res = d_res, a.ys = y_stride, a.rs = res_stride, a.partial = partial, a.err = d_err;
   a.w_scale = ldexpf(1.0f, w_exp), a.tok_inv = tok_inv;
   const uint32_t used_splits = (nb + a.blocks_per_split - 1u) / a.blocks_per_split;
   const dim3 grid((rows + TC_ROWS - 1) / TC_ROWS, nt, partial ? used_splits : 1u);
-  void (*k)(TcArgs) = kind == IE_B200_MAT_Q4 ? gemm_tc_kernel<IE_B200_MAT_Q4> : kind == IE_B200_MAT_Q4K ? gemm_tc_kernel<IE_B200_MAT_Q4K> : gemm_tc_kernel<IE_B200_MAT_Q6K>;
+  void (*k)(TcArgs) = kind == IE_B200_MAT_Q4 ? gemm_tc_kernel<IE_B200_MAT_Q4> : kind == IE_B200_MAT_Q8 ? gemm_tc_kernel<IE_B200_MAT_Q8>
+                      : kind == IE_B200_MAT_Q4K ? gemm_tc_kernel<IE_B200_MAT_Q4K> : gemm_tc_kernel<IE_B200_MAT_Q6K>;
   if (int r = ensure_dynamic_smem(reinterpret_cast<const void *>(k), TC_SMEM)) return r;
   IEB_LAUNCH_PDL("gemm_tc_kernel", k, grid, dim3(TC_THREADS), TC_SMEM, st, a);
   if (partial)

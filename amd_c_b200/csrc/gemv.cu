@@ -197,6 +197,15 @@ __global__ void block_dots_kernel(const uint8_t *__restrict__ w, size_t rowb, ui
   const uint8_t *rp = w + (size_t)r * rowb;
   const uint4 *a = reinterpret_cast<const uint4 *>(xq) + 2u * b;
   const uint4 a0 = a[0], a1 = a[1];
+  if (KIND == IE_B200_MAT_Q8) {  // eight signed dot4 (core/ie_core.h:220-233)
+    const int *q8 = reinterpret_cast<const int *>(rp + 32u * (size_t)b);
+    const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+    int dot = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) dot = __dp4a(q8[k], av[k], dot);
+    dots[i] = dot;
+    return;
+  }
   const uint4 q = *reinterpret_cast<const uint4 *>(rp + 16u * (size_t)b);
   if (KIND == IE_B200_MAT_Q6K) {
     const uint2 hw = *reinterpret_cast<const uint2 *>(rp + 16u * (size_t)nb + 8u * b);
@@ -276,6 +285,7 @@ extern "C" int ie_b200_gemv(int kind, const void *d_w, uint32_t rows, uint32_t c
   if (T > 1 && (x_stride & 15u) != 0) return fail(IE_B200_E_ARG, "ie_b200_gemv: x_stride must be a multiple of 16");
   switch (kind) {
     case IE_B200_MAT_Q4: return launch_q<IE_B200_MAT_Q4, 2, 4>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
+    case IE_B200_MAT_Q8: return launch_q<IE_B200_MAT_Q8, 2, 2>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
     case IE_B200_MAT_Q4K:
       if (nb % 8u) return fail(IE_B200_E_SIZE, "ie_b200_gemv: Q4_K needs cols %% 256 == 0");
       return launch_q<IE_B200_MAT_Q4K, 2, 4>(d_w, rows, cols, d_x, d_y, d_bias, d_res, T, x_stride, y_stride, res_stride, st);
@@ -297,6 +307,7 @@ extern "C" int ie_b200_block_dots(int kind, const void *d_w, uint32_t rows, uint
   const uint8_t *w = static_cast<const uint8_t *>(d_w), *x = static_cast<const uint8_t *>(d_xq);
   switch (kind) {
     case IE_B200_MAT_Q4: block_dots_kernel<IE_B200_MAT_Q4><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
+    case IE_B200_MAT_Q8: block_dots_kernel<IE_B200_MAT_Q8><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
     case IE_B200_MAT_Q4K: block_dots_kernel<IE_B200_MAT_Q4K><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
     case IE_B200_MAT_Q6K: block_dots_kernel<IE_B200_MAT_Q6K><<<grid, 256, 0, st>>>(w, row_bytes_of(kind, cols), rows, nb, x, d_dots); break;
     default: return fail(IE_B200_E_ARG, "ie_b200_block_dots: unknown matrix kind %d", kind);

@@ -43,6 +43,26 @@ struct Blk<IE_B200_MAT_Q4, SMEM> {
   }
 };
 
+// Q8_0: 32 signed bytes at 32 b (weights 4k .. 4k + 3 in word k, as the activations), f16 scale at 32 nb + 2 b.
+template <bool SMEM>
+struct Blk<IE_B200_MAT_Q8, SMEM> {
+  uint4 w0, w1;
+  uint16_t d;
+  __device__ __forceinline__ void load(const uint8_t *rp, uint32_t b, uint32_t nb) {
+    w0 = blk_ld16<SMEM>(rp + 32u * (size_t)b);
+    w1 = blk_ld16<SMEM>(rp + 32u * (size_t)b + 16u);
+    d = blk_ld2<SMEM>(rp + 32u * (size_t)nb + 2u * b);
+  }
+  // acc = acc + (dw * da) * (float)dot, dot = eight signed dot4 in word order.
+  __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int, uint32_t) const {
+    int dot = __dp4a((int)w0.x, (int)a0.x, 0);
+    dot = __dp4a((int)w0.y, (int)a0.y, dot), dot = __dp4a((int)w0.z, (int)a0.z, dot), dot = __dp4a((int)w0.w, (int)a0.w, dot);
+    dot = __dp4a((int)w1.x, (int)a1.x, dot), dot = __dp4a((int)w1.y, (int)a1.y, dot), dot = __dp4a((int)w1.z, (int)a1.z, dot);
+    dot = __dp4a((int)w1.w, (int)a1.w, dot);
+    return __fadd_rn(acc, __fmul_rn(__fmul_rn(h2f(d), da), (float)dot));
+  }
+};
+
 // Q4_K: nibbles as Q4_0; per super-block a 16 B header at 16 nb + 16 (b / 8).
 template <bool SMEM>
 struct Blk<IE_B200_MAT_Q4K, SMEM> {

@@ -209,6 +209,7 @@ template <bool NORM, bool TP>
 int dispatch_direct(int kind, const GdArgs &a, cudaStream_t st) {
   switch (kind) {
     case IE_B200_MAT_Q4: return pick_direct<IE_B200_MAT_Q4, NORM, TP>(a, st);
+    case IE_B200_MAT_Q8: return pick_direct<IE_B200_MAT_Q8, NORM, TP>(a, st);
     case IE_B200_MAT_Q4K: return pick_direct<IE_B200_MAT_Q4K, NORM, TP>(a, st);
     case IE_B200_MAT_Q6K: return pick_direct<IE_B200_MAT_Q6K, NORM, TP>(a, st);
     default: return fail(IE_B200_E_ARG, "gemv_direct: matrix kind %d has no streaming kernel", kind);

@@ -42,6 +42,17 @@ __global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t *w, size_t 
     o[e] = __fmul_rn(d, (float)((int)nib - 8));
   }
 }
+// Q8_0 row: d * (float)(int8) weight (mat_row, src/cpu.c:257-265)
+__global__ void __launch_bounds__(256) embed_q8_kernel(const uint8_t *w, size_t rowb, uint32_t nb, const uint32_t *tok, float *out, size_t os) {
+  pdl_prologue();
+  const uint32_t t = blockIdx.y;
+  const uint8_t *rp = w + (size_t)tok[t] * rowb;
+  float *o = row_ptr(out, os, t);
+  for (uint32_t e = blockIdx.x * blockDim.x + threadIdx.x; e < nb * 32u; e += gridDim.x * blockDim.x) {
+    const float d = h2f(reinterpret_cast<const uint16_t *>(rp + 32u * (size_t)nb)[e >> 5]);
+    o[e] = __fmul_rn(d, (float)reinterpret_cast<const int8_t *>(rp)[e]);
+  }
+}
 __global__ void __launch_bounds__(256) embed_f32_kernel(const float *w, uint32_t cols, const uint32_t *tok, float *out, size_t os) {
   pdl_prologue();
   const uint32_t t = blockIdx.y;
@@ -362,6 +373,10 @@ extern "C" int ie_b200_embed(int kind, const void *d_w, uint32_t cols, const uin
   if (kind == IE_B200_MAT_Q4) {
     if (cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_embed: cols %u is not a multiple of 32", cols);
     IEB_LAUNCH_PDL("embed_q4_kernel", embed_q4_kernel, grid, dim3(256), 0, st, static_cast<const uint8_t *>(d_w), row_bytes_of(kind, cols),
+                   cols / 32u, d_tok, d_out, out_stride);
+  } else if (kind == IE_B200_MAT_Q8) {
+    if (cols % 32u) return fail(IE_B200_E_SIZE, "ie_b200_embed: cols %u is not a multiple of 32", cols);
+    IEB_LAUNCH_PDL("embed_q8_kernel", embed_q8_kernel, grid, dim3(256), 0, st, static_cast<const uint8_t *>(d_w), row_bytes_of(kind, cols),
                    cols / 32u, d_tok, d_out, out_stride);
   } else if (kind == IE_B200_MAT_F32) {
     IEB_LAUNCH_PDL("embed_f32_kernel", embed_f32_kernel, grid, dim3(256), 0, st, static_cast<const float *>(d_w), cols, d_tok, d_out, out_stride);

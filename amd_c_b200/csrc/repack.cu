@@ -43,6 +43,20 @@ __global__ void repack_gguf_q4_0(const uint8_t *__restrict__ src, uint32_t rows,
   reinterpret_cast<uint16_t *>(rp + 16u * (size_t)nb)[b] = s[0];
 }
 
+// Q8_0: 34-byte blocks {f16 d, 32 int8}; the weight bytes keep their order (word k = weights 4k .. 4k + 3).
+__global__ void repack_gguf_q8_0(const uint8_t *__restrict__ src, uint32_t rows, uint32_t nb, uint8_t *dst, size_t rowb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nb) return;
+  const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
+  const uint16_t *s = reinterpret_cast<const uint16_t *>(src + i * 34u);  // 34 i is even
+  uint8_t *rp = dst + (size_t)r * rowb;
+  uint32_t w[8];
+  for (int k = 0; k < 8; k++) w[k] = (uint32_t)s[1 + 2 * k] | ((uint32_t)s[2 + 2 * k] << 16);
+  *reinterpret_cast<uint4 *>(rp + 32u * (size_t)b) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4 *>(rp + 32u * (size_t)b + 16u) = make_uint4(w[4], w[5], w[6], w[7]);
+  reinterpret_cast<uint16_t *>(rp + 32u * (size_t)nb)[b] = s[0];
+}
+
 __global__ void repack_gguf_q4_k(const uint8_t *__restrict__ src, uint32_t rows, uint32_t nb, uint8_t *dst, size_t rowb) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * nb) return;
@@ -100,6 +114,12 @@ __global__ void repack_ref_kernel(const uint32_t *__restrict__ qw, const uint16_
   if (i >= (size_t)rows * nb) return;
   const uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
   uint8_t *rp = dst + (size_t)r * rowb;
+  if (KIND == IE_B200_MAT_Q8) {  // eight words per block (core/ie_core.h:201-205), scales one per block
+    *reinterpret_cast<uint4 *>(rp + 32u * (size_t)b) = *reinterpret_cast<const uint4 *>(qw + i * 8u);
+    *reinterpret_cast<uint4 *>(rp + 32u * (size_t)b + 16u) = *reinterpret_cast<const uint4 *>(qw + i * 8u + 4u);
+    reinterpret_cast<uint16_t *>(rp + 32u * (size_t)nb)[b] = qs[i];
+    return;
+  }
   *reinterpret_cast<uint4 *>(rp + 16u * (size_t)b) = *reinterpret_cast<const uint4 *>(qw + i * 4u);
   if (KIND == IE_B200_MAT_Q4) {
     reinterpret_cast<uint16_t *>(rp + 16u * (size_t)nb)[b] = qs[i];
@@ -142,8 +162,8 @@ extern "C" int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t ro
     IEB_CUDA(cudaMemcpyAsync(d_dst, d_src, (size_t)rows * cols * 4u, cudaMemcpyDeviceToDevice, st));
     return IE_B200_OK;
   }
-  const int kind = ggml_type == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : ggml_type == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K
-                   : ggml_type == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
+  const int kind = ggml_type == IE_B200_GGML_Q4_0 ? IE_B200_MAT_Q4 : ggml_type == IE_B200_GGML_Q8_0 ? IE_B200_MAT_Q8
+                   : ggml_type == IE_B200_GGML_Q4_K ? IE_B200_MAT_Q4K : ggml_type == IE_B200_GGML_Q6_K ? IE_B200_MAT_Q6K : -1;
   if (kind < 0) return fail(IE_B200_E_ARG, "ie_b200_repack_gguf: GGML type %d unsupported", ggml_type);
   if (int e = check_shape("ie_b200_repack_gguf", kind, rows, cols)) return e;
   const uint32_t nb = cols / 32u;
@@ -152,6 +172,7 @@ extern "C" int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t ro
   const uint8_t *s = static_cast<const uint8_t *>(d_src);
   uint8_t *d = static_cast<uint8_t *>(d_dst);
   if (kind == IE_B200_MAT_Q4) repack_gguf_q4_0<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
+  else if (kind == IE_B200_MAT_Q8) repack_gguf_q8_0<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
   else if (kind == IE_B200_MAT_Q4K) repack_gguf_q4_k<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
   else repack_gguf_q6_k<<<grid, 128, 0, st>>>(s, rows, nb, d, rowb);
   IEB_LAUNCHED("repack_gguf");
@@ -176,6 +197,7 @@ extern "C" int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, 
   const uint16_t *qs = static_cast<const uint16_t *>(d_qs);
   uint8_t *d = static_cast<uint8_t *>(d_dst);
   if (kind == IE_B200_MAT_Q4) repack_ref_kernel<IE_B200_MAT_Q4><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
+  else if (kind == IE_B200_MAT_Q8) repack_ref_kernel<IE_B200_MAT_Q8><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
   else if (kind == IE_B200_MAT_Q4K) repack_ref_kernel<IE_B200_MAT_Q4K><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
   else if (kind == IE_B200_MAT_Q6K) repack_ref_kernel<IE_B200_MAT_Q6K><<<grid, 128, 0, st>>>(qw, qs, rows, nb, d, rowb);
   else return fail(IE_B200_E_ARG, "ie_b200_repack_ref: unknown matrix kind %d", kind);
@@ -208,9 +230,9 @@ __global__ void mat_part_kernel(const uint8_t *src, size_t src_rowb, uint8_t *ds
 extern "C" int ie_b200_mat_part(int kind, const void *d_src, uint32_t rows, uint32_t cols, uint32_t n_ranges, const uint32_t *row0, const uint32_t *n_rows,
                                 uint32_t col0, uint32_t n_cols, void *d_dst, void *stream) {
   if (!d_src || !d_dst || !row0 || !n_rows || n_ranges == 0) return fail(IE_B200_E_ARG, "ie_b200_mat_part: NULL argument");
-  if (kind != IE_B200_MAT_F32 && kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
+  if (kind != IE_B200_MAT_F32 && kind != IE_B200_MAT_Q4 && kind != IE_B200_MAT_Q8 && kind != IE_B200_MAT_Q4K && kind != IE_B200_MAT_Q6K)
     return fail(IE_B200_E_ARG, "ie_b200_mat_part: matrix kind %d", kind);
-  const uint32_t unit = kind == IE_B200_MAT_F32 ? 1u : kind == IE_B200_MAT_Q4 ? 32u : 256u;
+  const uint32_t unit = kind == IE_B200_MAT_F32 ? 1u : (kind == IE_B200_MAT_Q4 || kind == IE_B200_MAT_Q8) ? 32u : 256u;
   if (n_cols == 0 || col0 % unit || n_cols % unit || (uint64_t)col0 + n_cols > cols)
     return fail(IE_B200_E_SIZE, "ie_b200_mat_part: columns [%u, %u) of %u (whole blocks of %u)", col0, col0 + n_cols, cols, unit);
   if (kind != IE_B200_MAT_F32)
@@ -224,6 +246,11 @@ extern "C" int ie_b200_mat_part(int kind, const void *d_src, uint32_t rows, uint
       a.n = 2;
       a.src[0] = b0 * 16u, a.dst[0] = 0, a.len[0] = nbl * 16u;
       a.src[1] = nb * 16u + b0 * 2u, a.dst[1] = nbl * 16u, a.len[1] = nbl * 2u;
+      break;
+    case IE_B200_MAT_Q8:
+      a.n = 2;
+      a.src[0] = b0 * 32u, a.dst[0] = 0, a.len[0] = nbl * 32u;
+      a.src[1] = nb * 32u + b0 * 2u, a.dst[1] = nbl * 32u, a.len[1] = nbl * 2u;
       break;
     case IE_B200_MAT_Q4K:
       a.n = 2;

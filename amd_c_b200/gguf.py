@@ -13,7 +13,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 from . import synth
-from .synth import GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K
+from .synth import GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K, GGML_Q8_0
 
 T_U32, T_F32, T_STR = 4, 6, 8
 ALIGN = 32
@@ -83,6 +83,9 @@ def config(name: str) -> ModelConfig:
     if name == "tiny-kq":  # K-quants end to end (Q6_K output head, Q4_0 embedding), qwen2-style bias / rope, 16 / 8 heads of 64
         return ModelConfig(arch="qwen2", n_layer=2, dim=1024, ffn=1024, n_head=16, n_kv=8, vocab=512, ctx=256, eps=1e-6, rope_base=1e6,
                            qkv_bias=True, t_attn=GGML_Q4_K, t_v=GGML_Q6_K, t_ffn=GGML_Q4_K, t_down=GGML_Q6_K, t_embd=GGML_Q4_0, t_out=GGML_Q6_K)
+    if name == "tiny-q8":  # every matrix Q8_0 (what the reference keeps as its MAT_Q8 kind), f32 embedding, Q8_0 output head
+        return ModelConfig(n_layer=3, dim=256, ffn=768, n_head=8, n_kv=4, vocab=1024, ctx=512, t_attn=GGML_Q8_0, t_v=GGML_Q8_0, t_ffn=GGML_Q8_0,
+                           t_down=GGML_Q8_0, t_out=GGML_Q8_0)
     if name == "tiny-tp":  # all Q4_0, 16 / 8 heads of 64: shards over 2, 4 or 8 ranks
         return ModelConfig(n_layer=3, dim=1024, ffn=2048, n_head=16, n_kv=8, vocab=1024, ctx=512, t_embd=GGML_Q4_0, t_out=GGML_Q4_0)
     if name == "llama3-8b":

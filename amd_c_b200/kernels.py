@@ -10,7 +10,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import GGML_TO_MAT, MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K, check
+from ._lib import GGML_TO_MAT, MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K, MAT_Q8, check
 
 
 def _stream() -> int:
@@ -38,11 +38,11 @@ class Mat:
 
     @property
     def algorithmic_bytes(self) -> int:
-        """Bytes one GEMV must read: 18 B per Q4_0 / Q4_K block, 26.25 B per
+        """Bytes one GEMV must read: 18 B per Q4_0 / Q4_K block, 34 B per Q8_0 block, 26.25 B per
         Q6_K block, 4 B per f32 weight."""
         if self.kind == MAT_F32:
             return self.rows * self.cols * 4
-        per = {MAT_Q4: 18.0, MAT_Q4K: 18.0, MAT_Q6K: 26.25}[self.kind]
+        per = {MAT_Q4: 18.0, MAT_Q8: 34.0, MAT_Q4K: 18.0, MAT_Q6K: 26.25}[self.kind]
         return int(self.rows * self.nb * per)
 
     @staticmethod

@@ -14,8 +14,8 @@ from __future__ import annotations
 
 import numpy as np
 
-GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
-BLOCK_BYTES = {GGML_Q4_0: (32, 18), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
+GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+BLOCK_BYTES = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
 
 
 def gguf_nbytes(ggml_type: int, rows: int, cols: int) -> int:
@@ -46,6 +46,20 @@ def q4_0_normal(rng: np.random.Generator, rows: int, cols: int, sigma: float = 0
     return q4_0_from_weights(rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(sigma))
 
 
+def q8_0_normal(rng: np.random.Generator, rows: int, cols: int, sigma: float = 0.02) -> np.ndarray:
+    """GGUF Q8_0 bytes uint8 [rows, cols/32, 34] of N(0, sigma) weights: per block d = f16(amax / 127), q = round(w / d)."""
+    nb = cols // 32
+    wb = (rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(sigma)).reshape(rows, nb, 32)
+    d = (np.abs(wb).max(axis=2) / np.float32(127.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(df[..., None] != 0, np.round(wb / df[..., None]), 0.0)
+    blk = np.empty((rows, nb, 34), dtype=np.uint8)
+    blk[:, :, 0:2] = d.view(np.uint8).reshape(rows, nb, 2)
+    blk[:, :, 2:] = np.clip(q, -127, 127).astype(np.int8).view(np.uint8)
+    return blk
+
+
 def q4_k_random(rng: np.random.Generator, rows: int, cols: int, scale: float = 0.02) -> np.ndarray:
     """GGUF Q4_K bytes uint8 [rows, cols/256, 144]: random scales/codes, fixed small f16 d and dmin."""
     nsb = rows * cols // 256
@@ -67,6 +81,8 @@ def q6_k_random(rng: np.random.Generator, rows: int, cols: int, scale: float = 0
 def make_gguf_bytes(ggml_type: int, rng: np.random.Generator, rows: int, cols: int, sigma: float = 0.02) -> np.ndarray:
     if ggml_type == GGML_Q4_0:
         return q4_0_normal(rng, rows, cols, sigma)
+    if ggml_type == GGML_Q8_0:
+        return q8_0_normal(rng, rows, cols, sigma)
     if ggml_type == GGML_Q4_K:
         return q4_k_random(rng, rows, cols, sigma)
     if ggml_type == GGML_Q6_K:
@@ -93,6 +109,23 @@ def q4_0_normal_torch(gen, rows: int, cols: int, sigma: float = 0.02, device="cu
         q = (q + 8).clamp_(0, 15).to(torch.uint8)
         out[r0:r1, :, 0:2] = d.view(torch.uint8).reshape(r1 - r0, nb, 2)
         out[r0:r1, :, 2:] = q[:, :, :16] | (q[:, :, 16:] << 4)
+    return out
+
+
+def q8_0_normal_torch(gen, rows: int, cols: int, sigma: float = 0.02, device="cuda", chunk_rows: int = 8192):
+    """GGUF Q8_0 bytes as a uint8 CUDA tensor [rows, cols/32, 34] of N(0, sigma) weights, built in row chunks on the device."""
+    import torch
+
+    nb = cols // 32
+    out = torch.empty((rows, nb, 34), dtype=torch.uint8, device=device)
+    for r0 in range(0, rows, chunk_rows):
+        r1 = min(rows, r0 + chunk_rows)
+        w = torch.randn((r1 - r0, nb, 32), generator=gen, device=device, dtype=torch.float32) * sigma
+        d = (w.abs().amax(dim=2) / 127.0).to(torch.float16)
+        df = d.to(torch.float32).unsqueeze(2)
+        q = torch.where(df != 0, torch.round(w / df), torch.zeros_like(w)).clamp_(-127, 127).to(torch.int8)
+        out[r0:r1, :, 0:2] = d.view(torch.uint8).reshape(r1 - r0, nb, 2)
+        out[r0:r1, :, 2:] = q.view(torch.uint8)
     return out
 
 

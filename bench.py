@@ -251,11 +251,13 @@ def time_gemvs(b, reps: int = 20, repeats: int = 5) -> dict:
 # inside a benchmark run; the timing beside it is live.
 NCU_TRAFFIC_RATIO = 33.095 / 33.030
 SWEEP_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
+OTHER_KIND_SHAPES = [("q4_k", 37888, 3584), ("q6_k", 3584, 18944), ("q8_0", 14336, 4096)]  # the other weight kinds, one large shape each
 
 
 def time_gemv_sweep(device, peak: float) -> list[dict]:
-    """The stand-alone Q4_0 x Q8 GEMV at the Llama-3-8B shapes: seeded N(0, 0.02) weights, >= 1 GB of rotated copies
-    per shape (nothing is served from L2), 20 warm-up + 200 timed launches in one graph between two CUDA events."""
+    """The stand-alone Q4_0 x Q8 GEMV at the Llama-3-8B shapes (and one large shape of each other weight kind): seeded weights,
+    >= 1 GB of rotated copies per shape (nothing is served from L2), 20 warm-up + 200 timed launches in one graph between two
+    CUDA events."""
     import torch
 
     from amd_c_b200 import kernels as K
@@ -264,9 +266,11 @@ def time_gemv_sweep(device, peak: float) -> list[dict]:
     gen = torch.Generator(device=device).manual_seed(0)
     out = []
     s = torch.cuda.Stream(device=device)
-    for rows, cols in SWEEP_SHAPES:
-        raw = synth.q4_0_normal_torch(gen, rows, cols, device=device)
-        m = K.Mat.from_gguf(synth.GGML_Q4_0, raw.reshape(-1), rows, cols)
+    for kind, rows, cols in [("q4_0", r, c) for r, c in SWEEP_SHAPES] + OTHER_KIND_SHAPES:
+        typ = {"q4_0": synth.GGML_Q4_0, "q8_0": synth.GGML_Q8_0, "q4_k": synth.GGML_Q4_K, "q6_k": synth.GGML_Q6_K}[kind]
+        raw = (synth.q4_0_normal_torch(gen, rows, cols, device=device) if kind == "q4_0" else
+               synth.q8_0_normal_torch(gen, rows, cols, device=device) if kind == "q8_0" else synth.k_random_torch(typ, gen, rows, cols, device=device))
+        m = K.Mat.from_gguf(typ, raw.reshape(-1), rows, cols)
         del raw
         ncopy = max(4, min(64, int(1.2e9 // m.data.numel())))
         copies = [K.Mat(m.kind, rows, cols, m.data.clone()) for _ in range(ncopy)]
@@ -292,7 +296,7 @@ def time_gemv_sweep(device, peak: float) -> list[dict]:
                 reps.append(e0.elapsed_time(e1) * 1e3 / n)
         us, us_min = statistics.median(reps), min(reps)
         gbs = m.algorithmic_bytes / us / 1e3
-        out.append({"shape": f"{rows}x{cols}", "us": round(us, 2), "us_min": round(us_min, 2), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3),
+        out.append({"kind": kind, "shape": f"{rows}x{cols}", "us": round(us, 2), "us_min": round(us_min, 2), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3),
                     "frac_of_nominal_8000": round(gbs / 8000.0, 3), "copies": ncopy, "repeats": 5})
         del copies, m, g
         torch.cuda.empty_cache()

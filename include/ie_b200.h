@@ -37,10 +37,10 @@ enum {
 };
 
 /* Matrix kinds: the reference's MAT_* numbering (src/model.h:15). */
-enum { IE_B200_MAT_Q4 = 0, IE_B200_MAT_F32 = 1, IE_B200_MAT_Q4K = 3, IE_B200_MAT_Q6K = 4 };
+enum { IE_B200_MAT_Q4 = 0, IE_B200_MAT_F32 = 1, IE_B200_MAT_Q8 = 2, IE_B200_MAT_Q4K = 3, IE_B200_MAT_Q6K = 4 };
 
 /* GGML tensor types accepted by the GGUF repack (src/common.h:11-13). */
-enum { IE_B200_GGML_F32 = 0, IE_B200_GGML_Q4_0 = 2, IE_B200_GGML_Q4_K = 12, IE_B200_GGML_Q6_K = 14 };
+enum { IE_B200_GGML_F32 = 0, IE_B200_GGML_Q4_0 = 2, IE_B200_GGML_Q8_0 = 8, IE_B200_GGML_Q4_K = 12, IE_B200_GGML_Q6_K = 14 };
 
 const char *ie_b200_last_error(void);
 /* Number of CUDA devices visible (0 without a driver or a GPU). */
@@ -56,6 +56,7 @@ uint64_t ie_b200_launch_count(void);
  * ie_b200_row_bytes(). A warp that owns a row therefore streams one
  * contiguous span with 16-byte loads, and a group of rows is one bulk copy.
  *   Q4_0: nb x 16 B nibbles (the GGUF nibble bytes), nb x f16 d          = 18 B/block
+ *   Q8_0: nb x 32 B signed bytes (the GGUF weight bytes), nb x f16 d     = 34 B/block
  *   Q4_K: nb x 16 B nibbles (Q4_0 order per sub-block), nb/8 x 16 B
  *         {f16 d, f16 dmin, 8 x 12 bit (sc | mn << 6)}                     = 18 B/block
  *   Q6_K: nb x 16 B low nibbles, nb x 8 B high-bit words, nb x 2 B
@@ -68,7 +69,7 @@ size_t ie_b200_row_bytes(int kind, uint32_t cols);
 size_t ie_b200_mat_bytes(int kind, uint32_t rows, uint32_t cols);
 
 /* GGUF tensor bytes (already on the device) -> streaming layout. Stands in
- * for repack_q4 / repack_q4k / repack_q6k (src/model.c:205, :246, :271).
+ * for repack_q4 / repack_q8 / repack_q4k / repack_q6k (src/model.c:205, :221, :246, :271).
  * ggml_type: IE_B200_GGML_*; F32 is a plain copy. */
 int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t rows, uint32_t cols, void *d_dst, void *stream);
 /* The reference's repacked arrays qw / qs (on the device, as ie_mat_sink
@@ -76,7 +77,7 @@ int ie_b200_repack_gguf(int ggml_type, const void *d_src, uint32_t rows, uint32_
 int ie_b200_repack_ref(int kind, const void *d_qw, const void *d_qs, uint32_t rows, uint32_t cols, void *d_dst, void *stream);
 /* A part of a matrix that is already in the streaming layout, again in the streaming layout: n_ranges row ranges
  * [row0[k], row0[k] + n_rows[k]) one after the other, columns [col0, col0 + n_cols) (whole blocks: 32 columns for
- * MAT_Q4, 256 for the K kinds, any for MAT_F32). row0 / n_rows are host arrays. What a tensor-parallel shard holds of a
+ * MAT_Q4 / MAT_Q8, 256 for the K kinds, any for MAT_F32). row0 / n_rows are host arrays. What a tensor-parallel shard holds of a
  * matrix; the reference, which runs on one device, has no counterpart. */
 int ie_b200_mat_part(int kind, const void *d_src, uint32_t rows, uint32_t cols, uint32_t n_ranges, const uint32_t *row0, const uint32_t *n_rows,
                      uint32_t col0, uint32_t n_cols, void *d_dst, void *stream);
@@ -92,8 +93,8 @@ int ie_b200_quant_q8(const float *d_x, void *d_q, uint32_t nb, uint32_t T, size_
 /* y[T][rows] = W x (+bias) (+res): W in the streaming layout, x a Q8 buffer
  * per token (f32 for MAT_F32). One warp per (row, token); lane l accumulates
  * blocks l, l+32, ... in order and the warp reduces by shuffle-down 16, 8, 4,
- * 2, 1, so the result equals cpu_gemv_q4 / _q4k / _q6k / cpu_gemv_f32 bit for
- * bit (src/cpu.c:64-148, :238-249); epilogue y = acc (+bias[r]), y = res[r] + y
+ * 2, 1, so the result equals cpu_gemv_q4 / _q4k / _q6k / _q8 / cpu_gemv_f32 bit for
+ * bit (src/cpu.c:64-174, :238-249); epilogue y = acc (+bias[r]), y = res[r] + y
  * (src/cpu.c:515-520). Argument list after ie_gemv_q4q8
  * {qw,qs,xq,y,rows,nb,bias,res,...} (src/hip.c:930) and its multi-token
  * forms {...,T,xs,ys,rs} (src/hip.c:1000). res may alias y. */
@@ -157,12 +158,12 @@ int ie_b200_gemv_norm_tail(int kind, const void *d_w, uint32_t rows, uint32_t co
                            const float *d_res, const float *d_norm_w, float eps, float *d_xn_out, void *d_xq_out, uint32_t *d_counter,
                            void *stream);
 
-/* Test hook: the int32 dot of every (row, block) of a Q4_0 / Q4_K matrix
+/* Test hook: the int32 dot of every (row, block) of a Q4_0 / Q8_0 / Q4_K matrix
  * (Q4_K: the unsigned-nibble dot) and, for Q6_K, the two half dots
- * (dots[2 (r nb + b) + h]); what core/ie_core.h:161, :281, :385 define. */
+ * (dots[2 (r nb + b) + h]); what core/ie_core.h:161, :220, :281, :385 define. */
 int ie_b200_block_dots(int kind, const void *d_w, uint32_t rows, uint32_t cols, const void *d_xq, int32_t *d_dots, void *stream);
 
-/* Row `tok` of the token embedding as floats (MAT_Q4 or MAT_F32):
+/* Row `tok` of the token embedding as floats (MAT_Q4, MAT_Q8 or MAT_F32):
  * mat_row (src/cpu.c:252-274), ie_embed_q4 / _f32 (kernels/ie_kernels.c:171-191).
  * d_tok: T token ids on the device. */
 int ie_b200_embed(int kind, const void *d_w, uint32_t cols, const uint32_t *d_tok, float *d_out, uint32_t T, size_t out_stride,

@@ -15,8 +15,8 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 MAT_Q4, MAT_F32, MAT_Q8, MAT_Q4K, MAT_Q6K = 0, 1, 2, 3, 4
-GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
-GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
+GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+GGML_TO_MAT = {GGML_F32: MAT_F32, GGML_Q4_0: MAT_Q4, GGML_Q8_0: MAT_Q8, GGML_Q4_K: MAT_Q4K, GGML_Q6_K: MAT_Q6K}
 
 _vp, _u32, _f32, _int = C.c_void_p, C.c_uint32, C.c_float, C.c_int
 
@@ -50,10 +50,14 @@ class Oracle:
         for name, args in {
             "ora_quant_q8": [_vp, _vp, _u32],
             "ora_repack_q4_0": [_vp, _u32, _u32, _vp, _vp],
+            "ora_repack_q8_0": [_vp, _u32, _u32, _vp, _vp],
             "ora_repack_q4_k": [_vp, _u32, _u32, _vp, _vp],
             "ora_repack_q6_k": [_vp, _u32, _u32, _vp, _vp],
             "ora_block_dots_q4": [_vp, _u32, _u32, _vp, _vp],
             "ora_gemv_q4": [_vp, _vp, _u32, _u32, _vp, _vp],
+            "ora_gemv_q8": [_vp, _vp, _u32, _u32, _vp, _vp],
+            "ora_block_dots_q8": [_vp, _u32, _u32, _vp, _vp],
+            "ora_embed_q8": [_vp, _vp, _u32, _u32, _vp],
             "ora_gemv_q4k": [_vp, _vp, _u32, _u32, _vp, _vp],
             "ora_gemv_q6k": [_vp, _vp, _u32, _u32, _vp, _vp],
             "ora_gemv_f32": [_vp, _u32, _u32, _vp, _vp],
@@ -84,6 +88,9 @@ class Oracle:
         if ggml_type == GGML_Q4_0:
             qw, qs = np.zeros(rows * nb * 4, np.uint32), np.zeros(rows * nb, np.uint16)
             self.lib.ora_repack_q4_0(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
+        elif ggml_type == GGML_Q8_0:
+            qw, qs = np.zeros(rows * nb * 8, np.uint32), np.zeros(rows * nb, np.uint16)
+            self.lib.ora_repack_q8_0(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
         elif ggml_type == GGML_Q4_K:
             qw, qs = np.zeros(rows * nb * 4, np.uint32), np.zeros(rows * nb + rows * (nb // 8) * 2, np.uint16)
             self.lib.ora_repack_q4_k(_ptr(raw), rows, nb, _ptr(qw), _ptr(qs))
@@ -101,7 +108,7 @@ class Oracle:
         if kind == MAT_F32:
             self.lib.ora_gemv_f32(_ptr(qw), rows, cols, _ptr(np.ascontiguousarray(x, np.float32)), _ptr(y))
         else:
-            fn = {MAT_Q4: self.lib.ora_gemv_q4, MAT_Q4K: self.lib.ora_gemv_q4k, MAT_Q6K: self.lib.ora_gemv_q6k}[kind]
+            fn = {MAT_Q4: self.lib.ora_gemv_q4, MAT_Q8: self.lib.ora_gemv_q8, MAT_Q4K: self.lib.ora_gemv_q4k, MAT_Q6K: self.lib.ora_gemv_q6k}[kind]
             fn(_ptr(qw), _ptr(qs), rows, nb, _ptr(x), _ptr(y))
         if bias is not None or res is not None:
             self.lib.ora_epilogue(_ptr(y), rows, _ptr(bias), _ptr(res))
@@ -111,6 +118,16 @@ class Oracle:
         d = np.zeros(rows * nb, dtype=np.int32)
         self.lib.ora_block_dots_q4(_ptr(qw), rows, nb, _ptr(xq), _ptr(d))
         return d
+
+    def block_dots_q8(self, qw: np.ndarray, rows: int, nb: int, xq: np.ndarray) -> np.ndarray:
+        d = np.zeros(rows * nb, dtype=np.int32)
+        self.lib.ora_block_dots_q8(_ptr(qw), rows, nb, _ptr(xq), _ptr(d))
+        return d
+
+    def embed_q8(self, qw, qs, nb: int, r: int) -> np.ndarray:
+        out = np.zeros(nb * 32, np.float32)
+        self.lib.ora_embed_q8(_ptr(qw), _ptr(qs), nb, r, _ptr(out))
+        return out
 
     def embed_q4(self, qw, qs, nb: int, r: int) -> np.ndarray:
         out = np.zeros(nb * 32, np.float32)

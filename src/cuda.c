@@ -10,7 +10,7 @@
  * offsets: src/model.h:177-331) into engine calls. Errors follow the
  * reference's convention: a message and exit(1) through ie_die.
  *
- * Built for llama / qwen2 graphs: EMBED, RMSNORM, QUANT, GEMV (Q4_0, Q4_K,
+ * Built for llama / qwen2 graphs: EMBED, RMSNORM, QUANT, GEMV (Q4_0, Q8_0, Q4_K,
  * Q6_K, f32; bias, residual, fused norm tail), ROPE_KV, ATTN, SWIGLU, ARGMAX.
  * Other architectures' ops (qwen35, flint, MTP, DFlash) are refused by name.
  *
@@ -145,10 +145,11 @@ static part part_of(const cuda_backend *B, const mat *w, int role, uint32_t rank
 static int mat_kind(const mat *w) {
   switch (w->kind) {
     case MAT_Q4: return IE_B200_MAT_Q4;
+    case MAT_Q8: return IE_B200_MAT_Q8;
     case MAT_Q4K: return IE_B200_MAT_Q4K;
     case MAT_Q6K: return IE_B200_MAT_Q6K;
     case MAT_F32: return IE_B200_MAT_F32;
-    default: ie_die("cuda backend: matrix kind %d (Q8_0, Q5_K, IQ4_XS) is not built", w->kind);
+    default: ie_die("cuda backend: matrix kind %d (Q5_K, IQ4_XS) is not built", w->kind);
   }
   return -1;
 }
@@ -362,6 +363,7 @@ static void translate(cuda_backend *B, uint32_t rank, table *mats, table *vecs, 
       if (tp && o->a == tk->swi_buf) e.n = B->ffn_l;
       break;
     case OP_GEMV_Q4:
+    case OP_GEMV_Q8:
     case OP_GEMV_Q4K:
     case OP_GEMV_Q6K:
     case OP_GEMV_F32: {

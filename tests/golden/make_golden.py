@@ -6,13 +6,14 @@ The fixtures hold seeded inputs and the reference's outputs, so that the
 restatement (oracle/ie_oracle.c) and the CUDA kernels can be checked on
 machines that do not have the reference tree.
 
-  kernels.npz  Q8 quantiser outputs; GEMV outputs for Q4_0 / Q4_K / Q6_K on
+  kernels.npz  Q8 quantiser outputs; GEMV outputs for Q4_0 / Q4_K / Q6_K / Q8_0 on
                the shape list of the reference's tests/kernel_test.c plus
                K-quant shapes; the reference's repacked arrays' checksums
   tiny.npz     the tiny 4-layer Q4_0 llama (seed 0): greedy ids of 64 tokens
                from prompt 1,2,3 at context 512, logits of the first 8 steps,
                per-layer residual outputs of steps 0..3
   tiny_k.npz   the K-quant qwen2-style tiny model: 24 greedy ids, logits of 4 steps
+  tiny_q8.npz  the tiny llama with every matrix Q8_0: 24 greedy ids, logits of 4 steps
 """
 from __future__ import annotations
 
@@ -46,7 +47,9 @@ def kernels(ref: Ref) -> None:
     x[64] = 127.5 * 0.01
     x[65:96] = 0.01  # ties at .5 after division
     out["quant_x"], out["quant_q"] = x, ref.quant_q8(x)
-    for typ, shapes, tag in ((synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k")):
+    # (Q8_0 last: the draws of the kinds before it, and so their fixtures, stay what they were)
+    for typ, shapes, tag in ((synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k"),
+                             (synth.GGML_Q8_0, Q4_SHAPES, "q8_0")):
         for rows, nb in shapes:
             cols = nb * 32
             raw = synth.make_gguf_bytes(typ, rng, rows, cols)
@@ -93,5 +96,6 @@ if __name__ == "__main__":
     kernels(r)
     model(r, "tiny", 0, 512, 64, 8, 4, "tiny.npz")
     model(r, "tiny-k", 0, 256, 24, 4, 2, "tiny_k.npz")
+    model(r, "tiny-q8", 0, 256, 24, 4, 2, "tiny_q8.npz")
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -7,13 +7,14 @@ import pytest
 
 from amd_c_b200 import synth
 from conftest import bits
-from oracle.oracle import MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K
+from oracle.oracle import MAT_F32, MAT_Q4, MAT_Q4K, MAT_Q6K, MAT_Q8
 
 pytestmark = pytest.mark.gpu
 
 Q4_SHAPES = [(1, 1), (7, 3), (9, 11), (8, 32), (13, 33), (17, 36), (5, 64), (3, 100), (2, 511)]
 K_SHAPES = [(3, 8), (9, 16), (8, 40), (5, 112), (2, 448)]
-KINDS = [(synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k")]
+KINDS = [(synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k"),
+         (synth.GGML_Q8_0, Q4_SHAPES, "q8_0")]
 
 
 def dev(a, cuda):
@@ -26,6 +27,10 @@ def expected_layout(kind, qw, qs, rows, cols, row_bytes):
     """The streaming layout built in numpy from the reference-form arrays."""
     nb = cols // 32
     out = np.zeros((rows, row_bytes), np.uint8)
+    if kind == MAT_Q8:
+        out[:, : 32 * nb] = qw.view(np.uint8).reshape(rows, 32 * nb)
+        out[:, 32 * nb: 34 * nb] = qs.view(np.uint8).reshape(rows, 2 * nb)
+        return out
     out[:, : 16 * nb] = qw[: rows * nb * 4].view(np.uint8).reshape(rows, 16 * nb)
     if kind == MAT_Q4:
         out[:, 16 * nb: 18 * nb] = qs.view(np.uint8).reshape(rows, 2 * nb)
@@ -106,7 +111,7 @@ def test_repack_layout_and_gemv_bit_exact(ora, cuda, golden_kernels, lib, typ, s
         rowb = lib.ie_b200_row_bytes(kind, cols)
         want = expected_layout(kind, qw, qs, rows, cols, rowb)
         got = m.data.cpu().numpy()[: rows * rowb].reshape(rows, rowb)
-        used = {MAT_Q4: 18 * nb, MAT_Q4K: 18 * nb, MAT_Q6K: 26 * nb + nb // 4}[kind]
+        used = {MAT_Q4: 18 * nb, MAT_Q8: 34 * nb, MAT_Q4K: 18 * nb, MAT_Q6K: 26 * nb + nb // 4}[kind]
         assert (got[:, :used] == want[:, :used]).all(), key
         m2 = K.Mat.from_ref(kind, dev(qw, cuda), dev(qs, cuda), rows, cols)
         assert (m2.data.cpu().numpy()[: rows * rowb].reshape(rows, rowb)[:, :used] == want[:, :used]).all(), key
@@ -116,6 +121,9 @@ def test_repack_layout_and_gemv_bit_exact(ora, cuda, golden_kernels, lib, typ, s
         if kind == MAT_Q4:
             d = K.block_dots(m, dev(xq, cuda)).cpu().numpy()
             assert (d == ora.block_dots_q4(qw, rows, nb, xq)).all(), key
+        if kind == MAT_Q8:
+            d = K.block_dots(m, dev(xq, cuda)).cpu().numpy()
+            assert (d == ora.block_dots_q8(qw, rows, nb, xq)).all(), key
 
 
 @pytest.mark.parametrize("typ,rows,cols,ranges,c0,c1", [
@@ -125,6 +133,7 @@ def test_repack_layout_and_gemv_bit_exact(ora, cuda, golden_kernels, lib, typ, s
     (synth.GGML_Q6_K, 40, 2048, [(0, 40)], 1024, 2048),
     (synth.GGML_Q6_K, 40, 1024, [(4, 9), (20, 20)], 256, 768),             # rows and columns at once
     (synth.GGML_F32, 512, 512, [(256, 256)], 0, 512),                      # a vocabulary slice of an f32 head
+    (synth.GGML_Q8_0, 64, 1024, [(3, 20), (40, 24)], 96, 96 + 480),
 ])
 def test_mat_part_is_the_repack_of_the_slice(cuda, lib, typ, rows, cols, ranges, c0, c1):
     """A shard's part of a matrix, cut from the streaming layout on the device, equals the streaming layout of the same rows and
@@ -143,14 +152,15 @@ def test_mat_part_is_the_repack_of_the_slice(cuda, lib, typ, rows, cols, ranges,
     assert part.rows == n_rows and part.cols == c1 - c0
     nbytes = lib.ie_b200_mat_bytes(part.kind, n_rows, c1 - c0)
     rowb = lib.ie_b200_row_bytes(part.kind, c1 - c0)
-    used = {MAT_Q4: 18, MAT_Q4K: 18, MAT_Q6K: 26, MAT_F32: 128}[part.kind] * ((c1 - c0) // 32) + (((c1 - c0) // 128) if part.kind == MAT_Q6K else 0)
+    used = {MAT_Q4: 18, MAT_Q8: 34, MAT_Q4K: 18, MAT_Q6K: 26, MAT_F32: 128}[part.kind] * ((c1 - c0) // 32) + (((c1 - c0) // 128) if part.kind == MAT_Q6K else 0)
     got_b, want_b = part.data.cpu().numpy()[:nbytes].reshape(n_rows, rowb), want.data.cpu().numpy()[:nbytes].reshape(n_rows, rowb)
     assert (got_b[:, :used] == want_b[:, :used]).all()
     assert (got_b[:, used:] == 0).all()
 
 
 @pytest.mark.parametrize("typ,rows,cols", [(synth.GGML_Q4_0, 1000, 4096), (synth.GGML_Q4_0, 260, 14336), (synth.GGML_Q4_K, 520, 3584),
-                                           (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944), (synth.GGML_Q4_K, 96, 5120)])
+                                           (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944), (synth.GGML_Q4_K, 96, 5120),
+                                           (synth.GGML_Q8_0, 700, 4096), (synth.GGML_Q8_0, 130, 14336)])
 def test_gemv_model_shapes_with_epilogue(ora, cuda, typ, rows, cols):
     """Llama / Qwen column counts, rows not a multiple of the CTA tile, bias + residual, 3 tokens."""
     from amd_c_b200 import kernels as K
@@ -236,6 +246,13 @@ def test_embed_rmsnorm_swiglu_argmax(ora, cuda):
     e = K.embed(m, dev(toks, cuda)).cpu().numpy()
     for i, t in enumerate(toks):
         assert (bits(e[i]) == bits(ora.embed_q4(qw, qs, cols // 32, int(t)))).all()
+    # and of a Q8_0 matrix
+    raw8 = synth.make_gguf_bytes(synth.GGML_Q8_0, rng, rows, cols)
+    _, qw8, qs8 = ora.repack(synth.GGML_Q8_0, raw8, rows, cols)
+    m8 = K.Mat.from_gguf(synth.GGML_Q8_0, dev(raw8, cuda), rows, cols)
+    e8 = K.embed(m8, dev(toks, cuda)).cpu().numpy()
+    for i, t in enumerate(toks):
+        assert (bits(e8[i]) == bits(ora.embed_q8(qw8, qs8, cols // 32, int(t)))).all()
     # RMSNorm: tree sum vs sequential sum -> 1e-5 relative; the Q8 copy must be the quantiser of the kernel's own output
     for n in (256, 4096, 5120):
         x = rng.standard_normal((2, n)).astype(np.float32)
@@ -421,7 +438,8 @@ def test_attention_long_context_fused_step(ora, cuda):
 STREAM_SHAPES = [(synth.GGML_Q4_0, 1000, 4096), (synth.GGML_Q4_0, 260, 14336), (synth.GGML_Q4_0, 7, 96), (synth.GGML_Q4_0, 1536, 256),
                  (synth.GGML_Q4_0, 149, 1056), (synth.GGML_Q4_K, 520, 3584), (synth.GGML_Q6_K, 300, 3584), (synth.GGML_Q6_K, 64, 18944),
                  (synth.GGML_Q4_K, 333, 5120), (synth.GGML_Q4_0, 2, 16352), (synth.GGML_Q4_0, 4096, 14336), (synth.GGML_Q6_K, 3000, 18944),
-                 (synth.GGML_Q4_0, 9000, 4096), (synth.GGML_Q4_K, 5000, 256)]
+                 (synth.GGML_Q4_0, 9000, 4096), (synth.GGML_Q4_K, 5000, 256), (synth.GGML_Q8_0, 1000, 4096), (synth.GGML_Q8_0, 7, 96),
+                 (synth.GGML_Q8_0, 4096, 14336), (synth.GGML_Q8_0, 9000, 1056)]
 
 
 @pytest.mark.parametrize("typ,rows,cols", STREAM_SHAPES)
@@ -622,7 +640,8 @@ def test_gemm_matches_gemv(ora, cuda, typ, rows, cols, T):
 @pytest.mark.parametrize("typ,rows,cols,T", [(synth.GGML_Q4_0, 256, 256, 17), (synth.GGML_Q4_0, 1000, 4096, 100), (synth.GGML_Q4_K, 3584, 3584, 256),
                                              (synth.GGML_Q6_K, 512, 1024, 131), (synth.GGML_Q4_K, 96, 512, 40), (synth.GGML_Q4_0, 77, 192, 33),
                                              (synth.GGML_Q4_0, 130, 320, 20), (synth.GGML_Q4_0, 5000, 4096, 300), (synth.GGML_Q6_K, 300, 18944, 64),
-                                             (synth.GGML_Q4_K, 9000, 3584, 256), (synth.GGML_Q4_0, 1, 64, 1)])
+                                             (synth.GGML_Q4_K, 9000, 3584, 256), (synth.GGML_Q4_0, 1, 64, 1), (synth.GGML_Q8_0, 1000, 4096, 100),
+                                             (synth.GGML_Q8_0, 77, 192, 33), (synth.GGML_Q8_0, 4096, 14336, 256)])
 def test_gemm_tc_matches_gemv(ora, cuda, typ, rows, cols, T):
     """The prompt-chunk GEMM on tcgen05 / tensor memory (both operands as two half-precision terms, fp32 accumulation over the
     whole K in tensor memory) against the multi-token GEMV, which is bit-exact with the CPU reference: 1e-5 of the largest
@@ -701,7 +720,7 @@ def test_attention_prefill_chunk(ora, cuda, n_head, n_kv, hd, T, pos0):
 
 
 @pytest.mark.parametrize("typ,rows,cols,T", [(synth.GGML_Q4_0, 130, 1024, 11), (synth.GGML_Q4_K, 77, 512, 16), (synth.GGML_Q6_K, 40, 18944, 5),
-                                             (synth.GGML_Q4_0, 9, 64, 2)])
+                                             (synth.GGML_Q4_0, 9, 64, 2), (synth.GGML_Q8_0, 130, 1024, 11), (synth.GGML_Q8_0, 40, 4096, 16)])
 def test_gemv_several_tokens_one_pass(ora, cuda, typ, rows, cols, T):
     """2..16 tokens share one pass over the weights (groups of 8 tokens per CTA, ragged last group): every token's row is
     bit for bit the oracle's one-token GEMV."""
@@ -765,8 +784,9 @@ def test_allreduce_missing_rank_gives_up(cuda, lib):
             lib.ie_b200_ar_destroy(hs[r])
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world):
+@pytest.mark.parametrize("world,typ", [(2, synth.GGML_Q4_0), (4, synth.GGML_Q4_0), (8, synth.GGML_Q4_0), (2, synth.GGML_Q4_K), (4, synth.GGML_Q6_K),
+                                       (2, synth.GGML_Q8_0)])
+def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world, typ):
     """The tensor-parallel stop with real partners, the ranks of a world run one after the other on one GPU (their states
     connected in-process): every rank's K-split GEMV first (each stores its rows into the others' slots and waits for
     nobody), then every rank's reduction (all rows are there: no kernel waits for a later one). x + p_0 + p_1 + ... in rank
@@ -781,7 +801,7 @@ def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world):
 
     rows, cols = 512, 256 * world
     rng = np.random.default_rng(world)
-    raw = synth.q4_0_normal(rng, rows, cols)
+    raw = synth.make_gguf_bytes(typ, rng, rows, cols)
     nw = (1 + 0.1 * rng.standard_normal(rows)).astype(np.float32)
     hs = (C.c_void_p * world)()
     for r in range(world):
@@ -793,9 +813,9 @@ def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world):
             K.check(lib.ie_b200_ar_connect_local(hs[r], hs))
         shards, mats = [], []
         for r in range(world):
-            sub = np.ascontiguousarray(shard_cols(raw, synth.GGML_Q4_0, rows, cols, r * 256, (r + 1) * 256)).reshape(-1)
-            shards.append(ora.repack(synth.GGML_Q4_0, sub, rows, 256))
-            mats.append(K.Mat.from_gguf(synth.GGML_Q4_0, dev(sub, cuda), rows, 256))
+            sub = np.ascontiguousarray(shard_cols(raw.reshape(-1), typ, rows, cols, r * 256, (r + 1) * 256)).reshape(-1)
+            shards.append(ora.repack(typ, sub, rows, 256))
+            mats.append(K.Mat.from_gguf(typ, dev(sub, cuda), rows, 256))
         d_nw = dev(nw, cuda)
         err = torch.zeros(1, dtype=torch.int32, device=cuda)
         x0 = rng.standard_normal(rows).astype(np.float32)

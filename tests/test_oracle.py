@@ -15,7 +15,8 @@ from oracle.oracle import MAT_Q4, OracleModel
 sys_path_note = None
 Q4_SHAPES = [(1, 1), (7, 3), (9, 11), (8, 32), (13, 33), (17, 36), (5, 64), (3, 100), (2, 511)]
 K_SHAPES = [(3, 8), (9, 16), (8, 40), (5, 112), (2, 448)]
-KINDS = [(synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k")]
+KINDS = [(synth.GGML_Q4_0, Q4_SHAPES, "q4_0"), (synth.GGML_Q4_K, K_SHAPES, "q4_k"), (synth.GGML_Q6_K, K_SHAPES, "q6_k"),
+         (synth.GGML_Q8_0, Q4_SHAPES, "q8_0")]
 
 
 def sha(a):
@@ -77,7 +78,7 @@ def test_q4_gemv_known_answer(ora):
     assert worst < 1e-5  # the reference's own tolerance
 
 
-@pytest.mark.parametrize("name,fname,n_ctx", [("tiny", "tiny.npz", 512), ("tiny-k", "tiny_k.npz", 256)])
+@pytest.mark.parametrize("name,fname,n_ctx", [("tiny", "tiny.npz", 512), ("tiny-k", "tiny_k.npz", 256), ("tiny-q8", "tiny_q8.npz", 256)])
 def test_model_golden(ora, name, fname, n_ctx):
     """Greedy ids, logits and per-layer outputs of the synthetic tiny models: bit-exact with the reference CPU backend."""
     g = np.load(GOLDEN / fname)
@@ -109,7 +110,8 @@ def test_oracle_equals_compiled_reference(ora, ref):
     rng = np.random.default_rng(99)
     x = rng.standard_normal(4096).astype(np.float32)
     assert (ora.quant_q8(x) == ref.quant_q8(x)).all()
-    for typ, (rows, cols) in [(2, (13, 33 * 32)), (2, (2, 511 * 32)), (12, (9, 512)), (14, (9, 768)), (12, (16, 3584)), (14, (17, 2048))]:
+    for typ, (rows, cols) in [(2, (13, 33 * 32)), (2, (2, 511 * 32)), (12, (9, 512)), (14, (9, 768)), (12, (16, 3584)), (14, (17, 2048)),
+                              (8, (13, 33 * 32)), (8, (5, 2048))]:
         raw = synth.make_gguf_bytes(typ, rng, rows, cols)
         kind, qw, qs = ora.repack(typ, raw, rows, cols)
         rm = ref.mat(typ, raw, rows, cols)

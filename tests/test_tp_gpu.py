@@ -29,7 +29,7 @@ def test_tp_matches_single_gpu(cuda, world, mode, model):
     print(r.stdout[-300:])
 
 
-@pytest.mark.parametrize("world,model", [(2, "tiny-tp"), (2, "tiny-k"), (4, "tiny-tp")])
+@pytest.mark.parametrize("world,model", [(2, "tiny-tp"), (2, "tiny-k"), (2, "tiny-q8"), (4, "tiny-tp")])
 def test_ie_run_drop_in_sharded(cuda, tmp_path, world, model):
     """The reference's own ie-run host program with src/cuda.c as its GPU backend and IE_TP=N: one process drives the N
     shards (matrix parts cut from the reference loader's arrays, one exchange behind every column-split GEMV). Against

@@ -47,8 +47,9 @@ def main():
             w_tok, _ = single.step(tok, pos, want)
             d = float(np.abs(got - want).max()) / float(np.abs(want).max())
             worst = max(worst, d)
-            # 1e-4 until a rounding flips (see tests/test_model_gpu.py); flips stay in the cache
-            assert d <= (1e-4 if pos < 2 else 3e-2), (pos, d)
+            # 1e-4 until a rounding flips (see tests/test_model_gpu.py); flips stay in the cache. On the half cache the very
+            # first K / V rows may already round to the neighbouring half (one part in 2048 of an element)
+            assert d <= ((1e-4 if kv_f32 else 2e-3) if pos < 2 else 3e-2), (pos, d)
             top2 = np.sort(want)[-2:]
             if top2[1] - top2[0] > 2 * float(np.abs(got - want).max()):
                 assert nxt == w_tok, pos

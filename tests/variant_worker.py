@@ -14,7 +14,7 @@ from amd_c_b200.backend import Backend  # noqa: E402
 
 
 def main():
-    for name, fname, n_ctx in (("tiny", "tiny.npz", 512), ("tiny-k", "tiny_k.npz", 256)):
+    for name, fname, n_ctx in (("tiny", "tiny.npz", 512), ("tiny-k", "tiny_k.npz", 256), ("tiny-q8", "tiny_q8.npz", 256)):
         g = np.load(ROOT / "tests" / "golden" / fname)
         cfg = gguf.make_model(gguf.config(name), seed=int(g["seed"]))
         ids = [int(t) for t in g["ids"]]
@@ -28,7 +28,7 @@ def main():
         b.close()
     rng = np.random.default_rng(11)
     out = {}
-    for name in ("tiny", "tiny-k", "tiny-128"):
+    for name in ("tiny", "tiny-k", "tiny-128", "tiny-q8"):
         cfg = gguf.make_model(gguf.config(name), seed=0)
         prompt = [int(t) for t in rng.integers(0, cfg.vocab, 40)]
         b = Backend(cfg, 96, T=32, kv_f32=False)
