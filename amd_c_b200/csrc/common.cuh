@@ -126,21 +126,27 @@ __device__ __forceinline__ float ld_stream_f32(const void *p) {
 
 __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// dot4 of four unsigned bytes with four signed bytes, added to c (dp4a.u32.s32).
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8, int b_s8, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8), "r"(b_s8), "r"(c));
+  return d;
+}
+
 // Sum over the 32 nibbles q (0..15) of q * a. Word k of the weight block
 // holds weights 4k..4k+3 in its low nibbles and 16+4k..16+4k+3 in its high
 // nibbles; a0 are activation words 0..3, a1 words 4..7. Nibble bytes are
 // below 128, so the signed byte product equals the unsigned-by-signed one.
 __device__ __forceinline__ int q4_dot(const uint4 &w, const uint4 &a0, const uint4 &a1) {
-  int acc = 0;
-  acc = __dp4a((int)(w.x & 0x0F0F0F0Fu), (int)a0.x, acc);
-  acc = __dp4a((int)((w.x >> 4) & 0x0F0F0F0Fu), (int)a1.x, acc);
-  acc = __dp4a((int)(w.y & 0x0F0F0F0Fu), (int)a0.y, acc);
-  acc = __dp4a((int)((w.y >> 4) & 0x0F0F0F0Fu), (int)a1.y, acc);
-  acc = __dp4a((int)(w.z & 0x0F0F0F0Fu), (int)a0.z, acc);
-  acc = __dp4a((int)((w.z >> 4) & 0x0F0F0F0Fu), (int)a1.z, acc);
-  acc = __dp4a((int)(w.w & 0x0F0F0F0Fu), (int)a0.w, acc);
-  acc = __dp4a((int)((w.w >> 4) & 0x0F0F0F0Fu), (int)a1.w, acc);
-  return acc;
+  // low nibbles against words 0..3, high nibbles against words 4..7. The high nibbles stay where they are: a byte
+  // 0xN0 is 16 N, so their dot comes out as 16 times the wanted one and one exact shift at the end undoes it (one
+  // AND per word instead of shift + AND). Integer arithmetic: the same int32 as the nibble-by-nibble sum.
+  int lo = 0, hi = 0;
+  lo = dp4a_us(w.x & 0x0F0F0F0Fu, (int)a0.x, lo), hi = dp4a_us(w.x & 0xF0F0F0F0u, (int)a1.x, hi);
+  lo = dp4a_us(w.y & 0x0F0F0F0Fu, (int)a0.y, lo), hi = dp4a_us(w.y & 0xF0F0F0F0u, (int)a1.y, hi);
+  lo = dp4a_us(w.z & 0x0F0F0F0Fu, (int)a0.z, lo), hi = dp4a_us(w.z & 0xF0F0F0F0u, (int)a1.z, hi);
+  lo = dp4a_us(w.w & 0x0F0F0F0Fu, (int)a0.w, lo), hi = dp4a_us(w.w & 0xF0F0F0F0u, (int)a1.w, hi);
+  return lo + (hi >> 4);
 }
 
 // One byte-quad of Q6_K values minus 32 as signed bytes: v = nibbles | two
@@ -149,26 +155,36 @@ __device__ __forceinline__ int q6_sw(uint32_t nib4, uint32_t hword, int k) {
   const uint32_t v = nib4 | (((hword >> (2 * k)) & 0x03030303u) << 4);
   return (int)(((v | 0x80808080u) - 0x20202020u) ^ 0x80808080u);
 }
-// The two half dots of a Q6_K sub-block: weights 0..15 against a0, 16..31 against a1.
+// One byte-quad of Q6_K values as they are stored (0..63, without the - 32): nibbles | two high bits << 4. hi_half: the
+// nibbles are the high ones of nib_src.
+__device__ __forceinline__ uint32_t q6_uw(uint32_t nib_src, bool hi_half, uint32_t hword, int k) {
+  const uint32_t hs = k < 2 ? hword << (4 - 2 * k) : hword >> (2 * k - 4);  // the two bits of every byte moved to bits 4, 5
+  return ((hi_half ? nib_src >> 4 : nib_src) & 0x0F0F0F0Fu) | (hs & 0x30303030u);
+}
+// The two half dots of a Q6_K sub-block: weights 0..15 against a0, 16..31 against a1. sum (q - 32) a is taken as
+// sum q a - 32 sum a: the stored bytes go into the dot as they are (unsigned by signed), and the sums of the sixteen
+// activations of each half (four dot4 with ones; the same for every row that shares the activation block) replace the
+// three operations per word that would turn every byte into q - 32. Integer arithmetic: the same int32 either way.
 __device__ __forceinline__ void q6_dots(const uint4 &w, const uint2 &hw, const uint4 &a0, const uint4 &a1, int &d0, int &d1) {
-  int s0 = 0, s1 = 0;
-  s0 = __dp4a(q6_sw(w.x & 0x0F0F0F0Fu, hw.x, 0), (int)a0.x, s0);
-  s0 = __dp4a(q6_sw(w.y & 0x0F0F0F0Fu, hw.x, 1), (int)a0.y, s0);
-  s0 = __dp4a(q6_sw(w.z & 0x0F0F0F0Fu, hw.x, 2), (int)a0.z, s0);
-  s0 = __dp4a(q6_sw(w.w & 0x0F0F0F0Fu, hw.x, 3), (int)a0.w, s0);
-  s1 = __dp4a(q6_sw((w.x >> 4) & 0x0F0F0F0Fu, hw.y, 0), (int)a1.x, s1);
-  s1 = __dp4a(q6_sw((w.y >> 4) & 0x0F0F0F0Fu, hw.y, 1), (int)a1.y, s1);
-  s1 = __dp4a(q6_sw((w.z >> 4) & 0x0F0F0F0Fu, hw.y, 2), (int)a1.z, s1);
-  s1 = __dp4a(q6_sw((w.w >> 4) & 0x0F0F0F0Fu, hw.y, 3), (int)a1.w, s1);
-  d0 = s0, d1 = s1;
+  int s0 = 0, s1 = 0, h0 = 0, h1 = 0;
+  s0 = dp4a_us(q6_uw(w.x, false, hw.x, 0), (int)a0.x, s0), h0 = __dp4a(0x01010101, (int)a0.x, h0);
+  s0 = dp4a_us(q6_uw(w.y, false, hw.x, 1), (int)a0.y, s0), h0 = __dp4a(0x01010101, (int)a0.y, h0);
+  s0 = dp4a_us(q6_uw(w.z, false, hw.x, 2), (int)a0.z, s0), h0 = __dp4a(0x01010101, (int)a0.z, h0);
+  s0 = dp4a_us(q6_uw(w.w, false, hw.x, 3), (int)a0.w, s0), h0 = __dp4a(0x01010101, (int)a0.w, h0);
+  s1 = dp4a_us(q6_uw(w.x, true, hw.y, 0), (int)a1.x, s1), h1 = __dp4a(0x01010101, (int)a1.x, h1);
+  s1 = dp4a_us(q6_uw(w.y, true, hw.y, 1), (int)a1.y, s1), h1 = __dp4a(0x01010101, (int)a1.y, h1);
+  s1 = dp4a_us(q6_uw(w.z, true, hw.y, 2), (int)a1.z, s1), h1 = __dp4a(0x01010101, (int)a1.z, h1);
+  s1 = dp4a_us(q6_uw(w.w, true, hw.y, 3), (int)a1.w, s1), h1 = __dp4a(0x01010101, (int)a1.w, h1);
+  d0 = s0 - 32 * h0, d1 = s1 - 32 * h1;
 }
 
 // The 12-bit (sc | mn << 6) field j of a Q4_K super-block header (words y, z, w).
 __device__ __forceinline__ uint32_t q4k_field(const uint4 &h, int j) {
-  const int o = 12 * j, i = o >> 5, sh = o & 31;
-  const uint32_t lo = i == 0 ? h.y : i == 1 ? h.z : h.w;
-  const uint32_t hi = i == 0 ? h.z : h.w;
-  return __funnelshift_r(lo, hi, sh) & 0xFFFu;
+  // fields 0..2 start in word y, 3..5 in z, 6..7 in w (12 j >> 5); a field that crosses a word boundary (2 and 5) takes
+  // its upper bits from the next word through the funnel shift
+  const uint32_t lo = j < 3 ? h.y : j < 6 ? h.z : h.w;
+  const uint32_t hi = j < 3 ? h.z : h.w;
+  return __funnelshift_r(lo, hi, (12 * j) & 31) & 0xFFFu;
 }
 
 // The wave tree of the reference: shuffle down by 16, 8, 4, 2, 1; lane 0 holds the sum.

@@ -75,8 +75,9 @@ struct Blk<IE_B200_MAT_Q4K, SMEM> {
   __device__ __forceinline__ float accum(float acc, const uint4 &a0, const uint4 &a1, float da, int asum, uint32_t b) const {
     const int dq = q4_dot(w, a0, a1);
     const uint32_t f = q4k_field(h, (int)(b & 7u));
-    const float s = __fmul_rn(h2f((uint16_t)(h.x & 0xFFFFu)), (float)(f & 63u));
-    const float mm = __fmul_rn(h2f((uint16_t)(h.x >> 16)), (float)(f >> 6));
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));  // (d, dmin): both halves of the word in one unpack
+    const float s = __fmul_rn(dd.x, (float)(f & 63u));
+    const float mm = __fmul_rn(dd.y, (float)(f >> 6));
     return __fmaf_rn(-mm, __fmul_rn(da, (float)asum), __fmaf_rn(__fmul_rn(s, (float)dq), da, acc));
   }
 };
