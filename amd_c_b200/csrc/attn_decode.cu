@@ -83,13 +83,20 @@ __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) { r
 // then summed with many independent loads in flight per thread (a plain loop over the splits is one L2 round trip
 // per split and per pass: 16 us at 17 splits).
 // part: the records of this token's first head of the KV head, [G][S][hd + 2]; scr: (2 A + 2) G floats of shared memory.
+// A split's record of one head in global memory: out[hd], then (max, sum) and two floats of padding, so that records start
+// on 16-byte boundaries and the merge reads them four floats per load.
+template <int HD>
+struct AttRec {
+  static constexpr int FLOATS = HD + 4;
+};
+
 template <int G, int HD, int THREADS>
 __device__ __forceinline__ void merge_partials(const float *part, uint32_t S, uint32_t A, float *fin, float *scr) {
-  const size_t rec = HD + 2;
+  constexpr size_t rec = AttRec<HD>::FLOATS;
   float *mk = scr, *lk = scr + G * A, *mh = lk + G * A, *lh = mh + G;
   for (uint32_t i = threadIdx.x; i < G * A; i += THREADS) {
-    const float *pr = part + ((size_t)(i / A) * S + i % A) * rec;
-    mk[i] = __ldcg(pr), lk[i] = __ldcg(pr + 1);
+    const float2 ml2 = __ldcg(reinterpret_cast<const float2 *>(part + ((size_t)(i / A) * S + i % A) * rec + HD));
+    mk[i] = ml2.x, lk[i] = ml2.y;
   }
   __syncthreads();
   // one warp per head: its lanes share the splits (maximum, weights exp(max_k - max), denominator), no block-wide steps
@@ -108,35 +115,43 @@ __device__ __forceinline__ void merge_partials(const float *part, uint32_t S, ui
     if (lane == 0) mh[h] = M, lh[h] = L;
   }
   __syncthreads();
-  // all of a thread's elements together, four splits at a time: (elements x 4) independent loads per round trip
-  constexpr int EPT = (G * HD + THREADS - 1) / THREADS;
-  float acc[EPT];
+  // a thread owns groups of four consecutive output elements; four splits at a time: (groups x 4) independent 16-byte
+  // loads per round trip. The sum over the splits runs in split order for every element, as one element at a time would.
+  constexpr int QUADS = G * HD / 4, QPT = (QUADS + THREADS - 1) / THREADS;
+  float4 acc[QPT];
 #pragma unroll
-  for (int i = 0; i < EPT; i++) acc[i] = 0.0f;
+  for (int i = 0; i < QPT; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (uint32_t k0 = 0; k0 < A; k0 += 4u) {
-    float v[EPT][4];
+    float4 v[QPT][4];
 #pragma unroll
-    for (int i = 0; i < EPT; i++) {
-      const int e = threadIdx.x + THREADS * i;
-      const float *pr = part + (size_t)(e / HD) * S * rec + 2 + (e % HD);
+    for (int i = 0; i < QPT; i++) {
+      const int q = threadIdx.x + THREADS * i, e = 4 * q;
+      const float *pr = part + (size_t)(e / HD) * S * rec + (e % HD);
 #pragma unroll
-      for (int j = 0; j < 4; j++) v[i][j] = (e < G * HD && k0 + j < A) ? __ldcg(pr + (size_t)(k0 + j) * rec) : 0.0f;
+      for (int j = 0; j < 4; j++)
+        v[i][j] = (q < QUADS && k0 + j < A) ? __ldcg(reinterpret_cast<const float4 *>(pr + (size_t)(k0 + j) * rec)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int i = 0; i < EPT; i++) {
-      const int e = threadIdx.x + THREADS * i;
-      if (e < G * HD) {
+    for (int i = 0; i < QPT; i++) {
+      const int q = threadIdx.x + THREADS * i, e = 4 * q;
+      if (q < QUADS) {
         const float *w = mk + (e / HD) * A;
 #pragma unroll
         for (int j = 0; j < 4; j++)
-          if (k0 + j < A) acc[i] = fmaf(w[k0 + j], v[i][j], acc[i]);
+          if (k0 + j < A) {
+            acc[i].x = fmaf(w[k0 + j], v[i][j].x, acc[i].x), acc[i].y = fmaf(w[k0 + j], v[i][j].y, acc[i].y);
+            acc[i].z = fmaf(w[k0 + j], v[i][j].z, acc[i].z), acc[i].w = fmaf(w[k0 + j], v[i][j].w, acc[i].w);
+          }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < EPT; i++) {
-    const int e = threadIdx.x + THREADS * i;
-    if (e < G * HD) fin[e] = acc[i] * (1.0f / lh[e / HD]);
+  for (int i = 0; i < QPT; i++) {
+    const int q = threadIdx.x + THREADS * i, e = 4 * q;
+    if (q < QUADS) {
+      const float inv = 1.0f / lh[e / HD];
+      fin[e] = acc[i].x * inv, fin[e + 1] = acc[i].y * inv, fin[e + 2] = acc[i].z * inv, fin[e + 3] = acc[i].w * inv;
+    }
   }
 }
 
@@ -380,6 +395,7 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
   // final values of this KV head's G heads: directly when one split held everything, else through the partials
   // buffer, merged by the last split to arrive
   const size_t rec = HD + 2;
+  constexpr size_t grec = AttRec<HD>::FLOATS;  // the record in global memory
   for (int e = threadIdx.x; e < G * HD; e += THREADS) {
     const int h = e / HD;
     float M = -INFINITY;
@@ -395,9 +411,9 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     if (A == 1u) {
       fin[e] = acc * (1.0f / L);
     } else {
-      float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * rec;
-      pr[2 + (e % HD)] = acc;
-      if (e % HD == 0) pr[0] = M, pr[1] = L;
+      float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * grec;
+      pr[e % HD] = acc;
+      if (e % HD == 0) pr[HD] = M, pr[HD + 1] = L;
     }
   }
   if (A > 1u) {
@@ -411,7 +427,7 @@ __global__ void __launch_bounds__(ATT_THREADS * HS) attn_decode_kernel(const Att
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    merge_partials<G, HD, THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
+    merge_partials<G, HD, THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * grec, S, A, fin, fin + G * HD);
   }
   __syncthreads();
   // ---- write out, one warp per block of 32 values (which is also a Q8 block of the output vector)
@@ -712,6 +728,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   }
   __syncthreads();
   const size_t rec = HD + 2;
+  constexpr size_t grec = AttRec<HD>::FLOATS;  // the record in global memory
   float *recv = reinterpret_cast<float *>(reinterpret_cast<char *>(smem_raw) + am_main_bytes(HD, G, NB, S));  // [CL][G][HD + 2], used in the leader
   if (CL > 1) {
     // every CTA's record into the leader's memory, then one cluster barrier; a CTA without positions sends (max -inf, sum 0)
@@ -761,9 +778,9 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     if (A == 1u) {
       fin[e] = acc * (1.0f / L);
     } else {
-      float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * rec;
-      pr[2 + (e % HD)] = acc;
-      if (e % HD == 0) pr[0] = M, pr[1] = L;
+      float *pr = a.part + (((size_t)t * a.n_head + (size_t)g * G + h) * S + s) * grec;
+      pr[e % HD] = acc;
+      if (e % HD == 0) pr[HD] = M, pr[HD + 1] = L;
     }
   }
   if (A > 1u) {
@@ -777,7 +794,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    merge_partials<G, HD, AM_THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * rec, S, A, fin, fin + G * HD);
+    merge_partials<G, HD, AM_THREADS>(a.part + ((size_t)t * a.n_head + (size_t)g * G) * S * grec, S, A, fin, fin + G * HD);
   }
   __syncthreads();
   float *ot = reinterpret_cast<float *>(reinterpret_cast<char *>(a.out) + a.out_stride * t) + (size_t)g * G * HD;
@@ -1104,7 +1121,7 @@ using namespace ieb;
 extern "C" size_t ie_b200_attn_part_bytes(uint32_t n_head, uint32_t hd, uint32_t n_ctx, uint32_t T) {
   // an upper bound over every KV-head count: splits never exceed ceil(n_ctx / 256)
   const size_t S = (n_ctx + ATT_MIN_SPAN - 1u) / ATT_MIN_SPAN;
-  return (size_t)T * n_head * (S ? S : 1u) * (hd + 2u) * sizeof(float);
+  return (size_t)T * n_head * (S ? S : 1u) * (hd + 4u) * sizeof(float);
 }
 extern "C" size_t ie_b200_attn_count_words(uint32_t n_head, uint32_t T) { return (size_t)n_head * T; }
 

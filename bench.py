@@ -303,7 +303,7 @@ def time_gemv_sweep(device, peak: float) -> list[dict]:
     return out
 
 
-def time_attention(device, peak: float) -> list[dict]:
+def time_attention(device, peak: float, lengths=(256, 4096, 32768), n_kv: int = 8) -> list[dict]:
     """The decode attention kernel alone (32 query / 8 KV heads of 128, f16 cache, RoPE + KV store fused) at short and
     long contexts: a graph of 40 launches over rotating caches larger than L2, CUDA events on the capturing stream.
     Algorithmic bytes: 2 x (positions + 1) x n_kv x hd x 2 B."""
@@ -311,9 +311,9 @@ def time_attention(device, peak: float) -> list[dict]:
 
     from amd_c_b200 import kernels as K
 
-    n_head, n_kv, hd = 32, 8, 128
+    n_head, hd = 32, 128
     out = []
-    for positions in (256, 4096, 32768):
+    for positions in lengths:
         n_ctx = positions + 8
         gen = torch.Generator(device=device).manual_seed(positions)
         nl = max(2, int(300e6 // (2 * n_kv * n_ctx * hd * 2)) + 1)
