@@ -170,6 +170,7 @@ static int launch_op(ie_b200_engine *e, const ie_b200_op &o, uint32_t t0, uint32
       if (T >= 17 && m.kind != IE_B200_MAT_F32 && !e->no_gemm && (tc_ok || m.kind != IE_B200_MAT_Q8)) {
         if (tc_ok) {  // tcgen05 / tensor memory
           EMat &mm = e->mats[o.mat];
+          // (normally done by prepare_chunks before anything of the run is enqueued; here for callers that enqueue ranges themselves)
           if (mm.tc_exp == INT32_MIN)
             if (int r = ie_b200_mat_tc_exp(mm.kind, mm.d, mm.rows, mm.cols, &mm.tc_exp, st)) return r;
           const size_t need = ie_b200_gemm_tc_scratch_bytes(mm.rows, mm.cols, e->d.T_max);
@@ -992,10 +993,35 @@ extern "C" int ie_b200_engine_enqueue_kinds(ie_b200_engine *e, uint32_t first, u
   return enqueue_range(e, first, last, T, kind_mask, static_cast<cudaStream_t>(stream));
 }
 
+// What a prompt chunk's tensor-core GEMMs need once per matrix (the scale exponent, which is read back from the device) and
+// once per engine (the scratch), made ready BEFORE anything of the run is enqueued: both wait for the stream, and a wait in
+// the middle of a run would wait for exchange kernels whose partners on other GPUs this thread has not enqueued yet.
+static int prepare_chunks(ie_b200_engine *e, uint32_t T) {
+  if (T < 17 || e->no_gemm || e->gemm_mma) return IE_B200_OK;
+  size_t need = 0;
+  for (const ie_b200_op &o : e->ops) {
+    if (o.kind != IE_B200_OP_GEMV || o.mat < 0 || (size_t)o.mat >= e->mats.size() || o.a_stride % 16u) continue;
+    EMat &m = e->mats[o.mat];
+    if (m.kind == IE_B200_MAT_F32) continue;
+    if (m.tc_exp == INT32_MIN)
+      if (int r = ie_b200_mat_tc_exp(m.kind, m.d, m.rows, m.cols, &m.tc_exp, e->stream)) return r;
+    const size_t n = ie_b200_gemm_tc_scratch_bytes(m.rows, m.cols, e->d.T_max);
+    need = n > need ? n : need;
+  }
+  if (need > e->gemm_scratch_bytes) {
+    IEB_CUDA(cudaStreamSynchronize(e->stream));
+    cudaFree(e->gemm_scratch), e->gemm_scratch = nullptr, e->gemm_scratch_bytes = 0;
+    IEB_CUDA(cudaMalloc(&e->gemm_scratch, need));
+    e->gemm_scratch_bytes = need;
+  }
+  return IE_B200_OK;
+}
+
 extern "C" int ie_b200_engine_run_begin(ie_b200_engine *e, const uint32_t *toks, uint32_t T, uint32_t pos, int last_only) {
   if (!e || !toks) return fail(IE_B200_E_ARG, "ie_b200_engine_run: NULL argument");
   if (e->ops.empty()) return fail(IE_B200_E_STATE, "ie_b200_engine_run: no op list");
   IEB_CUDA(cudaSetDevice(e->device));
+  if (int r = prepare_chunks(e, T)) return r;
   cudaStream_t st = e->stream;
   if (int r = upload_input(e, toks, T, pos, st)) return r;
   const uint32_t n_ops = (uint32_t)e->ops.size(), ih = last_only ? e->i_head : n_ops;

@@ -52,11 +52,11 @@ def test_ie_run_drop_in_sharded(cuda, tmp_path, world, model):
     gguf.write_gguf(path, cfg)
     env = {**os.environ, "IE_KV_F32": "1"}
 
-    def run(*extra, tp=None):
+    def run(*extra, tp=None, tokens="1,2,3,7,300,12"):
         e = dict(env)
         if tp:
             e["IE_TP"] = str(tp)
-        r = subprocess.run([str(exe), str(path), "--tokens", "1,2,3,7,300,12", "--n", "24", "--ctx", "64", *extra], capture_output=True, text=True,
+        r = subprocess.run([str(exe), str(path), "--tokens", tokens, "--n", "24", "--ctx", "64", *extra], capture_output=True, text=True,
                            timeout=300, env=e)
         assert r.returncode == 0, r.stderr[-2000:]
         if tp:
@@ -88,7 +88,81 @@ def test_ie_run_drop_in_sharded(cuda, tmp_path, world, model):
     assert same >= 6 and got[:same] == want[:same]
     chunked = run("--backend", "gpu", "--chunk", "4", tp=world)  # the prompt in chunks of 4 through backend.run
     assert chunked[:7] == got[:7]
+    # a prompt long enough for the tensor-core GEMM (20 tokens in one chunk: every stop of the chunk one exchange over 20 rows)
+    long_prompt = ",".join(str((7 * i + 3) % 500) for i in range(20))
+    by_steps = run("--backend", "gpu", "--dump-logits", str(tmp_path / "gpu20.txt"), tp=world, tokens=long_prompt)
+    by_chunk = run("--backend", "gpu", "--chunk", "32", tp=world, tokens=long_prompt)
+    assert by_chunk[:22] == by_steps[:22]
     sampled = run("--backend", "gpu", "--temp", "0.8", "--top-k", "40", "--seed", "3", tp=world)
     env["IE_HOST_TOPK"] = "1"
     sampled_host = run("--backend", "gpu", "--temp", "0.8", "--top-k", "40", "--seed", "3", tp=world)
     assert sampled == sampled_host and sampled != got
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_one_thread_drives_the_shards(cuda, world):
+    """ie_b200_tp_group: the shards of one model on `world` GPUs of THIS process, driven by one host thread (what src/cuda.c does
+    under IE_TP): step with the gathered logits, a prompt chunk, and a device-chained decode run, against the unsharded engine
+    on GPU 0. Every shard's work is enqueued before any shard is waited for; the ranks' tokens must agree (the group checks)."""
+    import ctypes as C
+
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from amd_c_b200 import _lib, gguf
+    from amd_c_b200._lib import check
+    from amd_c_b200.backend import Backend
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    lib = _lib.load()
+    cfg = gguf.make_model(gguf.config("tiny-tp"), seed=0)
+    n_ctx, T = 160, 24
+    grp = C.c_void_p()
+    check(lib.ie_b200_tp_group_create(world, None, cfg.dim * T, C.byref(grp)))
+    shards = []
+    try:
+        for r in range(world):
+            check(lib.ie_b200_tp_group_use(grp, r))
+            b = Backend(cfg, n_ctx, T=T, kv_f32=True, tp=world, rank=r, device=torch.device(f"cuda:{r}"))
+            check(lib.ie_b200_tp_group_attach(grp, r, b.h, r * b.vocab_l, b.vocab_l))
+            b.collective = True
+            shards.append(b)
+        single = Backend(cfg, n_ctx, T=T, kv_f32=True, device=torch.device("cuda:0"))
+        got, want = np.zeros(cfg.vocab, np.float32), np.zeros(cfg.vocab, np.float32)
+        nxt, ms = C.c_uint32(), C.c_double()
+        tok, worst = 1, 0.0
+        for pos in range(10):
+            check(lib.ie_b200_tp_group_step(grp, tok, pos, got.ctypes.data_as(C.c_void_p), C.byref(nxt), C.byref(ms)))
+            w_tok, _ = single.step(tok, pos, want)
+            assert int(np.argmax(got)) == nxt.value
+            worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+            tok = w_tok  # the unsharded engine leads
+        assert worst <= 3e-2, worst
+        # a prompt chunk over the same history on both sides
+        chunk = ((np.arange(T, dtype=np.uint32) * 7 + 3) % cfg.vocab).astype(np.uint32)
+        out = np.zeros(T, np.uint32)
+        check(lib.ie_b200_tp_group_run(grp, chunk.ctypes.data_as(C.c_void_p), T, 10, 1, out.ctypes.data_as(C.c_void_p), None))
+        w_out = single.run(0, chunk, 10, last_only=True)
+        lg_w = np.ascontiguousarray(single.read_rows("logits", T - 1, 1)[0, : 4 * cfg.vocab]).view(np.float32)
+        lg_g = np.concatenate([np.ascontiguousarray(s.read_rows("logits", T - 1, 1)[0, : 4 * s.vocab_l]).view(np.float32) for s in shards])
+        d = float(np.abs(lg_g - lg_w).max() / np.abs(lg_w).max())
+        assert d <= 3e-2, d
+        top2 = np.sort(lg_w)[-2:]
+        if top2[1] - top2[0] > 2 * float(np.abs(lg_g - lg_w).max()):
+            assert int(out[-1]) == int(w_out[-1])
+        # K tokens chained on the devices: the same on every rank (checked inside), and the unsharded engine's while no close call parts them
+        K = 16
+        dec = np.zeros(K, np.uint32)
+        check(lib.ie_b200_tp_group_decode(grp, int(w_out[-1]), 10 + T, K, dec.ctypes.data_as(C.c_void_p), C.byref(ms)))
+        w_dec, _ = single.decode(int(w_out[-1]), 10 + T, K)
+        common = next((i for i, (a, b) in enumerate(zip(dec, w_dec)) if int(a) != int(b)), K)
+        print(f"one thread, {world} shards: logits within {worst:.1e}, chunk within {d:.1e}, {common} of {K} chained tokens identical, {ms.value / K:.3f} ms per token")
+        assert ms.value > 0
+        single.close()
+    finally:
+        lib.ie_b200_tp_group_destroy(grp)
+        for b in shards:
+            b.collective = False
+            b.close()
