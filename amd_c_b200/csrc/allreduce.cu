@@ -33,7 +33,7 @@
 
 namespace ieb {
 
-constexpr int AR_THREADS = 256, AR_MAX_CTAS = 32;
+constexpr int AR_THREADS = 256, AR_MAX_CTAS = 296;  // (all CTAs of a call are resident at once: 256 threads, few registers)
 
 struct ArDev {
   float *slots[AR_MAX_RANKS];     // rank j's receive buffer: [2][world][max_n] floats
@@ -84,13 +84,33 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
   // ---- sum in rank order from my own memory
   if (ok) {
     const float *mine = s.slots[s.rank] + (size_t)par * s.world * s.max_n;
-    for (uint32_t i = lo + 4u * threadIdx.x; i < hi; i += 4u * AR_THREADS) {
-      float4 acc = res ? *reinterpret_cast<const float4 *>(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-      for (uint32_t j = 0; j < s.world; j++) {
-        const float4 v = __ldcv(reinterpret_cast<const float4 *>(mine + (size_t)j * s.max_n + i));
-        acc.x = __fadd_rn(acc.x, v.x), acc.y = __fadd_rn(acc.y, v.y), acc.z = __fadd_rn(acc.z, v.z), acc.w = __fadd_rn(acc.w, v.w);
+    // four float4 per thread and round, every rank's loads of a round in flight before the first sum (a prompt chunk's
+    // exchange is megabytes: one dependent load per iteration left it bound by the latency of a load)
+    constexpr uint32_t UN = 4u, STEP = 4u * AR_THREADS;
+    for (uint32_t i0 = lo + 4u * threadIdx.x; i0 < hi; i0 += UN * STEP) {
+      float4 acc[UN];
+#pragma unroll
+      for (uint32_t u = 0; u < UN; u++) {
+        const uint32_t i = i0 + u * STEP;
+        acc[u] = (i < hi && res) ? *reinterpret_cast<const float4 *>(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      *reinterpret_cast<float4 *>(out + i) = acc;
+      for (uint32_t j = 0; j < s.world; j++) {
+        float4 v[UN];
+#pragma unroll
+        for (uint32_t u = 0; u < UN; u++) {
+          const uint32_t i = i0 + u * STEP;
+          v[u] = i < hi ? __ldcv(reinterpret_cast<const float4 *>(mine + (size_t)j * s.max_n + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < UN; u++)
+          acc[u].x = __fadd_rn(acc[u].x, v[u].x), acc[u].y = __fadd_rn(acc[u].y, v[u].y), acc[u].z = __fadd_rn(acc[u].z, v[u].z),
+          acc[u].w = __fadd_rn(acc[u].w, v[u].w);
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < UN; u++) {
+        const uint32_t i = i0 + u * STEP;
+        if (i < hi) *reinterpret_cast<float4 *>(out + i) = acc[u];
+      }
     }
   }
   // ---- the last CTA of the call advances the epoch

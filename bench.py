@@ -210,7 +210,7 @@ def build_backend(cfg, n_ctx: int, tp: int, rank: int, device, step_mode: str | 
     return b
 
 
-def time_gemvs(b, reps: int = 20, repeats: int = 5) -> dict:
+def time_gemvs(b, reps: int = 20, repeats: int = 5, mask: int | None = None) -> dict:
     """The GEMV kernels of one step alone, in op-list order on the real matrices (a chain of dependent launches, as
     in the step), captured into a graph and timed with CUDA events on the capturing stream. Every pass streams all
     weights (4.2 GB), so nothing is served from L2."""
@@ -220,7 +220,8 @@ def time_gemvs(b, reps: int = 20, repeats: int = 5) -> dict:
     from amd_c_b200.backend import OP_GEMV
 
     lib = _lib.load()
-    mask = 1 << OP_GEMV
+    if mask is None:
+        mask = 1 << OP_GEMV
     s = torch.cuda.Stream(device=b.device)
     with torch.cuda.device(b.device), torch.cuda.stream(s):
         before = lib.ie_b200_launch_count()
@@ -509,6 +510,50 @@ def time_long_context(device, positions: int = 32768, n_gen: int = 64) -> dict:
     return res
 
 
+def time_long_context_tp(device, group, rank: int, world: int, positions: int = 32768, n_gen: int = 40) -> dict | None:
+    """The same 27B-class model sharded over the ranks of `group` (8 KV heads, FFN 17408: 2 or 4 ranks; at 8 the K-quant
+    column slices of ffn_down would not be whole super-blocks): prefill in chunks of 256 (every stop of a chunk one exchange
+    over 256 x 5120 floats), then greedy decode; device time of the slowest rank."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from amd_c_b200 import gguf
+    from amd_c_b200.backend import Backend
+    from amd_c_b200.tp import TensorParallelBackend
+
+    cfg = gguf.config("dense-27b-q4km")
+    if cfg.n_kv % world or (cfg.ffn // world) % 256:
+        return None
+    tensors = gguf.make_model_device(cfg, seed=0, device=device)
+    b = Backend(cfg, positions + n_gen + 8, T=256, device_tensors=tensors, tp=world, rank=rank, device=device)
+    del tensors
+    torch.cuda.empty_cache()
+    tpb = TensorParallelBackend(b, group)
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, positions).astype(np.uint32)
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)
+    t0 = time.perf_counter()
+    tok = 0
+    for p0 in range(0, positions, 256):
+        tok = int(tpb.run(prompt[p0: p0 + 256], p0, last_only=True)[-1])
+    torch.cuda.synchronize(device)
+    dt = time.perf_counter() - t0
+    out = tpb.decode(tok, positions, 8)
+    out, ms = tpb.decode(int(out[-1]), positions + 8, n_gen - 8, timed=True)
+    t = torch.tensor([ms, dt * 1e3], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    ms, dt_ms = float(t[0]), float(t[1])
+    n = n_gen - 8
+    kv_bytes = 2.0 * (positions + n_gen // 2) * cfg.n_kv * cfg.hd * 2 * cfg.n_layer
+    res = {"workload": f"27B-class dense Q4_K_M sharded over {world} GPUs, {positions} positions prefilled in chunks of 256, then {n} timed greedy tokens",
+           "prefill_tokens_per_s": positions / (dt_ms * 1e-3), "decode_tokens_per_s": n / (ms * 1e-3), "decode_ms_per_step": ms / n,
+           "weight_gb_per_token_per_gpu": b.weight_bytes_per_token / 1e9, "kv_gb_per_token_per_gpu": kv_bytes / world / 1e9}
+    tpb.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours_single(args, cfg) -> dict:
     import numpy as np
     import torch
@@ -672,7 +717,14 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's device time is the job's time
     ms, e2e_ms = float(t[0]), float(t[1])
     gem = time_gemvs(b)
-    g = torch.tensor([gem["ms_per_pass"]], dtype=torch.float64, device=dev)
+    # the same chain with the exchanges: every K-split GEMV pushes its rows and the one-CTA kernel behind it reduces, adds the
+    # residual, normalises and quantises (all ranks replay in step; the difference per stop is what an exchange costs, waiting
+    # for the slowest rank included)
+    from amd_c_b200.backend import OP_ALLREDUCE, OP_GEMV, OP_RMSNORM
+    dist.barrier()
+    with_stops = time_gemvs(b, mask=(1 << OP_GEMV) | (1 << OP_ALLREDUCE) | (1 << OP_RMSNORM))
+    n_stops = sum(1 for o in b.ops if o.kind == OP_ALLREDUCE)
+    g = torch.tensor([gem["ms_per_pass"], with_stops["ms_per_pass"]], dtype=torch.float64, device=dev)
     dist.all_reduce(g, op=dist.ReduceOp.MAX)
     peak, peak_src = measured_peaks()
     achieved = gem["bytes"] / (float(g[0]) * 1e-3) / 1e9  # per GPU: this rank's shard bytes over the slowest rank's time
@@ -684,9 +736,17 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
             "roofline": {"bound": "hbm", "kernel": "gemv (Q4_0 x Q8, decode), per GPU", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_src} copy bandwidth", "frac_of_nominal_8000": achieved / 8000.0,
                          "traffic": None, "launches_per_step": gem["launches"], "algorithmic_bytes_per_step": gem["bytes"]},
-            "allreduce": tpb.describe(), "clocks": clocks, "tp_tokens_identical_prefix": identical,
+            "allreduce": {**tpb.describe(), "us_per_stop": (float(g[1]) - float(g[0])) * 1e3 / max(1, n_stops),
+                          "us_per_stop_note": "GEMVs + exchanges + norms of a step as a dependent chain, minus the GEMVs alone, per exchange"},
+            "clocks": clocks, "tp_tokens_identical_prefix": identical,
         }
     tpb.close()
+    torch.cuda.empty_cache()
+    dist.barrier()
+    if not args.quick:  # the long-context model sharded the same way (2 or 4 ranks), every rank takes part
+        long_tp = time_long_context_tp(dev, dist.group.WORLD, rank, world)
+        if res is not None and long_tp is not None:
+            res["dense_27b_q4km_32k"] = long_tp
     dist.barrier()
     dist.destroy_process_group()
     return res
