@@ -39,8 +39,9 @@ extern "C" int ie_b200_tp_group_create(uint32_t world, const int *devices, uint3
     }
     for (uint32_t q = 0; q < r; q++)
       if (g->dev[q] == g->dev[r]) {
+        const int twice = g->dev[r];
         delete g;
-        return fail(IE_B200_E_ARG, "ie_b200_tp_group_create: device %d twice (kernels that wait for one another must not share a GPU)", g->dev[r]);
+        return fail(IE_B200_E_ARG, "ie_b200_tp_group_create: device %d twice (kernels that wait for one another must not share a GPU)", twice);
       }
   }
   int rc = IE_B200_OK;
