@@ -933,3 +933,17 @@ def test_swiglu_interleaved_equals_planar(cuda, lib):
     q = torch.empty((T, 40 * (n // 32)), dtype=torch.uint8, device=cuda)
     K.check(lib.ie_b200_swiglu_il(il.data_ptr(), h.data_ptr(), n, q.data_ptr(), T, 2 * n * 4, n * 4, 40 * (n // 32), None))
     assert torch.equal(h, want.contiguous()) and torch.equal(q, want_q)
+
+
+def test_tp_group_refuses_one_gpu_twice(cuda, lib):
+    """Shards whose kernels wait for one another must not share a GPU: the group refuses a device named twice, a device
+    that does not exist, and more than eight ranks, before it allocates anything."""
+    import ctypes as C
+
+    grp = C.c_void_p()
+    twice = (C.c_int * 2)(0, 0)
+    assert lib.ie_b200_tp_group_create(2, twice, 1024, C.byref(grp)) < 0 and b"twice" in lib.ie_b200_last_error()
+    missing = (C.c_int * 2)(0, 99)
+    assert lib.ie_b200_tp_group_create(2, missing, 1024, C.byref(grp)) < 0
+    assert lib.ie_b200_tp_group_create(9, None, 1024, C.byref(grp)) < 0
+    assert not grp.value
