@@ -429,9 +429,9 @@ def time_step_kernel(cfg, device, prompt, K: int) -> dict:
 
     b = build_backend(cfg, PROMPT_LEN + K + 24, 1, 0, device, step_mode="kernel")
     tok = 0
-    mine = np.zeros(cfg.vocab, np.float32)
+    mine, mine_first = np.zeros(cfg.vocab, np.float32), np.zeros(cfg.vocab, np.float32)
     for pos, t in enumerate(prompt):
-        tok, _ = b.step(int(t), pos, mine if pos == PROMPT_LEN - 1 else None)
+        tok, _ = b.step(int(t), pos, mine_first if pos == 0 else mine if pos == PROMPT_LEN - 1 else None)
     out, _ = b.decode(tok, PROMPT_LEN, 8)
     b.phase_times(True)
     out, ms = b.decode(int(out[-1]), PROMPT_LEN + 8, K)
@@ -445,13 +445,15 @@ def time_step_kernel(cfg, device, prompt, K: int) -> dict:
     # order of a few float sums (split-KV merge, GEMV row tiling is the same), yet a last-bit difference flips a Q8 or f16
     # rounding here and there and 32 random layers amplify it. The scale against which the sharded runs' logits are read.
     g = build_backend(cfg, PROMPT_LEN + 8, 1, 0, device)
-    want = np.zeros(cfg.vocab, np.float32)
+    want, want_first = np.zeros(cfg.vocab, np.float32), np.zeros(cfg.vocab, np.float32)
     for pos, t in enumerate(prompt):
-        g.step(int(t), pos, want if pos == PROMPT_LEN - 1 else None)
+        g.step(int(t), pos, want_first if pos == 0 else want if pos == PROMPT_LEN - 1 else None)
     g.close()
     torch.cuda.empty_cache()
     res["last_prompt_token_logits_vs_graph"] = {"max_abs_diff": float(np.abs(mine - want).max()), "logit_range": [float(want.min()), float(want.max())],
                                                 "argmax_identical": bool(mine.argmax() == want.argmax())}
+    # the first position already: no cache, no history, only the int8 roundings of the activations between 32 random layers
+    res["first_position_logits_vs_graph"] = {"max_abs_diff": float(np.abs(mine_first - want_first).max())}
     return res
 
 
@@ -645,18 +647,21 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
     rng = np.random.default_rng(1)
     prompt = rng.integers(0, cfg.vocab, PROMPT_LEN)
     tok = 0
-    my_logits = np.zeros(b.vocab_l, np.float32)
+    my_logits, my_first = np.zeros(b.vocab_l, np.float32), np.zeros(b.vocab_l, np.float32)
     for pos, t in enumerate(prompt):
-        tok = tpb.step(int(t), pos, my_logits if pos == PROMPT_LEN - 1 else None)
+        tok = tpb.step(int(t), pos, my_first if pos == 0 else my_logits if pos == PROMPT_LEN - 1 else None)
     pos = PROMPT_LEN
     first_tok = tok
     out = tpb.decode(tok, pos, W)
     tok, pos = int(out[-1]), pos + W
     torch.cuda.synchronize()
-    sl = torch.from_numpy(my_logits).to(dev)
-    slices = [torch.empty_like(sl) for _ in range(world)]
-    dist.all_gather(slices, sl)  # rank r holds logits [r * vocab / world, (r + 1) * vocab / world)
-    tp_logits = torch.cat(slices).cpu().numpy()
+    def gathered(mine):  # rank r holds logits [r * vocab / world, (r + 1) * vocab / world)
+        sl = torch.from_numpy(mine).to(dev)
+        slices = [torch.empty_like(sl) for _ in range(world)]
+        dist.all_gather(slices, sl)
+        return torch.cat(slices).cpu().numpy()
+
+    tp_logits, tp_first = gathered(my_logits), gathered(my_first)
     # correctness beside the timing, outside the timed region, against an unsharded engine on rank 0's GPU (the other ranks
     # wait). The sharded sums add per-rank partial rows in rank order, the unsharded engine sums a whole row at once, and the
     # f16 KV cache turns a last-bit difference into a different cache entry here and there: the logits agree to about 1e-2,
@@ -666,10 +671,10 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
     identical = None
     if rank == 0:
         single = build_backend(cfg, n_ctx, 1, 0, dev)
-        want = np.zeros(cfg.vocab, np.float32)
+        want, want_first = np.zeros(cfg.vocab, np.float32), np.zeros(cfg.vocab, np.float32)
         t1 = 0
         for p1, t in enumerate(prompt):
-            t1, _ = single.step(int(t), p1, want if p1 == PROMPT_LEN - 1 else None)
+            t1, _ = single.step(int(t), p1, want_first if p1 == 0 else want if p1 == PROMPT_LEN - 1 else None)
         mine_seq = [first_tok] + [int(x) for x in out]
         srt = np.sort(want)
         first = {"max_abs_diff": float(np.abs(tp_logits - want).max()), "logit_range": [float(srt[0]), float(srt[-1])],
@@ -692,7 +697,8 @@ def run_ours_tp(args, cfg, rank: int, world: int) -> dict | None:
         torch.cuda.empty_cache()
         want_seq = [t1] + [int(x) for x in o1]
         prefix = next((i for i, (a, b) in enumerate(zip(mine_seq, want_seq)) if a != b), len(want_seq))
-        identical = {"tokens_compared": len(want_seq), "identical_prefix": prefix, "same_history_choices_identical": agree,
+        identical = {"first_position_logits_max_abs_diff": float(np.abs(tp_first - want_first).max()),  # before any rounding can have flipped: the float order of the sharded sums alone
+                     "tokens_compared": len(want_seq), "identical_prefix": prefix, "same_history_choices_identical": agree,
                      "margins_at_disagreements": margins, "last_prompt_token_logits": first}
     dist.barrier()
     with ClockSampler(local) as cs:
