@@ -456,13 +456,14 @@ static int launch_attn(const AttnArgs &a, uint32_t T, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------------------------
 // The half-precision-cache form on tensor cores (mma.sync m16n8k16, f16 x f16 -> f32): the scalar kernel above is
 // bound by instruction issue (about 8000 warp instructions per 64-position tile, 830 GB/s at 4096 positions); here
-// a tile is 4 warps x (64 MMAs + 16 ldmatrix), so the kernel waits on HBM only. The cache's f16 K / V rows are the
+// a tile is 4 warps x (32 MMAs + 16 ldmatrix), so the kernel waits on HBM only. The cache's f16 K / V rows are the
 // exact operands; the fp32 sides are split into two f16 terms so that nothing is rounded away: q = q_hi + q_lo
-// for S = q . k (two MMAs per step), p = p_hi + p_lo for O = p . v. Layout: S^T = Q[16 heads x hd] . K^T (rows =
-// the G heads, padded with zero rows; columns = positions), whose C fragment is directly the A fragment of
-// P[16 heads x 16 positions] for O[16 heads x hd] += P . V. Each warp owns 16 of the tile's 64 positions and keeps
-// its own running max / sum / output; rows are padded to hd + 8 halves so that the 8 rows of an ldmatrix hit 8
-// different bank groups.
+// for S = q . k (two MMAs per step), p = p_hi + p_lo for O = p . v. Layout of the decode kernel: the cache rows take
+// the 16-row side of the MMA, the group's (at most 8) heads the 8-column side, S[16 positions x heads] = K . Q^T and
+// O^T[16 dims x heads] += V^T . P^T, the C fragment of S turned into the B fragment of P^T by two 8 x 8 register
+// transposes (movmatrix) per term. (The chunk kernel further down keeps queries on the row side: it has 16 rows of
+// them.) Each warp owns 16 of the tile's 64 positions and keeps its own running max / sum / output; rows are
+// padded to hd + 8 halves so that the 8 rows of an ldmatrix hit 8 different bank groups.
 constexpr int AM_WARPS = 4, AM_THREADS = 128, AM_PAD = 8;
 // NB tile buffers (NB - 1 tiles in flight ahead of the one in use): 4 with one CTA per SM while the splits leave SMs
 // free anyway (short contexts: three of the first four tiles arrive during the kernel before this one), 3 with two
@@ -471,6 +472,12 @@ constexpr int AM_WARPS = 4, AM_THREADS = 128, AM_PAD = 8;
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void *p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+// An 8 x 8 block of 16-bit values held as one MMA fragment register per lane (row lane / 4, columns 2 (lane % 4), + 1), transposed.
+__device__ __forceinline__ uint32_t movm_t(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
 }
 __device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const void *p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -513,7 +520,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 template <int HD, int G, bool FUSED, int NB, int CL>
 __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_kernel(const AttnArgs a) {
   constexpr int TILE = ATT_TILE, ROW = HD + AM_PAD, TILE_ELEMS = TILE * ROW, KS = HD / 16;
-  static_assert(G <= 8, "the heads of a KV head fill the first 8 rows of the 16-row MMA");
+  static_assert(G <= 8, "the heads of a KV head fill the 8 columns of the MMA");
   extern __shared__ uint4 smem_raw[];
   __half *kbuf = reinterpret_cast<__half *>(smem_raw);  // [NB][TILE][ROW]
   __half *vbuf = kbuf + NB * TILE_ELEMS;                // [NB][TILE][ROW]
@@ -534,7 +541,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     p_hi = min(p_hi, lo2 + per * TILE), p_lo = lo2;
   }
   const bool owns_new = FUSED && s == A - 1u && p_lo < np && np <= p_hi;  // the CTA whose positions end with this step's own
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hq = lane >> 2, tq = lane & 3;  // hq: the head (MMA row), tq: the column pair
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hq = lane >> 2, tq = lane & 3;  // hq: the fragment row (a position, a dim) and the head whose q this lane holds; tq: the column pair (heads 2tq, + 1)
   const float *qt = reinterpret_cast<const float *>(reinterpret_cast<const char *>(a.q) + a.q_stride * t) + (size_t)g * G * HD;
   const __half *kh = static_cast<const __half *>(a.kc) + (size_t)g * a.kv_len * HD, *vh = static_cast<const __half *>(a.vc) + (size_t)g * a.kv_len * HD;
   const uint32_t n_tiles = (p_hi - p_lo + TILE - 1u) / TILE;
@@ -583,7 +590,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   if (early) load_tables();
   if (early) pdl_wait();
 
-  // ---- q of head hq in A-fragment order, rotated when fused, split into two f16 terms
+  // ---- q of head hq in fragment order (dims 16k + 2tq, + 1, + 8, + 9), rotated when fused, split into two f16 terms
   float qf[KS][4];
 #pragma unroll
   for (int k = 0; k < KS; k++) {
@@ -639,18 +646,21 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
       }
     }
   }
-  uint32_t qh[KS][2], ql[KS][2];  // A fragment registers a0, a2 (rows hq); a1, a3 (rows hq + 8) are zero
+  uint32_t qh[KS][2], ql[KS][2];  // B fragment registers b0, b1 of Q^T[16 dims x heads]: column hq
 #pragma unroll
   for (int k = 0; k < KS; k++) {
     split2(qf[k][0], qf[k][1], qh[k][0], ql[k][0]);
     split2(qf[k][2], qf[k][3], qh[k][1], ql[k][1]);
   }
 
-  float o[HD / 8][4], run_m = -INFINITY, run_l = 0.0f;  // O^T C fragments: o[n][0..1] = head hq, dims 8n + 2tq, + 1
+  // Both products run with the cache rows on the 16-row side of the MMA and the (at most 8) heads on its 8-column side, so
+  // that no half of a tile multiplies zero rows: S[16 positions x heads] = K . Q^T, then O^T[16 dims x heads] += V^T . P^T.
+  // A lane holds, in every C fragment, heads 2tq and 2tq + 1: their running max and sum live in its registers.
+  float o[HD / 16][4], run_m[2] = {-INFINITY, -INFINITY}, run_l[2] = {0.0f, 0.0f};  // o[u][j], o[u][2 + j]: head 2tq + j, dims 16u + hq, + 8
 #pragma unroll
-  for (int n = 0; n < HD / 8; n++)
+  for (int u = 0; u < HD / 16; u++)
 #pragma unroll
-    for (int e = 0; e < 4; e++) o[n][e] = 0.0f;
+    for (int e = 0; e < 4; e++) o[u][e] = 0.0f;
   const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: this lane supplies row lr of matrix lm
   for (uint32_t it = 0; it < n_tiles; it++) {
     const int buf = it % NB;
@@ -670,47 +680,48 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
     const int p0 = warp * 16;  // this warp's positions of the tile
     if ((uint32_t)p0 < valid) {
       const __half *kt = kbuf + buf * TILE_ELEMS, *vt = vbuf + buf * TILE_ELEMS;
-      // ---- S^T[heads x 16 positions] = Q . K^T: two column tiles (positions p0.. and p0 + 8..)
-      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+      // ---- S[16 positions x heads]: sc[j] = position p0 + hq, sc[2 + j] = position p0 + hq + 8, of head 2tq + j
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int k = 0; k < KS; k++) {
-        uint32_t kb[4];  // matrices: (tile a, dims lo), (tile a, dims hi), (tile b, dims lo), (tile b, dims hi)
-        ldsm4(kb, kt + (p0 + (lm >> 1) * 8 + lr) * ROW + 16 * k + (lm & 1) * 8);
-        mma_f16(sa, qh[k][0], 0u, qh[k][1], 0u, kb[0], kb[1]);
-        mma_f16(sa, ql[k][0], 0u, ql[k][1], 0u, kb[0], kb[1]);
-        mma_f16(sb, qh[k][0], 0u, qh[k][1], 0u, kb[2], kb[3]);
-        mma_f16(sb, ql[k][0], 0u, ql[k][1], 0u, kb[2], kb[3]);
+        uint32_t ka[4];  // matrices: (positions lo, dims lo), (positions hi, dims lo), (positions lo, dims hi), (positions hi, dims hi)
+        ldsm4(ka, kt + (p0 + (lm & 1) * 8 + lr) * ROW + 16 * k + (lm >> 1) * 8);
+        mma_f16(sc, ka[0], ka[1], ka[2], ka[3], qh[k][0], qh[k][1]);
+        mma_f16(sc, ka[0], ka[1], ka[2], ka[3], ql[k][0], ql[k][1]);
       }
-      // scores of head hq at positions p0 + 2tq, + 1 (sa[0..1]) and p0 + 8 + 2tq, + 1 (sb[0..1])
-      float sc[4];
-      sc[0] = (uint32_t)(p0 + 2 * tq) < valid ? sa[0] * a.scale : -INFINITY;
-      sc[1] = (uint32_t)(p0 + 2 * tq + 1) < valid ? sa[1] * a.scale : -INFINITY;
-      sc[2] = (uint32_t)(p0 + 8 + 2 * tq) < valid ? sb[0] * a.scale : -INFINITY;
-      sc[3] = (uint32_t)(p0 + 8 + 2 * tq + 1) < valid ? sb[1] * a.scale : -INFINITY;
-      float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-      const float m_new = fmaxf(run_m, mx), al = expf(run_m - m_new);  // position p0 exists: m_new is finite
-      float pv[4], sum = 0.0f;
+      const bool ok0 = (uint32_t)(p0 + hq) < valid, ok1 = (uint32_t)(p0 + hq + 8) < valid;
+      sc[0] = ok0 ? sc[0] * a.scale : -INFINITY, sc[1] = ok0 ? sc[1] * a.scale : -INFINITY;
+      sc[2] = ok1 ? sc[2] * a.scale : -INFINITY, sc[3] = ok1 ? sc[3] * a.scale : -INFINITY;
+      float al[2], pv[4];
 #pragma unroll
-      for (int e = 0; e < 4; e++) pv[e] = expf(sc[e] - m_new), sum += pv[e];
-      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-      run_l = run_l * al + sum, run_m = m_new;
-      uint32_t ph[2], pl[2];  // A fragment of P: a0 = positions 2tq, +1; a2 = positions 8 + 2tq, +1 (rows hq)
+      for (int j = 0; j < 2; j++) {  // a head's 16 positions sit in the 8 lanes of one tq
+        float mx = fmaxf(sc[j], sc[2 + j]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
+        const float m_new = fmaxf(run_m[j], mx);  // position p0 exists: m_new is finite
+        al[j] = expf(run_m[j] - m_new);
+        pv[j] = expf(sc[j] - m_new), pv[2 + j] = expf(sc[2 + j] - m_new);
+        float sum = pv[j] + pv[2 + j];
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
+        run_l[j] = run_l[j] * al[j] + sum, run_m[j] = m_new;
+      }
+      // P as two f16 terms, each 8 x 8 block [positions x heads] transposed into the B fragment [positions (k) x heads (n)]
+      uint32_t ph[2], pl[2];
       split2(pv[0], pv[1], ph[0], pl[0]);
       split2(pv[2], pv[3], ph[1], pl[1]);
-      // ---- O[heads x hd] = al * O + P . V, two 8-dim column tiles per ldmatrix
+#pragma unroll
+      for (int e = 0; e < 2; e++) ph[e] = movm_t(ph[e]), pl[e] = movm_t(pl[e]);
+      // ---- O^T[hd x heads] = al * O^T + V^T . P^T, 16 dims per ldmatrix
 #pragma unroll
       for (int u = 0; u < HD / 16; u++) {
-        uint32_t vb[4];  // matrices: (positions lo, dims 16u..), (positions hi, dims 16u..), (positions lo, dims 16u + 8..), (positions hi, ...)
-        ldsm4t(vb, vt + (p0 + (lm & 1) * 8 + lr) * ROW + 16 * u + (lm >> 1) * 8);
-#pragma unroll
-        for (int e = 0; e < 4; e++) o[2 * u][e] *= al, o[2 * u + 1][e] *= al;
-        mma_f16(o[2 * u], ph[0], 0u, ph[1], 0u, vb[0], vb[1]);
-        mma_f16(o[2 * u], pl[0], 0u, pl[1], 0u, vb[0], vb[1]);
-        mma_f16(o[2 * u + 1], ph[0], 0u, ph[1], 0u, vb[2], vb[3]);
-        mma_f16(o[2 * u + 1], pl[0], 0u, pl[1], 0u, vb[2], vb[3]);
+        uint32_t va[4];  // transposed on load: (dims lo, positions lo), (dims hi, positions lo), (dims lo, positions hi), (dims hi, positions hi)
+        ldsm4t(va, vt + (p0 + (lm >> 1) * 8 + lr) * ROW + 16 * u + (lm & 1) * 8);
+        o[u][0] *= al[0], o[u][1] *= al[1], o[u][2] *= al[0], o[u][3] *= al[1];
+        mma_f16(o[u], va[0], va[1], va[2], va[3], ph[0], ph[1]);
+        mma_f16(o[u], va[0], va[1], va[2], va[3], pl[0], pl[1]);
       }
     }
   }
@@ -721,10 +732,14 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   float *red = reinterpret_cast<float *>(smem_raw);  // [AM_WARPS][G][HD]
   float *ml = red + AM_WARPS * G * HD;                // [AM_WARPS][G][2]
   float *fin = ml + AM_WARPS * G * 2;                 // [G][HD]
-  if (hq < G) {
 #pragma unroll
-    for (int n = 0; n < HD / 8; n++) *reinterpret_cast<float2 *>(red + (warp * G + hq) * HD + 8 * n + 2 * tq) = make_float2(o[n][0], o[n][1]);
-    if (tq == 0) ml[(warp * G + hq) * 2] = run_m, ml[(warp * G + hq) * 2 + 1] = run_l;
+  for (int j = 0; j < 2; j++) {
+    const int h = 2 * tq + j;
+    if (h < G) {
+#pragma unroll
+      for (int u = 0; u < HD / 16; u++) red[(warp * G + h) * HD + 16 * u + hq] = o[u][j], red[(warp * G + h) * HD + 16 * u + hq + 8] = o[u][2 + j];
+      if (hq == 0) ml[(warp * G + h) * 2] = run_m[j], ml[(warp * G + h) * 2 + 1] = run_l[j];
+    }
   }
   __syncthreads();
   const size_t rec = HD + 2;
