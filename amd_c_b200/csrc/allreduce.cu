@@ -126,24 +126,31 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_kernel(const ArDev s
 
 
 constexpr int ARN_MAX_THREADS = 1024;
+constexpr int ARN_CL = 8, ARN_CL_THREADS = 128;  // the cluster form: 8 CTAs of 128 threads
 
-// One CTA: x (= res, may alias out) + the ranks' partials in rank order, then y = x * rsqrt(mean x^2 + eps) * w
+// x (= res, may alias out) + the ranks' partials in rank order, then y = x * rsqrt(mean x^2 + eps) * w
 // and the Q8 copy of y (the same arithmetic as the RMSNorm kernel and the norm tail of the GEMV).
-// Thread t owns elements 4 (t + 1024 it) .. + 3; eight neighbouring threads hold one Q8 block.
-// PEERS: how many ranks' words a thread polls together (4: worlds of up to four ranks at 1024 threads; 8: larger worlds at 512
-// threads, whose 128 registers hold all seven peers' loads in flight at once: one trip to L2 per poll instead of two).
-template <int ITERS, int ARN_THREADS, int PEERS>
+// Thread t owns elements 4 (t + all threads * it) .. + 3; eight neighbouring threads hold one Q8 block.
+// PEERS: how many ranks' words a thread polls together (4: worlds of up to four ranks; 8: larger worlds, all seven peers'
+// loads in flight at once: one trip to L2 per poll instead of two).
+// CL = 1: one CTA. CL = ARN_CL: one thread-block cluster of CL CTAs, each polling, summing, normalising and quantising
+// its own columns; only the sum of squares crosses CTAs (distributed shared memory, one cluster barrier). What a rank
+// receives grows with the world (world - 1 rows of 8-byte words: 229 KB at 8 ranks of a 4096-float row), and one SM's
+// path to L2 carries that in microseconds; eight SMs take an eighth each.
+template <int ITERS, int ARN_THREADS, int PEERS, int CL>
 __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, const float *part, const float *res, float *out, const float *norm_w, float eps,
                                                               float *xn, uint8_t *xq, uint32_t n, uint32_t *err, int pushed, int early) {
-  __shared__ float red[32];
-  const int tid = threadIdx.x;
+  __shared__ float red[32 + ARN_CL];
+  const int tid = CL > 1 ? (int)(blockIdx.x * ARN_THREADS + threadIdx.x) : (int)threadIdx.x;  // the thread's place in the vector
+  constexpr int ALL = ARN_THREADS * CL;
   float4 acc[ITERS], mine[ITERS], w4[ITERS];
+  if (CL > 1) cluster_arrive();
   pdl_launch_dependents();
   // ahead of the dependency wait: the norm weights (constant) and, when the kernel before this one releases its
   // dependents late (`early`), everything older than that kernel: the epoch and the residual stream
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
-    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    const uint32_t i = 4u * (tid + ALL * it);
     acc[it] = w4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < n && norm_w) w4[it] = *reinterpret_cast<const float4 *>(norm_w + i);
     if (i < n && early) acc[it] = *reinterpret_cast<const float4 *>(res + i);
@@ -155,7 +162,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   const uint32_t par = k & 1u;
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
-    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    const uint32_t i = 4u * (tid + ALL * it);
     mine[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < n) {
       mine[it] = *reinterpret_cast<const float4 *>(part + i);
@@ -175,7 +182,7 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   const unsigned long long *my = s.ll[s.rank] + (size_t)par * s.world * s.max_n;
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
-    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    const uint32_t i = 4u * (tid + ALL * it);
     if (i >= n) continue;
     for (uint32_t j0 = 0; j0 < s.world; j0 += PEERS) {
       unsigned long long v[PEERS][4];
@@ -217,11 +224,12 @@ __global__ void __launch_bounds__(ARN_THREADS) ar_norm_kernel(const ArDev s, con
   if (gave_up && err) atomicExch(err, 3u);
 #pragma unroll
   for (int it = 0; it < ITERS; it++) {
-    const uint32_t i = 4u * (tid + ARN_THREADS * it);
+    const uint32_t i = 4u * (tid + ALL * it);
     if (i < n) *reinterpret_cast<float4 *>(out + i) = acc[it];
   }
-  if (norm_w) norm_quant_vec<ITERS, ARN_THREADS>(acc, w4, n, eps, xn, xq, red);
-  if (tid == 0) *(volatile uint32_t *)s.epoch = k;
+  if (CL > 1) cluster_wait();  // every CTA of the cluster runs (and has read the epoch) from here on
+  if (norm_w) norm_quant_vec<ITERS, ARN_THREADS, CL>(acc, w4, n, eps, xn, xq, red);  // (norm_w is the same in every CTA: all reach its cluster barrier)
+  if (tid == 0) *(volatile uint32_t *)s.epoch = k;  // read by later kernels only, and those start after every CTA of this one
 }
 
 // One warp: every rank's (logit, global index) of its local argmax to every rank; the largest logit wins, ties
@@ -376,6 +384,18 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
   return IE_B200_OK;
 }
 
+// Which form of the reduction kernel a row takes: the cluster once a rank receives more than one SM fetches quickly
+// (worlds of more than four ranks, rows of a real model); measured at two ranks the cluster's barrier costs more than
+// its CTAs save (4.5 against 4.1 us per stop). IE_B200_AR_NORM=single / cluster: one form for every world (for comparison).
+static bool ar_norm_cluster_on(uint32_t world, uint32_t n) {
+  static const int mode = [] {
+    const char *v = getenv("IE_B200_AR_NORM");
+    return !v ? 0 : !strcmp(v, "single") ? 1 : !strcmp(v, "cluster") ? 2 : 0;
+  }();
+  if (mode == 1 || n < 1024u) return false;
+  return mode == 2 || world > 4u;
+}
+
 // d_res: what the ranks' partials are added to (NULL: d_x itself, in place); d_x receives the sum.
 static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, const float *d_res, float *d_x, const float *d_norm_w, float eps, float *d_xn,
                           void *d_xq, uint32_t n, uint32_t *d_err, void *stream, int pushed, int early = 0) {
@@ -389,9 +409,27 @@ static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, const float
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t *xq = static_cast<uint8_t *>(d_xq);
 #define IEB_ARN(IT, TH, PE)                                                                                                                  \
-  IEB_LAUNCH_PDL("ar_norm_kernel", (ar_norm_kernel<IT, TH, PE>), dim3(1), dim3(TH), 0, st, a->d, d_part, d_res, d_x, d_norm_w, eps, d_xn, xq, n, d_err, \
+  IEB_LAUNCH_PDL("ar_norm_kernel", (ar_norm_kernel<IT, TH, PE, 1>), dim3(1), dim3(TH), 0, st, a->d, d_part, d_res, d_x, d_norm_w, eps, d_xn, xq, n, d_err, \
                  pushed, early)
-  if (a->d.world > 4u) {  // 512 threads, all peers polled together
+#define IEB_ARN_CL(IT, PE)                                                                                                                    \
+  do {                                                                                                                                       \
+    cudaError_t e_ = launch_pdl_cluster(ar_norm_kernel<IT, ARN_CL_THREADS, PE, ARN_CL>, dim3(ARN_CL), dim3(ARN_CL_THREADS), 0, st, ARN_CL, a->d, d_part, \
+                                        d_res, d_x, d_norm_w, eps, d_xn, xq, n, d_err, pushed, early);                                       \
+    count_launch();                                                                                                                          \
+    if (e_ != cudaSuccess) return cuda_fail(e_, "ar_norm_kernel (cluster)");                                                                 \
+  } while (0)
+  if (ar_norm_cluster_on(a->d.world, n)) {
+    const uint32_t iters = (n + 4u * ARN_CL * ARN_CL_THREADS - 1u) / (4u * ARN_CL * ARN_CL_THREADS);
+    if (a->d.world > 4u) {
+      if (iters <= 1) IEB_ARN_CL(1, 8);
+      else if (iters <= 2) IEB_ARN_CL(2, 8);
+      else IEB_ARN_CL(4, 8);
+    } else {
+      if (iters <= 1) IEB_ARN_CL(1, 4);
+      else if (iters <= 2) IEB_ARN_CL(2, 4);
+      else IEB_ARN_CL(4, 4);
+    }
+  } else if (a->d.world > 4u) {  // 512 threads, all peers polled together
     const uint32_t iters = (n + 4u * 512u - 1u) / (4u * 512u);
     if (iters <= 1) IEB_ARN(1, 512, 8);
     else if (iters <= 2) IEB_ARN(2, 512, 8);
@@ -404,6 +442,7 @@ static int ar_norm_launch(ie_b200_allreduce *a, const float *d_part, const float
     else IEB_ARN(4, 1024, 4);
   }
 #undef IEB_ARN
+#undef IEB_ARN_CL
   return IE_B200_OK;
 }
 

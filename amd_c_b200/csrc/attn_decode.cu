@@ -503,17 +503,6 @@ __host__ __device__ constexpr size_t am_main_bytes(int HD, int G, int NB, uint32
   return ((tile > red ? tile : red) + 15u) & ~(size_t)15u;
 }
 
-__device__ __forceinline__ uint32_t cluster_map_shared(const void *p, uint32_t cta_rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(cta_rank));
-  return remote;
-}
-__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 // CL: CTAs per split. 1: a CTA streams its whole split. 4: a thread-block cluster shares the split, a CTA takes every
 // CL-th part of its tiles, and the parts meet in the leader's shared memory (distributed shared memory, one cluster
 // barrier): for short contexts, where one CTA per KV head leaves the fetch of the cache rows to a single SM.
@@ -534,6 +523,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   const uint32_t span = att_span(np, S);
   const uint32_t A = (np + span - 1u) / span;
   if (s >= A) return;  // (the whole cluster of such a split returns here)
+  if (CL > 1) cluster_arrive();
   uint32_t p_lo = s * span, p_hi = min(np, p_lo + span);
   if (CL > 1) {  // this CTA's tiles of the split: ceil(tiles / CL) consecutive ones; the last CTAs may hold none
     const uint32_t tiles = (p_hi - p_lo + TILE - 1u) / TILE, per = (tiles + CL - 1u) / CL;
@@ -747,6 +737,7 @@ __global__ void __launch_bounds__(AM_THREADS, NB == 3 ? 2 : 1) attn_decode_mma_k
   float *recv = reinterpret_cast<float *>(reinterpret_cast<char *>(smem_raw) + am_main_bytes(HD, G, NB, S));  // [CL][G][HD + 2], used in the leader
   if (CL > 1) {
     // every CTA's record into the leader's memory, then one cluster barrier; a CTA without positions sends (max -inf, sum 0)
+    cluster_wait();  // (the leader runs: its memory may be written)
     const uint32_t base = cluster_map_shared(recv + (size_t)cr * G * rec, 0u);
     for (int e = threadIdx.x; e < G * HD; e += AM_THREADS) {
       const int h = e / HD;
