@@ -385,15 +385,16 @@ extern "C" int ie_b200_ar_allreduce_add(ie_b200_allreduce *a, const float *d_par
 }
 
 // Which form of the reduction kernel a row takes: the cluster once a rank receives more than one SM fetches quickly
-// (worlds of more than four ranks, rows of a real model); measured at two ranks the cluster's barrier costs more than
-// its CTAs save (4.5 against 4.1 us per stop). IE_B200_AR_NORM=single / cluster: one form for every world (for comparison).
+// (worlds of four ranks and more, rows of a real model). Measured on the 8B-class model, one CTA against the cluster:
+// 2 ranks 4.1 / 4.5 us per stop (the cluster's barrier costs more than its CTAs save), 4 ranks 0.970 / 0.942 ms per
+// step of 65 stops, 8 ranks 7.8 / 5.7 us per stop. IE_B200_AR_NORM=single / cluster: one form for every world (for comparison).
 static bool ar_norm_cluster_on(uint32_t world, uint32_t n) {
   static const int mode = [] {
     const char *v = getenv("IE_B200_AR_NORM");
     return !v ? 0 : !strcmp(v, "single") ? 1 : !strcmp(v, "cluster") ? 2 : 0;
   }();
   if (mode == 1 || n < 1024u) return false;
-  return mode == 2 || world > 4u;
+  return mode == 2 || world > 2u;
 }
 
 // d_res: what the ranks' partials are added to (NULL: d_x itself, in place); d_x receives the sum.
