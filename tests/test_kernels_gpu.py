@@ -784,9 +784,11 @@ def test_allreduce_missing_rank_gives_up(cuda, lib):
             lib.ie_b200_ar_destroy(hs[r])
 
 
-@pytest.mark.parametrize("world,typ", [(2, synth.GGML_Q4_0), (4, synth.GGML_Q4_0), (8, synth.GGML_Q4_0), (2, synth.GGML_Q4_K), (4, synth.GGML_Q6_K),
-                                       (2, synth.GGML_Q8_0)])
-def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world, typ):
+@pytest.mark.parametrize("world,typ,rows", [(2, synth.GGML_Q4_0, 512), (4, synth.GGML_Q4_0, 512), (8, synth.GGML_Q4_0, 512), (2, synth.GGML_Q4_K, 512),
+                                            (4, synth.GGML_Q6_K, 512), (2, synth.GGML_Q8_0, 512),
+                                            # rows of a real model: from four ranks up the reduction is a cluster of 8 CTAs (1, 2 and 3 passes)
+                                            (2, synth.GGML_Q4_0, 4096), (4, synth.GGML_Q4_0, 5120), (8, synth.GGML_Q4_0, 4096), (8, synth.GGML_Q4_K, 12288)])
+def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world, typ, rows):
     """The tensor-parallel stop with real partners, the ranks of a world run one after the other on one GPU (their states
     connected in-process): every rank's K-split GEMV first (each stores its rows into the others' slots and waits for
     nobody), then every rank's reduction (all rows are there: no kernel waits for a later one). x + p_0 + p_1 + ... in rank
@@ -799,7 +801,7 @@ def test_tp_stop_ranks_in_order_bit_exact(ora, cuda, lib, world, typ):
     from amd_c_b200 import kernels as K
     from amd_c_b200.backend import shard_cols
 
-    rows, cols = 512, 256 * world
+    cols = 256 * world
     rng = np.random.default_rng(world)
     raw = synth.make_gguf_bytes(typ, rng, rows, cols)
     nw = (1 + 0.1 * rng.standard_normal(rows)).astype(np.float32)
